@@ -1,0 +1,285 @@
+// Eltwise activation forward / backward (the bodies of ddActivationForward / ddActivationBackward).
+//
+//   forward   y  = alpha*act(x)       + beta*y       algorithmic bytes/element: 2*sizeof(T)
+//   backward  dx = alpha*act'(x)*dy   + beta*dx      algorithmic bytes/element: 3*sizeof(T)
+//
+// Dense tensors with identical strides (the layer case) run as a flat 16-byte vector stream;
+// anything else goes through the strided kernel.  Both are HBM-bound.
+//
+// Arithmetic follows oneDNN's documented eltwise definitions (the reference binds them in
+// dnnl/impl.clj:324-341, algorithm keywords dnnl/constants.clj:277-308), evaluated in fp32 (fp64
+// for double tensors) with the derivative taken from the forward source:
+//   relu      f = x>0 ? x : a*x            f' = x>0 ? 1 : a
+//   logistic  f = 1/(1+exp(-x))            f' = f*(1-f)
+//   tanh      f = tanh(x)                  f' = 1-f^2
+//   elu       f = x>0 ? x : a*(exp(x)-1)   f' = x>0 ? 1 : a*exp(x)
+//   linear    f = a*x+b                    f' = a
+//   clip-relu f = min(max(x,0),a)          f' = 0<x<=a ? 1 : 0
+//   abs       f = |x|                      f' = sign(x)
+// f*(1-f) and 1-f^2 are evaluated as e/(1+e)^2 forms (no cancellation near saturation).
+#include "dd_internal.cuh"
+
+template <typename C> struct dd_math;
+template <> struct dd_math<float> {
+  static __device__ __forceinline__ float exp(float x) { return expf(x); }
+  static __device__ __forceinline__ float expm1(float x) { return expm1f(x); }
+  static __device__ __forceinline__ float tanh(float x) { return tanhf(x); }
+  static __device__ __forceinline__ float abs(float x) { return fabsf(x); }
+  static __device__ __forceinline__ float fma(float a, float b, float c) { return fmaf(a, b, c); }
+  static __device__ __forceinline__ float max(float a, float b) { return fmaxf(a, b); }
+  static __device__ __forceinline__ float min(float a, float b) { return fminf(a, b); }
+  static __device__ __forceinline__ float div(float a, float b) { return __fdiv_rn(a, b); }
+};
+template <> struct dd_math<double> {
+  static __device__ __forceinline__ double exp(double x) { return ::exp(x); }
+  static __device__ __forceinline__ double expm1(double x) { return ::expm1(x); }
+  static __device__ __forceinline__ double tanh(double x) { return ::tanh(x); }
+  static __device__ __forceinline__ double abs(double x) { return ::fabs(x); }
+  static __device__ __forceinline__ double fma(double a, double b, double c) { return ::fma(a, b, c); }
+  static __device__ __forceinline__ double max(double a, double b) { return ::fmax(a, b); }
+  static __device__ __forceinline__ double min(double a, double b) { return ::fmin(a, b); }
+  static __device__ __forceinline__ double div(double a, double b) { return __ddiv_rn(a, b); }
+};
+
+struct ddActArgs {
+  double coef, shift;
+  int nanProp;
+};
+
+template <typename C, int MODE>
+__device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp) {
+  typedef dd_math<C> M;
+  if (MODE == DD_ACTIVATION_RELU) {
+    if (coef == (C)0) {
+      if (nanProp && x != x) return x;
+      return M::max(x, (C)0);
+    }
+    return x > (C)0 ? x : dd_mul_rn(coef, x);
+  } else if (MODE == DD_ACTIVATION_SIGMOID) {
+    // e = exp(-|x|) in (0,1]; 1/(1+e) for x>=0, e/(1+e) for x<0
+    C e = M::exp(-M::abs(x));
+    C r = M::div((C)1, dd_add_rn((C)1, e));
+    C s = x >= (C)0 ? r : dd_mul_rn(e, r);
+    return x != x ? x : s;
+  } else if (MODE == DD_ACTIVATION_TANH) {
+    return M::tanh(x);
+  } else if (MODE == DD_ACTIVATION_ELU) {
+    return x > (C)0 ? x : dd_mul_rn(coef, M::expm1(x));
+  } else if (MODE == DD_ACTIVATION_LINEAR) {
+    return M::fma(coef, x, shift);
+  } else if (MODE == DD_ACTIVATION_CLIPPED_RELU) {
+    if (nanProp && x != x) return x;
+    return M::min(M::max(x, (C)0), coef);
+  } else {  // ABS
+    return M::abs(x);
+  }
+}
+
+// returns act'(x) * dy
+template <typename C, int MODE>
+__device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef) {
+  typedef dd_math<C> M;
+  if (MODE == DD_ACTIVATION_RELU) {
+    return x > (C)0 ? dy : dd_mul_rn(coef, dy);
+  } else if (MODE == DD_ACTIVATION_SIGMOID) {
+    // s(1-s) = e/(1+e)^2 with e = exp(-|x|)
+    C e = M::exp(-M::abs(x));
+    C r = M::div((C)1, dd_add_rn((C)1, e));
+    C d = dd_mul_rn(dd_mul_rn(e, r), r);
+    return dd_mul_rn(dy, x != x ? x : d);
+  } else if (MODE == DD_ACTIVATION_TANH) {
+    // 1 - tanh^2 = 4e/(1+e)^2 with e = exp(-2|x|)
+    C e = M::exp((C)-2 * M::abs(x));
+    C r = M::div((C)1, dd_add_rn((C)1, e));
+    C d = dd_mul_rn(dd_mul_rn((C)4 * e, r), r);
+    return dd_mul_rn(dy, x != x ? x : d);
+  } else if (MODE == DD_ACTIVATION_ELU) {
+    return x > (C)0 ? dy : dd_mul_rn(dy, dd_mul_rn(coef, M::exp(x)));
+  } else if (MODE == DD_ACTIVATION_LINEAR) {
+    return dd_mul_rn(coef, dy);
+  } else if (MODE == DD_ACTIVATION_CLIPPED_RELU) {
+    return (x > (C)0 && x <= coef) ? dy : (C)0;
+  } else {  // ABS
+    return x > (C)0 ? dy : (x < (C)0 ? -dy : (C)0);
+  }
+}
+
+template <typename C>
+__device__ __forceinline__ C dd_blend(C alpha, C v, C beta, C old, bool useOld) {
+  C t = dd_scale(alpha, v);
+  return useOld ? dd_add_rn(t, dd_mul_rn(beta, old)) : t;
+}
+
+struct ddEltFlatParams {
+  const void *x;   // forward: source.  backward: forward source
+  const void *dy;  // backward only
+  void *out;       // forward: y.  backward: dx
+  int64_t n;
+  double alpha, beta;
+  ddActArgs act;
+  int vec;
+};
+
+template <typename T, typename C, int MODE, bool BWD>
+__global__ void __launch_bounds__(256) dd_elt_flat_kernel(ddEltFlatParams p) {
+  constexpr int V = 16 / sizeof(T);
+  const T *x = (const T *)p.x;
+  const T *dy = (const T *)p.dy;
+  T *out = (T *)p.out;
+  const C alpha = (C)p.alpha, beta = (C)p.beta, coef = (C)p.act.coef, shift = (C)p.act.shift;
+  const bool useOld = p.beta != 0.0, nanProp = p.act.nanProp != 0;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  int64_t done = 0;
+  if (p.vec) {
+    const int64_t nv = p.n / V;
+    for (int64_t i = tid; i < nv; i += nthreads) {
+      uint4 xin = *(const uint4 *)(x + i * V);
+      uint4 din = BWD ? *(const uint4 *)(dy + i * V) : make_uint4(0, 0, 0, 0);
+      uint4 oin = useOld ? *(const uint4 *)(out + i * V) : make_uint4(0, 0, 0, 0);
+      uint4 res;
+      const T *xv = (const T *)&xin, *dv = (const T *)&din, *ov = (const T *)&oin;
+      T *rv = (T *)&res;
+#pragma unroll
+      for (int k = 0; k < V; k++) {
+        C xc = dd_load<C, T>(xv[k]);
+        C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dv[k]), coef)
+                  : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+        rv[k] = dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
+      }
+      *(uint4 *)(out + i * V) = res;
+    }
+    done = nv * V;
+  }
+  for (int64_t i = done + tid; i < p.n; i += nthreads) {
+    C xc = dd_load<C, T>(x[i]);
+    C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dy[i]), coef)
+              : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+    C old = useOld ? dd_load<C, T>(out[i]) : (C)0;
+    out[i] = dd_store<T, C>(dd_blend(alpha, v, beta, old, useOld));
+  }
+}
+
+struct ddEltStridedParams {
+  const void *x;
+  const void *dy;
+  void *out;
+  ddStridedParams<3> sp;  // operands: 0 = x, 1 = dy (backward), 2 = out
+  double alpha, beta;
+  ddActArgs act;
+};
+
+template <typename T, typename C, int MODE, bool BWD>
+__global__ void __launch_bounds__(256) dd_elt_strided_kernel(ddEltStridedParams p) {
+  const T *x = (const T *)p.x;
+  const T *dy = (const T *)p.dy;
+  T *out = (T *)p.out;
+  const C alpha = (C)p.alpha, beta = (C)p.beta, coef = (C)p.act.coef, shift = (C)p.act.shift;
+  const bool useOld = p.beta != 0.0, nanProp = p.act.nanProp != 0;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.sp.total; i += nthreads) {
+    int64_t off[3];
+    dd_offsets<3, int64_t>(p.sp, i, off);
+    C xc = dd_load<C, T>(x[off[0]]);
+    C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dy[off[1]]), coef)
+              : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+    C old = useOld ? dd_load<C, T>(out[off[2]]) : (C)0;
+    out[off[2]] = dd_store<T, C>(dd_blend(alpha, v, beta, old, useOld));
+  }
+}
+
+template <typename T, typename C, int MODE, bool BWD>
+static ddStatus_t launch_elt(ddHandle_t h, const ddCanon &c, const void *x, const void *dy, void *out,
+                             double alpha, double beta, const ddActArgs &act) {
+  bool dense = c.nd == 1 && c.st[0][0] == 1 && c.st[2][0] == 1 && (!BWD || c.st[1][0] == 1);
+  if (dense) {
+    ddEltFlatParams p;
+    p.x = x;
+    p.dy = dy;
+    p.out = out;
+    p.n = c.total;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.act = act;
+    uintptr_t bits = (uintptr_t)x | (uintptr_t)out | (BWD ? (uintptr_t)dy : 0);
+    p.vec = (bits & 15) == 0;
+    constexpr int V = 16 / sizeof(T);
+    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
+    dd_elt_flat_kernel<T, C, MODE, BWD><<<grid, 256, 0, h->stream>>>(p);
+    DD_LAUNCHED(h, BWD ? "activation-bwd/flat" : "activation-fwd/flat");
+  } else {
+    ddEltStridedParams p;
+    p.x = x;
+    p.dy = dy;
+    p.out = out;
+    p.sp = dd_strided_params<3>(c);
+    p.alpha = alpha;
+    p.beta = beta;
+    p.act = act;
+    unsigned grid = dd_flat_grid(h, c.total, 256, 16);
+    dd_elt_strided_kernel<T, C, MODE, BWD><<<grid, 256, 0, h->stream>>>(p);
+    DD_LAUNCHED(h, BWD ? "activation-bwd/strided" : "activation-fwd/strided");
+  }
+  return DD_STATUS_SUCCESS;
+}
+
+template <typename T, typename C, bool BWD>
+static ddStatus_t dispatch_mode(ddHandle_t h, int mode, const ddCanon &c, const void *x,
+                                const void *dy, void *out, double alpha, double beta,
+                                const ddActArgs &act) {
+  switch (mode) {
+    case DD_ACTIVATION_SIGMOID: return launch_elt<T, C, DD_ACTIVATION_SIGMOID, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_RELU: return launch_elt<T, C, DD_ACTIVATION_RELU, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_TANH: return launch_elt<T, C, DD_ACTIVATION_TANH, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_CLIPPED_RELU: return launch_elt<T, C, DD_ACTIVATION_CLIPPED_RELU, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_ELU: return launch_elt<T, C, DD_ACTIVATION_ELU, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_LINEAR: return launch_elt<T, C, DD_ACTIVATION_LINEAR, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_ABS: return launch_elt<T, C, DD_ACTIVATION_ABS, BWD>(h, c, x, dy, out, alpha, beta, act);
+  }
+  DD_FAIL(h, DD_STATUS_BAD_PARAM, "activation: unknown mode %d", mode);
+}
+
+template <bool BWD>
+static ddStatus_t dispatch_type(ddHandle_t h, ddDataType_t t, int mode, const ddCanon &c,
+                                const void *x, const void *dy, void *out, double alpha, double beta,
+                                const ddActArgs &act) {
+  switch (t) {
+    case DD_DATA_FLOAT: return dispatch_mode<float, float, BWD>(h, mode, c, x, dy, out, alpha, beta, act);
+    case DD_DATA_DOUBLE: return dispatch_mode<double, double, BWD>(h, mode, c, x, dy, out, alpha, beta, act);
+    case DD_DATA_HALF: return dispatch_mode<__half, float, BWD>(h, mode, c, x, dy, out, alpha, beta, act);
+    case DD_DATA_BFLOAT16: return dispatch_mode<__nv_bfloat16, float, BWD>(h, mode, c, x, dy, out, alpha, beta, act);
+    default: break;
+  }
+  DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "activation: data type must be floating point");
+}
+
+ddStatus_t dd_activation_fwd_impl(ddHandle_t h, const ddActivationStruct *a, double alpha,
+                                  const ddTensorStruct *xd, const void *x, double beta,
+                                  const ddTensorStruct *yd, void *y) {
+  int64_t st[3][DD_DIM_MAX];
+  for (int i = 0; i < xd->nd; i++) {
+    st[0][i] = xd->strides[i];
+    st[1][i] = xd->strides[i];
+    st[2][i] = yd->strides[i];
+  }
+  ddCanon c;
+  dd_canonicalize(&c, xd->nd, xd->dims, 3, st, 2);
+  ddActArgs act = {a->coef, a->shift, a->nan == DD_PROPAGATE_NAN};
+  return dispatch_type<false>(h, xd->dtype, a->mode, c, x, nullptr, y, alpha, beta, act);
+}
+
+ddStatus_t dd_activation_bwd_impl(ddHandle_t h, const ddActivationStruct *a, double alpha,
+                                  const ddTensorStruct *dyd, const void *dy,
+                                  const ddTensorStruct *xd, const void *x, double beta,
+                                  const ddTensorStruct *dxd, void *dx) {
+  int64_t st[3][DD_DIM_MAX];
+  for (int i = 0; i < xd->nd; i++) {
+    st[0][i] = xd->strides[i];
+    st[1][i] = dyd->strides[i];
+    st[2][i] = dxd->strides[i];
+  }
+  ddCanon c;
+  dd_canonicalize(&c, xd->nd, xd->dims, 3, st, 2);
+  ddActArgs act = {a->coef, a->shift, a->nan == DD_PROPAGATE_NAN};
+  return dispatch_type<true>(h, xd->dtype, a->mode, c, x, dy, dx, alpha, beta, act);
+}

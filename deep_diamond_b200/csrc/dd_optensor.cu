@@ -1,0 +1,427 @@
+// Op-tensor family: fill, scale, broadcast binary ops and the n-ary scaled sum (the bodies of
+// ddSetTensor, ddScaleTensor, ddAddTensor, ddOpTensor, ddSumTensors).
+//
+//   C = op(alpha1*A, alpha2*bcast(B)) + beta*C
+//
+// Fast path ("flat"): A and C dense with identical strides, B either dense like A or indexed by one
+// middle dim only (the bias / per-channel-scale case: dims collapse to [outer, channel, inner] with
+// B varying along `channel`).  One 16-byte vector of A in, one of C out per thread-iteration; B comes
+// from L1/L2 (a few KB).  Algorithmic bytes/element: 2*sizeof(T) (+ the tiny B).  Everything else
+// runs through the strided kernel.  Each product and the final sums round separately (no FMA
+// contraction), a factor of exactly 1 is skipped and a zero factor means "operand not read".
+#include "dd_internal.cuh"
+
+template <typename C>
+__device__ __forceinline__ C dd_binop(int op, C a, C b) {
+  switch (op) {
+    case DD_OP_TENSOR_ADD: return dd_add_rn(a, b);
+    case DD_OP_TENSOR_MUL: return dd_mul_rn(a, b);
+    case DD_OP_TENSOR_MIN: return a < b ? a : b;
+    case DD_OP_TENSOR_MAX: return a > b ? a : b;
+    case DD_OP_TENSOR_SUB: return dd_add_rn(a, -b);
+    default: return a / b;  // DIV (IEEE round-to-nearest division)
+  }
+}
+
+struct ddOpFlatParams {
+  const void *A;
+  const void *B;
+  void *C;
+  int64_t n;         // elements of A / C
+  int64_t inner;     // bmode 1: run length over which B is constant
+  int64_t channels;  // bmode 1: extent of the dim B varies along
+  int64_t sB;        // bmode 1: B's stride along that dim
+  int bmode;         // 0: B dense like A; 1: B indexed by channel
+  int op;
+  int readA;         // 0: alpha1 == 0, A is not read (its term is +0)
+  int vec;
+  double alpha1, alpha2, beta;
+};
+
+template <typename T, typename C>
+__global__ void __launch_bounds__(256) dd_op_flat_kernel(ddOpFlatParams p) {
+  constexpr int V = 16 / sizeof(T);
+  const T *A = (const T *)p.A;
+  const T *B = (const T *)p.B;
+  T *Cp = (T *)p.C;
+  const C a1 = (C)p.alpha1, a2 = (C)p.alpha2, beta = (C)p.beta;
+  const bool useOld = p.beta != 0.0, readA = p.readA != 0;
+  const int op = p.op;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  int64_t done = 0;
+  if (p.vec) {
+    const int64_t nv = p.n / V;
+    for (int64_t i = tid; i < nv; i += nthreads) {
+      const int64_t e0 = i * V;
+      uint4 ain = readA ? *(const uint4 *)(A + e0) : make_uint4(0, 0, 0, 0);
+      uint4 oin = useOld ? *(const uint4 *)(Cp + e0) : make_uint4(0, 0, 0, 0);
+      uint4 bin;
+      C bs = (C)0;
+      if (p.bmode == 0) {
+        bin = *(const uint4 *)(B + e0);
+      } else {  // inner % V == 0: the whole vector shares one channel
+        const int64_t ch = (e0 / p.inner) % p.channels;
+        bs = dd_scale(a2, dd_load<C, T>(__ldg(B + ch * p.sB)));
+      }
+      uint4 res;
+      const T *av = (const T *)&ain, *bv = (const T *)&bin, *ov = (const T *)&oin;
+      T *rv = (T *)&res;
+#pragma unroll
+      for (int k = 0; k < V; k++) {
+        C a = readA ? dd_scale(a1, dd_load<C, T>(av[k])) : (C)0;
+        C b = p.bmode == 0 ? dd_scale(a2, dd_load<C, T>(bv[k])) : bs;
+        C r = dd_binop<C>(op, a, b);
+        if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
+        rv[k] = dd_store<T, C>(r);
+      }
+      *(uint4 *)(Cp + e0) = res;
+    }
+    done = nv * V;
+  }
+  for (int64_t i = done + tid; i < p.n; i += nthreads) {
+    C a = readA ? dd_scale(a1, dd_load<C, T>(A[i])) : (C)0;
+    C b = p.bmode == 0 ? dd_load<C, T>(B[i]) : dd_load<C, T>(B[((i / p.inner) % p.channels) * p.sB]);
+    C r = dd_binop<C>(op, a, dd_scale(a2, b));
+    if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(Cp[i])));
+    Cp[i] = dd_store<T, C>(r);
+  }
+}
+
+struct ddOpStridedParams {
+  const void *A;
+  const void *B;
+  void *C;
+  ddStridedParams<3> sp;  // operands 0 = A, 1 = B (stride 0 where broadcast), 2 = C
+  int op;
+  int readA;
+  double alpha1, alpha2, beta;
+};
+
+template <typename T, typename C>
+__global__ void __launch_bounds__(256) dd_op_strided_kernel(ddOpStridedParams p) {
+  const T *A = (const T *)p.A;
+  const T *B = (const T *)p.B;
+  T *Cp = (T *)p.C;
+  const C a1 = (C)p.alpha1, a2 = (C)p.alpha2, beta = (C)p.beta;
+  const bool useOld = p.beta != 0.0, readA = p.readA != 0;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.sp.total; i += nthreads) {
+    int64_t off[3];
+    dd_offsets<3, int64_t>(p.sp, i, off);
+    C a = readA ? dd_scale(a1, dd_load<C, T>(A[off[0]])) : (C)0;
+    C b = dd_scale(a2, dd_load<C, T>(B[off[1]]));
+    C r = dd_binop<C>(p.op, a, b);
+    if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(Cp[off[2]])));
+    Cp[off[2]] = dd_store<T, C>(r);
+  }
+}
+
+template <typename T, typename C>
+static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
+                                 const ddTensorStruct *ad, const void *A, double alpha2,
+                                 const ddTensorStruct *bd, const void *B, double beta,
+                                 const ddTensorStruct *cd, void *Cp) {
+  int64_t st[3][DD_DIM_MAX];
+  for (int i = 0; i < cd->nd; i++) {
+    st[0][i] = ad->strides[i];
+    st[1][i] = bd->dims[i] == 1 && cd->dims[i] != 1 ? 0 : bd->strides[i];
+    st[2][i] = cd->strides[i];
+  }
+  ddCanon c;
+  dd_canonicalize(&c, cd->nd, cd->dims, 3, st, 2);
+  // for ADD a zero factor on A means "A is not read" (beta == 0 semantics of ddAddTensor)
+  const int readA = !(alpha1 == 0.0 && op == DD_OP_TENSOR_ADD);
+  constexpr int V = 16 / sizeof(T);
+
+  // dense A and C?  After canonicalisation they are dense iff, walking from the innermost dim,
+  // each stride equals the product of the inner extents.
+  bool dense = true;
+  int64_t run = 1;
+  for (int i = c.nd - 1; i >= 0; i--) {
+    if (c.st[0][i] != run || c.st[2][i] != run) dense = false;
+    run *= c.dims[i];
+  }
+  int bmode = -1;
+  int64_t inner = 1, channels = 1, sB = 0;
+  if (dense) {
+    if (c.nd == 1 && c.st[1][0] == 1) {
+      bmode = 0;
+    } else {
+      // B must vary along exactly one dim
+      int vary = -1, nvary = 0;
+      for (int i = 0; i < c.nd; i++)
+        if (c.st[1][i] != 0) { vary = i; nvary++; }
+      if (nvary == 1) {
+        bmode = 1;
+        channels = c.dims[vary];
+        sB = c.st[1][vary];
+        for (int i = vary + 1; i < c.nd; i++) inner *= c.dims[i];
+      } else if (nvary == 0) {  // B is a single element
+        bmode = 1;
+        channels = 1;
+        sB = 0;
+        inner = c.total;
+      }
+    }
+  }
+  if (bmode >= 0) {
+    ddOpFlatParams p;
+    p.A = A;
+    p.B = B;
+    p.C = Cp;
+    p.n = c.total;
+    p.inner = inner;
+    p.channels = channels;
+    p.sB = sB;
+    p.bmode = bmode;
+    p.op = (int)op;
+    p.readA = readA;
+    p.alpha1 = alpha1;
+    p.alpha2 = alpha2;
+    p.beta = beta;
+    uintptr_t bits = (uintptr_t)A | (uintptr_t)Cp | (bmode == 0 ? (uintptr_t)B : 0);
+    p.vec = (bits & 15) == 0 && (bmode == 0 || inner % V == 0);
+    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
+    dd_op_flat_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
+    DD_LAUNCHED(h, bmode == 0 ? "optensor/flat" : "optensor/flat-bcast");
+    return DD_STATUS_SUCCESS;
+  }
+  ddOpStridedParams p;
+  p.A = A;
+  p.B = B;
+  p.C = Cp;
+  p.sp = dd_strided_params<3>(c);
+  p.op = (int)op;
+  p.readA = readA;
+  p.alpha1 = alpha1;
+  p.alpha2 = alpha2;
+  p.beta = beta;
+  unsigned grid = dd_flat_grid(h, c.total, 256, 16);
+  dd_op_strided_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
+  DD_LAUNCHED(h, "optensor/strided");
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t dd_optensor_impl(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
+                            const ddTensorStruct *ad, const void *A, double alpha2,
+                            const ddTensorStruct *bd, const void *B, double beta,
+                            const ddTensorStruct *cd, void *C) {
+  if (!dd_same_dims(ad, cd)) DD_FAIL(h, DD_STATUS_BAD_PARAM, "op-tensor: A and C dims differ");
+  if (bd->nd != cd->nd) DD_FAIL(h, DD_STATUS_BAD_PARAM, "op-tensor: operand ranks differ");
+  for (int i = 0; i < cd->nd; i++)
+    if (bd->dims[i] != cd->dims[i] && bd->dims[i] != 1)
+      DD_FAIL(h, DD_STATUS_BAD_PARAM, "op-tensor: dim %d of the broadcast operand must equal the destination's or be 1", i);
+  if (ad->dtype != cd->dtype || bd->dtype != cd->dtype)
+    DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "op-tensor: operands must share one data type");
+  switch (cd->dtype) {
+    case DD_DATA_FLOAT: return optensor_typed<float, float>(h, op, alpha1, ad, A, alpha2, bd, B, beta, cd, C);
+    case DD_DATA_DOUBLE: return optensor_typed<double, double>(h, op, alpha1, ad, A, alpha2, bd, B, beta, cd, C);
+    case DD_DATA_HALF: return optensor_typed<__half, float>(h, op, alpha1, ad, A, alpha2, bd, B, beta, cd, C);
+    case DD_DATA_BFLOAT16: return optensor_typed<__nv_bfloat16, float>(h, op, alpha1, ad, A, alpha2, bd, B, beta, cd, C);
+    case DD_DATA_INT8: return optensor_typed<int8_t, float>(h, op, alpha1, ad, A, alpha2, bd, B, beta, cd, C);
+    case DD_DATA_UINT8: return optensor_typed<uint8_t, float>(h, op, alpha1, ad, A, alpha2, bd, B, beta, cd, C);
+    case DD_DATA_INT32: return optensor_typed<int32_t, double>(h, op, alpha1, ad, A, alpha2, bd, B, beta, cd, C);
+    default: break;
+  }
+  DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "op-tensor: unsupported data type");
+}
+
+// ------------------------------------------------------------------ set / scale --------------
+
+struct ddFillParams {
+  void *y;
+  ddStridedParams<1> sp;
+  double value;
+  int scale;  // 0: y = value, 1: y *= value
+  int flat;
+};
+
+template <typename T, typename C>
+__global__ void __launch_bounds__(256) dd_fill_kernel(ddFillParams p) {
+  T *y = (T *)p.y;
+  const C v = (C)p.value;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (p.flat) {
+    constexpr int V = 16 / sizeof(T);
+    const int64_t n = p.sp.total;
+    int64_t done = 0;
+    if ((((uintptr_t)y) & 15) == 0) {
+      const int64_t nv = n / V;
+      for (int64_t i = tid; i < nv; i += nthreads) {
+        uint4 w;
+        T *wv = (T *)&w;
+        if (p.scale) {
+          w = *(const uint4 *)(y + i * V);
+#pragma unroll
+          for (int k = 0; k < V; k++) wv[k] = dd_store<T, C>(dd_mul_rn(v, dd_load<C, T>(wv[k])));
+        } else {
+#pragma unroll
+          for (int k = 0; k < V; k++) wv[k] = dd_store<T, C>(v);
+        }
+        *(uint4 *)(y + i * V) = w;
+      }
+      done = nv * V;
+    }
+    for (int64_t i = done + tid; i < n; i += nthreads)
+      y[i] = p.scale ? dd_store<T, C>(dd_mul_rn(v, dd_load<C, T>(y[i]))) : dd_store<T, C>(v);
+  } else {
+    for (int64_t i = tid; i < p.sp.total; i += nthreads) {
+      int64_t off[1];
+      dd_offsets<1, int64_t>(p.sp, i, off);
+      y[off[0]] = p.scale ? dd_store<T, C>(dd_mul_rn(v, dd_load<C, T>(y[off[0]]))) : dd_store<T, C>(v);
+    }
+  }
+}
+
+template <typename T, typename C>
+static ddStatus_t fill_typed(ddHandle_t h, const ddTensorStruct *yd, void *y, double value, int scale) {
+  int64_t st[1][DD_DIM_MAX];
+  for (int i = 0; i < yd->nd; i++) st[0][i] = yd->strides[i];
+  ddCanon c;
+  dd_canonicalize(&c, yd->nd, yd->dims, 1, st, 0);
+  ddFillParams p;
+  p.y = y;
+  p.sp = dd_strided_params<1>(c);
+  p.value = value;
+  p.scale = scale;
+  p.flat = c.nd == 1 && c.st[0][0] == 1;
+  constexpr int V = 16 / sizeof(T);
+  unsigned grid = dd_flat_grid(h, p.flat ? (c.total + V - 1) / V : c.total, 256, 16);
+  dd_fill_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
+  DD_LAUNCHED(h, scale ? (p.flat ? "scale/flat" : "scale/strided") : (p.flat ? "set/flat" : "set/strided"));
+  return DD_STATUS_SUCCESS;
+}
+
+static ddStatus_t fill_dispatch(ddHandle_t h, const ddTensorStruct *yd, void *y, double v, int scale) {
+  switch (yd->dtype) {
+    case DD_DATA_FLOAT: return fill_typed<float, float>(h, yd, y, v, scale);
+    case DD_DATA_DOUBLE: return fill_typed<double, double>(h, yd, y, v, scale);
+    case DD_DATA_HALF: return fill_typed<__half, float>(h, yd, y, v, scale);
+    case DD_DATA_BFLOAT16: return fill_typed<__nv_bfloat16, float>(h, yd, y, v, scale);
+    case DD_DATA_INT8: return fill_typed<int8_t, float>(h, yd, y, v, scale);
+    case DD_DATA_UINT8: return fill_typed<uint8_t, float>(h, yd, y, v, scale);
+    case DD_DATA_INT32: return fill_typed<int32_t, double>(h, yd, y, v, scale);
+    case DD_DATA_INT64: return fill_typed<int64_t, double>(h, yd, y, v, scale);
+  }
+  DD_FAIL(h, DD_STATUS_BAD_PARAM, "unknown data type");
+}
+
+ddStatus_t dd_set_impl(ddHandle_t h, const ddTensorStruct *yd, void *y, double value) {
+  return fill_dispatch(h, yd, y, value, 0);
+}
+ddStatus_t dd_scale_impl(ddHandle_t h, const ddTensorStruct *yd, void *y, double alpha) {
+  return fill_dispatch(h, yd, y, alpha, 1);
+}
+
+// ------------------------------------------------------------------ n-ary sum ----------------
+
+#define DD_SUM_MAX 8
+struct ddSumParams {
+  const void *src[DD_SUM_MAX];
+  float scale[DD_SUM_MAX];
+  void *dst;
+  int n;
+  int64_t total;
+  int vec;
+};
+
+// dst = (((s0*x0) + s1*x1) + s2*x2) ... : one pass over n dense same-layout sources.
+// Algorithmic bytes/element: (n + 1)*sizeof(T).
+template <typename T, typename C>
+__global__ void __launch_bounds__(256) dd_sum_kernel(ddSumParams p) {
+  constexpr int V = 16 / sizeof(T);
+  T *dst = (T *)p.dst;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  int64_t done = 0;
+  if (p.vec) {
+    const int64_t nv = p.total / V;
+    for (int64_t i = tid; i < nv; i += nthreads) {
+      C acc[V];
+#pragma unroll
+      for (int s = 0; s < DD_SUM_MAX; s++) {
+        if (s < p.n) {
+          uint4 in = *(const uint4 *)((const T *)p.src[s] + i * V);
+          const T *iv = (const T *)&in;
+          const C sc = (C)p.scale[s];
+#pragma unroll
+          for (int k = 0; k < V; k++) {
+            C t = dd_scale(sc, dd_load<C, T>(iv[k]));
+            acc[k] = s == 0 ? t : dd_add_rn(acc[k], t);
+          }
+        }
+      }
+      uint4 res;
+      T *rv = (T *)&res;
+#pragma unroll
+      for (int k = 0; k < V; k++) rv[k] = dd_store<T, C>(acc[k]);
+      *(uint4 *)(dst + i * V) = res;
+    }
+    done = nv * V;
+  }
+  for (int64_t i = done + tid; i < p.total; i += nthreads) {
+    C acc = (C)0;
+    for (int s = 0; s < p.n; s++) {
+      C t = dd_scale((C)p.scale[s], dd_load<C, T>(((const T *)p.src[s])[i]));
+      acc = s == 0 ? t : dd_add_rn(acc, t);
+    }
+    dst[i] = dd_store<T, C>(acc);
+  }
+}
+
+template <typename T, typename C>
+static ddStatus_t sum_typed(ddHandle_t h, const ddSumParams &p) {
+  constexpr int V = 16 / sizeof(T);
+  unsigned grid = dd_flat_grid(h, (p.total + V - 1) / V, 256, 16);
+  dd_sum_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
+  DD_LAUNCHED(h, "sum/flat");
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t dd_sum_impl(ddHandle_t h, int n, const float *scales, const ddTensorStruct *const *sd,
+                       const void *const *srcs, const ddTensorStruct *dd, void *dst) {
+  // one-pass kernel when every operand is dense with the destination's strides
+  bool same = true;
+  for (int s = 0; s < n; s++) {
+    if (!dd_same_dims(sd[s], dd) || sd[s]->dtype != dd->dtype)
+      DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddSumTensors: source %d differs from dst in dims or data type", s);
+    for (int i = 0; i < dd->nd; i++)
+      if (dd->dims[i] != 1 && sd[s]->strides[i] != dd->strides[i]) same = false;
+  }
+  int64_t st[1][DD_DIM_MAX];
+  for (int i = 0; i < dd->nd; i++) st[0][i] = dd->strides[i];
+  ddCanon c;
+  dd_canonicalize(&c, dd->nd, dd->dims, 1, st, 0);
+  const bool flat = same && c.nd == 1 && c.st[0][0] == 1;
+  if (flat) {
+    ddSumParams p;
+    memset(&p, 0, sizeof(p));
+    p.n = n;
+    p.total = c.total;
+    p.dst = dst;
+    uintptr_t bits = (uintptr_t)dst;
+    for (int s = 0; s < n; s++) {
+      p.src[s] = srcs[s];
+      p.scale[s] = scales[s];
+      bits |= (uintptr_t)srcs[s];
+    }
+    p.vec = (bits & 15) == 0;
+    switch (dd->dtype) {
+      case DD_DATA_FLOAT: return sum_typed<float, float>(h, p);
+      case DD_DATA_DOUBLE: return sum_typed<double, double>(h, p);
+      case DD_DATA_HALF: return sum_typed<__half, float>(h, p);
+      case DD_DATA_BFLOAT16: return sum_typed<__nv_bfloat16, float>(h, p);
+      default: DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddSumTensors: data type must be floating point");
+    }
+  }
+  // general layouts: dst = s0*src0 (a transform), then dst += si*srci, one pass each
+  ddStatus_t st0 = dd_transform_impl(h, (double)scales[0], sd[0], srcs[0], 0.0, dd, dst);
+  if (st0 != DD_STATUS_SUCCESS) return st0;
+  for (int s = 1; s < n; s++) {
+    ddStatus_t r = dd_optensor_impl(h, DD_OP_TENSOR_ADD, 1.0, dd, dst, (double)scales[s], sd[s], srcs[s], 0.0, dd, dst);
+    if (r != DD_STATUS_SUCCESS) return r;
+  }
+  return DD_STATUS_SUCCESS;
+}

@@ -1,0 +1,235 @@
+// ddReduceTensor: host-side planning (which dims are reduced, kernel family, splits, workspace)
+// and dispatch.  Kernels are in dd_reduce_kernels.cuh, instantiated per element type in
+// dd_reduce_{f32,f64,f16,bf16}.cu.
+#include "dd_reduce_kernels.cuh"
+
+static int next_pow2(int64_t v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd,
+                          const void *x, const ddTensorStruct *yd, ddRedPlan *pl) {
+  memset(pl, 0, sizeof(*pl));
+  switch (red->op) {
+    case DD_REDUCE_TENSOR_ADD: pl->opc = DD_OPC_SUM; pl->p.post = DD_POST_NONE; break;
+    case DD_REDUCE_TENSOR_AVG: pl->opc = DD_OPC_SUM; pl->p.post = DD_POST_AVG; break;
+    case DD_REDUCE_TENSOR_NORM1: pl->opc = DD_OPC_SUMABS; pl->p.post = DD_POST_NONE; break;
+    case DD_REDUCE_TENSOR_NORM2: pl->opc = DD_OPC_SUMSQ; pl->p.post = DD_POST_SQRT; break;
+    case DD_REDUCE_TENSOR_MUL: pl->opc = DD_OPC_PROD; pl->p.post = DD_POST_NONE; break;
+    case DD_REDUCE_TENSOR_MUL_NO_ZEROS: pl->opc = DD_OPC_PRODNZ; pl->p.post = DD_POST_NONE; break;
+    case DD_REDUCE_TENSOR_MIN: pl->opc = DD_OPC_MIN; pl->p.post = DD_POST_NONE; break;
+    case DD_REDUCE_TENSOR_MAX: pl->opc = DD_OPC_MAX; pl->p.post = DD_POST_NONE; break;
+    case DD_REDUCE_TENSOR_AMAX: pl->opc = DD_OPC_AMAX; pl->p.post = DD_POST_NONE; break;
+    default: DD_FAIL(h, DD_STATUS_BAD_PARAM, "reduce: unknown op");
+  }
+  if (xd->dtype != yd->dtype) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: x and y must share one data type");
+  const int esize = dd_type_size(xd->dtype);
+  const int csize = xd->dtype == DD_DATA_DOUBLE ? 8 : 4;
+  const int V = 16 / esize;
+
+  int64_t st[2][DD_DIM_MAX];
+  for (int i = 0; i < xd->nd; i++) {
+    st[0][i] = xd->strides[i];
+    st[1][i] = (yd->dims[i] == 1 && xd->dims[i] != 1) ? 0 : yd->strides[i];
+  }
+  ddCanon c;
+  dd_canonicalize(&c, xd->nd, xd->dims, 2, st, 0);
+
+  int64_t nout = 1, nred = 1;
+  for (int i = 0; i < c.nd; i++) {
+    if (c.st[1][i] != 0) nout *= c.dims[i];
+    else nred *= c.dims[i];
+  }
+  if (c.nd == 1 && c.dims[0] == 1) { nout = 1; nred = 1; }
+  pl->nout = nout;
+
+  // match x[k1][r1][k2][r2] from the innermost dim outwards
+  int slotDim[4] = {-1, -1, -1, -1};  // canonical dim index held by K1, R1, K2, R2
+  bool fits = true;
+  {
+    int slot = 3;
+    for (int i = c.nd - 1; i >= 0 && fits; i--) {
+      const bool kept = c.st[1][i] != 0;
+      // next free slot at or below `slot` of the right kind (odd slots reduce, even slots keep)
+      while (slot >= 0 && ((slot & 1) == 1) == kept) slot--;
+      if (slot < 0) { fits = false; break; }
+      slotDim[slot] = i;
+      slot--;
+    }
+  }
+  ddRedParams &p = pl->p;
+  auto ext = [&](int s) { return slotDim[s] < 0 ? (int64_t)1 : c.dims[slotDim[s]]; };
+  auto sx = [&](int s) { return slotDim[s] < 0 ? (int64_t)0 : c.st[0][slotDim[s]]; };
+  auto sy = [&](int s) { return slotDim[s] < 0 ? (int64_t)0 : c.st[1][slotDim[s]]; };
+  if (c.nd == 1 && c.dims[0] == 1) { slotDim[0] = slotDim[1] = slotDim[2] = slotDim[3] = -1; fits = true; }
+  p.x = x;
+  p.K1 = ext(0); p.R1 = ext(1); p.K2 = ext(2); p.R2 = ext(3);
+  p.sxK1 = sx(0); p.sxR1 = sx(1); p.sxK2 = sx(2); p.sxR2 = sx(3);
+  p.syK1 = sy(0); p.syK2 = sy(2);
+  p.count = (double)nred;
+  p.nanProp = red->nan == DD_PROPAGATE_NAN;
+  p.S = 1;
+
+  const int64_t desired = (int64_t)h->smCount * 6;
+  const bool aligned = (((uintptr_t)x) & 15) == 0;
+  auto mult = [&](int64_t extent, int64_t stride) { return extent == 1 || stride % V == 0; };
+
+  if (fits && p.R2 > 1 && p.sxR2 == 1 && nred > 32) {
+    pl->kind = DD_RED_ROW;
+    pl->vec = aligned && p.R2 % V == 0 && mult(p.K1, p.sxK1) && mult(p.R1, p.sxR1) && mult(p.K2, p.sxK2);
+    const int v = pl->vec ? V : 1;
+    p.G = nred <= 2048 ? 32 : 256;
+    const int gpb = 256 / p.G;
+    p.CH = (int64_t)p.G * v;
+    p.cpr = (p.R2 + p.CH - 1) / p.CH;
+    const int64_t want = desired * gpb;
+    if (nout < want) {
+      int64_t units = p.R1 * p.cpr;
+      int64_t S = (want + nout - 1) / nout;
+      if (S > units / 4) S = units / 4;
+      if (S > 1024) S = 1024;
+      if (S > 1) {
+        if (p.R1 >= S) {
+          p.splitR1 = 1;
+          int64_t per = (p.R1 + S - 1) / S;
+          S = (p.R1 + per - 1) / per;
+        } else {
+          p.splitR1 = 0;
+          if (S > p.cpr) S = p.cpr;
+          int64_t per = (p.cpr + S - 1) / S;
+          S = (p.cpr + per - 1) / per;
+        }
+      }
+      p.S = S < 1 ? 1 : (int)S;
+    }
+    int64_t groups = nout * p.S;
+    int64_t ctas = (groups + gpb - 1) / gpb;
+    if (ctas > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: too many outputs");
+    pl->grid = (unsigned)ctas;
+  } else if (fits && p.R2 == 1 && (p.K2 == 1 || p.sxK2 == 1)) {
+    pl->kind = DD_RED_COL;
+    pl->vec = aligned && p.K2 % V == 0 && mult(p.K1, p.sxK1) && mult(p.R1, p.sxR1);
+    const int v = pl->vec ? V : 1;
+    int tx = next_pow2((p.K2 + v - 1) / v);
+    p.TX = tx > 32 ? 32 : tx;
+    const int TY = 256 / p.TX;
+    p.tilesK2 = (p.K2 + (int64_t)p.TX * v - 1) / ((int64_t)p.TX * v);
+    int64_t ctas0 = p.K1 * p.tilesK2;
+    if (ctas0 < desired) {
+      int64_t S = (desired + ctas0 - 1) / ctas0;
+      int64_t cap = p.R1 / ((int64_t)TY * 4);
+      if (S > cap) S = cap;
+      if (S > 1024) S = 1024;
+      if (S > 1) {
+        int64_t per = (p.R1 + S - 1) / S;
+        S = (p.R1 + per - 1) / per;
+      }
+      p.S = S < 1 ? 1 : (int)S;
+    }
+    int64_t ctas = ctas0 * p.S;
+    if (ctas > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: too many outputs");
+    pl->grid = (unsigned)ctas;
+  } else {
+    pl->kind = DD_RED_GENERIC;
+    ddRedGenericParams &g = pl->g;
+    g.x = x;
+    g.nk = g.nr = 0;
+    for (int i = 0; i < c.nd; i++) {
+      if (c.nd == 1 && c.dims[0] == 1) break;
+      if (c.st[1][i] != 0) {
+        g.kd[g.nk] = c.dims[i]; g.kx[g.nk] = c.st[0][i]; g.ky[g.nk] = c.st[1][i]; g.nk++;
+      } else {
+        g.rd[g.nr] = c.dims[i]; g.rx[g.nr] = c.st[0][i]; g.nr++;
+      }
+    }
+    g.nout = nout;
+    g.nred = nred;
+    g.count = (double)nred;
+    g.post = p.post;
+    g.nanProp = p.nanProp;
+    pl->grid = dd_flat_grid(h, nout, 256, 16);
+  }
+  pl->wsBytes = p.S > 1 ? (size_t)nout * p.S * csize : 0;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t dd_reduce_ws_size(ddHandle_t h, const ddReduceTensorStruct *red,
+                             const ddTensorStruct *xd, const ddTensorStruct *yd, size_t *bytes) {
+  ddRedPlan pl;
+  // alignment of x is unknown here: plan as if aligned (the split count does not depend on it
+  // beyond the vector width, and an unaligned x only lowers the chunk size, never raises S*nout
+  // above what the aligned plan needs ... so take the larger of both plans)
+  ddStatus_t st = dd_reduce_plan(h, red, xd, (const void *)0, yd, &pl);
+  if (st != DD_STATUS_SUCCESS) return st;
+  size_t a = pl.wsBytes;
+  st = dd_reduce_plan(h, red, xd, (const void *)4, yd, &pl);
+  if (st != DD_STATUS_SUCCESS) return st;
+  *bytes = a > pl.wsBytes ? a : pl.wsBytes;
+  return DD_STATUS_SUCCESS;
+}
+
+static ddStatus_t launch_by_type(ddHandle_t h, ddDataType_t t, const ddRedPlan &pl) {
+  switch (t) {
+    case DD_DATA_FLOAT: return dd_reduce_launch<float, float>(h, pl);
+    case DD_DATA_DOUBLE: return dd_reduce_launch<double, double>(h, pl);
+    case DD_DATA_HALF: return dd_reduce_launch<__half, float>(h, pl);
+    case DD_DATA_BFLOAT16: return dd_reduce_launch<__nv_bfloat16, float>(h, pl);
+    default: break;
+  }
+  DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
+}
+
+ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *ws, size_t wsBytes,
+                          double alpha, const ddTensorStruct *xd, const void *x, double beta,
+                          const ddTensorStruct *yd, void *y, bool partialOnly, void *partialOut) {
+  ddRedPlan pl;
+  ddStatus_t st = dd_reduce_plan(h, red, xd, x, yd, &pl);
+  if (st != DD_STATUS_SUCCESS) return st;
+  if (partialOnly && pl.kind == DD_RED_GENERIC)
+    DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
+  if (pl.wsBytes > 0) {
+    if (!ws) {
+      ws = h->scratch;
+      wsBytes = h->scratchBytes;
+    }
+    if (wsBytes < pl.wsBytes)
+      DD_FAIL(h, DD_STATUS_BAD_PARAM, "reduce: workspace of %zu bytes needed, %zu given", pl.wsBytes, wsBytes);
+    if (((uintptr_t)ws) & 7) DD_FAIL(h, DD_STATUS_BAD_PARAM, "reduce: workspace must be 8-byte aligned");
+  }
+  pl.p.y = y;
+  pl.p.part = ws;
+  pl.p.partOut = partialOut;
+  pl.p.alpha = alpha;
+  pl.p.beta = beta;
+  pl.p.partialOnly = partialOnly ? 1 : 0;
+  pl.g.y = y;
+  pl.g.partOut = partialOut;
+  pl.g.alpha = alpha;
+  pl.g.beta = beta;
+  pl.g.partialOnly = partialOnly ? 1 : 0;
+  return launch_by_type(h, xd->dtype, pl);
+}
+
+ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, const void *partial,
+                                 double count, double alpha, double beta, const ddTensorStruct *xd,
+                                 const ddTensorStruct *yd, void *y) {
+  ddRedPlan pl;
+  ddStatus_t st = dd_reduce_plan(h, red, xd, (const void *)0, yd, &pl);
+  if (st != DD_STATUS_SUCCESS) return st;
+  if (pl.kind == DD_RED_GENERIC)
+    DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
+  pl.p.y = y;
+  pl.p.alpha = alpha;
+  pl.p.beta = beta;
+  pl.p.count = count;
+  switch (xd->dtype) {
+    case DD_DATA_FLOAT: return dd_reduce_finish_launch<float, float>(h, pl, partial);
+    case DD_DATA_DOUBLE: return dd_reduce_finish_launch<double, double>(h, pl, partial);
+    case DD_DATA_HALF: return dd_reduce_finish_launch<__half, float>(h, pl, partial);
+    case DD_DATA_BFLOAT16: return dd_reduce_finish_launch<__nv_bfloat16, float>(h, pl, partial);
+    default: break;
+  }
+  DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
+}

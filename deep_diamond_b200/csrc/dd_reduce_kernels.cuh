@@ -1,0 +1,425 @@
+// Reduce-tensor kernels: y = alpha*post(reduce(pre(x))) + beta*y over the dims where y's extent is 1.
+//
+// The canonical iteration space (dims ordered by x stride, merged) is matched against the form
+//     x[k1][r1][k2][r2]      k* kept, r* reduced, any of the four may have extent 1
+// which covers nchw/nhwc reductions over any subset of (N, C, spatial).  Two kernel families:
+//
+//   row   r2 > 1 and contiguous in x (reduce over the innermost run; e.g. nchw sum over (N,H,W)
+//         or norm over (C,H,W)).  A group of 32 or 256 threads owns one (output, split): 16-byte
+//         loads along r2, register accumulation, warp shuffle tree, shared-memory tree across warps.
+//   col   r2 == 1 and k2 contiguous in x (reduce across a strided dim; e.g. nchw max over C).
+//         Lanes run along k2 with 16-byte loads, warps stride over r1, shared-memory combine.
+//
+// When an output's reduce range is split over several CTAs (few outputs, long ranges) each split
+// writes one partial to the workspace and dd_reduce_finish_kernel combines them in a fixed order,
+// so results are run-to-run identical.  Anything that does not fit the 4-level form runs one
+// thread per output (generic).  All are HBM-bound: algorithmic bytes = input bytes + output bytes.
+#pragma once
+#include "dd_internal.cuh"
+
+enum { DD_OPC_SUM = 0, DD_OPC_SUMABS, DD_OPC_SUMSQ, DD_OPC_PROD, DD_OPC_PRODNZ, DD_OPC_MIN, DD_OPC_MAX, DD_OPC_AMAX, DD_OPC_COUNT };
+enum { DD_POST_NONE = 0, DD_POST_AVG = 1, DD_POST_SQRT = 2 };
+
+template <typename C> __device__ __forceinline__ C dd_inf();
+template <> __device__ __forceinline__ float dd_inf<float>() { return __int_as_float(0x7f800000); }
+template <> __device__ __forceinline__ double dd_inf<double>() { return __longlong_as_double(0x7ff0000000000000LL); }
+__device__ __forceinline__ float dd_abs(float v) { return fabsf(v); }
+__device__ __forceinline__ double dd_abs(double v) { return fabs(v); }
+__device__ __forceinline__ float dd_fma(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double dd_fma(double a, double b, double c) { return fma(a, b, c); }
+__device__ __forceinline__ float dd_sqrt(float v) { return __fsqrt_rn(v); }
+__device__ __forceinline__ double dd_sqrt(double v) { return __dsqrt_rn(v); }
+__device__ __forceinline__ float dd_div(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ double dd_div(double a, double b) { return __ddiv_rn(a, b); }
+
+template <typename C, int OPC>
+struct dd_red {
+  static __device__ __forceinline__ C identity() {
+    if (OPC == DD_OPC_PROD || OPC == DD_OPC_PRODNZ) return (C)1;
+    if (OPC == DD_OPC_MIN) return dd_inf<C>();
+    if (OPC == DD_OPC_MAX) return -dd_inf<C>();
+    return (C)0;
+  }
+  // acc (+)= pre(v)
+  static __device__ __forceinline__ C accum(C acc, C v, bool nanProp) {
+    if (OPC == DD_OPC_SUM) return dd_add_rn(acc, v);
+    if (OPC == DD_OPC_SUMABS) return dd_add_rn(acc, dd_abs(v));
+    if (OPC == DD_OPC_SUMSQ) return dd_fma(v, v, acc);
+    if (OPC == DD_OPC_PROD) return dd_mul_rn(acc, v);
+    if (OPC == DD_OPC_PRODNZ) return v == (C)0 ? acc : dd_mul_rn(acc, v);
+    if (OPC == DD_OPC_AMAX) return comb(acc, dd_abs(v), nanProp);
+    return comb(acc, v, nanProp);
+  }
+  // combines two accumulators
+  static __device__ __forceinline__ C comb(C a, C b, bool nanProp) {
+    if (OPC == DD_OPC_SUM || OPC == DD_OPC_SUMABS || OPC == DD_OPC_SUMSQ) return dd_add_rn(a, b);
+    if (OPC == DD_OPC_PROD || OPC == DD_OPC_PRODNZ) return dd_mul_rn(a, b);
+    C r;
+    if (OPC == DD_OPC_MIN) r = a < b ? a : b;
+    else r = a > b ? a : b;  // MAX, AMAX
+    if (a != a) r = nanProp ? a : b;
+    if (b != b) r = nanProp ? b : (a != a ? b : a);
+    return r;
+  }
+};
+
+struct ddRedParams {
+  const void *x;
+  void *y;
+  void *part;     // workspace: [out][split] accumulators of the compute type (used when S > 1)
+  void *partOut;  // partialOnly: [out] raw accumulators (no post/alpha/beta) instead of y
+  int64_t K1, R1, K2, R2;
+  int64_t sxK1, sxR1, sxK2, sxR2;
+  int64_t syK1, syK2;
+  int S;             // CTAs (groups) per output
+  int G;             // row: threads per group (32 or 256)
+  int64_t CH;        // row: elements of r2 covered per group iteration (G * V)
+  int64_t cpr;       // row: chunks per r2 run
+  int splitR1;       // row: 1 = splits partition r1, 0 = splits partition the chunks of r2
+  int TX;            // col: lanes along k2
+  int64_t tilesK2;   // col: tiles along k2
+  double alpha, beta, count;
+  int post;
+  int nanProp;
+  int partialOnly;   // 1: store the raw accumulator into partOut[out] and leave y alone
+};
+
+template <typename T, typename C>
+__device__ __forceinline__ void dd_red_finish(const ddRedParams &p, int64_t k1, int64_t k2, C acc) {
+  if (p.partialOnly) {
+    ((C *)p.partOut)[k1 * p.K2 + k2] = acc;
+    return;
+  }
+  C v = acc;
+  if (p.post == DD_POST_AVG) v = dd_div(v, (C)p.count);
+  if (p.post == DD_POST_SQRT) v = dd_sqrt(v);
+  v = dd_scale((C)p.alpha, v);
+  T *yp = (T *)p.y + k1 * p.syK1 + k2 * p.syK2;
+  if (p.beta != 0.0) v = dd_add_rn(v, dd_mul_rn((C)p.beta, dd_load<C, T>(*yp)));
+  *yp = dd_store<T, C>(v);
+}
+
+// Tree over the G threads of a group (G = 32: one warp; G = 256: the CTA).  Result valid in lane 0
+// of the group.
+template <typename C, int OPC>
+__device__ __forceinline__ C dd_group_reduce(C acc, int G, bool nanProp, C *smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    C other = __shfl_down_sync(0xffffffffu, acc, o);
+    acc = dd_red<C, OPC>::comb(acc, other, nanProp);
+  }
+  if (G == 32) return acc;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    acc = lane < (int)(blockDim.x >> 5) ? smem[lane] : dd_red<C, OPC>::identity();
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      C other = __shfl_down_sync(0xffffffffu, acc, o);
+      acc = dd_red<C, OPC>::comb(acc, other, nanProp);
+    }
+  }
+  return acc;
+}
+
+template <typename T, typename C, int OPC, bool VEC>
+__global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
+  constexpr int V = VEC ? 16 / sizeof(T) : 1;
+  constexpr int U = 4;  // independent loads in flight per thread
+  __shared__ C smem[8];
+  const bool nanProp = p.nanProp != 0;
+  const int G = p.G;
+  const int gpb = 256 / G;  // groups per CTA
+  const int64_t g = (int64_t)blockIdx.x * gpb + threadIdx.x / G;
+  const int lane = threadIdx.x % G;
+  const int64_t nout = p.K1 * p.K2;
+  C acc = dd_red<C, OPC>::identity();
+  const bool live = g < nout * p.S;  // G == 32 only: trailing groups of the last CTA idle
+  int64_t out = 0, k1 = 0, k2 = 0;
+  int s = 0;
+  if (live) {
+    out = g / p.S;
+    s = (int)(g - out * p.S);
+    k1 = out / p.K2;
+    k2 = out - k1 * p.K2;
+    int64_t r1lo = 0, r1hi = p.R1, jlo = 0, jhi = p.cpr;
+    if (p.S > 1) {
+      if (p.splitR1) {
+        int64_t per = (p.R1 + p.S - 1) / p.S;
+        r1lo = s * per;
+        r1hi = r1lo + per < p.R1 ? r1lo + per : p.R1;
+      } else {
+        int64_t per = (p.cpr + p.S - 1) / p.S;
+        jlo = s * per;
+        jhi = jlo + per < p.cpr ? jlo + per : p.cpr;
+      }
+    }
+    const T *xb = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2;
+    const int64_t nj = jhi - jlo;
+    const int64_t iters = (r1hi > r1lo && nj > 0) ? (r1hi - r1lo) * nj : 0;
+    int64_t r1 = r1lo, j = jlo;
+    for (int64_t it = 0; it < iters; it += U) {
+      C vals[U][V];
+      bool ok[U];
+#pragma unroll
+      for (int q = 0; q < U; q++) {
+        const int64_t e = j * p.CH + (int64_t)lane * V;
+        ok[q] = (it + q < iters) && (e < p.R2);
+        if (ok[q]) {
+          const T *ptr = xb + r1 * p.sxR1 + e;
+          if (VEC) {
+            uint4 w = *(const uint4 *)ptr;
+            const T *wv = (const T *)&w;
+#pragma unroll
+            for (int k = 0; k < V; k++) vals[q][k] = dd_load<C, T>(wv[k]);
+          } else {
+            vals[q][0] = dd_load<C, T>(*ptr);
+          }
+        }
+        j++;
+        if (j == jhi) { j = jlo; r1++; }
+      }
+#pragma unroll
+      for (int q = 0; q < U; q++) {
+        if (ok[q]) {
+#pragma unroll
+          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, vals[q][k], nanProp);
+        }
+      }
+    }
+  }
+  acc = dd_group_reduce<C, OPC>(acc, G, nanProp, smem);
+  if (live && lane == 0) {
+    if (p.S == 1) dd_red_finish<T, C>(p, k1, k2, acc);
+    else ((C *)p.part)[out * p.S + s] = acc;
+  }
+}
+
+// col: CTA = TX lanes along k2 (V elements each) x TY = 256/TX row groups striding over r1.
+template <typename T, typename C, int OPC, bool VEC>
+__global__ void __launch_bounds__(256) dd_reduce_col_kernel(ddRedParams p) {
+  constexpr int V = VEC ? 16 / sizeof(T) : 1;
+  constexpr int U = 4;
+  __shared__ C smem[256 * V];
+  const bool nanProp = p.nanProp != 0;
+  const int TX = p.TX, TY = 256 / TX;
+  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+  int64_t id = blockIdx.x;
+  const int s = (int)(id % p.S);
+  id /= p.S;
+  const int64_t tk = id % p.tilesK2;
+  const int64_t k1 = id / p.tilesK2;
+  const int64_t k2 = (tk * TX + tx) * V;
+  int64_t lo = 0, hi = p.R1;
+  if (p.S > 1) {
+    int64_t per = (p.R1 + p.S - 1) / p.S;
+    lo = s * per;
+    hi = lo + per < p.R1 ? lo + per : p.R1;
+  }
+  C acc[V];
+#pragma unroll
+  for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::identity();
+  if (k2 < p.K2) {
+    const T *xb = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2;
+    for (int64_t r0 = lo + ty; r0 < hi; r0 += (int64_t)TY * U) {
+      C vals[U][V];
+      bool ok[U];
+#pragma unroll
+      for (int q = 0; q < U; q++) {
+        const int64_t r1 = r0 + (int64_t)q * TY;
+        ok[q] = r1 < hi;
+        if (ok[q]) {
+          const T *ptr = xb + r1 * p.sxR1;
+          if (VEC) {
+            uint4 w = *(const uint4 *)ptr;
+            const T *wv = (const T *)&w;
+#pragma unroll
+            for (int k = 0; k < V; k++) vals[q][k] = dd_load<C, T>(wv[k]);
+          } else {
+            vals[q][0] = dd_load<C, T>(*ptr);
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < U; q++) {
+        if (ok[q]) {
+#pragma unroll
+          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], vals[q][k], nanProp);
+        }
+      }
+    }
+  }
+  // combine the TY row groups: smem[ty][tx*V + k], then the first TX*V threads fold TY values in
+  // a fixed order
+#pragma unroll
+  for (int k = 0; k < V; k++) smem[ty * (TX * V) + tx * V + k] = acc[k];
+  __syncthreads();
+  const int col = threadIdx.x;
+  if (col < TX * V) {
+    C a = smem[col];
+    for (int r = 1; r < TY; r++) a = dd_red<C, OPC>::comb(a, smem[r * (TX * V) + col], nanProp);
+    const int64_t kk = tk * TX * V + col;
+    if (kk < p.K2) {
+      if (p.S == 1) dd_red_finish<T, C>(p, k1, kk, a);
+      else ((C *)p.part)[(k1 * p.K2 + kk) * p.S + s] = a;
+    }
+  }
+}
+
+// Combines the S partials of each output in index order and finishes.  `part` may be an
+// all-reduced buffer (S == 1) on the multi-GPU path.
+template <typename T, typename C, int OPC>
+__global__ void __launch_bounds__(256) dd_reduce_finish_kernel(ddRedParams p, const void *part) {
+  const bool nanProp = p.nanProp != 0;
+  const int64_t nout = p.K1 * p.K2;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < nout; o += nthreads) {
+    const C *pp = (const C *)part + o * p.S;
+    C acc = pp[0];
+    for (int s = 1; s < p.S; s++) acc = dd_red<C, OPC>::comb(acc, pp[s], nanProp);
+    const int64_t k1 = o / p.K2;
+    dd_red_finish<T, C>(p, k1, o - k1 * p.K2, acc);
+  }
+}
+
+// generic: one thread per output, serial walk over the reduced dims.
+struct ddRedGenericParams {
+  const void *x;
+  void *y;
+  void *partOut;
+  int nk, nr;
+  int64_t kd[DD_DIM_MAX], kx[DD_DIM_MAX], ky[DD_DIM_MAX];  // kept dims: extent, x stride, y stride
+  int64_t rd[DD_DIM_MAX], rx[DD_DIM_MAX];                  // reduced dims: extent, x stride
+  int64_t nout, nred;
+  double alpha, beta, count;
+  int post, nanProp, partialOnly;
+};
+
+template <typename T, typename C, int OPC>
+__global__ void __launch_bounds__(256) dd_reduce_generic_kernel(ddRedGenericParams p) {
+  const bool nanProp = p.nanProp != 0;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < p.nout; o += nthreads) {
+    int64_t ox = 0, oy = 0, rem = o;
+    for (int d = p.nk - 1; d >= 0; d--) {
+      int64_t q = rem / p.kd[d], r = rem - q * p.kd[d];
+      ox += r * p.kx[d];
+      oy += r * p.ky[d];
+      rem = q;
+    }
+    C acc = dd_red<C, OPC>::identity();
+    for (int64_t i = 0; i < p.nred; i++) {
+      int64_t off = ox, rr = i;
+      for (int d = p.nr - 1; d >= 0; d--) {
+        int64_t q = rr / p.rd[d];
+        off += (rr - q * p.rd[d]) * p.rx[d];
+        rr = q;
+      }
+      acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(((const T *)p.x)[off]), nanProp);
+    }
+    if (p.partialOnly) {
+      ((C *)p.partOut)[o] = acc;
+    } else {
+      C v = acc;
+      if (p.post == DD_POST_AVG) v = dd_div(v, (C)p.count);
+      if (p.post == DD_POST_SQRT) v = dd_sqrt(v);
+      v = dd_scale((C)p.alpha, v);
+      T *yp = (T *)p.y + oy;
+      if (p.beta != 0.0) v = dd_add_rn(v, dd_mul_rn((C)p.beta, dd_load<C, T>(*yp)));
+      *yp = dd_store<T, C>(v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host plan ----------------
+
+enum { DD_RED_ROW = 0, DD_RED_COL = 1, DD_RED_GENERIC = 2 };
+
+struct ddRedPlan {
+  int kind;
+  int vec;
+  int opc;
+  ddRedParams p;
+  ddRedGenericParams g;
+  int64_t nout;
+  size_t wsBytes;  // workspace needed (0 when every output has a single split)
+  unsigned grid;
+};
+
+ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd,
+                          const void *x, const ddTensorStruct *yd, ddRedPlan *pl);
+
+template <typename T, typename C>
+ddStatus_t dd_reduce_launch(ddHandle_t h, const ddRedPlan &pl);
+template <typename T, typename C>
+ddStatus_t dd_reduce_finish_launch(ddHandle_t h, const ddRedPlan &pl, const void *part);
+#define DD_REDUCE_DECLARE(T, C)                                                   \
+  template <> ddStatus_t dd_reduce_launch<T, C>(ddHandle_t, const ddRedPlan &);   \
+  template <> ddStatus_t dd_reduce_finish_launch<T, C>(ddHandle_t, const ddRedPlan &, const void *);
+DD_REDUCE_DECLARE(float, float)
+DD_REDUCE_DECLARE(double, double)
+DD_REDUCE_DECLARE(__half, float)
+DD_REDUCE_DECLARE(__nv_bfloat16, float)
+
+#define DD_REDUCE_DEFINE(T, C)                                                                     \
+  template <int OPC>                                                                               \
+  static ddStatus_t launch_opc_##T(ddHandle_t h, const ddRedPlan &pl) {                            \
+    if (pl.kind == DD_RED_ROW) {                                                                   \
+      if (pl.vec) dd_reduce_row_kernel<T, C, OPC, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);     \
+      else dd_reduce_row_kernel<T, C, OPC, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);           \
+      DD_LAUNCHED(h, "reduce/row");                                                                \
+    } else if (pl.kind == DD_RED_COL) {                                                            \
+      if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);     \
+      else dd_reduce_col_kernel<T, C, OPC, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);           \
+      DD_LAUNCHED(h, "reduce/col");                                                                \
+    } else {                                                                                       \
+      dd_reduce_generic_kernel<T, C, OPC><<<pl.grid, 256, 0, h->stream>>>(pl.g);                   \
+      DD_LAUNCHED(h, "reduce/generic");                                                            \
+      return DD_STATUS_SUCCESS;                                                                    \
+    }                                                                                              \
+    if (pl.p.S > 1) {                                                                              \
+      unsigned fg = dd_flat_grid(h, pl.nout, 256, 8);                                              \
+      dd_reduce_finish_kernel<T, C, OPC><<<fg, 256, 0, h->stream>>>(pl.p, pl.p.part);              \
+      DD_LAUNCHED(h, pl.kind == DD_RED_ROW ? "reduce/row+finish" : "reduce/col+finish");           \
+    }                                                                                              \
+    return DD_STATUS_SUCCESS;                                                                      \
+  }                                                                                                \
+  template <int OPC>                                                                               \
+  static ddStatus_t finish_opc_##T(ddHandle_t h, const ddRedPlan &pl, const void *part) {          \
+    ddRedParams p = pl.p;                                                                          \
+    p.S = 1;                                                                                       \
+    p.partialOnly = 0;                                                                             \
+    unsigned fg = dd_flat_grid(h, pl.nout, 256, 8);                                                \
+    dd_reduce_finish_kernel<T, C, OPC><<<fg, 256, 0, h->stream>>>(p, part);                        \
+    DD_LAUNCHED(h, "reduce/finish");                                                               \
+    return DD_STATUS_SUCCESS;                                                                      \
+  }                                                                                                \
+  template <>                                                                                      \
+  ddStatus_t dd_reduce_launch<T, C>(ddHandle_t h, const ddRedPlan &pl) {                           \
+    switch (pl.opc) {                                                                              \
+      case DD_OPC_SUM: return launch_opc_##T<DD_OPC_SUM>(h, pl);                                   \
+      case DD_OPC_SUMABS: return launch_opc_##T<DD_OPC_SUMABS>(h, pl);                             \
+      case DD_OPC_SUMSQ: return launch_opc_##T<DD_OPC_SUMSQ>(h, pl);                               \
+      case DD_OPC_PROD: return launch_opc_##T<DD_OPC_PROD>(h, pl);                                 \
+      case DD_OPC_PRODNZ: return launch_opc_##T<DD_OPC_PRODNZ>(h, pl);                             \
+      case DD_OPC_MIN: return launch_opc_##T<DD_OPC_MIN>(h, pl);                                   \
+      case DD_OPC_MAX: return launch_opc_##T<DD_OPC_MAX>(h, pl);                                   \
+      case DD_OPC_AMAX: return launch_opc_##T<DD_OPC_AMAX>(h, pl);                                 \
+    }                                                                                              \
+    return DD_STATUS_INTERNAL_ERROR;                                                               \
+  }                                                                                                \
+  template <>                                                                                      \
+  ddStatus_t dd_reduce_finish_launch<T, C>(ddHandle_t h, const ddRedPlan &pl, const void *part) {  \
+    switch (pl.opc) {                                                                              \
+      case DD_OPC_SUM: return finish_opc_##T<DD_OPC_SUM>(h, pl, part);                             \
+      case DD_OPC_SUMABS: return finish_opc_##T<DD_OPC_SUMABS>(h, pl, part);                       \
+      case DD_OPC_SUMSQ: return finish_opc_##T<DD_OPC_SUMSQ>(h, pl, part);                         \
+      case DD_OPC_PROD: return finish_opc_##T<DD_OPC_PROD>(h, pl, part);                           \
+      case DD_OPC_PRODNZ: return finish_opc_##T<DD_OPC_PRODNZ>(h, pl, part);                       \
+      case DD_OPC_MIN: return finish_opc_##T<DD_OPC_MIN>(h, pl, part);                             \
+      case DD_OPC_MAX: return finish_opc_##T<DD_OPC_MAX>(h, pl, part);                             \
+      case DD_OPC_AMAX: return finish_opc_##T<DD_OPC_AMAX>(h, pl, part);                           \
+    }                                                                                              \
+    return DD_STATUS_INTERNAL_ERROR;                                                               \
+  }

@@ -1,0 +1,451 @@
+// Reorder + data type conversion kernels: y = alpha*convert(x) + beta*y over equal dims and any
+// strides (the body of ddTransformTensor / ddGatherTransform).  Three kernel families:
+//
+//   flat     both tensors walk memory as one dense run (same layout): 16-byte vector stream.
+//   tile     the x-contiguous dim (A) and the y-contiguous dim (B) differ (nchw <-> nhwc and every
+//            other stride permutation whose rows are 16-byte aligned): a CTA moves a TA x TB tile;
+//            each thread loads 16-byte vectors along A, converts, transposes its VS x VD micro
+//            block in registers, parks 16-byte vectors along B in XOR-swizzled shared memory, and
+//            the CTA writes them back as contiguous 16-byte vectors along B.  Global traffic is
+//            16-byte on both sides, shared-memory traffic is conflict-free 16-byte on both sides.
+//   strided  anything else: one element per thread, index decomposition over <= 8 dims.
+//
+// All three are HBM-bound: algorithmic bytes per element = sizeof(S) + sizeof(D).
+#pragma once
+#include "dd_internal.cuh"
+#include <type_traits>
+
+// ------------------------------------------------------------------ conversion ---------------
+
+template <typename S, typename D, typename C, bool RAW>
+struct dd_cvt {
+  static __device__ __forceinline__ D f(S v, C alpha) {
+    return dd_store<D, C>(dd_scale(alpha, dd_load<C, S>(v)));
+  }
+  static __device__ __forceinline__ D blend(S v, C alpha, C beta, D old) {
+    C t = dd_scale(alpha, dd_load<C, S>(v));
+    C u = dd_scale(beta, dd_load<C, D>(old));
+    return dd_store<D, C>(dd_add_rn(t, u));
+  }
+};
+// RAW: S == D (as an unsigned integer of the same width), alpha == 1, beta == 0: a bit copy.
+template <typename S, typename C>
+struct dd_cvt<S, S, C, true> {
+  static __device__ __forceinline__ S f(S v, C) { return v; }
+  static __device__ __forceinline__ S blend(S v, C, C, S) { return v; }
+};
+
+// ------------------------------------------------------------------ flat ---------------------
+
+// BYTES of payload moved with the widest legal accesses (16-byte units above 16 bytes).
+template <int BYTES> struct dd_vec_unit { typedef uint4 U; };
+template <> struct dd_vec_unit<8> { typedef uint2 U; };
+template <> struct dd_vec_unit<4> { typedef uint32_t U; };
+template <> struct dd_vec_unit<2> { typedef uint16_t U; };
+template <> struct dd_vec_unit<1> { typedef uint8_t U; };
+
+template <int BYTES>
+struct dd_vec {
+  typedef typename dd_vec_unit<BYTES> ::U U;
+  static constexpr int N = BYTES <= 16 ? 1 : BYTES / 16;
+  U v[N];
+};
+
+template <int BYTES>
+__device__ __forceinline__ dd_vec<BYTES> dd_vload(const void *p) {
+  dd_vec<BYTES> r;
+  typedef typename dd_vec<BYTES>::U U;
+#pragma unroll
+  for (int i = 0; i < dd_vec<BYTES>::N; i++) r.v[i] = ((const U *)p)[i];
+  return r;
+}
+template <int BYTES>
+__device__ __forceinline__ void dd_vstore(void *p, const dd_vec<BYTES> &r) {
+  typedef typename dd_vec<BYTES>::U U;
+#pragma unroll
+  for (int i = 0; i < dd_vec<BYTES>::N; i++) ((U *)p)[i] = r.v[i];
+}
+
+struct ddFlatParams {
+  const void *x;
+  void *y;
+  int64_t n;     // elements
+  double alpha, beta;
+  int vec;       // 1: both pointers 16-byte aligned, vector main loop + scalar tail
+};
+
+// V = elements per thread-iteration so that the narrower side still moves 16 bytes.
+template <typename S, typename D, typename C, bool RAW>
+__global__ void __launch_bounds__(256) dd_flat_kernel(ddFlatParams p) {
+  constexpr int MINW = sizeof(S) < sizeof(D) ? sizeof(S) : sizeof(D);
+  constexpr int V = 16 / MINW;
+  const S *x = (const S *)p.x;
+  D *y = (D *)p.y;
+  const C alpha = (C)p.alpha, beta = (C)p.beta;
+  const bool blend = p.beta != 0.0;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  int64_t done = 0;
+  if (p.vec) {
+    const int64_t nv = p.n / V;
+    for (int64_t i = tid; i < nv; i += nthreads) {
+      dd_vec<V * sizeof(S)> in = dd_vload<V * sizeof(S)>(x + i * V);
+      dd_vec<V * sizeof(D)> out;
+      const S *sv = (const S *)&in;
+      D *dv = (D *)&out;
+      if (blend) {
+        dd_vec<V * sizeof(D)> old = dd_vload<V * sizeof(D)>(y + i * V);
+        const D *ov = (const D *)&old;
+#pragma unroll
+        for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::blend(sv[k], alpha, beta, ov[k]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::f(sv[k], alpha);
+      }
+      dd_vstore<V * sizeof(D)>(y + i * V, out);
+    }
+    done = nv * V;
+  }
+  for (int64_t i = done + tid; i < p.n; i += nthreads) {
+    y[i] = blend ? dd_cvt<S, D, C, RAW>::blend(x[i], alpha, beta, y[i])
+                 : dd_cvt<S, D, C, RAW>::f(x[i], alpha);
+  }
+}
+
+// ------------------------------------------------------------------ tile ---------------------
+
+#define DD_TILE_BATCH_DIMS 6
+
+struct ddTileParams {
+  const void *x;
+  void *y;
+  int64_t LA, LB;    // extents of dim A (stride 1 in x) and dim B (stride 1 in y)
+  int64_t sxB, syA;  // x stride along B, y stride along A (elements)
+  int nb;            // number of batch dims
+  int64_t bdims[DD_TILE_BATCH_DIMS], bsx[DD_TILE_BATCH_DIMS], bsy[DD_TILE_BATCH_DIMS];
+  int64_t tilesA, tilesB;
+  double alpha;
+};
+
+template <typename S, typename D>
+struct dd_tile_geom {
+  static constexpr int VS = 16 / sizeof(S);  // elements per 16-byte load along A
+  static constexpr int VD = 16 / sizeof(D);  // elements per 16-byte store along B
+  static constexpr int NA = 16;              // threads along A
+  static constexpr int NB = (VS >= 16) ? 8 : 16;  // threads along B (keeps the tile <= 32 KB)
+  static constexpr int TA = NA * VS;
+  static constexpr int TB = NB * VD;
+  static constexpr int NT = NA * NB;
+  static constexpr int SMEM = TA * NB * 16;
+};
+
+template <typename S, typename D, typename C, bool RAW>
+__global__ void __launch_bounds__((dd_tile_geom<S, D>::NT)) dd_tile_kernel(ddTileParams p) {
+  typedef dd_tile_geom<S, D> G;
+  constexpr int VS = G::VS, VD = G::VD, NA = G::NA, NB = G::NB, TA = G::TA, TB = G::TB;
+  __shared__ uint4 tile[TA * NB];
+
+  // tile id -> (batch index, tile along B, tile along A); A varies fastest
+  int64_t id = blockIdx.x;
+  const int64_t ta = id % p.tilesA;
+  id /= p.tilesA;
+  const int64_t tb = id % p.tilesB;
+  id /= p.tilesB;
+  int64_t offx = 0, offy = 0;
+  for (int d = p.nb - 1; d >= 0; d--) {
+    int64_t q = id / p.bdims[d];
+    int64_t r = id - q * p.bdims[d];
+    offx += r * p.bsx[d];
+    offy += r * p.bsy[d];
+    id = q;
+  }
+  const S *xb = (const S *)p.x + offx;
+  D *yb = (D *)p.y + offy;
+  const int64_t a0 = ta * TA, b0 = tb * TB;
+  const C alpha = (C)p.alpha;
+
+  const int t = threadIdx.x;
+  {  // load 16-byte vectors along A for VD consecutive rows of B, convert, transpose in registers
+    const int ma = t % NA, mb = t / NA;
+    const int64_t a = a0 + ma * VS;
+    uint4 in[VD];
+#pragma unroll
+    for (int j = 0; j < VD; j++) {
+      const int64_t b = b0 + mb * VD + j;
+      if (a < p.LA && b < p.LB)
+        in[j] = *(const uint4 *)(xb + b * p.sxB + a);
+      else
+        in[j] = make_uint4(0, 0, 0, 0);
+    }
+    __align__(16) D reg[VS][VD];
+#pragma unroll
+    for (int j = 0; j < VD; j++) {
+      const S *sv = (const S *)&in[j];
+#pragma unroll
+      for (int i = 0; i < VS; i++) reg[i][j] = dd_cvt<S, D, C, RAW>::f(sv[i], alpha);
+    }
+    // row = index along A inside the tile; 16-byte chunk index along B swizzled by the row's
+    // micro-block number so that the 8 lanes of a quarter warp hit 8 different bank groups
+#pragma unroll
+    for (int i = 0; i < VS; i++) {
+      const int row = ma * VS + i;
+      tile[row * NB + (mb ^ (ma & 7))] = *(const uint4 *)reg[i];
+    }
+  }
+  __syncthreads();
+  {  // write rows of the tile: NB consecutive lanes cover one contiguous run along B
+    const int rb = t % NB, ra = t / NB;
+    const int64_t b = b0 + rb * VD;
+#pragma unroll
+    for (int k = 0; k < VS; k++) {
+      const int row = ra + k * NA;
+      const int64_t a = a0 + row;
+      if (a < p.LA && b < p.LB) {
+        uint4 v = tile[row * NB + (rb ^ ((row / VS) & 7))];
+        *(uint4 *)(yb + a * p.syA + b) = v;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ strided ------------------
+
+struct ddStridedXformParams {
+  const void *x;
+  void *y;
+  ddStridedParams<2> sp;  // operand 0 = x, operand 1 = y
+  double alpha, beta;
+};
+
+template <typename S, typename D, typename C, bool RAW, typename I>
+__global__ void __launch_bounds__(256) dd_strided_kernel(ddStridedXformParams p) {
+  const S *x = (const S *)p.x;
+  D *y = (D *)p.y;
+  const C alpha = (C)p.alpha, beta = (C)p.beta;
+  const bool blend = p.beta != 0.0;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.sp.total; i += nthreads) {
+    int64_t off[2];
+    dd_offsets<2, I>(p.sp, (I)i, off);
+    S v = x[off[0]];
+    y[off[1]] = blend ? dd_cvt<S, D, C, RAW>::blend(v, alpha, beta, y[off[1]])
+                      : dd_cvt<S, D, C, RAW>::f(v, alpha);
+  }
+}
+
+// Gather form: `count` items, item k starts at element offsets so[k] / do_[k]; inside an item the
+// walk is the strided one.  Offsets travel in the kernel parameters (no device scratch).
+#define DD_GATHER_CHUNK 512
+struct ddGatherParams {
+  const void *x;
+  void *y;
+  ddStridedParams<2> sp;  // one item
+  int count;
+  int64_t so[DD_GATHER_CHUNK], do_[DD_GATHER_CHUNK];
+};
+
+template <typename S, typename D, typename C, bool RAW>
+__global__ void __launch_bounds__(256) dd_gather_kernel(const __grid_constant__ ddGatherParams p) {
+  const S *x = (const S *)p.x;
+  D *y = (D *)p.y;
+  const int64_t per = p.sp.total;
+  const int64_t total = per * p.count;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+    const int64_t k = i / per;
+    const int64_t r = i - k * per;
+    int64_t off[2];
+    dd_offsets<2, int64_t>(p.sp, r, off);
+    y[p.do_[k] + off[1]] = dd_cvt<S, D, C, RAW>::f(x[p.so[k] + off[0]], (C)1);
+  }
+}
+
+// ------------------------------------------------------------------ launchers ----------------
+
+struct ddXformPlan {
+  ddCanon canon;  // ordered by y strides
+  double alpha, beta;
+  const void *x;
+  void *y;
+};
+
+template <typename S, typename D, typename C, bool RAW>
+static ddStatus_t dd_launch_flat(ddHandle_t h, const ddXformPlan &pl) {
+  ddFlatParams p;
+  p.x = pl.x;
+  p.y = pl.y;
+  p.n = pl.canon.total;
+  p.alpha = pl.alpha;
+  p.beta = pl.beta;
+  p.vec = (((uintptr_t)pl.x | (uintptr_t)pl.y) & 15) == 0;
+  constexpr int MINW = sizeof(S) < sizeof(D) ? sizeof(S) : sizeof(D);
+  constexpr int V = 16 / MINW;
+  unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
+  dd_flat_kernel<S, D, C, RAW><<<grid, 256, 0, h->stream>>>(p);
+  DD_LAUNCHED(h, "transform/flat");
+  return DD_STATUS_SUCCESS;
+}
+
+// Fills tile parameters if the canonical space fits the tile kernel; returns false otherwise.
+template <typename S, typename D>
+static bool dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
+  typedef dd_tile_geom<S, D> G;
+  const ddCanon &c = pl.canon;
+  if (pl.beta != 0.0 || c.nd < 2) return false;
+  const int B = c.nd - 1;
+  if (c.st[1][B] != 1) return false;
+  int A = -1;
+  for (int i = 0; i < c.nd - 1; i++)
+    if (c.st[0][i] == 1) A = i;
+  if (A < 0) return false;
+  if (c.nd - 2 > DD_TILE_BATCH_DIMS) return false;
+  if ((((uintptr_t)pl.x) | ((uintptr_t)pl.y)) & 15) return false;
+  if (c.dims[A] % G::VS || c.dims[B] % G::VD) return false;
+  for (int i = 0; i < c.nd; i++) {
+    if (i != A && (c.st[0][i] % G::VS)) return false;
+    if (i != B && (c.st[1][i] % G::VD)) return false;
+  }
+  // a tile that is mostly padding wastes the machine: leave short dims to the strided kernel
+  if (c.dims[A] < G::VS * 2 || c.dims[B] < G::VD * 2) return false;
+  tp->x = pl.x;
+  tp->y = pl.y;
+  tp->LA = c.dims[A];
+  tp->LB = c.dims[B];
+  tp->sxB = c.st[0][B];
+  tp->syA = c.st[1][A];
+  tp->nb = 0;
+  for (int i = 0; i < c.nd - 1; i++) {
+    if (i == A) continue;
+    tp->bdims[tp->nb] = c.dims[i];
+    tp->bsx[tp->nb] = c.st[0][i];
+    tp->bsy[tp->nb] = c.st[1][i];
+    tp->nb++;
+  }
+  tp->tilesA = (tp->LA + G::TA - 1) / G::TA;
+  tp->tilesB = (tp->LB + G::TB - 1) / G::TB;
+  tp->alpha = pl.alpha;
+  return true;
+}
+
+template <typename S, typename D, typename C, bool RAW>
+static ddStatus_t dd_launch_tile(ddHandle_t h, const ddTileParams &tp) {
+  typedef dd_tile_geom<S, D> G;
+  int64_t tiles = tp.tilesA * tp.tilesB;
+  for (int i = 0; i < tp.nb; i++) tiles *= tp.bdims[i];
+  if (tiles > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "transform/tile: too many tiles");
+  dd_tile_kernel<S, D, C, RAW><<<(unsigned)tiles, G::NT, 0, h->stream>>>(tp);
+  DD_LAUNCHED(h, "transform/tile");
+  return DD_STATUS_SUCCESS;
+}
+
+template <typename S, typename D, typename C, bool RAW>
+static ddStatus_t dd_launch_strided(ddHandle_t h, const ddXformPlan &pl) {
+  ddStridedXformParams p;
+  p.x = pl.x;
+  p.y = pl.y;
+  p.sp = dd_strided_params<2>(pl.canon);
+  p.alpha = pl.alpha;
+  p.beta = pl.beta;
+  unsigned grid = dd_flat_grid(h, pl.canon.total, 256, 16);
+  if (pl.canon.total < 0x7fffffffLL)
+    dd_strided_kernel<S, D, C, RAW, uint32_t><<<grid, 256, 0, h->stream>>>(p);
+  else
+    dd_strided_kernel<S, D, C, RAW, int64_t><<<grid, 256, 0, h->stream>>>(p);
+  DD_LAUNCHED(h, "transform/strided");
+  return DD_STATUS_SUCCESS;
+}
+
+template <typename S, typename D, typename C, bool RAW>
+static ddStatus_t dd_xform_typed(ddHandle_t h, const ddXformPlan &pl) {
+  const ddCanon &c = pl.canon;
+  if (c.nd == 1 && c.st[0][0] == 1 && c.st[1][0] == 1) return dd_launch_flat<S, D, C, RAW>(h, pl);
+  ddTileParams tp;
+  if (dd_tile_plan<S, D>(pl, &tp)) return dd_launch_tile<S, D, C, RAW>(h, tp);
+  return dd_launch_strided<S, D, C, RAW>(h, pl);
+}
+
+struct ddGatherPlan {
+  ddCanon canon;  // one item, ordered by y strides
+  const void *x;
+  void *y;
+  int count;
+  const int64_t *so, *do_;
+};
+
+template <typename S, typename D, typename C, bool RAW>
+static ddStatus_t dd_gather_typed(ddHandle_t h, const ddGatherPlan &pl) {
+  static ddGatherParams p;  // 8 KB: kept off the stack; a handle is driven by one thread
+  for (int base = 0; base < pl.count; base += DD_GATHER_CHUNK) {
+    int n = pl.count - base < DD_GATHER_CHUNK ? pl.count - base : DD_GATHER_CHUNK;
+    p.x = pl.x;
+    p.y = pl.y;
+    p.sp = dd_strided_params<2>(pl.canon);
+    p.count = n;
+    for (int i = 0; i < n; i++) {
+      p.so[i] = pl.so[base + i];
+      p.do_[i] = pl.do_[base + i];
+    }
+    unsigned grid = dd_flat_grid(h, pl.canon.total * n, 256, 16);
+    dd_gather_kernel<S, D, C, RAW><<<grid, 256, 0, h->stream>>>(p);
+    DD_LAUNCHED(h, "transform/gather");
+  }
+  return DD_STATUS_SUCCESS;
+}
+
+// Compute type: double when a 64-bit or 32-bit-integer type is involved on the source side or a
+// 64-bit type on the destination side (so every conversion rounds once); float otherwise.
+template <typename S, typename D>
+struct dd_compute_type {
+  static constexpr bool dbl = sizeof(S) == 8 || sizeof(D) == 8 || (sizeof(S) == 4 && !std::is_same<S, float>::value);
+  typedef typename std::conditional<dbl, double, float>::type type;
+};
+
+// One translation unit per source type instantiates these for every destination type.
+template <typename S>
+ddStatus_t dd_xform_from(ddHandle_t h, ddDataType_t dstType, const ddXformPlan &pl);
+template <typename S>
+ddStatus_t dd_gather_from(ddHandle_t h, ddDataType_t dstType, const ddGatherPlan &pl);
+ddStatus_t dd_xform_raw(ddHandle_t h, int width, const ddXformPlan &pl);
+ddStatus_t dd_gather_raw(ddHandle_t h, int width, const ddGatherPlan &pl);
+
+#define DD_XFORM_DECLARE_FROM(S)                                                          \
+  template <> ddStatus_t dd_xform_from<S>(ddHandle_t, ddDataType_t, const ddXformPlan &); \
+  template <> ddStatus_t dd_gather_from<S>(ddHandle_t, ddDataType_t, const ddGatherPlan &);
+DD_XFORM_DECLARE_FROM(float)
+DD_XFORM_DECLARE_FROM(double)
+DD_XFORM_DECLARE_FROM(__half)
+DD_XFORM_DECLARE_FROM(int8_t)
+DD_XFORM_DECLARE_FROM(int32_t)
+DD_XFORM_DECLARE_FROM(uint8_t)
+DD_XFORM_DECLARE_FROM(__nv_bfloat16)
+DD_XFORM_DECLARE_FROM(int64_t)
+
+#define DD_XFORM_DEFINE_FROM(S)                                                              \
+  template <>                                                                                \
+  ddStatus_t dd_xform_from<S>(ddHandle_t h, ddDataType_t dt, const ddXformPlan &pl) {        \
+    switch (dt) {                                                                            \
+      case DD_DATA_FLOAT: return dd_xform_typed<S, float, dd_compute_type<S, float>::type, false>(h, pl); \
+      case DD_DATA_DOUBLE: return dd_xform_typed<S, double, dd_compute_type<S, double>::type, false>(h, pl); \
+      case DD_DATA_HALF: return dd_xform_typed<S, __half, dd_compute_type<S, __half>::type, false>(h, pl); \
+      case DD_DATA_INT8: return dd_xform_typed<S, int8_t, dd_compute_type<S, int8_t>::type, false>(h, pl); \
+      case DD_DATA_INT32: return dd_xform_typed<S, int32_t, dd_compute_type<S, int32_t>::type, false>(h, pl); \
+      case DD_DATA_UINT8: return dd_xform_typed<S, uint8_t, dd_compute_type<S, uint8_t>::type, false>(h, pl); \
+      case DD_DATA_BFLOAT16: return dd_xform_typed<S, __nv_bfloat16, dd_compute_type<S, __nv_bfloat16>::type, false>(h, pl); \
+      case DD_DATA_INT64: return dd_xform_typed<S, int64_t, dd_compute_type<S, int64_t>::type, false>(h, pl); \
+    }                                                                                        \
+    return DD_STATUS_BAD_PARAM;                                                              \
+  }                                                                                          \
+  template <>                                                                                \
+  ddStatus_t dd_gather_from<S>(ddHandle_t h, ddDataType_t dt, const ddGatherPlan &pl) {      \
+    switch (dt) {                                                                            \
+      case DD_DATA_FLOAT: return dd_gather_typed<S, float, dd_compute_type<S, float>::type, false>(h, pl); \
+      case DD_DATA_DOUBLE: return dd_gather_typed<S, double, dd_compute_type<S, double>::type, false>(h, pl); \
+      case DD_DATA_HALF: return dd_gather_typed<S, __half, dd_compute_type<S, __half>::type, false>(h, pl); \
+      case DD_DATA_INT8: return dd_gather_typed<S, int8_t, dd_compute_type<S, int8_t>::type, false>(h, pl); \
+      case DD_DATA_INT32: return dd_gather_typed<S, int32_t, dd_compute_type<S, int32_t>::type, false>(h, pl); \
+      case DD_DATA_UINT8: return dd_gather_typed<S, uint8_t, dd_compute_type<S, uint8_t>::type, false>(h, pl); \
+      case DD_DATA_BFLOAT16: return dd_gather_typed<S, __nv_bfloat16, dd_compute_type<S, __nv_bfloat16>::type, false>(h, pl); \
+      case DD_DATA_INT64: return dd_gather_typed<S, int64_t, dd_compute_type<S, int64_t>::type, false>(h, pl); \
+    }                                                                                        \
+    return DD_STATUS_BAD_PARAM;                                                              \
+  }

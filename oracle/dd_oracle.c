@@ -1,0 +1,579 @@
+/*
+ * dd_oracle.c -- TEST INFRASTRUCTURE, not product code.
+ *
+ * A plain-C, CPU restatement of what the reference's DNNL backend computes on the tensor hot path
+ * (reorder with data type conversion, eltwise forward/backward, binary with broadcast, scaled sum,
+ * reduction).  Only tests, the smoke check and the CPU-baseline leg of the benchmark may load it;
+ * the GPU library never does.
+ *
+ * PARITY PINNING.  The reference (Clojure on the JVM calling oneDNN 3.13 through the bytedeco
+ * preset `dnnl-platform 3.13-1.5.14`, deep-diamond-dnnl/project.clj:17) holds no arithmetic of its
+ * own for these ops: it builds descriptors and calls oneDNN, which is not vendored in the reference
+ * tree and cannot be run without a JVM.  This file therefore restates oneDNN's published
+ * definitions of the primitives and is pinned by
+ *   (1) every known-answer vector the reference's own tests hold for the path
+ *       (tests/test_oracle_golden.py lists them with file:line), and
+ *   (2) outputs of real oneDNN (the build bundled with PyTorch) for eltwise forward, same-shape
+ *       add/mul and f32->bf16 conversion, committed under tests/golden/ with their generator.
+ * Not pinned by either: elu, eltwise backward on non-trivial data, broadcast binary, mean, and
+ * reductions on non-trivial floating data ("parity unpinned" for those).
+ *
+ * What each function follows in the reference (paths relative to the reference project):
+ *   oracle_reorder      dnnl/core.clj:523-529 `reorder` + dnnl/impl.clj:372-376 (attr = NULL: no
+ *                       scales) as used by DnnlTransformer, dnnl/tensor.clj:102-151; the alpha/beta
+ *                       blend is cuDNN's transform-tensor form, cudnn/core.clj:131-144.
+ *   oracle_eltwise_fwd  dnnl/core.clj:345-362 `eltwise-fwd`, dnnl/impl.clj:324-331; algorithm
+ *                       keywords dnnl/constants.clj:277-308; alpha/beta defaults base/dnn.clj:79-82.
+ *   oracle_eltwise_bwd  dnnl/core.clj:364-388 `eltwise-bwd` with args SRC, DIFF_DST, DIFF_SRC:
+ *                       the derivative is taken from the forward SOURCE.
+ *   oracle_binary       dnnl/core.clj:430-447 `binary` (+ cudnn/core.clj:117-129 add-tensor form).
+ *   oracle_sum          dnnl/core.clj:392-426 `sum!`.
+ *   oracle_reduce       dnnl/core.clj:796-803 `reduction`, kinds dnnl/constants.clj:393-402
+ *                       (+ cudnn/core.clj:213-231 reduce-tensor's alpha/beta and op set).
+ * (prefix dnnl/ = deep-diamond-dnnl/src/uncomplicate/diamond/internal/dnnl/,
+ *  cudnn/ = deep-diamond-cuda/src/clojure/uncomplicate/diamond/internal/cudnn/,
+ *  base/ = deep-diamond-base/src/uncomplicate/diamond/.)
+ *
+ * Arithmetic rules (shared with the GPU kernels so that "bit-exact" is well defined):
+ *   - conversions: to bf16/f16 round-to-nearest-even; to s8/u8/s32/s64 saturate then
+ *     round-to-nearest-even, NaN -> 0; compute type float unless a 64-bit type (or an s32 source)
+ *     is involved, then double.
+ *   - alpha*v + beta*old: each product and the sum rounded separately (compile with
+ *     -ffp-contract=off), a factor of exactly 1 skipped, beta == 0 does not read `old`.
+ *   - transcendental eltwise in fp32 uses the C library's float functions on oneDNN's documented
+ *     formulas; *_truth variants evaluate the same definitions in double.
+ *   - reductions accumulate sequentially in the compute type, in logical (row-major) order of the
+ *     reduced dims; *_truth variants accumulate in long double.
+ *
+ * Build: gcc -O2 -fopenmp -ffp-contract=off -fPIC -shared -o oracle/libdd_oracle.so oracle/dd_oracle.c -lm
+ */
+#include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+enum { T_F32 = 0, T_F64 = 1, T_F16 = 2, T_S8 = 3, T_S32 = 4, T_U8 = 6, T_BF16 = 9, T_S64 = 15 };
+#define MAXD 8
+
+static int tsize(int t) {
+  switch (t) {
+    case T_F32: case T_S32: return 4;
+    case T_F64: case T_S64: return 8;
+    case T_F16: case T_BF16: return 2;
+    case T_S8: case T_U8: return 1;
+  }
+  return 0;
+}
+
+/* ------------------------------------------------------------ scalar conversions ------------ */
+
+static float bf16_to_f32(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+static uint16_t f32_to_bf16(float f) { /* round-to-nearest-even; NaN stays NaN (quiet) */
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return (uint16_t)(u >> 16);
+}
+
+static float f16_to_f32(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1fu, man = h & 0x3ffu, u;
+  if (exp == 0) {
+    if (man == 0) u = sign;
+    else { /* subnormal: normalise */
+      int e = -1;
+      do { e++; man <<= 1; } while (!(man & 0x400u));
+      u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+    }
+  } else if (exp == 31) u = sign | 0x7f800000u | (man << 13);
+  else u = sign | ((exp + 112u) << 23) | (man << 13);
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+static uint16_t f32_to_f16(float f) { /* round-to-nearest-even */
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  uint32_t sign = (u >> 16) & 0x8000u;
+  uint32_t a = u & 0x7fffffffu;
+  if (a > 0x7f800000u) return (uint16_t)(sign | 0x7e00u | ((a >> 13) & 0x1ffu)); /* NaN */
+  if (a >= 0x47800000u) return (uint16_t)(sign | 0x7c00u);                        /* >= 65536: inf (65520 rounds below) */
+  if (a < 0x38800000u) { /* result is subnormal or zero: value < 2^-14 */
+    if (a < 0x33000000u) return (uint16_t)sign; /* < 2^-25 rounds to 0 */
+    uint32_t exp = a >> 23;
+    uint32_t man = (a & 0x7fffffu) | 0x800000u;
+    uint32_t shift = 126u - exp; /* 14..24 */
+    uint32_t half = man >> shift;
+    uint32_t rem = man & ((1u << shift) - 1u);
+    uint32_t halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (half & 1u))) half++;
+    return (uint16_t)(sign | half);
+  }
+  uint32_t exp = (a >> 23) - 112u;
+  uint32_t man = a & 0x7fffffu;
+  uint32_t half = (exp << 10) | (man >> 13);
+  uint32_t rem = man & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (half & 1u))) half++; /* may carry into exp: correct */
+  return (uint16_t)(sign | half);
+}
+
+static uint16_t f64_to_f16(double d) { /* single rounding from double */
+  /* round d to the f16 grid directly: go through float only when exact */
+  float f = (float)d;
+  if ((double)f == d) return f32_to_f16(f);
+  /* inexact in float: nudge toward d so that the float keeps a sticky bit */
+  uint16_t lo = f32_to_f16(nextafterf(f, (double)f < d ? INFINITY : -INFINITY));
+  uint16_t hi = f32_to_f16(f);
+  /* if both neighbours agree the result is settled; otherwise pick by distance in double */
+  if (lo == hi) return hi;
+  double dlo = fabs((double)f16_to_f32(lo) - d), dhi = fabs((double)f16_to_f32(hi) - d);
+  if (dlo < dhi) return lo;
+  if (dhi < dlo) return hi;
+  return (lo & 1u) ? hi : lo;
+}
+
+static uint16_t f64_to_bf16(double d) {
+  float f = (float)d;
+  if ((double)f == d) return f32_to_bf16(f);
+  uint16_t a = f32_to_bf16(f);
+  uint16_t b = f32_to_bf16(nextafterf(f, (double)f < d ? INFINITY : -INFINITY));
+  if (a == b) return a;
+  double da = fabs((double)bf16_to_f32(a) - d), db = fabs((double)bf16_to_f32(b) - d);
+  if (da < db) return a;
+  if (db < da) return b;
+  return (a & 1u) ? b : a;
+}
+
+static double load_as_double(const void *p, int t, int64_t i) {
+  switch (t) {
+    case T_F32: return ((const float *)p)[i];
+    case T_F64: return ((const double *)p)[i];
+    case T_F16: return f16_to_f32(((const uint16_t *)p)[i]);
+    case T_BF16: return bf16_to_f32(((const uint16_t *)p)[i]);
+    case T_S8: return ((const int8_t *)p)[i];
+    case T_U8: return ((const uint8_t *)p)[i];
+    case T_S32: return ((const int32_t *)p)[i];
+    case T_S64: return (double)((const int64_t *)p)[i];
+  }
+  return 0;
+}
+static float load_as_float(const void *p, int t, int64_t i) { return (float)load_as_double(p, t, i); }
+
+static void store_from_float(void *p, int t, int64_t i, float v) {
+  switch (t) {
+    case T_F32: ((float *)p)[i] = v; break;
+    case T_F64: ((double *)p)[i] = v; break;
+    case T_F16: ((uint16_t *)p)[i] = f32_to_f16(v); break;
+    case T_BF16: ((uint16_t *)p)[i] = f32_to_bf16(v); break;
+    case T_S8: ((int8_t *)p)[i] = v != v ? 0 : (int8_t)nearbyintf(fminf(fmaxf(v, -128.f), 127.f)); break;
+    case T_U8: ((uint8_t *)p)[i] = v != v ? 0 : (uint8_t)nearbyintf(fminf(fmaxf(v, 0.f), 255.f)); break;
+    case T_S32:
+      if (v != v) ((int32_t *)p)[i] = 0;
+      else if (v >= 2147483648.f) ((int32_t *)p)[i] = INT32_MAX;
+      else if (v <= -2147483648.f) ((int32_t *)p)[i] = INT32_MIN;
+      else ((int32_t *)p)[i] = (int32_t)nearbyintf(v);
+      break;
+    case T_S64:
+      if (v != v) ((int64_t *)p)[i] = 0;
+      else if (v >= 9223372036854775808.f) ((int64_t *)p)[i] = INT64_MAX;
+      else if (v <= -9223372036854775808.f) ((int64_t *)p)[i] = INT64_MIN;
+      else ((int64_t *)p)[i] = (int64_t)nearbyintf(v);
+      break;
+  }
+}
+
+static void store_from_double(void *p, int t, int64_t i, double v) {
+  switch (t) {
+    case T_F32: ((float *)p)[i] = (float)v; break;
+    case T_F64: ((double *)p)[i] = v; break;
+    case T_F16: ((uint16_t *)p)[i] = f64_to_f16(v); break;
+    case T_BF16: ((uint16_t *)p)[i] = f64_to_bf16(v); break;
+    case T_S8: ((int8_t *)p)[i] = v != v ? 0 : (int8_t)nearbyint(fmin(fmax(v, -128.0), 127.0)); break;
+    case T_U8: ((uint8_t *)p)[i] = v != v ? 0 : (uint8_t)nearbyint(fmin(fmax(v, 0.0), 255.0)); break;
+    case T_S32:
+      if (v != v) ((int32_t *)p)[i] = 0;
+      else if (v >= 2147483647.0) ((int32_t *)p)[i] = INT32_MAX;
+      else if (v <= -2147483648.0) ((int32_t *)p)[i] = INT32_MIN;
+      else ((int32_t *)p)[i] = (int32_t)nearbyint(v);
+      break;
+    case T_S64:
+      if (v != v) ((int64_t *)p)[i] = 0;
+      else if (v >= 9223372036854775808.0) ((int64_t *)p)[i] = INT64_MAX;
+      else if (v <= -9223372036854775808.0) ((int64_t *)p)[i] = INT64_MIN;
+      else ((int64_t *)p)[i] = (int64_t)nearbyint(v);
+      break;
+  }
+}
+
+static int compute_is_double(int st, int dt) { return tsize(st) == 8 || tsize(dt) == 8 || st == T_S32; }
+
+/* ------------------------------------------------------------ index helpers ------------------ */
+
+static int64_t total_of(int nd, const int64_t *dims) {
+  int64_t n = 1;
+  for (int i = 0; i < nd; i++) n *= dims[i];
+  return n;
+}
+
+/* logical (row-major) linear index -> element offset under `st` */
+static int64_t offset_of(int nd, const int64_t *dims, const int64_t *st, int64_t idx) {
+  int64_t off = 0;
+  for (int d = nd - 1; d >= 0; d--) {
+    int64_t q = idx / dims[d];
+    off += (idx - q * dims[d]) * st[d];
+    idx = q;
+  }
+  return off;
+}
+
+/* ------------------------------------------------------------ reorder ------------------------ */
+
+int oracle_reorder(int nd, const int64_t *dims, int st, const int64_t *sst, const void *src, int dt,
+                   const int64_t *dst_st, void *dst, double alpha, double beta) {
+  if (nd < 1 || nd > MAXD) return 1;
+  const int64_t n = total_of(nd, dims);
+  const int64_t inner = dims[nd - 1], outer = n / (inner ? inner : 1);
+  const int dbl = compute_is_double(st, dt);
+  const int raw = (st == dt && alpha == 1.0 && beta == 0.0);
+  const int w = tsize(st);
+#pragma omp parallel for schedule(static)
+  for (int64_t o = 0; o < outer; o++) {
+    int64_t so = offset_of(nd - 1, dims, sst, o), dof = offset_of(nd - 1, dims, dst_st, o);
+    for (int64_t i = 0; i < inner; i++) {
+      int64_t si = so + i * sst[nd - 1], di = dof + i * dst_st[nd - 1];
+      if (raw) {
+        memcpy((char *)dst + di * w, (const char *)src + si * w, (size_t)w);
+      } else if (dbl) {
+        double v = load_as_double(src, st, si);
+        if (alpha != 1.0) v = alpha * v;
+        if (beta != 0.0) {
+          double u = load_as_double(dst, dt, di);
+          if (beta != 1.0) u = beta * u;
+          v = v + u;
+        }
+        store_from_double(dst, dt, di, v);
+      } else {
+        float v = load_as_float(src, st, si);
+        if (alpha != 1.0) v = (float)alpha * v;
+        if (beta != 0.0) {
+          float u = load_as_float(dst, dt, di);
+          if (beta != 1.0) u = (float)beta * u;
+          v = v + u;
+        }
+        store_from_float(dst, dt, di, v);
+      }
+    }
+  }
+  return 0;
+}
+
+/* ------------------------------------------------------------ eltwise ------------------------ */
+
+enum { A_SIGMOID = 0, A_RELU = 1, A_TANH = 2, A_CLIP = 3, A_ELU = 4, A_LINEAR = 5, A_ABS = 6 };
+
+static float act_fwd_f(int alg, float x, float a, float b, int nanprop) {
+  switch (alg) {
+    case A_RELU:
+      if (a == 0.f) {
+        if (nanprop && x != x) return x;
+        return fmaxf(x, 0.f);
+      }
+      return x > 0.f ? x : a * x;
+    case A_SIGMOID: return 1.f / (1.f + expf(-x));
+    case A_TANH: return tanhf(x);
+    case A_ELU: return x > 0.f ? x : a * expm1f(x);
+    case A_LINEAR: return fmaf(a, x, b);
+    case A_CLIP:
+      if (nanprop && x != x) return x;
+      return fminf(fmaxf(x, 0.f), a);
+    case A_ABS: return fabsf(x);
+  }
+  return NAN;
+}
+
+static double act_fwd_d(int alg, double x, double a, double b, int nanprop) {
+  switch (alg) {
+    case A_RELU:
+      if (a == 0.0) {
+        if (nanprop && x != x) return x;
+        return fmax(x, 0.0);
+      }
+      return x > 0.0 ? x : a * x;
+    case A_SIGMOID: return 1.0 / (1.0 + exp(-x));
+    case A_TANH: return tanh(x);
+    case A_ELU: return x > 0.0 ? x : a * expm1(x);
+    case A_LINEAR: return fma(a, x, b);
+    case A_CLIP:
+      if (nanprop && x != x) return x;
+      return fmin(fmax(x, 0.0), a);
+    case A_ABS: return fabs(x);
+  }
+  return NAN;
+}
+
+/* derivative times dy, from the forward source */
+static float act_bwd_f(int alg, float x, float dy, float a) {
+  switch (alg) {
+    case A_RELU: return x > 0.f ? dy : a * dy;
+    case A_SIGMOID: { float v = 1.f / (1.f + expf(-x)); return dy * v * (1.f - v); }
+    case A_TANH: { float t = tanhf(x); return dy * (1.f - t) * (1.f + t); }
+    case A_ELU: return x > 0.f ? dy : dy * (a * expf(x));
+    case A_LINEAR: return a * dy;
+    case A_CLIP: return (x > 0.f && x <= a) ? dy : 0.f;
+    case A_ABS: return x > 0.f ? dy : (x < 0.f ? -dy : 0.f);
+  }
+  return NAN;
+}
+
+static double act_bwd_d(int alg, double x, double dy, double a) {
+  switch (alg) {
+    case A_RELU: return x > 0.0 ? dy : a * dy;
+    case A_SIGMOID: { double e = exp(-fabs(x)); double r = 1.0 / (1.0 + e); return dy * (e * r * r); }
+    case A_TANH: { double e = exp(-2.0 * fabs(x)); double r = 1.0 / (1.0 + e); return dy * (4.0 * e * r * r); }
+    case A_ELU: return x > 0.0 ? dy : dy * (a * exp(x));
+    case A_LINEAR: return a * dy;
+    case A_CLIP: return (x > 0.0 && x <= a) ? dy : 0.0;
+    case A_ABS: return x > 0.0 ? dy : (x < 0.0 ? -dy : 0.0);
+  }
+  return NAN;
+}
+
+static float blend_f(float alpha, float v, float beta, const void *y, int t, int64_t off) {
+  if (alpha != 1.f) v = alpha * v;
+  if (beta != 0.f) v = v + beta * load_as_float(y, t, off);
+  return v;
+}
+static double blend_d(double alpha, double v, double beta, const void *y, int t, int64_t off) {
+  if (alpha != 1.0) v = alpha * v;
+  if (beta != 0.0) v = v + beta * load_as_double(y, t, off);
+  return v;
+}
+
+int oracle_eltwise_fwd(int alg, double coef, double shift, int nanprop, int t, int nd,
+                       const int64_t *dims, const int64_t *xst, const void *x, const int64_t *yst,
+                       void *y, double alpha, double beta) {
+  const int64_t n = total_of(nd, dims);
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    int64_t xo = offset_of(nd, dims, xst, i), yo = offset_of(nd, dims, yst, i);
+    if (t == T_F64) {
+      double v = act_fwd_d(alg, ((const double *)x)[xo], coef, shift, nanprop);
+      ((double *)y)[yo] = blend_d(alpha, v, beta, y, t, yo);
+    } else {
+      float v = act_fwd_f(alg, load_as_float(x, t, xo), (float)coef, (float)shift, nanprop);
+      store_from_float(y, t, yo, blend_f((float)alpha, v, (float)beta, y, t, yo));
+    }
+  }
+  return 0;
+}
+
+int oracle_eltwise_bwd(int alg, double coef, int t, int nd, const int64_t *dims, const int64_t *xst,
+                       const void *x, const int64_t *dyst, const void *dy, const int64_t *dxst,
+                       void *dx, double alpha, double beta) {
+  const int64_t n = total_of(nd, dims);
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    int64_t xo = offset_of(nd, dims, xst, i), go = offset_of(nd, dims, dyst, i),
+            oo = offset_of(nd, dims, dxst, i);
+    if (t == T_F64) {
+      double v = act_bwd_d(alg, ((const double *)x)[xo], ((const double *)dy)[go], coef);
+      ((double *)dx)[oo] = blend_d(alpha, v, beta, dx, t, oo);
+    } else {
+      float v = act_bwd_f(alg, load_as_float(x, t, xo), load_as_float(dy, t, go), (float)coef);
+      store_from_float(dx, t, oo, blend_f((float)alpha, v, (float)beta, dx, t, oo));
+    }
+  }
+  return 0;
+}
+
+/* The same definitions evaluated in double on float inputs (error attribution). */
+int oracle_eltwise_fwd_truth(int alg, double coef, double shift, int64_t n, const float *x, double *out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) out[i] = act_fwd_d(alg, (double)x[i], coef, shift, 1);
+  return 0;
+}
+int oracle_eltwise_bwd_truth(int alg, double coef, int64_t n, const float *x, const float *dy, double *out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) out[i] = act_bwd_d(alg, (double)x[i], (double)dy[i], coef);
+  return 0;
+}
+
+/* ------------------------------------------------------------ binary / sum ------------------- */
+
+enum { B_ADD = 0, B_MUL = 1, B_MIN = 2, B_MAX = 3, B_SUB = 4, B_DIV = 5 };
+
+/* C = op(alpha1*A, alpha2*bcast(B)) + beta*C; bdims[i] is dims[i] or 1. */
+int oracle_binary(int op, int t, int nd, const int64_t *dims, double alpha1, const int64_t *ast,
+                  const void *A, double alpha2, const int64_t *bdims, const int64_t *bst,
+                  const void *B, double beta, const int64_t *cst, void *C) {
+  const int64_t n = total_of(nd, dims);
+  int64_t bs[MAXD];
+  for (int i = 0; i < nd; i++) bs[i] = (bdims[i] == 1 && dims[i] != 1) ? 0 : bst[i];
+  const int dbl = (t == T_F64 || t == T_S32);
+  const int readA = !(alpha1 == 0.0 && op == B_ADD);
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    int64_t ao = offset_of(nd, dims, ast, i), bo = offset_of(nd, dims, bs, i),
+            co = offset_of(nd, dims, cst, i);
+    if (dbl) {
+      double a = readA ? load_as_double(A, t, ao) : 0.0, b = load_as_double(B, t, bo), r;
+      if (readA && alpha1 != 1.0) a = alpha1 * a;
+      if (alpha2 != 1.0) b = alpha2 * b;
+      switch (op) {
+        case B_ADD: r = a + b; break;
+        case B_MUL: r = a * b; break;
+        case B_MIN: r = a < b ? a : b; break;
+        case B_MAX: r = a > b ? a : b; break;
+        case B_SUB: r = a - b; break;
+        default: r = a / b; break;
+      }
+      if (beta != 0.0) r = r + beta * load_as_double(C, t, co);
+      store_from_double(C, t, co, r);
+    } else {
+      float a = readA ? load_as_float(A, t, ao) : 0.f, b = load_as_float(B, t, bo), r;
+      if (readA && alpha1 != 1.0) a = (float)alpha1 * a;
+      if (alpha2 != 1.0) b = (float)alpha2 * b;
+      switch (op) {
+        case B_ADD: r = a + b; break;
+        case B_MUL: r = a * b; break;
+        case B_MIN: r = a < b ? a : b; break;
+        case B_MAX: r = a > b ? a : b; break;
+        case B_SUB: r = a - b; break;
+        default: r = a / b; break;
+      }
+      if (beta != 0.0) r = r + (float)beta * load_as_float(C, t, co);
+      store_from_float(C, t, co, r);
+    }
+  }
+  return 0;
+}
+
+/* dst = ((s0*x0) + s1*x1) + ... over n dense same-layout sources; dst may alias srcs[0]. */
+int oracle_sum(int n, const float *scales, int t, int64_t total, const void *const *srcs, void *dst) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < total; i++) {
+    if (t == T_F64) {
+      double acc = 0;
+      for (int s = 0; s < n; s++) {
+        double v = ((const double *)srcs[s])[i];
+        if (scales[s] != 1.f) v = (double)scales[s] * v;
+        acc = s == 0 ? v : acc + v;
+      }
+      ((double *)dst)[i] = acc;
+    } else {
+      float acc = 0;
+      for (int s = 0; s < n; s++) {
+        float v = load_as_float(srcs[s], t, i);
+        if (scales[s] != 1.f) v = scales[s] * v;
+        acc = s == 0 ? v : acc + v;
+      }
+      store_from_float(dst, t, i, acc);
+    }
+  }
+  return 0;
+}
+
+/* ------------------------------------------------------------ reduction ---------------------- */
+
+enum { R_ADD = 0, R_MUL = 1, R_MIN = 2, R_MAX = 3, R_AMAX = 4, R_AVG = 5, R_NORM1 = 6, R_NORM2 = 7, R_MULNZ = 8 };
+
+static double minmax_d(int op, double a, double b, int nanprop) {
+  double r = (op == R_MIN) ? (a < b ? a : b) : (a > b ? a : b);
+  if (a != a) r = nanprop ? a : b;
+  if (b != b) r = nanprop ? b : (a != a ? b : a);
+  return r;
+}
+
+/* y = alpha*reduce(x) + beta*y; reduced dims are those with ydims == 1 and xdims != 1.
+ * `truth`, if not NULL, receives the reduction (before alpha/beta) accumulated in long double, one
+ * value per output in logical order of y. */
+int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, const int64_t *xst,
+                  const void *x, const int64_t *ydims, const int64_t *yst, void *y, double alpha,
+                  double beta, double *truth) {
+  int64_t kd[MAXD], rd[MAXD], kx[MAXD], rx[MAXD], ky[MAXD];
+  int nk = 0, nr = 0;
+  for (int i = 0; i < nd; i++) {
+    if (ydims[i] == 1 && xdims[i] != 1) { rd[nr] = xdims[i]; rx[nr] = xst[i]; nr++; }
+    else { kd[nk] = xdims[i]; kx[nk] = xst[i]; ky[nk] = yst[i]; nk++; }
+  }
+  const int64_t nout = total_of(nk, kd), nred = total_of(nr, rd);
+  const int dbl = (t == T_F64);
+#pragma omp parallel for schedule(static)
+  for (int64_t o = 0; o < nout; o++) {
+    const int64_t xo = offset_of(nk, kd, kx, o), yo = offset_of(nk, kd, ky, o);
+    double accd;
+    float accf;
+    long double acct;
+    switch (op) {
+      case R_MUL: case R_MULNZ: accd = 1; accf = 1; acct = 1; break;
+      case R_MIN: accd = INFINITY; accf = INFINITY; acct = INFINITY; break;
+      case R_MAX: accd = -INFINITY; accf = -INFINITY; acct = -INFINITY; break;
+      default: accd = 0; accf = 0; acct = 0; break;
+    }
+    for (int64_t r = 0; r < nred; r++) {
+      const int64_t off = xo + offset_of(nr, rd, rx, r);
+      const double vd = load_as_double(x, t, off);
+      const float vf = (float)vd;
+      switch (op) {
+        case R_ADD: case R_AVG: accd += vd; accf += vf; acct += vd; break;
+        case R_NORM1: accd += fabs(vd); accf += fabsf(vf); acct += fabs(vd); break;
+        case R_NORM2: accd += vd * vd; accf += vf * vf; acct += (long double)vd * vd; break;
+        case R_MUL: accd *= vd; accf *= vf; acct *= vd; break;
+        case R_MULNZ: if (vd != 0) { accd *= vd; accf *= vf; acct *= vd; } break;
+        case R_MIN: case R_MAX:
+          accd = minmax_d(op, accd, vd, nanprop); accf = (float)minmax_d(op, accf, vf, nanprop);
+          acct = minmax_d(op, (double)acct, vd, nanprop); break;
+        case R_AMAX:
+          accd = minmax_d(R_MAX, accd, fabs(vd), nanprop); accf = (float)minmax_d(R_MAX, accf, fabsf(vf), nanprop);
+          acct = minmax_d(R_MAX, (double)acct, fabs(vd), nanprop); break;
+      }
+    }
+    if (op == R_AVG) { accd = accd / (double)nred; accf = accf / (float)nred; acct = acct / (long double)nred; }
+    if (op == R_NORM2) { accd = sqrt(accd); accf = sqrtf(accf); acct = sqrtl(acct); }
+    if (truth) truth[o] = (double)acct;
+    if (dbl) {
+      store_from_double(y, t, yo, blend_d(alpha, accd, beta, y, t, yo));
+    } else {
+      store_from_float(y, t, yo, blend_f((float)alpha, accf, (float)beta, y, t, yo));
+    }
+  }
+  return 0;
+}
+
+/* any-mismatch over two strided views (typed compare) -- restates blas-plus.cu:9-101 of the
+ * reference (deep-diamond-cuda/src/device/uncomplicate/diamond/internal/cuda/). */
+int oracle_equals(int t, int nd, const int64_t *dims, const int64_t *xst, const void *x,
+                  const int64_t *yst, const void *y) {
+  const int64_t n = total_of(nd, dims);
+  int diff = 0;
+  for (int64_t i = 0; i < n && !diff; i++) {
+    double a = load_as_double(x, t, offset_of(nd, dims, xst, i));
+    double b = load_as_double(y, t, offset_of(nd, dims, yst, i));
+    if (a != b) diff = 1;
+  }
+  return !diff;
+}
+
+int oracle_num_threads(void) {
+  int n = 1;
+#ifdef _OPENMP
+#pragma omp parallel
+  {
+#pragma omp master
+    n = omp_get_num_threads();
+  }
+#endif
+  return n;
+}

@@ -1,0 +1,71 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    import oracle as _oracle
+    _oracle.build()
+    return _oracle
+
+
+@pytest.fixture(scope="session")
+def fact():
+    """One B200 factory (handle + stream) for the whole GPU session."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from deep_diamond_b200 import b200_factory
+    f = b200_factory()
+    yield f
+    f.release()
+
+
+class Dev:
+    """Moves numpy storage to the device and back as raw bytes (plumbing for the parity tests)."""
+
+    def __init__(self, fact):
+        import torch
+        self.torch = torch
+        self.fact = fact
+
+    def put(self, arr):
+        t = self.torch.from_numpy(np.ascontiguousarray(arr).reshape(-1).view(np.uint8).copy())
+        return t.to(self.fact.device)
+
+    def empty(self, nbytes, fill=0xCD):
+        return self.torch.full((max(int(nbytes), 1),), fill, dtype=self.torch.uint8, device=self.fact.device)
+
+    def get(self, t, np_dtype):
+        self.fact.synchronize()
+        self.torch.cuda.synchronize()
+        return t.cpu().numpy().view(np_dtype).copy()
+
+
+@pytest.fixture(scope="session")
+def dev(fact):
+    return Dev(fact)
+
+
+def ulp_diff_f32(a, b):
+    """Distance in units of float32 last place between two float32 arrays (NaN == NaN -> 0)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    ia = a.view(np.int32).astype(np.int64)
+    ib = b.view(np.int32).astype(np.int64)
+    ia = np.where(ia < 0, np.int64(-(2 ** 31)) - ia, ia)  # monotone mapping of the float order
+    ib = np.where(ib < 0, np.int64(-(2 ** 31)) - ib, ib)
+    d = np.abs(ia - ib)
+    both_nan = np.isnan(a) & np.isnan(b)
+    return np.where(both_nan, 0, d)

@@ -1,0 +1,169 @@
+"""GPU parity: ddReduceTensor against the CPU oracle.
+
+Bars: max/min/amax bit-exact; sums, means and norms within 1e-5 relative of the fp32 oracle and of the
+long-double truth, the denominator conditioned as max(|truth|, eps * sum|x|) so that cancelling sums
+are judged against what fp32 summation can deliver.  Reference vectors:
+deep-diamond-dnnl/test/.../dnnl/core_test.clj:888-943, deep-diamond-cuda/test/.../cudnn/core_test.clj:149-178.
+"""
+import numpy as np
+import pytest
+
+from deep_diamond_b200 import core
+
+pytestmark = pytest.mark.gpu
+
+EXACT = {"max", "min", "amax"}
+
+
+def run_reduce(fact, dev, oracle, op, shape, yshape, sx=None, sy=None, alpha=1.0, beta=0.0, seed=0,
+               dtype="float", expect=None, data=None):
+    np_t = {"float": np.float32, "double": np.float64}[dtype]
+    sx = sx or oracle.default_strides(shape)
+    sy = sy or oracle.default_strides(yshape)
+    rng = np.random.default_rng(seed)
+    nx, ny = oracle.span(shape, sx), oracle.span(yshape, sy)
+    if data is None:
+        data = (np.exp(rng.standard_normal(nx)) * np.where(rng.random(nx) < 0.5, -1, 1)).astype(np_t)
+        if op in ("mul", "mul-no-zeros"):
+            data = (1.0 + 0.01 * rng.standard_normal(nx)).astype(np_t)
+    y0 = rng.standard_normal(ny).astype(np_t)
+    want = y0.copy()
+    _, truth = oracle.reduce(op, oracle.as_layout(data, shape, sx), oracle.as_layout(want, yshape, sy),
+                             alpha=alpha, beta=beta, want_truth=True)
+    tx, ty = dev.put(data), dev.put(y0)
+    xd, yd = core.tensor_descriptor(shape, dtype, sx), core.tensor_descriptor(yshape, dtype, sy)
+    rtd = core.reduce_tensor_descriptor(op, dtype)
+    core.reduce_tensor(fact.handle, rtd, alpha, xd, tx, beta, yd, ty)
+    got = dev.get(ty, np_t)
+    if expect:
+        assert fact.handle.last_kernel().startswith(expect), fact.handle.last_kernel()
+    if op in EXACT and beta == 0.0:
+        assert np.array_equal(got, want)
+        return got
+    # conditioned relative error against the truth and the fp32 oracle
+    absx = np.abs(oracle.as_layout(data, shape, sx).astype(np.float64))
+    axes = tuple(i for i in range(len(shape)) if yshape[i] == 1 and shape[i] != 1)
+    if op in ("add", "avg"):
+        scale = absx.sum(axis=axes, keepdims=True)
+        if op == "avg":
+            scale = scale / np.prod([shape[i] for i in axes])
+    else:
+        scale = np.abs(truth)
+    gv = oracle.as_layout(got, yshape, sy).astype(np.float64)
+    wv = oracle.as_layout(want, yshape, sy).astype(np.float64)
+    y0v = oracle.as_layout(y0, yshape, sy).astype(np.float64)
+    tv = alpha * truth + beta * y0v
+    eps = np.finfo(np_t).eps
+    den = np.maximum(np.abs(tv), abs(alpha) * eps * scale.reshape(tv.shape) * 64)
+    tol = 1e-5 if dtype == "float" else 1e-13
+    assert (np.abs(gv - tv) / den).max() <= tol
+    assert (np.abs(gv - wv) / np.maximum(np.abs(wv), den)).max() <= tol
+    return got
+
+
+OPS = ["add", "avg", "max", "min", "amax", "norm1", "norm2", "mul"]
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_nchw_patterns(fact, dev, oracle, op):
+    shape = [6, 20, 12, 16]
+    run_reduce(fact, dev, oracle, op, shape, [1, 20, 1, 1], seed=1, expect="reduce/row")      # keep C
+    run_reduce(fact, dev, oracle, op, shape, [6, 1, 12, 16], seed=2, expect="reduce/col")     # over C
+    run_reduce(fact, dev, oracle, op, shape, [6, 1, 1, 1], seed=3, expect="reduce/row")       # keep N
+    run_reduce(fact, dev, oracle, op, shape, [1, 1, 1, 1], seed=4, expect="reduce/row")       # everything
+    run_reduce(fact, dev, oracle, op, shape, [6, 20, 12, 1], seed=5)                          # over W
+    run_reduce(fact, dev, oracle, op, shape, [6, 20, 1, 1], seed=6)                           # over H, W
+    run_reduce(fact, dev, oracle, op, shape, [1, 1, 12, 16], seed=7, expect="reduce/col")     # over N, C
+    run_reduce(fact, dev, oracle, op, shape, [6, 20, 12, 16], seed=8)                         # nothing reduced
+
+
+@pytest.mark.parametrize("op", ["add", "max", "norm2"])
+def test_nhwc_and_odd_shapes(fact, dev, oracle, op):
+    shape = [3, 24, 5, 7]
+    sx = oracle.nhwc_strides(shape)
+    run_reduce(fact, dev, oracle, op, shape, [1, 24, 1, 1], sx=sx, seed=9, expect="reduce/col")
+    run_reduce(fact, dev, oracle, op, shape, [3, 1, 5, 7], sx=sx, seed=10)
+    run_reduce(fact, dev, oracle, op, [5, 3, 7, 11], [1, 3, 1, 1], seed=11)   # unaligned rows: scalar loads
+    run_reduce(fact, dev, oracle, op, [5, 3, 7, 11], [5, 1, 7, 11], seed=12)
+    run_reduce(fact, dev, oracle, op, [2, 2, 3, 2], [2, 1, 3, 1], sx=[48, 100, 8, 3], seed=13,
+               expect="reduce/generic")
+
+
+@pytest.mark.parametrize("op", ["add", "avg", "max", "norm2"])
+def test_split_ranges_use_the_workspace(fact, dev, oracle, op):
+    # few outputs with long reduce ranges: several CTAs per output + the finishing kernel
+    run_reduce(fact, dev, oracle, op, [4, 64, 32, 32], [4, 1, 1, 1], seed=14, expect="reduce/row+finish")
+    run_reduce(fact, dev, oracle, op, [1, 1, 1, 1 << 20], [1, 1, 1, 1], seed=15, expect="reduce/row+finish")
+    run_reduce(fact, dev, oracle, op, [2048, 8, 1, 16], [1, 8, 1, 16], seed=16, expect="reduce/col+finish")
+    run_reduce(fact, dev, oracle, op, [64, 16, 32, 32], [1, 16, 1, 1], seed=17, expect="reduce/row+finish")
+
+
+def test_alpha_beta_and_double(fact, dev, oracle):
+    run_reduce(fact, dev, oracle, "add", [6, 20, 12, 16], [1, 20, 1, 1], alpha=3.0, beta=2.0, seed=18)
+    run_reduce(fact, dev, oracle, "max", [6, 20, 12, 16], [6, 1, 12, 16], alpha=2.5, beta=0.0, seed=19)
+    run_reduce(fact, dev, oracle, "add", [6, 20, 12, 16], [1, 20, 1, 1], dtype="double", seed=20)
+    run_reduce(fact, dev, oracle, "norm2", [6, 20, 12, 16], [6, 1, 1, 1], dtype="double", seed=21)
+    run_reduce(fact, dev, oracle, "max", [6, 20, 12, 16], [6, 1, 12, 16], dtype="double", seed=22)
+
+
+def test_reference_vectors(fact, dev, oracle):
+    x = np.arange(120, dtype=np.float32)
+    # core_test.clj:888-905 sum over W
+    got = run_reduce(fact, dev, oracle, "add", [2, 3, 4, 5], [2, 3, 4, 1], data=x)
+    assert got[:3].tolist() == [10.0, 35.0, 60.0]
+    # :907-924 max over (N,H,W)
+    got = run_reduce(fact, dev, oracle, "max", [2, 3, 4, 5], [1, 3, 1, 1], data=x)
+    assert got.tolist() == [79.0, 99.0, 119.0]
+    # :926-943 L2 over W
+    got = run_reduce(fact, dev, oracle, "norm2", [2, 3, 4, 5], [2, 3, 4, 1], data=x)
+    want = [np.float32(np.sqrt(sum(i * i for i in range(a, a + 5)))) for a in (0, 5, 10)]
+    assert np.allclose(got[:3], want, rtol=1e-6)
+    # cudnn core_test.clj:149-178: 3*sum + 2*y, 2.5*max, 1.5*prod over [2 3 1 1] -> [1 1 1 1]
+    v = np.array([1, 2, 3, 4, 5, 6], dtype=np.float32)
+    d_x = core.tensor_descriptor([2, 3, 1, 1], "float", "nchw")
+    d_y = core.tensor_descriptor([1, 1, 1, 1], "float", "nchw")
+    tx, ty = dev.put(v), dev.put(np.zeros(1, np.float32))
+    core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor("add", "float"), 3.0, d_x, tx, 2.0, d_y, ty)
+    assert dev.get(ty, np.float32)[0] == 63.0
+    core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor("max", "float"), 2.5, d_x, tx, 0.0, d_y, ty)
+    assert dev.get(ty, np.float32)[0] == 15.0
+    core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor("mul", "float"), 1.5, d_x, tx, 0.0, d_y, ty)
+    assert dev.get(ty, np.float32)[0] == 1080.0
+
+
+def test_caller_workspace_and_run_to_run_identity(fact, dev, oracle):
+    import torch
+    shape, yshape = [4, 64, 32, 32], [4, 1, 1, 1]
+    x = np.random.default_rng(30).standard_normal(int(np.prod(shape))).astype(np.float32)
+    xd = core.tensor_descriptor(shape, "float", "nchw")
+    yd = core.tensor_descriptor(yshape, "float", "nchw")
+    rtd = core.reduce_tensor_descriptor("add", "float")
+    need = core.reduction_workspace_size(fact.handle, rtd, xd, yd)
+    assert need > 0 and core.reduction_indices_size(fact.handle, rtd, xd, yd) == 0
+    ws = torch.empty(need, dtype=torch.uint8, device=fact.device)
+    tx = dev.put(x)
+    outs = []
+    for _ in range(3):
+        ty = dev.put(np.zeros(4, np.float32))
+        core.reduce_tensor(fact.handle, rtd, None, ws, 1.0, xd, tx, 0.0, yd, ty)
+        outs.append(dev.get(ty, np.float32))
+    ty = dev.put(np.zeros(4, np.float32))
+    core.reduce_tensor(fact.handle, rtd, 1.0, xd, tx, 0.0, yd, ty)   # handle-owned scratch
+    outs.append(dev.get(ty, np.float32))
+    for o in outs[1:]:
+        assert np.array_equal(o.view(np.uint32), outs[0].view(np.uint32))
+    from deep_diamond_b200._lib import DiamondError
+    small = torch.empty(8, dtype=torch.uint8, device=fact.device)
+    with pytest.raises(DiamondError):
+        core.reduce_tensor(fact.handle, rtd, None, small, 1.0, xd, tx, 0.0, yd, ty)
+
+
+def test_nan_propagation(fact, dev):
+    v = np.array([1, np.nan, 3, 4, 5, 6], dtype=np.float32)
+    d_x = core.tensor_descriptor([2, 3, 1, 1], "float", "nchw")
+    d_y = core.tensor_descriptor([1, 1, 1, 1], "float", "nchw")
+    tx, ty = dev.put(v), dev.put(np.zeros(1, np.float32))
+    core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor("max", "float", True), 1.0, d_x, tx, 0.0, d_y, ty)
+    assert np.isnan(dev.get(ty, np.float32)[0])
+    core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor("max", "float", False), 1.0, d_x, tx, 0.0, d_y, ty)
+    assert dev.get(ty, np.float32)[0] == 6.0

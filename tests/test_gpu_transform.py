@@ -1,0 +1,187 @@
+"""GPU parity: ddTransformTensor (reorder + data type conversion) against the CPU oracle, bit for bit.
+
+Covers the reference's reorder tests at the C level (dnnl core_test "Reordering memory" blocks,
+deep-diamond-dnnl/test/uncomplicate/diamond/internal/dnnl/core_test.clj:260-361) and the stride /
+data type space around them: every kernel family (flat, tile, strided, gather) and edge shapes.
+"""
+import numpy as np
+import pytest
+
+from deep_diamond_b200 import core
+
+pytestmark = pytest.mark.gpu
+
+NP = {"float": np.float32, "double": np.float64, "half": np.float16, "byte": np.int8,
+      "int": np.int32, "uint8": np.uint8, "bf16": np.uint16, "long": np.int64}
+TAG = {"float": "f32", "double": "f64", "half": "f16", "byte": "s8", "int": "s32", "uint8": "u8",
+       "bf16": "bf16", "long": "s64"}
+
+
+def make_values(rng, n, dt):
+    """Source storage for data type `dt` with values that exercise rounding and saturation."""
+    if dt in ("float", "double"):
+        v = rng.standard_normal(n) * 100.0
+        v[::7] = np.rint(v[::7]) + 0.5  # ties for round-to-nearest-even
+        v[::13] *= 1e3                   # saturation for narrow integer destinations
+        return v.astype(NP[dt])
+    if dt == "half":
+        return (rng.standard_normal(n) * 50.0).astype(np.float16)
+    if dt == "bf16":
+        f = (rng.standard_normal(n) * 50.0).astype(np.float32).view(np.uint32)
+        return (f >> 16).astype(np.uint16)
+    if dt == "byte":
+        return rng.integers(-128, 128, n).astype(np.int8)
+    if dt == "uint8":
+        return rng.integers(0, 256, n).astype(np.uint8)
+    if dt == "int":
+        return rng.integers(-70000, 70000, n).astype(np.int32)
+    return rng.integers(-70000, 70000, n).astype(np.int64)
+
+
+def run_case(fact, dev, oracle, shape, sx, sy, sdt, ddt, alpha=1.0, beta=0.0, seed=0, expect=None):
+    rng = np.random.default_rng(seed)
+    nx, ny = oracle.span(shape, sx), oracle.span(shape, sy)
+    xs = make_values(rng, nx, sdt)
+    y0 = make_values(rng, ny, ddt) if beta != 0.0 else np.full(ny, 0, dtype=NP[ddt])
+    if beta == 0.0:
+        y0 = y0.view(np.uint8).copy()
+        y0[:] = 0xCD  # canary: untouched padding must survive
+        y0 = y0.view(NP[ddt])
+    want = y0.copy()
+    oracle.reorder(oracle.as_layout(xs, shape, sx), oracle.as_layout(want, shape, sy),
+                   TAG[sdt], TAG[ddt], alpha, beta)
+    dx, dy = dev.put(xs), dev.put(y0)
+    xd = core.tensor_descriptor(shape, sdt, sx)
+    yd = core.tensor_descriptor(shape, ddt, sy)
+    core.transform_tensor(fact.handle, alpha, xd, dx, beta, yd, dy)
+    got = dev.get(dy, NP[ddt])
+    if expect:
+        assert fact.handle.last_kernel() == expect
+    same = got.view(np.uint8) == want.view(np.uint8)
+    if not same.all() and ddt in ("half", "bf16", "float", "double"):
+        # NaN payloads may differ between the CPU and GPU converters; everything else is exact
+        g = got.astype(np.float64) if ddt != "bf16" else (got.astype(np.uint32) << 16).view(np.float32)
+        w = want.astype(np.float64) if ddt != "bf16" else (want.astype(np.uint32) << 16).view(np.float32)
+        same = (got == want) | (np.isnan(g) & np.isnan(w))
+    assert same.all(), "mismatch at %s" % np.flatnonzero(~same.reshape(-1))[:8]
+
+
+def nchw(shape):
+    import oracle
+    return oracle.default_strides(shape)
+
+
+def nhwc(shape):
+    import oracle
+    return oracle.nhwc_strides(shape)
+
+
+def perm_strides(shape, order):
+    """Dense strides whose physical order of dims (outermost first) is `order`."""
+    st, run = [0] * len(shape), 1
+    for d in reversed(order):
+        st[d] = run
+        run *= shape[d]
+    return st
+
+
+ALL = ["float", "double", "half", "byte", "int", "uint8", "bf16", "long"]
+
+
+@pytest.mark.parametrize("sdt", ALL)
+@pytest.mark.parametrize("ddt", ALL)
+def test_every_type_pair_flat_tile_strided(fact, dev, oracle, sdt, ddt):
+    # flat (same layout), tile (aligned nchw -> nhwc) and strided (odd shape) for each pair
+    run_case(fact, dev, oracle, [3, 5, 7, 9], nchw([3, 5, 7, 9]), nchw([3, 5, 7, 9]), sdt, ddt, seed=1,
+             expect="transform/flat")
+    run_case(fact, dev, oracle, [2, 32, 8, 16], nchw([2, 32, 8, 16]), nhwc([2, 32, 8, 16]), sdt, ddt, seed=2,
+             expect="transform/tile")
+    run_case(fact, dev, oracle, [2, 3, 5, 7], nchw([2, 3, 5, 7]), nhwc([2, 3, 5, 7]), sdt, ddt, seed=3,
+             expect="transform/strided")
+
+
+@pytest.mark.parametrize("shape", [[2, 2, 3, 2], [1, 64, 56, 56], [4, 64, 8, 8], [2, 256, 28, 28],
+                                   [3, 48, 4, 20], [2, 96, 1, 132], [5, 16, 3, 24], [1, 512, 2, 2]])
+@pytest.mark.parametrize("pair", [("float", "float"), ("float", "bf16"), ("byte", "byte"),
+                                  ("float", "byte"), ("half", "float")])
+def test_nchw_nhwc_both_ways(fact, dev, oracle, shape, pair):
+    sdt, ddt = pair
+    run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), sdt, ddt, seed=4)
+    run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=5)
+
+
+def test_tile_ragged_edges(fact, dev, oracle):
+    # extents that are vector-aligned but not tile-aligned, in both tiled dims, with batch dims
+    for shape in ([3, 72, 5, 12], [2, 200, 3, 28], [7, 8, 2, 68]):
+        run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), "float", "float", seed=6,
+                 expect="transform/tile")
+    run_case(fact, dev, oracle, [2, 144, 4, 40], nchw([2, 144, 4, 40]), nhwc([2, 144, 4, 40]), "byte", "byte",
+             seed=7, expect="transform/tile")
+    run_case(fact, dev, oracle, [2, 144, 4, 40], nchw([2, 144, 4, 40]), nhwc([2, 144, 4, 40]), "float", "bf16",
+             seed=8, expect="transform/tile")
+
+
+def test_padded_strides_round_trip(fact, dev, oracle):
+    # core_test.clj:301-340: [2 2 3 2] through strides [48 100 8 3]; tensor_test.clj:171-194
+    run_case(fact, dev, oracle, [2, 2, 3, 2], nchw([2, 2, 3, 2]), [48, 100, 8, 3], "float", "float", seed=9)
+    run_case(fact, dev, oracle, [2, 2, 3, 2], [48, 100, 8, 3], nhwc([2, 2, 3, 2]), "float", "float", seed=10)
+    run_case(fact, dev, oracle, [2, 3, 2, 1], [48, 16, 5, 2], [48, 13, 4, 2], "float", "float", seed=11)
+    run_case(fact, dev, oracle, [2, 3, 2, 1], [48, 12, 4, 2], [48, 14, 4, 2], "float", "float", seed=12)
+
+
+def test_alpha_beta_blend(fact, dev, oracle):
+    for shape, sy in (([3, 5, 7, 9], nchw([3, 5, 7, 9])), ([2, 32, 8, 16], nhwc([2, 32, 8, 16]))):
+        run_case(fact, dev, oracle, shape, nchw(shape), sy, "float", "float", alpha=3.0, beta=2.0, seed=13)
+        run_case(fact, dev, oracle, shape, nchw(shape), sy, "float", "half", alpha=0.5, beta=0.0, seed=14)
+        run_case(fact, dev, oracle, shape, nchw(shape), sy, "byte", "float", alpha=1.0, beta=1.0, seed=15)
+        run_case(fact, dev, oracle, shape, nchw(shape), sy, "double", "double", alpha=2.0, beta=-1.0, seed=16)
+
+
+def test_ranks_1_to_6_and_size_one_dims(fact, dev, oracle):
+    run_case(fact, dev, oracle, [17], [1], [3], "float", "float", seed=17)
+    run_case(fact, dev, oracle, [4, 6], [6, 1], [1, 4], "float", "float", seed=18)
+    run_case(fact, dev, oracle, [2, 7, 1], [7, 1, 1], [1, 2, 1], "float", "float", seed=19)
+    run_case(fact, dev, oracle, [1, 1, 1, 1], [1, 1, 1, 1], [1, 1, 1, 1], "float", "double", seed=20)
+    run_case(fact, dev, oracle, [2, 3, 4, 5, 6], nchw([2, 3, 4, 5, 6]), nhwc([2, 3, 4, 5, 6]), "float", "float", seed=21)
+    shape6 = [2, 3, 2, 3, 2, 4]
+    run_case(fact, dev, oracle, shape6, nchw(shape6), perm_strides(shape6, [3, 0, 5, 1, 4, 2]), "float", "float", seed=22)
+    run_case(fact, dev, oracle, shape6, perm_strides(shape6, [5, 4, 3, 2, 1, 0]), nchw(shape6), "byte", "float", seed=23)
+
+
+def test_gather_matches_separate_transforms(fact, dev, oracle):
+    # a shuffler invocation: rows [0 2 1] of a [6 2 1 1] source into a [3 2 1 1] destination with
+    # another layout (tensor_test.clj:263-275), plus a typed case with larger items
+    rng = np.random.default_rng(23)
+    for (n_src, item, sdt, ddt) in ((6, [1, 2, 1, 1], "float", "float"), (9, [1, 16, 4, 8], "float", "half")):
+        shape_src = [n_src] + item[1:]
+        cols = [0, 2, 1, 5, 2]
+        shape_dst = [len(cols)] + item[1:]
+        sx, sy = nchw(shape_src), nhwc(shape_dst)
+        xs = make_values(rng, oracle.span(shape_src, sx), sdt)
+        want = np.zeros(oracle.span(shape_dst, sy), dtype=NP[ddt])
+        for d, c in enumerate(cols):
+            oracle.reorder(oracle.as_layout(xs, item, sx, offset=c * sx[0]),
+                           oracle.as_layout(want, item, sy, offset=d * sy[0]), TAG[sdt], TAG[ddt])
+        dx, dy = dev.put(xs), dev.put(np.zeros_like(want))
+        xd = core.tensor_descriptor(item, sdt, sx)
+        yd = core.tensor_descriptor(item, ddt, sy)
+        core.gather_transform(fact.handle, [c * sx[0] for c in cols], [d * sy[0] for d in range(len(cols))],
+                              xd, dx, yd, dy)
+        got = dev.get(dy, NP[ddt])
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
+        assert fact.handle.last_kernel() == "transform/gather"
+
+
+def test_bad_arguments_are_reported_not_executed(fact, dev):
+    import ctypes
+    from deep_diamond_b200._lib import DiamondError
+    x = dev.empty(1024)
+    a = core.tensor_descriptor([2, 3, 4, 5], "float", "nchw")
+    b = core.tensor_descriptor([2, 3, 4, 4], "float", "nchw")
+    with pytest.raises(DiamondError) as e:
+        core.transform_tensor(fact.handle, 1.0, a, x, 0.0, b, x)
+    assert e.value.data["type"] == "bad-param"
+    with pytest.raises(DiamondError):
+        core.tensor_descriptor([2, 0, 4, 5], "float", "nchw")
+    with pytest.raises(DiamondError):
+        core.tensor_descriptor([2, 3], "f128", [3, 1])
