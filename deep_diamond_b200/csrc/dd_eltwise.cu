@@ -16,8 +16,10 @@
 //   linear    f = a*x+b                    f' = a
 //   clip-relu f = min(max(x,0),a)          f' = 0<x<=a ? 1 : 0
 //   abs       f = |x|                      f' = sign(x)
-// f*(1-f) and 1-f^2 are evaluated as e/(1+e)^2 forms (no cancellation near saturation).
+// f*(1-f) and 1-f^2 are evaluated as e/(1+e)^2 forms (no cancellation near saturation); the fp32
+// exp/logistic/tanh come from dd_math_f32.cuh (under 1 ulp), not from the CUDA math library.
 #include "dd_internal.cuh"
+#include "dd_math_f32.cuh"
 
 template <typename C> struct dd_math;
 template <> struct dd_math<float> {
@@ -29,6 +31,19 @@ template <> struct dd_math<float> {
   static __device__ __forceinline__ float max(float a, float b) { return fmaxf(a, b); }
   static __device__ __forceinline__ float min(float a, float b) { return fminf(a, b); }
   static __device__ __forceinline__ float div(float a, float b) { return __fdiv_rn(a, b); }
+  static __device__ __forceinline__ float sigmoid(float x) { return dd_sigmoid_f32(x); }
+  // s*(1-s) = e/(1+e)^2 with e = exp(-|x|)
+  static __device__ __forceinline__ float dsigmoid(float x) {
+    float d = dd_e_over_one_plus_e_sq(fmaxf(-fabsf(x), -104.0f), 0);
+    return x != x ? x : d;
+  }
+  static __device__ __forceinline__ float tanh_(float x) { return dd_tanh_f32(x); }
+  // 1 - tanh^2 = 4e/(1+e)^2 with e = exp(-2|x|)
+  static __device__ __forceinline__ float dtanh(float x) {
+    float d = dd_e_over_one_plus_e_sq(fmaxf(-2.0f * fabsf(x), -104.0f), 2);
+    return x != x ? x : d;
+  }
+  static __device__ __forceinline__ float exp_neg(float x) { return dd_exp_neg_rounded(x); }
 };
 template <> struct dd_math<double> {
   static __device__ __forceinline__ double exp(double x) { return ::exp(x); }
@@ -39,6 +54,23 @@ template <> struct dd_math<double> {
   static __device__ __forceinline__ double max(double a, double b) { return ::fmax(a, b); }
   static __device__ __forceinline__ double min(double a, double b) { return ::fmin(a, b); }
   static __device__ __forceinline__ double div(double a, double b) { return __ddiv_rn(a, b); }
+  static __device__ __forceinline__ double sigmoid(double x) {
+    double e = ::exp(-::fabs(x));
+    double r = 1.0 / (1.0 + e);
+    return x != x ? x : (x >= 0.0 ? r : e * r);
+  }
+  static __device__ __forceinline__ double dsigmoid(double x) {
+    double e = ::exp(-::fabs(x));
+    double r = 1.0 / (1.0 + e);
+    return x != x ? x : e * r * r;
+  }
+  static __device__ __forceinline__ double tanh_(double x) { return ::tanh(x); }
+  static __device__ __forceinline__ double dtanh(double x) {
+    double e = ::exp(-2.0 * ::fabs(x));
+    double r = 1.0 / (1.0 + e);
+    return x != x ? x : 4.0 * e * r * r;
+  }
+  static __device__ __forceinline__ double exp_neg(double x) { return ::exp(x); }
 };
 
 struct ddActArgs {
@@ -56,13 +88,9 @@ __device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp) {
     }
     return x > (C)0 ? x : dd_mul_rn(coef, x);
   } else if (MODE == DD_ACTIVATION_SIGMOID) {
-    // e = exp(-|x|) in (0,1]; 1/(1+e) for x>=0, e/(1+e) for x<0
-    C e = M::exp(-M::abs(x));
-    C r = M::div((C)1, dd_add_rn((C)1, e));
-    C s = x >= (C)0 ? r : dd_mul_rn(e, r);
-    return x != x ? x : s;
+    return M::sigmoid(x);
   } else if (MODE == DD_ACTIVATION_TANH) {
-    return M::tanh(x);
+    return M::tanh_(x);
   } else if (MODE == DD_ACTIVATION_ELU) {
     return x > (C)0 ? x : dd_mul_rn(coef, M::expm1(x));
   } else if (MODE == DD_ACTIVATION_LINEAR) {
@@ -82,19 +110,11 @@ __device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef) {
   if (MODE == DD_ACTIVATION_RELU) {
     return x > (C)0 ? dy : dd_mul_rn(coef, dy);
   } else if (MODE == DD_ACTIVATION_SIGMOID) {
-    // s(1-s) = e/(1+e)^2 with e = exp(-|x|)
-    C e = M::exp(-M::abs(x));
-    C r = M::div((C)1, dd_add_rn((C)1, e));
-    C d = dd_mul_rn(dd_mul_rn(e, r), r);
-    return dd_mul_rn(dy, x != x ? x : d);
+    return dd_mul_rn(dy, M::dsigmoid(x));
   } else if (MODE == DD_ACTIVATION_TANH) {
-    // 1 - tanh^2 = 4e/(1+e)^2 with e = exp(-2|x|)
-    C e = M::exp((C)-2 * M::abs(x));
-    C r = M::div((C)1, dd_add_rn((C)1, e));
-    C d = dd_mul_rn(dd_mul_rn((C)4 * e, r), r);
-    return dd_mul_rn(dy, x != x ? x : d);
+    return dd_mul_rn(dy, M::dtanh(x));
   } else if (MODE == DD_ACTIVATION_ELU) {
-    return x > (C)0 ? dy : dd_mul_rn(dy, dd_mul_rn(coef, M::exp(x)));
+    return x > (C)0 ? dy : dd_mul_rn(dy, dd_scale(coef, M::exp_neg(x)));
   } else if (MODE == DD_ACTIVATION_LINEAR) {
     return dd_mul_rn(coef, dy);
   } else if (MODE == DD_ACTIVATION_CLIPPED_RELU) {

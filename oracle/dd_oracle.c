@@ -40,10 +40,13 @@
  *     is involved, then double.
  *   - alpha*v + beta*old: each product and the sum rounded separately (compile with
  *     -ffp-contract=off), a factor of exactly 1 skipped, beta == 0 does not read `old`.
- *   - transcendental eltwise in fp32 uses the C library's float functions on oneDNN's documented
- *     formulas; *_truth variants evaluate the same definitions in double.
- *   - reductions accumulate sequentially in the compute type, in logical (row-major) order of the
- *     reduced dims; *_truth variants accumulate in long double.
+ *   - transcendental eltwise (logistic, tanh, elu) in fp32: oneDNN's documented definition
+ *     evaluated in double and rounded to float once -- the value every fp32 implementation
+ *     (oneDNN's JIT polynomial, its libm-based reference, the GPU kernel) approximates to within
+ *     its own few ulp; measured: oneDNN 3.10.2 is within 2 ulp of it for logistic, 1 for tanh.
+ *     Backward = that rounded derivative times dy in fp32.  *_truth variants return doubles.
+ *   - sum-type reductions add in pairwise order in the compute type over the logical (row-major)
+ *     order of the reduced dims; max/min/mul run left to right; *_truth accumulates in long double.
  *
  * Build: gcc -O2 -fopenmp -ffp-contract=off -fPIC -shared -o oracle/libdd_oracle.so oracle/dd_oracle.c -lm
  */
@@ -291,9 +294,10 @@ static float act_fwd_f(int alg, float x, float a, float b, int nanprop) {
         return fmaxf(x, 0.f);
       }
       return x > 0.f ? x : a * x;
-    case A_SIGMOID: return 1.f / (1.f + expf(-x));
-    case A_TANH: return tanhf(x);
-    case A_ELU: return x > 0.f ? x : a * expm1f(x);
+    /* transcendental modes: the definition evaluated in double, rounded to float once */
+    case A_SIGMOID: { double e = exp(-fabs((double)x)); double r = 1.0 / (1.0 + e); return (float)(x >= 0.f ? r : e * r); }
+    case A_TANH: return (float)tanh((double)x);
+    case A_ELU: return x > 0.f ? x : a * (float)expm1((double)x);
     case A_LINEAR: return fmaf(a, x, b);
     case A_CLIP:
       if (nanprop && x != x) return x;
@@ -327,9 +331,10 @@ static double act_fwd_d(int alg, double x, double a, double b, int nanprop) {
 static float act_bwd_f(int alg, float x, float dy, float a) {
   switch (alg) {
     case A_RELU: return x > 0.f ? dy : a * dy;
-    case A_SIGMOID: { float v = 1.f / (1.f + expf(-x)); return dy * v * (1.f - v); }
-    case A_TANH: { float t = tanhf(x); return dy * (1.f - t) * (1.f + t); }
-    case A_ELU: return x > 0.f ? dy : dy * (a * expf(x));
+    /* derivative evaluated in double and rounded once, then one fp32 product with dy */
+    case A_SIGMOID: { double e = exp(-fabs((double)x)); double r = 1.0 / (1.0 + e); return dy * (float)(e * r * r); }
+    case A_TANH: { double e = exp(-2.0 * fabs((double)x)); double r = 1.0 / (1.0 + e); return dy * (float)(4.0 * e * r * r); }
+    case A_ELU: { float ex = (float)exp((double)x); return x > 0.f ? dy : dy * (a == 1.f ? ex : a * ex); }
     case A_LINEAR: return a * dy;
     case A_CLIP: return (x > 0.f && x <= a) ? dy : 0.f;
     case A_ABS: return x > 0.f ? dy : (x < 0.f ? -dy : 0.f);
@@ -496,6 +501,48 @@ static double minmax_d(int op, double a, double b, int nanprop) {
   return r;
 }
 
+/* Sum-type reductions (sum, mean, norm1, norm2) add in pairwise (binary tree) order over the
+ * logical order of the reduced elements, leaves of <= 8 elements added left to right: a fixed,
+ * reproducible fp32 order whose error grows with log(n), like the vectorised/blocked orders real
+ * implementations use (a single left-to-right fp32 accumulator is off by 5e-4 relative at 2^20
+ * terms and is nobody's algorithm).  max/min/mul run left to right. */
+typedef struct {
+  int op, t, nr;
+  const int64_t *rd, *rx;
+  const void *x;
+  int64_t xo;
+} red_ctx;
+
+static double red_value(const red_ctx *c, int64_t r) {
+  return load_as_double(c->x, c->t, c->xo + offset_of(c->nr, c->rd, c->rx, r));
+}
+
+static float pair_f(const red_ctx *c, int64_t lo, int64_t hi) {
+  if (hi - lo <= 8) {
+    float acc = 0.f;
+    for (int64_t r = lo; r < hi; r++) {
+      float v = (float)red_value(c, r);
+      acc += c->op == R_NORM1 ? fabsf(v) : (c->op == R_NORM2 ? v * v : v);
+    }
+    return acc;
+  }
+  int64_t mid = lo + (hi - lo) / 2;
+  return pair_f(c, lo, mid) + pair_f(c, mid, hi);
+}
+
+static double pair_d(const red_ctx *c, int64_t lo, int64_t hi) {
+  if (hi - lo <= 8) {
+    double acc = 0.0;
+    for (int64_t r = lo; r < hi; r++) {
+      double v = red_value(c, r);
+      acc += c->op == R_NORM1 ? fabs(v) : (c->op == R_NORM2 ? v * v : v);
+    }
+    return acc;
+  }
+  int64_t mid = lo + (hi - lo) / 2;
+  return pair_d(c, lo, mid) + pair_d(c, mid, hi);
+}
+
 /* y = alpha*reduce(x) + beta*y; reduced dims are those with ydims == 1 and xdims != 1.
  * `truth`, if not NULL, receives the reduction (before alpha/beta) accumulated in long double, one
  * value per output in logical order of y. */
@@ -510,6 +557,7 @@ int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, cons
   }
   const int64_t nout = total_of(nk, kd), nred = total_of(nr, rd);
   const int dbl = (t == T_F64);
+  const int sumlike = (op == R_ADD || op == R_AVG || op == R_NORM1 || op == R_NORM2);
 #pragma omp parallel for schedule(static)
   for (int64_t o = 0; o < nout; o++) {
     const int64_t xo = offset_of(nk, kd, kx, o), yo = offset_of(nk, kd, ky, o);
@@ -522,14 +570,19 @@ int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, cons
       case R_MAX: accd = -INFINITY; accf = -INFINITY; acct = -INFINITY; break;
       default: accd = 0; accf = 0; acct = 0; break;
     }
+    if (sumlike) {
+      red_ctx c = {op, t, nr, rd, rx, x, xo};
+      if (dbl) accd = pair_d(&c, 0, nred);
+      else accf = pair_f(&c, 0, nred);
+    }
     for (int64_t r = 0; r < nred; r++) {
       const int64_t off = xo + offset_of(nr, rd, rx, r);
       const double vd = load_as_double(x, t, off);
       const float vf = (float)vd;
       switch (op) {
-        case R_ADD: case R_AVG: accd += vd; accf += vf; acct += vd; break;
-        case R_NORM1: accd += fabs(vd); accf += fabsf(vf); acct += fabs(vd); break;
-        case R_NORM2: accd += vd * vd; accf += vf * vf; acct += (long double)vd * vd; break;
+        case R_ADD: case R_AVG: acct += vd; break;
+        case R_NORM1: acct += fabs(vd); break;
+        case R_NORM2: acct += (long double)vd * vd; break;
         case R_MUL: accd *= vd; accf *= vf; acct *= vd; break;
         case R_MULNZ: if (vd != 0) { accd *= vd; accf *= vf; acct *= vd; } break;
         case R_MIN: case R_MAX:

@@ -181,3 +181,58 @@ def test_strided_views(fact, dev, oracle):
                             core.tensor_descriptor(shape, "float", sx), tx, 0.0,
                             core.tensor_descriptor(shape, "float", sy), ty)
     assert np.array_equal(dev.get(ty, np.float32), w)
+
+
+def _ordered(t):
+    """float32 tensor -> int64 keys that are monotone in the float order (ulp distance = key diff)."""
+    import torch
+    i = t.view(torch.int32).to(torch.int64)
+    return torch.where(i < 0, -(2 ** 31) - i, i)
+
+
+@pytest.mark.parametrize("mode,bwd", [("logistic", False), ("tanh", False), ("logistic", True),
+                                      ("tanh", True), ("elu", True), ("elu", False)])
+def test_every_float32_input(fact, dev, mode, bwd):
+    """All 2^32 float32 bit patterns through the kernel, against the definition evaluated in double on
+    the device and rounded once.  Bar: 2 ulp (1 ulp is what is actually reached; printed)."""
+    import torch
+    chunk = 1 << 27
+    ad = core.activation_descriptor(mode, True, COEF[mode])
+    d = core.tensor_descriptor([chunk], "float", [1])
+    out = torch.empty(chunk, dtype=torch.float32, device=fact.device)
+    ones = torch.ones(chunk, dtype=torch.float32, device=fact.device)
+    worst, worst_at = 0, (0.0, 0.0, 0.0)
+    for start in range(0, 1 << 32, chunk):
+        bits = torch.arange(start, start + chunk, dtype=torch.int64, device=fact.device)
+        x = bits.to(torch.int32).view(torch.float32) if start + chunk <= (1 << 31) else \
+            (bits - (1 << 32)).to(torch.int32).view(torch.float32)
+        if bwd:
+            core.activation_backward(fact.handle, ad, 1.0, d, None, d, ones, d, x, 0.0, d, out)
+        else:
+            core.activation_forward(fact.handle, ad, 1.0, d, x, 0.0, d, out)
+        fact.synchronize()
+        xd = x.double()
+        if mode == "logistic":
+            e = torch.exp(-xd.abs())
+            truth = e / (1 + e) ** 2 if bwd else torch.where(xd >= 0, 1 / (1 + e), e / (1 + e))
+        elif mode == "tanh":
+            e = torch.exp(-2 * xd.abs())
+            truth = 4 * e / (1 + e) ** 2 if bwd else torch.tanh(xd)
+        else:
+            truth = torch.where(xd > 0, torch.ones_like(xd), torch.exp(xd)) if bwd else \
+                torch.where(xd > 0, xd, torch.expm1(xd))
+        t32 = truth.float()
+        fin = torch.isfinite(t32) & torch.isfinite(x)
+        diff = (_ordered(out) - _ordered(t32)).abs()
+        diff = torch.where(fin, diff, torch.zeros_like(diff))
+        # signed zero: -0.0 and +0.0 are one key apart in this ordering but equal in value
+        diff = torch.where((out == 0) & (t32 == 0), torch.zeros_like(diff), diff)
+        w = int(diff.max().item())
+        if w > worst:
+            worst = w
+            at = int(diff.argmax().item())
+            worst_at = (float(x[at]), float(out[at]), float(t32[at]))
+        nan_in = torch.isnan(x)
+        assert bool((torch.isnan(out) == nan_in).all()), "NaN must propagate and only NaN"
+    print("%s %s: worst ulp distance over all float32 inputs = %d" % (mode, "bwd" if bwd else "fwd", worst))
+    assert worst <= 2, "x=%r got=%r truth=%r" % worst_at

@@ -80,8 +80,9 @@ def test_reference_sum_and_binary_vectors(fact, dev):
     src = np.zeros(120, np.float32); src[:2] = [-100, 10]
     dst = np.zeros(120, np.float32); dst[:2] = [-200, 20]
     ts, td = dev.put(src), dev.put(dst)
-    core.sum_tensors(fact.handle, [2.0, 3.0], [d, d], [td, ts], d, td)   # dst = 2*dst + 3*src
-    assert dev.get(td, np.float32)[:2].tolist() == [-700.0, 70.0]
+    core.sum_tensors(fact.handle, [2.0, 3.0], [d, d], [ts, td], d, td)   # dst = 2*src + 3*dst
+    assert dev.get(td, np.float32)[:2].tolist() == [-800.0, 80.0]
+    assert dev.get(ts, np.float32)[:2].tolist() == [-100.0, 10.0]
     s0 = np.zeros(120, np.float32); s0[:2] = [-100, 20]
     s1 = np.zeros(120, np.float32); s1[:2] = [-1000, 200]
     out = np.full(120, 1e5, np.float32)
