@@ -172,7 +172,8 @@ class B200Tensor:
             sub_desc = core.tensor_descriptor(dims, self.desc.dtype_code, self.desc.strides)
         else:
             shp = _shape_of(sub)
-            dt = _dtype_of(sub) or self.desc.dtype_code
+            dt = _dtype_of(sub)
+            dt = self.desc.dtype_code if dt is None else dt
             lay = _layout_of(sub)
             sub_desc = core.tensor_descriptor(shp, dt, lay if lay is not None else self.desc.strides)
         need = _span(sub_desc.dims, sub_desc.strides) * DATA_TYPE_WIDTH[sub_desc.dtype_code]
@@ -539,6 +540,13 @@ class B200Factory:
         storage = raw.view(NUMPY_TYPE[tz.desc.dtype_code]).copy()
         return HostTensor(tz.shape, tz.desc.dtype_code, tz.layout, storage)
 
+    def download_into(self, tz, host_array):
+        """Raw storage copy device -> a caller-owned (ideally pinned) numpy array of the same dtype."""
+        dst = torch.from_numpy(host_array.reshape(-1)[:tz.storage_elems].view(np.uint8))
+        with torch.cuda.stream(self.stream):
+            dst.copy_(self._bytes(tz), non_blocking=False)
+        return host_array
+
     def _bytes(self, tz):
         start = tz.base + tz.position * tz.width
         return tz.alloc[start:start + tz.storage_elems * tz.width]
@@ -650,6 +658,18 @@ def b200_factory(device=None, stream=None):
 
 # ====================== transfer! ===============================================
 
+def _host_values(source, n, dtype_code):
+    """`n` values from a host sequence in the storage dtype of `dtype_code`; a numpy array that already
+    has that dtype is used as is (no copy, so pinned buffers stay pinned)."""
+    want = NUMPY_TYPE[dtype_code]
+    if isinstance(source, np.ndarray) and source.dtype == want and dtype_code != 9:
+        flat = source.reshape(-1)
+        if flat.size < n:
+            raise DiamondError(DOES_NOT_FIT_MSG, {"source": flat.size, "destination": n})
+        return flat[:n]
+    return _encode(_take(source, n, np.float64 if dtype_code in (0, 1, 2, 9) else np.int64), dtype_code)
+
+
 def _take(source, n, np_dtype):
     if isinstance(source, np.ndarray):
         flat = source.reshape(-1)
@@ -699,14 +719,10 @@ def transfer(source, destination):
             return destination
         # [Object CUDnnTensor] (:582-594)
         if destination.is_contiguous():
-            data = _encode(_take(source, destination.nc, np.float64 if destination.desc.dtype_code in (0, 1, 2, 9) else np.int64),
-                           destination.desc.dtype_code)
-            return fact.upload(data, destination)
+            return fact.upload(_host_values(source, destination.nc, destination.desc.dtype_code), destination)
         conn = fact.create_tensor(core.tensor_descriptor(destination.shape, destination.desc.dtype_code,
                                                          default_strides(destination.shape)), 0, False)
-        data = _encode(_take(source, destination.nc, np.float64 if destination.desc.dtype_code in (0, 1, 2, 9) else np.int64),
-                       destination.desc.dtype_code)
-        fact.upload(data, conn)
+        fact.upload(_host_values(source, destination.nc, destination.desc.dtype_code), conn)
         fact.copy(conn, destination)
         return destination
 
@@ -723,6 +739,10 @@ def transfer(source, destination):
             destination.storage[...] = fact.download(source).storage
             return destination
         # [CUDnnTensor Object] (:596-608): a numpy array or list to fill
+        if (isinstance(destination, np.ndarray) and source.is_contiguous()
+                and destination.dtype == NUMPY_TYPE[source.desc.dtype_code] and source.desc.dtype_code != 9
+                and destination.flags["C_CONTIGUOUS"] and destination.size >= source.nc):
+            return fact.download_into(source, destination)  # straight into the caller's buffer
         if source.is_contiguous():
             host = fact.download(source)
         else:

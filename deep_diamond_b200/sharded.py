@@ -1,0 +1,108 @@
+"""Batch-dim sharding over the GPUs of one box: one process per GPU, each holding its own slice of
+every tensor.  The reference has nothing like it (one CUDA context, one stream,
+deep-diamond-cuda/src/clojure/uncomplicate/diamond/internal/cudnn/factory.clj:481-494); its closest
+primitives are the batch sub-tensors of ``view-tz`` / ``offset!`` (cudnn/tensor.clj:478-497), whose
+arithmetic `shard_range` repeats.
+
+Reorder, eltwise and broadcast op-tensor need no communication: every rank just runs the
+single-GPU call on its slice.  Only a reduction that spans the sharded dim exchanges data: the
+local partial result (a few KB) is all-reduced over NCCL on the compute stream, then finished.
+"""
+import ctypes
+
+import numpy as np
+
+from . import core
+from ._lib import DiamondError, check, lib
+
+UNIQUE_ID_BYTES = 128
+
+
+def shard_range(n, world_size, rank):
+    """[lo, hi) of the batch entries rank `rank` owns: equal slices, n divisible by world_size."""
+    if n % world_size:
+        raise DiamondError("The batch dim must divide evenly over the ranks.",
+                           {"batch": n, "world-size": world_size})
+    per = n // world_size
+    return rank * per, (rank + 1) * per
+
+
+def shard_shape(shape, world_size, batch_index=0):
+    s = list(shape)
+    lo, hi = shard_range(s[batch_index], world_size, 0)
+    s[batch_index] = hi - lo
+    return s
+
+
+def spans_sharded_dim(x_shape, y_shape, batch_index=0):
+    """True when the reduction y <- x folds the sharded (batch) dim."""
+    return y_shape[batch_index] == 1 and x_shape[batch_index] != 1
+
+
+def get_unique_id():
+    buf = (ctypes.c_ubyte * UNIQUE_ID_BYTES)()
+    check(lib.ddShardedGetUniqueId(buf), None, "ddShardedGetUniqueId")
+    return bytes(buf)
+
+
+class ShardedHandle:
+    """The library's communicator for one rank (wraps ddShardedCreate)."""
+
+    def __init__(self, fact, world_size, rank, unique_id):
+        self.fact, self.world_size, self.rank = fact, world_size, rank
+        h = ctypes.c_void_p()
+        idbuf = (ctypes.c_ubyte * UNIQUE_ID_BYTES).from_buffer_copy(unique_id)
+        check(lib.ddShardedCreate(ctypes.byref(h), fact.handle.ptr, world_size, rank, idbuf),
+              fact.handle.ptr, "ddShardedCreate")
+        self.ptr = h
+
+    def reduce_tensor(self, rtd, alpha, desc_x, x, beta, desc_y, y, spans=None):
+        dx, dy = core.desc(desc_x), core.desc(desc_y)
+        if spans is None:
+            spans = spans_sharded_dim(dx.dims, dy.dims)
+        a, b = core._scalar(alpha, dx.dtype_code), core._scalar(beta, dy.dtype_code)
+        check(lib.ddShardedReduceTensor(self.ptr, rtd.ptr, 1 if spans else 0, ctypes.byref(a), dx.ptr,
+                                        core._ptr(x), ctypes.byref(b), dy.ptr, core._ptr(y)),
+              self.fact.handle.ptr, "ddShardedReduceTensor")
+        return y
+
+    def check(self):
+        check(lib.ddShardedCheck(self.ptr), self.fact.handle.ptr, "ddShardedCheck")
+        return True
+
+    def release(self):
+        if self.ptr is not None:
+            lib.ddShardedDestroy(self.ptr)
+            self.ptr = None
+        return True
+
+
+def create_from_torch_distributed(fact):
+    """Builds the library communicator for this rank from an initialised torch.distributed group:
+    rank 0 makes the id, the group broadcasts it (any transport: gloo or nccl)."""
+    import torch
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(), dist.get_rank()
+    payload = [get_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(payload, src=0)
+    with torch.cuda.device(fact.device):
+        return ShardedHandle(fact, world, rank, payload[0])
+
+
+def combine_partials_host(op, partials, local_count, world_size):
+    """What the all-reduce + finish step computes, on host arrays (used by the CPU tests of the
+    multi-rank logic): `partials` is one array per rank of pre-finish accumulators."""
+    stack = np.stack([np.asarray(p, dtype=np.float64) for p in partials])
+    if op in ("add", "avg", "norm1", "norm2"):
+        acc = stack.sum(axis=0)
+    elif op in ("mul", "mul-no-zeros"):
+        acc = stack.prod(axis=0)
+    elif op == "min":
+        acc = stack.min(axis=0)
+    else:
+        acc = stack.max(axis=0)
+    if op == "avg":
+        acc = acc / (local_count * world_size)
+    if op == "norm2":
+        acc = np.sqrt(acc)
+    return acc

@@ -366,13 +366,24 @@ static double blend_d(double alpha, double v, double beta, const void *y, int t,
   return v;
 }
 
+/* 1 if `st` is the row-major (dense, default) stride vector of `dims` */
+static int is_default(int nd, const int64_t *dims, const int64_t *st) {
+  int64_t run = 1;
+  for (int d = nd - 1; d >= 0; d--) {
+    if (dims[d] != 1 && st[d] != run) return 0;
+    run *= dims[d];
+  }
+  return 1;
+}
+
 int oracle_eltwise_fwd(int alg, double coef, double shift, int nanprop, int t, int nd,
                        const int64_t *dims, const int64_t *xst, const void *x, const int64_t *yst,
                        void *y, double alpha, double beta) {
   const int64_t n = total_of(nd, dims);
+  const int dense = is_default(nd, dims, xst) && is_default(nd, dims, yst);
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; i++) {
-    int64_t xo = offset_of(nd, dims, xst, i), yo = offset_of(nd, dims, yst, i);
+    int64_t xo = dense ? i : offset_of(nd, dims, xst, i), yo = dense ? i : offset_of(nd, dims, yst, i);
     if (t == T_F64) {
       double v = act_fwd_d(alg, ((const double *)x)[xo], coef, shift, nanprop);
       ((double *)y)[yo] = blend_d(alpha, v, beta, y, t, yo);
@@ -388,10 +399,11 @@ int oracle_eltwise_bwd(int alg, double coef, int t, int nd, const int64_t *dims,
                        const void *x, const int64_t *dyst, const void *dy, const int64_t *dxst,
                        void *dx, double alpha, double beta) {
   const int64_t n = total_of(nd, dims);
+  const int dense = is_default(nd, dims, xst) && is_default(nd, dims, dyst) && is_default(nd, dims, dxst);
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; i++) {
-    int64_t xo = offset_of(nd, dims, xst, i), go = offset_of(nd, dims, dyst, i),
-            oo = offset_of(nd, dims, dxst, i);
+    int64_t xo = dense ? i : offset_of(nd, dims, xst, i), go = dense ? i : offset_of(nd, dims, dyst, i),
+            oo = dense ? i : offset_of(nd, dims, dxst, i);
     if (t == T_F64) {
       double v = act_bwd_d(alg, ((const double *)x)[xo], ((const double *)dy)[go], coef);
       ((double *)dx)[oo] = blend_d(alpha, v, beta, dx, t, oo);
