@@ -1,7 +1,8 @@
 """Builds libdd_b200.so (the C-ABI library of hand-written sm_100a kernels) in-tree with nvcc.
 
-Usage: python -m deep_diamond_b200.build [--force]
-The library has no Python or torch dependency; it links the CUDA runtime statically.
+Usage: python deep_diamond_b200/build.py [--force]
+(run as a script: importing the package itself needs the built library).  The library has no
+Python or torch dependency; it links the CUDA runtime statically.
 """
 import concurrent.futures
 import os
