@@ -2,7 +2,7 @@
 (deep-diamond-cuda/src/clojure/uncomplicate/diamond/internal/cudnn/impl.clj: one function per C
 call plus ``with-check``, impl.clj:30-41).
 
-The library must have been built (``python -m deep_diamond_b200.build``); importing this module
+The library must have been built (``python deep_diamond_b200/build.py``); importing this module
 without it raises: there is no fallback path.
 """
 import ctypes
@@ -29,7 +29,7 @@ STATUS = {
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        "libdd_b200.so is missing at %s: build it with `python -m deep_diamond_b200.build` "
+        "libdd_b200.so is missing at %s: build it with `python deep_diamond_b200/build.py` "
         "(there is no CPU or library fallback for these ops)" % LIB_PATH)
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -80,6 +80,7 @@ _SIGS = {
     "ddGetReductionIndicesSize": [_vp, _vp, _vp, _vp, ctypes.POINTER(_sz)],
     "ddGetReductionWorkspaceSize": [_vp, _vp, _vp, _vp, ctypes.POINTER(_sz)],
     "ddReduceTensor": [_vp, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ddReduceTensorNoAlloc": [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_char_p, _sz],
     "ddShardedGetUniqueId": [_vp],
     "ddShardedCreate": [ctypes.POINTER(_vp), _vp, _int, _int, _vp],
     "ddShardedDestroy": [_vp],

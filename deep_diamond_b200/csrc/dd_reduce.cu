@@ -233,3 +233,112 @@ ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, 
   }
   DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
 }
+
+// ------------------------------------------------------------------ no-allocation entry ------
+//
+// ddReduceTensorNoAlloc: the same planning and the same kernels as ddReduceTensor, for callers
+// that must not allocate device memory (no handle, hence no ddCreate and no cudaMalloc).  The
+// partial-result workspace is this file-scope device array.  Its name is only a host-side
+// stand-in here: the device address is looked up with cudaGetSymbolAddress once per device (with
+// that device current) and handed to the kernels like any caller-owned workspace.
+
+#include <mutex>
+
+static __device__ __align__(256) unsigned char dd_static_scratch[DD_NOALLOC_SCRATCH_BYTES];
+
+#define DD_NOALLOC_MAX_DEVICES 64
+static std::mutex g_noalloc_mu;
+static void *g_noalloc_ptr[DD_NOALLOC_MAX_DEVICES];
+static int g_noalloc_sms[DD_NOALLOC_MAX_DEVICES];
+
+static void noalloc_msg(char *buf, size_t len, const char *text) {
+  if (buf && len) snprintf(buf, len, "%s", text);
+}
+
+extern "C" ddStatus_t ddReduceTensorNoAlloc(void *stream, ddReduceTensorOp_t op, ddNanPropagation_t nanOpt,
+                                            const void *alpha, ddTensorDescriptor_t xd, const void *x,
+                                            const void *beta, ddTensorDescriptor_t yd, void *y,
+                                            char *errbuf, size_t errbufLen) {
+  noalloc_msg(errbuf, errbufLen, "");
+  if (!alpha || !beta || !x || !y || !xd || !yd || !xd->set || !yd->set) {
+    noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: null pointer or unset descriptor");
+    return DD_STATUS_BAD_PARAM;
+  }
+  if ((int)op < 0 || (int)op > DD_REDUCE_TENSOR_MUL_NO_ZEROS) {
+    noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: unknown reduce op");
+    return DD_STATUS_BAD_PARAM;
+  }
+  if (xd->nd != yd->nd) {
+    noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: x and y ranks differ");
+    return DD_STATUS_BAD_PARAM;
+  }
+  for (int i = 0; i < xd->nd; i++)
+    if (yd->dims[i] != xd->dims[i] && yd->dims[i] != 1) {
+      noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: each y dim must equal x's or be 1");
+      return DD_STATUS_BAD_PARAM;
+    }
+  if (!dd_type_is_float(xd->dtype) || !dd_type_is_float(yd->dtype)) {
+    noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: data types must be floating point");
+    return DD_STATUS_NOT_SUPPORTED;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= DD_NOALLOC_MAX_DEVICES) {
+    noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: no usable current CUDA device");
+    return DD_STATUS_NOT_INITIALIZED;
+  }
+  void *scratch = nullptr;
+  int sms = 0;
+  {
+    // per-device set-up on the first call made with that device current
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      void *ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, dd_static_scratch);
+      if (e != cudaSuccess || !ptr) {
+        cudaGetLastError();
+        if (errbuf && errbufLen)
+          snprintf(errbuf, errbufLen, "ddReduceTensorNoAlloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        return DD_STATUS_NOT_INITIALIZED;
+      }
+      int n = 0;
+      e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: cannot query the device");
+        return DD_STATUS_NOT_INITIALIZED;
+      }
+      g_noalloc_sms[dev] = n;
+      g_noalloc_ptr[dev] = ptr;
+    }
+    scratch = g_noalloc_ptr[dev];
+    sms = g_noalloc_sms[dev];
+  }
+  // a handle-shaped context on the stack: nothing in it is allocated
+  ddContext ctx;
+  memset(&ctx, 0, sizeof(ctx));
+  ctx.device = dev;
+  ctx.smCount = sms;
+  ctx.stream = (cudaStream_t)stream;
+  ctx.scratch = scratch;
+  ctx.scratchBytes = DD_NOALLOC_SCRATCH_BYTES;
+  ctx.lastKernel = "";
+  ddReduceTensorStruct red;
+  red.op = op;
+  red.comp = xd->dtype == DD_DATA_DOUBLE ? DD_DATA_DOUBLE : DD_DATA_FLOAT;
+  red.nan = nanOpt;
+  ddRedPlan pl;
+  ddStatus_t st = dd_reduce_plan(&ctx, &red, xd, x, yd, &pl);
+  if (st == DD_STATUS_SUCCESS && pl.wsBytes > DD_NOALLOC_SCRATCH_BYTES) {
+    if (errbuf && errbufLen)
+      snprintf(errbuf, errbufLen,
+               "ddReduceTensorNoAlloc: this reduction needs %zu bytes of scratch, the built-in array holds %u; "
+               "use ddReduceTensor with a caller-owned workspace",
+               pl.wsBytes, (unsigned)DD_NOALLOC_SCRATCH_BYTES);
+    return DD_STATUS_NOT_SUPPORTED;
+  }
+  if (st == DD_STATUS_SUCCESS)
+    st = dd_reduce_impl(&ctx, &red, scratch, DD_NOALLOC_SCRATCH_BYTES, dd_read_scalar(alpha, xd->dtype), xd, x,
+                        dd_read_scalar(beta, yd->dtype), yd, y, false, nullptr);
+  if (st != DD_STATUS_SUCCESS) noalloc_msg(errbuf, errbufLen, ctx.msg);
+  return st;
+}

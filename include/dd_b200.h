@@ -281,6 +281,33 @@ DD_API ddStatus_t ddReduceTensor(ddHandle_t handle, ddReduceTensorDescriptor_t r
                           const void *alpha, ddTensorDescriptor_t xDesc, const void *x,
                           const void *beta, ddTensorDescriptor_t yDesc, void *y);
 
+/* ---------------------------------------------------------------- no-allocation reduce ------- */
+
+/* No counterpart in the reference.  ddReduceTensor for callers that cannot allocate device memory:
+ * code running where cudaMalloc is off limits (inside a real-time or latency-critical loop, under a
+ * memory pool that owns the whole device, in a plugin whose host forbids allocations after start-up).
+ * Such callers cannot make a handle either (ddCreate allocates the handle's scratch), so this entry
+ * point takes the stream directly and no handle.  It calls no cudaMalloc, cudaFree or allocating
+ * library routine; the caller passes inputs and outputs as usual.
+ *
+ * The partial results of split reductions live in an array built into the library,
+ * DD_NOALLOC_SCRATCH_BYTES per GPU, which every GPU that loads the library holds until the process
+ * exits.  A reduction whose plan needs more is refused with DD_STATUS_NOT_SUPPORTED and the reason in
+ * `errbuf` (use ddReduceTensor with your own workspace then).  Nothing in the array has to start at
+ * zero: every slot that is read was written earlier in the same call.  But all calls share the one
+ * array, so two calls whose kernels overlap on the GPU (different streams, no ordering) race on it:
+ * keep these calls on one stream or order them with events.
+ *
+ * The first call made with a given device current looks up the array's device address and the SM
+ * count of that device; make that first call outside any stream capture.
+ * Results are identical to ddReduceTensor's (same plan, same kernels).
+ * `errbuf` (may be NULL) receives a NUL-terminated reason when the status is not success. */
+#define DD_NOALLOC_SCRATCH_BYTES (512u << 10)
+DD_API ddStatus_t ddReduceTensorNoAlloc(void *stream, ddReduceTensorOp_t op, ddNanPropagation_t nanOpt,
+                                        const void *alpha, ddTensorDescriptor_t xDesc, const void *x,
+                                        const void *beta, ddTensorDescriptor_t yDesc, void *y,
+                                        char *errbuf, size_t errbufLen);
+
 /* ---------------------------------------------------------------- multi-GPU ----------------- */
 
 /* No counterpart in the reference (it has no multi-device code).  One process per GPU; a tensor is
