@@ -186,6 +186,8 @@ def run_reference(args):
 # ------------------------------------------------------------------ GPU helpers ----------------
 
 def event_ms(torch, fn, stream, reps, warm):
+    """Per-launch device time with one CUDA-event pair per launch (used where a launch cannot be
+    captured in a graph, i.e. the NCCL path).  Includes any host launch gap."""
     for _ in range(warm):
         fn()
     stream.synchronize()
@@ -201,6 +203,41 @@ def event_ms(torch, fn, stream, reps, warm):
     return t[len(t) // 2], t[max(0, len(t) // 10)], t[min(len(t) - 1, (9 * len(t)) // 10)]
 
 
+def graph_ms(torch, fact, fn, per_graph, replays, warm=3):
+    """Per-launch device time of `fn` (one library call = one kernel) with the host taken out of the
+    loop: `per_graph` calls are captured into a CUDA graph on a side stream, the graph is replayed
+    `replays` times with an event pair around each replay, and the median replay time is divided by
+    the launches it holds.  A Python + ctypes call costs 10-20 us of host time, more than the
+    smaller kernels run, so timing un-captured launches would measure the host."""
+    h = fact.handle
+    side = torch.cuda.Stream(device=fact.device)
+    side.wait_stream(fact.stream)
+    h.set_stream(side)
+    try:
+        with torch.cuda.stream(side):
+            for _ in range(warm):
+                fn()
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(per_graph):
+                    fn()
+            g.replay()
+            side.synchronize()
+            evs = []
+            for _ in range(replays):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(side)
+                g.replay()
+                b.record(side)
+                evs.append((a, b))
+            side.synchronize()
+    finally:
+        h.set_stream(fact.stream)
+    t = sorted(a.elapsed_time(b) / per_graph for a, b in evs)
+    return t[len(t) // 2], t[max(0, len(t) // 10)], t[min(len(t) - 1, (9 * len(t)) // 10)]
+
+
 def op_row(name, cfg, nbytes, ms, peak, elems):
     med, p10, p90 = ms
     gbs = nbytes / (med * 1e-3) / 1e9
@@ -211,8 +248,9 @@ def op_row(name, cfg, nbytes, ms, peak, elems):
 
 
 def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
-    """Every other configuration's ops, each timed alone with CUDA events (median of the launches).
-    Small tensors rotate through enough distinct buffers to exceed L2, so every launch is cold."""
+    """Every other configuration's ops, each timed alone: launches captured in a CUDA graph and
+    replayed between CUDA events (see graph_ms).  Small tensors rotate through enough distinct
+    buffers to exceed L2, so every launch is cold."""
     rows = []
     h, dev, stream = fact.handle, fact.device, fact.stream
     L2 = 126 << 20
@@ -239,12 +277,12 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
         it[0] += 1
         core.transform_tensor(h, 1.0, xd, xs[i], 0.0, yd, ys[i])
     rows.append(op_row("reorder f32 nchw->nhwc", "C1 [32,64,56,56], cold L2 (rotating %d buffer pairs)" % sets,
-                       n * 8, event_ms(torch, c1, stream, 200, 20), peak, n))
+                       n * 8, graph_ms(torch, fact, c1, 4 * sets, 20), peak, n))
 
     def c1w():
         core.transform_tensor(h, 1.0, xd, xs[0], 0.0, yd, ys[0])
     rows.append(op_row("reorder f32 nchw->nhwc (warm L2)", "C1 [32,64,56,56], same buffers every launch",
-                       n * 8, event_ms(torch, c1w, stream, 200, 20), peak, n))
+                       n * 8, graph_ms(torch, fact, c1w, 24, 20), peak, n))
     del xs, ys
 
     # C3: broadcast op-tensor on [128,512,14,14]
@@ -269,9 +307,9 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
         it[0] += 1
         core.op_tensor(h, "mul", 1.0, xd, xs[i], 1.0, bd, scale, 0.0, xd, outs[i])
     rows.append(op_row("op-tensor a*x + b*bias[c]", "C3 [128,512,14,14], a=1 b=0.5, cold L2", n * 8 + 2048,
-                       event_ms(torch, c3add, stream, 200, 20), peak, n))
+                       graph_ms(torch, fact, c3add, 4 * sets, 20), peak, n))
     rows.append(op_row("op-tensor x * scale[c]", "C3 [128,512,14,14], cold L2", n * 8 + 2048,
-                       event_ms(torch, c3mul, stream, 200, 20), peak, n))
+                       graph_ms(torch, fact, c3mul, 4 * sets, 20), peak, n))
     del xs, outs
 
     # C4: reductions on [64,1024,32,32] (268 MB: larger than L2).  With world > 1 each rank holds
@@ -292,8 +330,9 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
         else:
             fn = lambda rtd=rtd, yd=yd, y=y: core.reduce_tensor(h, rtd, 1.0, xd, x, 0.0, yd, y)  # noqa: E731
             tag = "C4 [%d,1024,32,32]" % shp[0]
-        rows.append(op_row("reduce " + label, tag, n * 4 + int(np.prod(yshape)) * 4,
-                           event_ms(torch, fn, stream, 100, 10), peak, n))
+        ms = event_ms(torch, fn, stream, 100, 10) if (sharded is not None and yshape[0] == 1) else \
+            graph_ms(torch, fact, fn, 10, 20)
+        rows.append(op_row("reduce " + label, tag, n * 4 + int(np.prod(yshape)) * 4, ms, peak, n))
     del x
 
     # C5: [2048/world,256,28,28] f32 nchw -> bf16 nhwc, then s8 nchw -> s8 nhwc
@@ -311,9 +350,9 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
     q = torch.clamp(torch.round(x * 127.0), -128, 127).to(torch.int8)
     z = dbuf(n)
     rows.append(op_row("reorder+convert f32 nchw -> bf16 nhwc", "C5 [%d,256,28,28]" % shp[0], n * 6,
-                       event_ms(torch, lambda: core.transform_tensor(h, 1.0, xd, x, 0.0, yd, y), stream, 30, 5), peak, n))
+                       graph_ms(torch, fact, lambda: core.transform_tensor(h, 1.0, xd, x, 0.0, yd, y), 5, 10), peak, n))
     rows.append(op_row("reorder s8 nchw -> nhwc", "C5 [%d,256,28,28]" % shp[0], n * 2,
-                       event_ms(torch, lambda: core.transform_tensor(h, 1.0, qd, q, 0.0, zd, z), stream, 30, 5), peak, n))
+                       graph_ms(torch, fact, lambda: core.transform_tensor(h, 1.0, qd, q, 0.0, zd, z), 5, 10), peak, n))
     return rows
 
 

@@ -112,6 +112,14 @@ ddStatus_t ddCreate(ddHandle_t *handle) {
     delete h;
     return DD_STATUS_ALLOC_FAILED;
   }
+  // the first 64 KB are arrival counters of split reductions: zero now, kept zero by the kernels
+  h->counterSlots = (64 << 10) / sizeof(unsigned);
+  if (cudaMemset(h->scratch, 0, h->counterSlots * sizeof(unsigned)) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(h->scratch);
+    delete h;
+    return DD_STATUS_ALLOC_FAILED;
+  }
   *handle = h;
   return DD_STATUS_SUCCESS;
 }

@@ -34,13 +34,13 @@ template <> struct dd_math<float> {
   static __device__ __forceinline__ float sigmoid(float x) { return dd_sigmoid_f32(x); }
   // s*(1-s) = e/(1+e)^2 with e = exp(-|x|)
   static __device__ __forceinline__ float dsigmoid(float x) {
-    float d = dd_e_over_one_plus_e_sq(fmaxf(-fabsf(x), -104.0f), 0);
+    float d = dd_e_over_one_plus_e_sq<0>(fmaxf(-fabsf(x), -104.0f));
     return x != x ? x : d;
   }
   static __device__ __forceinline__ float tanh_(float x) { return dd_tanh_f32(x); }
   // 1 - tanh^2 = 4e/(1+e)^2 with e = exp(-2|x|)
   static __device__ __forceinline__ float dtanh(float x) {
-    float d = dd_e_over_one_plus_e_sq(fmaxf(-2.0f * fabsf(x), -104.0f), 2);
+    float d = dd_e_over_one_plus_e_sq<2>(fmaxf(-2.0f * fabsf(x), -104.0f));
     return x != x ? x : d;
   }
   static __device__ __forceinline__ float exp_neg(float x) { return dd_exp_neg_rounded(x); }

@@ -39,6 +39,7 @@ struct ddContext {
   cudaStream_t stream;
   void *scratch;        // DD_HANDLE_SCRATCH_BYTES of device memory, allocated once in ddCreate
   size_t scratchBytes;
+  int64_t counterSlots;  // leading unsigned counters of `scratch` kept zero between launches (0: none)
   uint64_t launches;
   const char *lastKernel;
   char msg[256];
@@ -112,6 +113,36 @@ static inline int64_t dd_canon_span(const ddCanon *c, int op) {
 ddStatus_t dd_check_desc(ddHandle_t h, const ddTensorStruct *d, const char *what);
 bool dd_same_dims(const ddTensorStruct *a, const ddTensorStruct *b);
 
+// Division of a 31-bit unsigned value by a fixed divisor as multiply-high + shift (round-up method
+// of Granlund & Montgomery): q = (umulhi(x, m) + x) >> s with s = ceil(log2 d) and
+// m = ceil(2^(32+s) / d) - 2^32.  Exact for 0 <= x < 2^31, 1 <= d < 2^31.
+struct ddFastDiv {
+  uint32_t d, m, s;
+};
+
+static inline ddFastDiv dd_fastdiv(uint32_t d) {
+  ddFastDiv f;
+  f.d = d;
+  uint32_t s = 0;
+  while (s < 32 && ((uint64_t)1 << s) < d) s++;
+  f.s = s;
+  unsigned __int128 one = 1;
+  unsigned __int128 num = one << (32 + s);
+  uint64_t m = (uint64_t)((num + d - 1) / d);
+  f.m = (uint32_t)(m - ((uint64_t)1 << 32));
+  return f;
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ uint32_t dd_div(uint32_t x, const ddFastDiv &f) {
+  return (__umulhi(x, f.m) + x) >> f.s;
+}
+__device__ __forceinline__ void dd_divmod(uint32_t x, const ddFastDiv &f, uint32_t &q, uint32_t &r) {
+  q = dd_div(x, f);
+  r = x - q * f.d;
+}
+#endif
+
 // Kernel-side form of ddCanon for the generic strided kernels.
 template <int NOPS>
 struct ddStridedParams {
@@ -119,6 +150,7 @@ struct ddStridedParams {
   int64_t total;
   int64_t dims[DD_DIM_MAX];
   int64_t st[NOPS][DD_DIM_MAX];
+  ddFastDiv fd[DD_DIM_MAX];  // valid when total < 2^31 (the 32-bit index path)
 };
 
 template <int NOPS>
@@ -129,6 +161,7 @@ static inline ddStridedParams<NOPS> dd_strided_params(const ddCanon &c) {
   p.total = c.total;
   for (int i = 0; i < c.nd; i++) {
     p.dims[i] = c.dims[i];
+    if (c.total < 0x7fffffffLL) p.fd[i] = dd_fastdiv((uint32_t)c.dims[i]);
     for (int o = 0; o < NOPS; o++) p.st[o][i] = c.st[o][i];
   }
   return p;
@@ -239,8 +272,28 @@ template <typename C>
 __device__ __forceinline__ C dd_scale(C alpha, C v) { return alpha == (C)1 ? v : dd_mul_rn(alpha, v); }
 
 // Decomposes a linear index over the canonical dims into per-operand element offsets.
+// 32-bit indices (total < 2^31) divide by multiply-shift; 64-bit indices by plain division.
+template <int NOPS>
+__device__ __forceinline__ void dd_offsets32(const ddStridedParams<NOPS> &p, uint32_t idx, int64_t (&off)[NOPS]) {
+#pragma unroll
+  for (int o = 0; o < NOPS; o++) off[o] = 0;
+  for (int d = p.nd - 1; d > 0; d--) {
+    uint32_t q, r;
+    dd_divmod(idx, p.fd[d], q, r);
+#pragma unroll
+    for (int o = 0; o < NOPS; o++) off[o] += (int64_t)r * p.st[o][d];
+    idx = q;
+  }
+#pragma unroll
+  for (int o = 0; o < NOPS; o++) off[o] += (int64_t)idx * p.st[o][0];
+}
+
 template <int NOPS, typename I>
 __device__ __forceinline__ void dd_offsets(const ddStridedParams<NOPS> &p, I idx, int64_t (&off)[NOPS]) {
+  if (sizeof(I) == 4 || p.total < 0x7fffffffLL) {
+    dd_offsets32<NOPS>(p, (uint32_t)idx, off);
+    return;
+  }
 #pragma unroll
   for (int o = 0; o < NOPS; o++) off[o] = 0;
   for (int d = p.nd - 1; d > 0; d--) {

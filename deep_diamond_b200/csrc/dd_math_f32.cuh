@@ -10,7 +10,6 @@
 //                  exp(r) - 1 = r + r^2*g(r), g a degree-5 polynomial fitted by least squares on
 //                  Chebyshev nodes over |r| <= 1.02*ln2/2 (max error 1.6e-9 in g, 2e-10 in exp);
 //                  result = (1 + t) * 2^n with the rounding error of 1 + t kept as the low word.
-// tanh(x), |x| < 0.3:  x + x^3*q(x^2), q a degree-3 least-squares fit (error 4e-10 relative).
 #pragma once
 #include <cuda_runtime.h>
 
@@ -24,17 +23,13 @@ __device__ __forceinline__ float dd_rcp_approx(float x) {
   return r;
 }
 
-// v * 2^n for n in [-152, 2], in two normal factors so that a denormal result rounds once.
-__device__ __forceinline__ float dd_scale2(float v, int n) {
-  const int n1 = n >> 1, n2 = n - n1;
-  const float s1 = __int_as_float((n1 + 127) << 23), s2 = __int_as_float((n2 + 127) << 23);
-  return __fmul_rn(__fmul_rn(v, s1), s2);
-}
-
 // exp(x) = (p + pl) * 2^n for x in [-104, 0] (callers clamp): p in [0.7, 1.43] is the rounded
 // mantissa part, pl its rounding error, n in [-150, 0].
 __device__ __forceinline__ void dd_exp_neg_raw(float x, float &p, float &pl, int &n) {
-  const float fn = rintf(__fmul_rn(x, DD_LOG2E));
+  // n = rint(x * log2 e) by the add-a-big-constant trick: both the rounded float and the integer
+  // come out of one FMA (no round / float-to-int conversions, which run on the quarter-rate unit)
+  const float big = fmaf(x, DD_LOG2E, 12582912.0f);  // 1.5 * 2^23: the sum's low mantissa bits are n
+  const float fn = __fsub_rn(big, 12582912.0f);
   float r = fmaf(fn, -DD_LN2_HI, x);
   r = fmaf(fn, -DD_LN2_LO, r);
   float g = 0.00019901622727047652f;
@@ -46,16 +41,26 @@ __device__ __forceinline__ void dd_exp_neg_raw(float x, float &p, float &pl, int
   const float t = fmaf(__fmul_rn(r, r), g, r);  // exp(r) - 1, |t| <= 0.43
   p = __fadd_rn(1.0f, t);
   pl = __fsub_rn(t, __fsub_rn(p, 1.0f));        // exact: 1 + t = p + pl
-  n = (int)fn;
+  n = __float_as_int(big) - 0x4B400000;
 }
 
-// exp(x) = hi + lo: hi carries the rounded value, lo its error.
-__device__ __forceinline__ void dd_exp_neg(float x, float &hi, float &lo) {
+// 2^n as a float, n in [-126, 127].
+__device__ __forceinline__ float dd_pow2(int n) { return __int_as_float((n + 127) << 23); }
+
+// exp(x) for x in [-104, 0] reaches 2^-150, below the normal range.  To stay branch-free the kernels
+// carry E = exp(x) * 2^64 (always a normal float, scaled exactly by one factor) wherever exp(x) is a
+// NUMERATOR and multiply the final quotient by 2^-64 (exact unless the result is denormal, where it
+// is the single rounding), and the plain e = E * 2^-64 only where it is added to 1.
+#define DD_EXP_BIAS 64
+#define DD_UNBIAS 5.421010862427522e-20f  // 2^-64
+
+__device__ __forceinline__ void dd_exp_neg_biased(float x, float &Eh, float &El) {
   float p, pl;
   int n;
   dd_exp_neg_raw(x, p, pl, n);
-  hi = dd_scale2(p, n);
-  lo = dd_scale2(pl, n);
+  const float sc = dd_pow2(n + DD_EXP_BIAS);
+  Eh = __fmul_rn(p, sc);
+  El = __fmul_rn(pl, sc);
 }
 
 // (nh + nl) / (dh + dl) with dh in [1, 2]: approximate quotient + one residual correction.
@@ -74,24 +79,23 @@ __device__ __forceinline__ void dd_one_plus(float eh, float el, float &dh, float
 }
 
 __device__ __forceinline__ float dd_sigmoid_f32(float x) {
-  const float xc = fmaxf(-fabsf(x), -104.0f);
-  float eh, el, dh, dl;
-  dd_exp_neg(xc, eh, el);
-  dd_one_plus(eh, el, dh, dl);
+  float Eh, El, dh, dl;
+  dd_exp_neg_biased(fmaxf(-fabsf(x), -104.0f), Eh, El);
+  dd_one_plus(__fmul_rn(Eh, DD_UNBIAS), __fmul_rn(El, DD_UNBIAS), dh, dl);
   const bool pos = x >= 0.0f;
-  const float s = dd_quot(pos ? 1.0f : eh, pos ? 0.0f : el, dh, dl);
+  float s = dd_quot(pos ? 1.0f : Eh, pos ? 0.0f : El, dh, dl);  // 1/(1+e) or (e/(1+e)) * 2^64
+  s = pos ? s : __fmul_rn(s, DD_UNBIAS);
   return x != x ? x : s;
 }
 
-// 2^k * e / (1 + e)^2 for e = exp(xneg), xneg in [-104, 0]: the derivative kernel of both logistic
-// (k = 0, e = exp(-|x|): s*(1-s)) and tanh (k = 2, e = exp(-2|x|): 1 - tanh^2).  The factor 2^k goes
-// into the numerator's exponent so that results near the denormal range still round once.
-__device__ __forceinline__ float dd_e_over_one_plus_e_sq(float xneg, int k) {
-  float p, pl, dh, dl;
-  int n;
-  dd_exp_neg_raw(xneg, p, pl, n);
-  dd_one_plus(dd_scale2(p, n), dd_scale2(pl, n), dh, dl);
-  const float nh = dd_scale2(p, n + k), nl = dd_scale2(pl, n + k);
+// 2^K * e / (1 + e)^2 for e = exp(xneg), xneg in [-104, 0]: the derivative kernel of both logistic
+// (K = 0, e = exp(-|x|): s*(1-s)) and tanh (K = 2, e = exp(-2|x|): 1 - tanh^2).
+template <int K>
+__device__ __forceinline__ float dd_e_over_one_plus_e_sq(float xneg) {
+  float Eh, El, dh, dl;
+  dd_exp_neg_biased(xneg, Eh, El);
+  dd_one_plus(__fmul_rn(Eh, DD_UNBIAS), __fmul_rn(El, DD_UNBIAS), dh, dl);
+  const float nh = Eh * (float)(1 << K), nl = El * (float)(1 << K);  // exact
   const float r0 = dd_rcp_approx(dh);
   const float rr = __fmul_rn(r0, r0);
   const float q = __fmul_rn(nh, rr);
@@ -102,33 +106,29 @@ __device__ __forceinline__ float dd_e_over_one_plus_e_sq(float xneg, int k) {
   res = fmaf(-wl, dh, res);
   res = fmaf(-2.0f * w, dl, res);
   res = __fadd_rn(res, nl);
-  return fmaf(res, rr, q);
+  return __fmul_rn(fmaf(res, rr, q), DD_UNBIAS);
 }
 
+// tanh(x) = (1 - e) / (1 + e), e = exp(-2|x|).  No separate small-|x| branch: 1 - e is formed from
+// the hi/lo pair, and for |x| < 0.17 (n == 0) that difference is exactly -(exp(r) - 1), which the
+// exp kernel computed without cancellation.  Here e only ever meets 1, so its scale factor is simply
+// clamped at 2^-126 (for |x| > 43.6, where tanh is 1 to the last bit anyway).
 __device__ __forceinline__ float dd_tanh_f32(float x) {
-  const float ax = fabsf(x);
-  float t;
-  if (ax < 0.3f) {
-    const float z = __fmul_rn(x, x);
-    float q = 0.0203524362295866f;
-    q = fmaf(q, z, -0.053884357213974f);
-    q = fmaf(q, z, 0.13333183526992798f);
-    q = fmaf(q, z, -0.3333333432674408f);
-    t = fmaf(__fmul_rn(x, z), q, x);
-  } else {
-    float eh, el, dh, dl;
-    dd_exp_neg(fmaxf(-2.0f * ax, -104.0f), eh, el);
-    dd_one_plus(eh, el, dh, dl);
-    const float nh = __fsub_rn(1.0f, eh);                                    // 1 - e as a pair
-    const float nl = __fsub_rn(__fsub_rn(__fsub_rn(1.0f, nh), eh), el);
-    t = copysignf(dd_quot(nh, nl, dh, dl), x);
-  }
+  float p, pl, dh, dl;
+  int n;
+  dd_exp_neg_raw(fmaxf(-2.0f * fabsf(x), -104.0f), p, pl, n);
+  const float sc = dd_pow2(max(n, -126));
+  const float eh = __fmul_rn(p, sc), el = __fmul_rn(pl, sc);
+  dd_one_plus(eh, el, dh, dl);
+  const float nh = __fsub_rn(1.0f, eh);                                    // 1 - e as a pair
+  const float nl = __fsub_rn(__fsub_rn(__fsub_rn(1.0f, nh), eh), el);
+  const float t = copysignf(dd_quot(nh, nl, dh, dl), x);
   return x != x ? x : t;
 }
 
 // exp(x) rounded once, for x <= 0 (elu backward)
 __device__ __forceinline__ float dd_exp_neg_rounded(float x) {
-  float eh, el;
-  dd_exp_neg(fmaxf(x, -104.0f), eh, el);
-  return x != x ? x : __fadd_rn(eh, el);
+  float Eh, El;
+  dd_exp_neg_biased(fmaxf(x, -104.0f), Eh, El);
+  return x != x ? x : __fmul_rn(__fadd_rn(Eh, El), DD_UNBIAS);
 }

@@ -35,8 +35,19 @@ struct ddOpFlatParams {
   int op;
   int readA;         // 0: alpha1 == 0, A is not read (its term is +0)
   int vec;
+  int fast;          // n < 2^31: channel index by multiply-shift division
+  ddFastDiv fdInner, fdChannels;
   double alpha1, alpha2, beta;
 };
+
+__device__ __forceinline__ int64_t dd_channel_of(const ddOpFlatParams &p, int64_t e) {
+  if (p.fast) {
+    uint32_t q = dd_div((uint32_t)e, p.fdInner), c, r;
+    dd_divmod(q, p.fdChannels, c, r);
+    return r;
+  }
+  return (e / p.inner) % p.channels;
+}
 
 template <typename T, typename C>
 __global__ void __launch_bounds__(256) dd_op_flat_kernel(ddOpFlatParams p) {
@@ -61,7 +72,7 @@ __global__ void __launch_bounds__(256) dd_op_flat_kernel(ddOpFlatParams p) {
       if (p.bmode == 0) {
         bin = *(const uint4 *)(B + e0);
       } else {  // inner % V == 0: the whole vector shares one channel
-        const int64_t ch = (e0 / p.inner) % p.channels;
+        const int64_t ch = dd_channel_of(p, e0);
         bs = dd_scale(a2, dd_load<C, T>(__ldg(B + ch * p.sB)));
       }
       uint4 res;
@@ -81,7 +92,7 @@ __global__ void __launch_bounds__(256) dd_op_flat_kernel(ddOpFlatParams p) {
   }
   for (int64_t i = done + tid; i < p.n; i += nthreads) {
     C a = readA ? dd_scale(a1, dd_load<C, T>(A[i])) : (C)0;
-    C b = p.bmode == 0 ? dd_load<C, T>(B[i]) : dd_load<C, T>(B[((i / p.inner) % p.channels) * p.sB]);
+    C b = p.bmode == 0 ? dd_load<C, T>(B[i]) : dd_load<C, T>(B[dd_channel_of(p, i) * p.sB]);
     C r = dd_binop<C>(op, a, dd_scale(a2, b));
     if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(Cp[i])));
     Cp[i] = dd_store<T, C>(r);
@@ -182,6 +193,11 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
     p.beta = beta;
     uintptr_t bits = (uintptr_t)A | (uintptr_t)Cp | (bmode == 0 ? (uintptr_t)B : 0);
     p.vec = (bits & 15) == 0 && (bmode == 0 || inner % V == 0);
+    p.fast = c.total < 0x7fffffffLL;
+    if (p.fast) {
+      p.fdInner = dd_fastdiv((uint32_t)inner);
+      p.fdChannels = dd_fastdiv((uint32_t)channels);
+    }
     unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
     dd_op_flat_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
     DD_LAUNCHED(h, bmode == 0 ? "optensor/flat" : "optensor/flat-bcast");

@@ -114,8 +114,12 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
     const int v = pl->vec ? V : 1;
     int tx = next_pow2((p.K2 + v - 1) / v);
     p.TX = tx > 32 ? 32 : tx;
+    // narrower tiles (down to 8 lanes = 128 contiguous bytes) while that is what it takes to fill
+    // the machine without splitting the reduced range
+    auto tiles = [&](int t) { return (p.K2 + (int64_t)t * v - 1) / ((int64_t)t * v); };
+    while (p.TX > 8 && p.K1 * tiles(p.TX) < desired) p.TX /= 2;
     const int TY = 256 / p.TX;
-    p.tilesK2 = (p.K2 + (int64_t)p.TX * v - 1) / ((int64_t)p.TX * v);
+    p.tilesK2 = tiles(p.TX);
     int64_t ctas0 = p.K1 * p.tilesK2;
     if (ctas0 < desired) {
       int64_t S = (desired + ctas0 - 1) / ctas0;
@@ -189,10 +193,16 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
   if (st != DD_STATUS_SUCCESS) return st;
   if (partialOnly && pl.kind == DD_RED_GENERIC)
     DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
+  unsigned *counters = nullptr;
   if (pl.wsBytes > 0) {
+    // arrival counters live in the first DD_COUNTER_BYTES of the handle's own scratch (zeroed at
+    // ddCreate, reset by the kernels); a context without them (counterSlots == 0) or a reduction with
+    // more counters than fit falls back to the separate finishing kernel
+    const int64_t nctr = pl.kind == DD_RED_ROW ? pl.nout : pl.p.K1 * pl.p.tilesK2;
+    if (h->counterSlots > 0 && nctr <= h->counterSlots) counters = (unsigned *)h->scratch;
     if (!ws) {
-      ws = h->scratch;
-      wsBytes = h->scratchBytes;
+      ws = (char *)h->scratch + h->counterSlots * sizeof(unsigned);
+      wsBytes = h->scratchBytes - h->counterSlots * sizeof(unsigned);
     }
     if (wsBytes < pl.wsBytes)
       DD_FAIL(h, DD_STATUS_BAD_PARAM, "reduce: workspace of %zu bytes needed, %zu given", pl.wsBytes, wsBytes);
@@ -201,6 +211,7 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
   pl.p.y = y;
   pl.p.part = ws;
   pl.p.partOut = partialOut;
+  pl.p.counters = counters;
   pl.p.alpha = alpha;
   pl.p.beta = beta;
   pl.p.partialOnly = partialOnly ? 1 : 0;

@@ -11,8 +11,10 @@
 //         Lanes run along k2 with 16-byte loads, warps stride over r1, shared-memory combine.
 //
 // When an output's reduce range is split over several CTAs (few outputs, long ranges) each split
-// writes one partial to the workspace and dd_reduce_finish_kernel combines them in a fixed order,
-// so results are run-to-run identical.  Anything that does not fit the 4-level form runs one
+// writes one partial to the workspace and bumps an arrival counter; the split that arrives last
+// combines all partials in index order and finishes (one launch, nobody waits, and the order of
+// the combine is fixed, so results are run-to-run identical).  Without counters (caller-owned
+// set-up that cannot guarantee zeroed memory) dd_reduce_finish_kernel does the combine instead.  Anything that does not fit the 4-level form runs one
 // thread per output (generic).  All are HBM-bound: algorithmic bytes = input bytes + output bytes.
 #pragma once
 #include "dd_internal.cuh"
@@ -68,6 +70,9 @@ struct ddRedParams {
   void *y;
   void *part;     // workspace: [out][split] accumulators of the compute type (used when S > 1)
   void *partOut;  // partialOnly: [out] raw accumulators (no post/alpha/beta) instead of y
+  unsigned *counters;  // S > 1: per-output (row) / per-tile (col) arrival counters, zero between launches;
+                       // the last split to arrive combines all partials and finishes.  NULL: a separate
+                       // finishing kernel does it.
   int64_t K1, R1, K2, R2;
   int64_t sxK1, sxR1, sxK2, sxR2;
   int64_t syK1, syK2;
@@ -191,12 +196,29 @@ __global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
   }
   acc = dd_group_reduce<C, OPC>(acc, G, nanProp, smem);
   if (live && lane == 0) {
-    if (p.S == 1) dd_red_finish<T, C>(p, k1, k2, acc);
-    else ((C *)p.part)[out * p.S + s] = acc;
+    if (p.S == 1) {
+      dd_red_finish<T, C>(p, k1, k2, acc);
+    } else {
+      C *part = (C *)p.part + out * p.S;
+      part[s] = acc;
+      if (p.counters) {
+        // last split to arrive folds all S partials in index order (same order as the finishing
+        // kernel, so the result does not depend on which split came last).  No waiting anywhere.
+        __threadfence();
+        if (atomicAdd(p.counters + out, 1u) == (unsigned)(p.S - 1)) {
+          __threadfence();
+          C a = __ldcg(part);
+          for (int i = 1; i < p.S; i++) a = dd_red<C, OPC>::comb(a, __ldcg(part + i), nanProp);
+          dd_red_finish<T, C>(p, k1, k2, a);
+          p.counters[out] = 0;
+        }
+      }
+    }
   }
 }
 
-// col: CTA = TX lanes along k2 (V elements each) x TY = 256/TX row groups striding over r1.
+// col: CTA = TX lanes along k2 (V elements each, TX a power of two <= 256) x TY = 256/TX row
+// groups striding over r1.
 template <typename T, typename C, int OPC, bool VEC>
 __global__ void __launch_bounds__(256) dd_reduce_col_kernel(ddRedParams p) {
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
@@ -255,14 +277,35 @@ __global__ void __launch_bounds__(256) dd_reduce_col_kernel(ddRedParams p) {
 #pragma unroll
   for (int k = 0; k < V; k++) smem[ty * (TX * V) + tx * V + k] = acc[k];
   __syncthreads();
-  const int col = threadIdx.x;
-  if (col < TX * V) {
+  for (int col = threadIdx.x; col < TX * V; col += 256) {
     C a = smem[col];
     for (int r = 1; r < TY; r++) a = dd_red<C, OPC>::comb(a, smem[r * (TX * V) + col], nanProp);
     const int64_t kk = tk * TX * V + col;
     if (kk < p.K2) {
       if (p.S == 1) dd_red_finish<T, C>(p, k1, kk, a);
       else ((C *)p.part)[(k1 * p.K2 + kk) * p.S + s] = a;
+    }
+  }
+  if (p.S > 1 && p.counters) {
+    // one counter per (k1, tile): the last split's CTA folds the partials of the whole tile
+    __shared__ int lastFlag;
+    __threadfence();
+    __syncthreads();
+    unsigned *ctr = p.counters + (k1 * p.tilesK2 + tk);
+    if (threadIdx.x == 0) lastFlag = atomicAdd(ctr, 1u) == (unsigned)(p.S - 1);
+    __syncthreads();
+    if (lastFlag) {
+      __threadfence();
+      for (int col = threadIdx.x; col < TX * V; col += 256) {
+        const int64_t kk = tk * TX * V + col;
+        if (kk < p.K2) {
+          const C *pp = (const C *)p.part + (k1 * p.K2 + kk) * p.S;
+          C a = __ldcg(pp);
+          for (int i = 1; i < p.S; i++) a = dd_red<C, OPC>::comb(a, __ldcg(pp + i), nanProp);
+          dd_red_finish<T, C>(p, k1, kk, a);
+        }
+      }
+      if (threadIdx.x == 0) *ctr = 0;
     }
   }
 }
@@ -378,7 +421,7 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       DD_LAUNCHED(h, "reduce/generic");                                                            \
       return DD_STATUS_SUCCESS;                                                                    \
     }                                                                                              \
-    if (pl.p.S > 1) {                                                                              \
+    if (pl.p.S > 1 && pl.p.counters == nullptr) {                                                  \
       unsigned fg = dd_flat_grid(h, pl.nout, 256, 8);                                              \
       dd_reduce_finish_kernel<T, C, OPC><<<fg, 256, 0, h->stream>>>(pl.p, pl.p.part);              \
       DD_LAUNCHED(h, pl.kind == DD_RED_ROW ? "reduce/row+finish" : "reduce/col+finish");           \

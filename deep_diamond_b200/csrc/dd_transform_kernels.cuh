@@ -124,6 +124,7 @@ struct ddTileParams {
   int nb;            // number of batch dims
   int64_t bdims[DD_TILE_BATCH_DIMS], bsx[DD_TILE_BATCH_DIMS], bsy[DD_TILE_BATCH_DIMS];
   int64_t tilesA, tilesB;
+  ddFastDiv fdA, fdB, fdBatch[DD_TILE_BATCH_DIMS];  // divisors tilesA, tilesB, bdims[] (tile count < 2^31)
   double alpha;
 };
 
@@ -146,22 +147,19 @@ __global__ void __launch_bounds__((dd_tile_geom<S, D>::NT)) dd_tile_kernel(ddTil
   __shared__ uint4 tile[TA * NB];
 
   // tile id -> (batch index, tile along B, tile along A); A varies fastest
-  int64_t id = blockIdx.x;
-  const int64_t ta = id % p.tilesA;
-  id /= p.tilesA;
-  const int64_t tb = id % p.tilesB;
-  id /= p.tilesB;
+  uint32_t id = blockIdx.x, ta, tb;
+  dd_divmod(id, p.fdA, id, ta);
+  dd_divmod(id, p.fdB, id, tb);
   int64_t offx = 0, offy = 0;
   for (int d = p.nb - 1; d >= 0; d--) {
-    int64_t q = id / p.bdims[d];
-    int64_t r = id - q * p.bdims[d];
-    offx += r * p.bsx[d];
-    offy += r * p.bsy[d];
-    id = q;
+    uint32_t r;
+    dd_divmod(id, p.fdBatch[d], id, r);
+    offx += (int64_t)r * p.bsx[d];
+    offy += (int64_t)r * p.bsy[d];
   }
   const S *xb = (const S *)p.x + offx;
   D *yb = (D *)p.y + offy;
-  const int64_t a0 = ta * TA, b0 = tb * TB;
+  const int64_t a0 = (int64_t)ta * TA, b0 = (int64_t)tb * TB;
   const C alpha = (C)p.alpha;
 
   const int t = threadIdx.x;
@@ -323,6 +321,12 @@ static bool dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
   }
   tp->tilesA = (tp->LA + G::TA - 1) / G::TA;
   tp->tilesB = (tp->LB + G::TB - 1) / G::TB;
+  int64_t tiles = tp->tilesA * tp->tilesB;
+  for (int i = 0; i < tp->nb; i++) tiles *= tp->bdims[i];
+  if (tiles >= 0x7fffffffLL) return false;
+  tp->fdA = dd_fastdiv((uint32_t)tp->tilesA);
+  tp->fdB = dd_fastdiv((uint32_t)tp->tilesB);
+  for (int i = 0; i < tp->nb; i++) tp->fdBatch[i] = dd_fastdiv((uint32_t)tp->bdims[i]);
   tp->alpha = pl.alpha;
   return true;
 }

@@ -208,7 +208,14 @@ def connector(in_, out):
 
 # ---------------------------------------------------------------- Neanderthal generics --------
 
-transfer = _f.transfer
+def transfer(source, destination):
+    """``transfer!``: see factory.transfer; vector views of device tensors stand for their tensor."""
+    src = source.tz if isinstance(source, VectorView) else source
+    if isinstance(destination, VectorView):
+        _f.transfer(src, destination.tz)
+        return destination
+    return _f.transfer(src, destination)
+
 
 
 def native(x):

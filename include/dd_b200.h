@@ -262,7 +262,7 @@ DD_API ddStatus_t ddActivationBackward(ddHandle_t handle, ddActivationDescriptor
  * DD_DATA_DOUBLE) in a fixed tree order: results are run-to-run identical.
  * y = alpha*reduce(x) + beta*y.  No indices are produced (indices size is always 0).
  * Workspace: pass the size ddGetReductionWorkspaceSize returns, or workspace == NULL to use the
- * handle's own scratch (then the size needed must not exceed DD_HANDLE_SCRATCH_BYTES). */
+ * handle's own scratch (then the size needed must not exceed DD_HANDLE_SCRATCH_BYTES - 64 KB). */
 #define DD_HANDLE_SCRATCH_BYTES (8u << 20)
 DD_API ddStatus_t ddCreateReduceTensorDescriptor(ddReduceTensorDescriptor_t *desc);
 DD_API ddStatus_t ddDestroyReduceTensorDescriptor(ddReduceTensorDescriptor_t desc);

@@ -1,0 +1,407 @@
+"""The reference's factory-parametric suites, transcribed function for function and run against the
+B200 factory through the public API.  This is how the reference accepts a backend: its cuDNN suite
+just calls these with its own factory (deep-diamond-cuda/test/.../cudnn_tensor_test.clj:70-94,
+directed_test.clj:16-53).
+
+Sources: deep-diamond-test/src/uncomplicate/diamond/tensor_test.clj (tt) and dnn_test.clj (dt).
+"""
+import itertools
+
+import numpy as np
+import pytest
+
+from deep_diamond_b200 import dnn
+from deep_diamond_b200 import tensor as T
+from deep_diamond_b200._lib import DiamondError
+from deep_diamond_b200.tensor import (asum, batcher, connector, desc, entry, entry_, input, native, offset_,
+                                      output, shuffler, tensor, transfer, transformer, view_tz, view_vctr)
+
+pytestmark = pytest.mark.gpu
+
+
+def seq(x):
+    return list(native(x))
+
+
+def test_tensor(fact):
+    """tt :22-27"""
+    tz = tensor(fact, [2, 3, 4, 5], "float", "nchw")
+    assert asum(tz) == 0.0
+    assert asum(entry_(tz, 1)) == 120.0
+    assert T.shape(tz) == [2, 3, 4, 5]
+
+
+def test_zero(fact):
+    """tt :29-35"""
+    tz = tensor(fact, [2, 3, 4, 5], "float", "nchw")
+    tz_zero = T.zero(tz)
+    assert asum(tz) == 0.0
+    assert asum(entry_(tz, 1)) == 120.0
+    assert asum(tz_zero) == 0.0
+
+
+def test_create(fact):
+    """tt :37-48"""
+    t1 = tensor(fact, [1, 1, 1, 1], "float", "nchw")
+    td3221 = desc([3, 2, 2, 1], "float", "nhwc")
+    t3221 = tensor(fact, td3221)
+    with pytest.raises(DiamondError):
+        tensor(fact, [1, -1, 1, 1], "float", "nchw")
+    assert T.dim(t1) == 1 and T.shape(t1) == [1, 1, 1, 1] and T.layout(t1) == [1, 1, 1, 1]
+    assert T.data_type(t1) == "float"
+    assert T.dim(t3221) == 12 and T.layout(t3221) == [4, 1, 2, 2]
+
+
+def test_equality(fact):
+    """tt :50-63"""
+    x1 = tensor(fact, [2, 1, 2, 3], "float", "nchw")
+    y1 = tensor(fact, [2, 1, 2, 3], "float", "nchw")
+    y3 = tensor(fact, [2, 1, 2, 3], "float", "nhwc")
+    y4 = tensor(fact, [2, 1, 2, 2], "float", "nchw")
+    x5 = tensor(fact, [2, 2, 2, 2], "float", "nchw")
+    y5 = tensor(fact, [2, 2, 2, 2], "float", "nhwc")
+    assert (x1 == None) is False  # noqa: E711
+    assert x1 == y1
+    assert not (x1 == y3) and not (x1 == y4) and not (x5 == y5)
+    assert transfer(itertools.count(), x1) == transfer(itertools.count(), y1)
+
+
+def test_release(fact):
+    """tt :65-69"""
+    t1 = tensor(fact, [2, 3, 1, 1], "float", "nchw")
+    assert T.release(view_tz(t1)) is True and T.release(t1) is True
+
+
+def test_transfer(fact):
+    """tt :71-87 with both factories the B200 one (the reference also runs it as fact0 = fact1)."""
+    x1 = tensor(fact, [2, 1, 2, 1], "float", "nchw")
+    x2 = tensor(fact, [2, 1, 2, 1], "float", "nchw")
+    y1 = tensor(fact, [2, 1, 2, 1], "float", "nchw")
+    y2 = tensor(fact, [2, 1, 1, 1], "float", [1, 1, 1, 1])
+    assert transfer(np.array([1, 2, 3, 4], np.float32), x1) is x1
+    assert list(transfer(x1, np.zeros(4, np.float32))) == [1.0, 2.0, 3.0, 4.0]
+    assert seq(transfer(np.array([4, 3, 2, 1], np.float32), x1)) == [4.0, 3.0, 2.0, 1.0]
+    assert seq(transfer([10, 20, 30, 40], x1)) == [10.0, 20.0, 30.0, 40.0]
+    assert transfer(x1, x2) is x2 and seq(x2) == [10.0, 20.0, 30.0, 40.0]
+    assert transfer(x1, y1) is y1 and seq(y1) == [10.0, 20.0, 30.0, 40.0]
+    assert entry_(y1, 100) is y1
+    assert seq(transfer(y1, x1)) == [100.0] * 4
+    with pytest.raises(DiamondError):
+        transfer(x2, y2)
+
+
+def test_transfer_to_and_from_host_mirror(fact):
+    """tt :71-87 with fact1 = the native (host) factory, as cudnn_tensor_test.clj:79 runs it."""
+    host = fact.native_diamond_factory()
+    x1 = tensor(fact, [2, 1, 2, 1], "float", "nchw")
+    y1 = tensor(host, [2, 1, 2, 1], "float", "nchw")
+    transfer([10, 20, 30, 40], x1)
+    assert transfer(x1, y1) is y1 and list(y1) == [10.0, 20.0, 30.0, 40.0]
+    transfer([100, 100, 100, 100], y1)
+    assert seq(transfer(y1, x1)) == [100.0] * 4
+    y2 = tensor(host, [2, 1, 1, 1], "float", [1, 1, 1, 1])
+    with pytest.raises(DiamondError):
+        transfer(x1, y2)
+
+
+def test_contiguous(fact):
+    """tt :89-96"""
+    x1 = tensor(fact, [2, 3, 2, 2], "float", "nchw")
+    assert T.contiguous(x1)
+    transfer(itertools.count(), x1)
+    assert view_tz(x1, [2, 3, 2, 2]) == x1
+    assert seq(view_tz(x1, [1, 3, 2, 2])) == [float(i) for i in range(12)]
+    assert T.contiguous(x1)
+
+
+def test_subtensor(fact):
+    """tt :98-117"""
+    tz_x = tensor(fact, [6, 1, 1, 1], "float", [1, 1, 1, 1])
+    sub_x = view_tz(tz_x, [2, 1, 1, 1])
+    sub_y = view_tz(tz_x, desc([1, 3, 1, 1], [3, 1, 1, 1]))
+    sub_z = view_tz(tz_x, 4)
+    transfer(itertools.count(), tz_x)
+    assert seq(tz_x) == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0]
+    assert seq(sub_x) == [0.0, 1.0] and seq(sub_y) == [0.0, 1.0, 2.0] and seq(sub_z) == [0.0, 1.0, 2.0, 3.0]
+    sub_y.offset(3)
+    assert seq(sub_y) == [3.0, 4.0, 5.0] and seq(sub_x) == [0.0, 1.0]
+    sub_z.offset(1)
+    assert seq(sub_z) == [1.0, 2.0, 3.0, 4.0] and seq(sub_x) == [0.0, 1.0]
+    assert seq(tz_x) == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0]
+    entry_(view_vctr(sub_y), 0)
+    assert seq(tz_x) == [0.0, 1.0, 2.0, 0.0, 0.0, 0.0]
+
+
+def test_transformer(fact):
+    """tt :152-169"""
+    tz_x = tensor(fact, [2, 3, 4, 5], "float", "nchw")
+    tz_y = tensor(fact, [2, 3, 4, 5], "float", "nhwc")
+    tz_sub_x = view_tz(tz_x, [1, 3, 4, 5])
+    tz_sub_y = view_tz(tz_y, [1, 3, 4, 5])
+    transform = transformer(tz_x, tz_y)
+    sub_transform = transformer(tz_sub_x, tz_sub_y)
+    assert entry(view_vctr(native(transfer(itertools.count(), tz_x))), 119) == 119.0
+    assert entry(view_vctr(native(tz_y)), 119) == 0.0
+    assert T.buffer(input(transform)) == T.buffer(tz_x)
+    assert T.buffer(output(transform)) == T.buffer(tz_y)
+    assert transform() == tz_y
+    assert asum(tz_y) == asum(tz_x)
+    assert entry(view_vctr(native(tz_y)), 119) == 119.0
+    transfer(range(0, 1000, 10), tz_x)
+    assert sub_transform() == tz_sub_y
+    assert entry(view_vctr(native(tz_y)), 34) == 310.0
+
+
+def test_transformer_any(fact):
+    """tt :171-182"""
+    tz_x = tensor(fact, [2, 3, 2, 1], "float", [48, 16, 5, 2])
+    in_x = connector(desc([2, 3, 2, 1], "float", "nchw"), tz_x)
+    tz_y = tensor(fact, [2, 3, 2, 1], "float", [48, 13, 4, 2])
+    out_y = connector(tz_y, desc([2, 3, 2, 1], "float", "nchw"))
+    transform = transformer(tz_x, tz_y)
+    transfer(itertools.count(), input(in_x))
+    in_x()
+    transform()
+    out_y()
+    assert output(out_y) == input(in_x)
+
+
+def test_transfer_any(fact):
+    """tt :184-194"""
+    tz_x = tensor(fact, [2, 3, 2, 1], "float", [48, 12, 4, 2])
+    in_x = connector(desc([2, 3, 2, 1], "float", "nchw"), tz_x)
+    tz_y = tensor(fact, [2, 3, 2, 1], "float", [48, 14, 4, 2])
+    out_y = connector(tz_y, desc([2, 3, 2, 1], "float", "nchw"))
+    transfer(itertools.count(), input(in_x))
+    in_x()
+    transfer(tz_x, tz_y)
+    out_y()
+    assert asum(output(out_y)) == float(sum(range(12)))
+
+
+def test_transfer_view_tz(fact):
+    """tt :196-203"""
+    tz = tensor(fact, [1, 3, 3, 1], "float", "nchw")
+    entry_(tz, 100.0)
+    ibtz = view_tz(tz, [1, 2, 1, 1])
+    offset_(ibtz, 1)
+    offset_(ibtz, 1)
+    transfer(range(1, 3), ibtz)
+    assert seq(tz) == [100.0, 1.0, 100.0, 100.0, 2.0, 100.0, 100.0, 100.0, 100.0]
+
+
+def test_heterogenous_transfer(fact):
+    """tt :205-221"""
+    tz_x = tensor(fact, [6, 2, 1, 1], "byte", "nchw")
+    sub_x = offset_(view_tz(tz_x, 2), 2 * 4)
+    tz_y = tensor(fact, [6, 2, 1, 1], "float", "nchw")
+    sub_y = offset_(view_tz(tz_y, 2), 2 * 2)
+    tz_z = tensor(fact, [6, 2, 1, 1], "uint8", "nchw")
+    sub_z = offset_(view_tz(tz_z, 2), 2 * 1)
+    transfer(range(-6, 6), tz_x)
+    assert seq(tz_x) == list(range(-6, 6))
+    transfer(tz_x, tz_y)
+    assert asum(transfer(tz_x, tz_y)) == 36.0
+    assert seq(transfer(tz_y, tz_z)) == [0, 0, 0, 0, 0, 0, 0, 1, 2, 3, 4, 5]
+    assert asum(native(transfer(sub_x, sub_y))) == 14.0
+    assert seq(transfer(sub_y, sub_z)) == [2, 3, 4, 5]
+    assert seq(tz_z) == [0, 0, 2, 3, 4, 5, 0, 1, 2, 3, 4, 5]
+
+
+def test_pull_push_connectors(fact):
+    """tt :223-261"""
+    tz_x = tensor(fact, [2, 3, 4, 5], "float", "nchw")
+    connection = connector(tz_x, desc([2, 3, 4, 5], "float", "nhwc"))       # pull, different
+    assert entry(view_vctr(native(transfer(itertools.count(), tz_x))), 119) == 119.0
+    assert T.buffer(input(connection)) == T.buffer(tz_x)
+    assert T.buffer(input(connection)) != T.buffer(output(connection))
+    assert entry(native(view_vctr(connection())), 119) == 119.0
+    same = connector(tz_x, desc([2, 3, 4, 5], "float", "nchw"))              # pull, same
+    assert T.buffer(input(same)) == T.buffer(tz_x) == T.buffer(output(same))
+    assert entry(native(view_vctr(same())), 119) == 119.0
+    tz_y = tensor(fact, [2, 3, 4, 5], "float", "nchw")
+    push = connector(desc([2, 3, 4, 5], "float", "nhwc"), tz_y)              # push, different
+    assert entry(native(transfer(itertools.count(), view_vctr(input(push)))), 119) == 119.0
+    assert T.buffer(output(push)) == T.buffer(tz_y)
+    assert T.buffer(input(push)) != T.buffer(output(push))
+    assert entry(native(view_vctr(push())), 119) == 119.0
+    push_same = connector(desc([2, 3, 4, 5], "float", "nchw"), tz_y)         # push, same
+    assert T.buffer(output(push_same)) == T.buffer(tz_y) == T.buffer(input(push_same))
+
+
+def test_shuffler(fact):
+    """tt :263-275"""
+    tz_x = tensor(fact, [6, 2, 1, 1], "float", [2, 1, 1, 1])
+    tz_y = tensor(fact, [3, 2, 1, 1], "float", [1, 3, 1, 1])
+    shuff = shuffler(tz_x, tz_y)
+    transfer(range(1, 13), tz_x)
+    assert seq(tz_x) == [float(i) for i in range(1, 13)]
+    assert seq(tz_y) == [0.0] * 6
+    shuff([0, 2, 1])
+    assert seq(tz_y) == [1.0, 5.0, 3.0, 2.0, 6.0, 4.0]
+    assert fact.handle.last_kernel() == "transform/gather"
+    with pytest.raises(DiamondError):
+        shuff([0, 2, 1, 1])
+    with pytest.raises(DiamondError):
+        shuff([0, 2, 8])
+    assert shuff([0, 1]) == tz_y
+
+
+def _batcher_checks(tz_x, tz_y, batch, batch_2):
+    assert seq(tz_y) == [0.0] * 6
+    assert batch(0, 0) == tz_y
+    assert seq(tz_y) == [1.0, 3.0, 5.0, 2.0, 4.0, 6.0]
+    transfer(itertools.repeat(0), tz_y)
+    assert batch(1, 0) == tz_y
+    assert seq(tz_y) == [3.0, 5.0, 7.0, 4.0, 6.0, 8.0]
+    transfer(itertools.repeat(0), tz_y)
+    assert batch_2(1, 1) == tz_y
+    assert seq(tz_y) == [0.0, 3.0, 5.0, 0.0, 4.0, 6.0]
+    for bad in ((8,), (0, -1), (7, -1), (-1,)):
+        with pytest.raises(DiamondError):
+            batch(*bad)
+
+
+def test_batcher(fact):
+    """tt :277-297"""
+    tz_x = tensor(fact, [7, 2, 1, 1], "float", [2, 1, 1, 1])
+    tz_y = tensor(fact, [3, 2, 1, 1], "float", [1, 3, 1, 1])
+    batch, batch_2 = batcher(tz_x, tz_y, 3), batcher(tz_x, tz_y, 2)
+    transfer(range(1, 15), tz_x)
+    assert seq(tz_x) == [float(i) for i in range(1, 15)]
+    _batcher_checks(tz_x, tz_y, batch, batch_2)
+
+
+def test_batcher_tnc(fact):
+    """tt :299-326"""
+    tz_x_ntc = tensor(fact, [2, 7, 1], "float", "ntc")
+    tz_x = tensor(fact, [2, 7, 1], "float", "tnc")
+    tz_y = tensor(fact, [2, 3, 1], "float", "tnc")
+    assert tz_x.batch_index() == 1
+    sub_x = view_tz(tz_x, 3)
+    batch, batch_2 = batcher(tz_x, tz_y, 3), batcher(tz_x, tz_y, 2)
+    transfer(range(1, 15), tz_x)
+    assert seq(transfer(sub_x, tensor(fact, [2, 3, 1], "float", "tnc"))) == [1.0, 2.0, 3.0, 8.0, 9.0, 10.0]
+    sub_x.offset(3)
+    assert seq(transfer(sub_x, tensor(fact, [2, 3, 1], "float", "tnc"))) == [4.0, 5.0, 6.0, 11.0, 12.0, 13.0]
+    transfer(range(1, 15), tz_x_ntc)
+    transfer(tz_x_ntc, tz_x)
+    assert seq(tz_x) == [1.0, 3.0, 5.0, 7.0, 9.0, 11.0, 13.0, 2.0, 4.0, 6.0, 8.0, 10.0, 12.0, 14.0]
+    _batcher_checks(tz_x, tz_y, batch, batch_2)
+
+
+def test_half_and_bf16_storage(fact):
+    """cudnn_tensor_test.clj:49-68 (f32 <-> f16, 100..400 survive) and the same for the new :bf16."""
+    src = tensor(fact, [1, 4, 1, 1], "float", "nchw")
+    transfer([100, 200, 300, 400], src)
+    for dt in ("half", "bf16"):
+        mid = tensor(fact, [1, 4, 1, 1], dt, "nchw")
+        back = tensor(fact, [1, 4, 1, 1], "float", "nchw")
+        transfer(src, mid)
+        transfer(mid, back)
+        assert seq(back) == [100.0, 200.0, 300.0, 400.0]
+        assert list(native(mid)) == [100.0, 200.0, 300.0, 400.0]
+
+
+# ---------------------------------------------------------------------------------- dnn -------
+
+def vctr_of(tz, values):
+    return T.vctr(tz, values).tolist()
+
+
+def test_activation_relu(fact):
+    """dt :28-54"""
+    src_tz = tensor(fact, [1, 3, 2, 1], "float", "nchw")
+    activ_bluep = dnn.activation(fact, src_tz, "relu")
+    activ_infer = activ_bluep(src_tz)
+    activ_train = activ_bluep(src_tz, src_tz)
+    transfer([-0.5, 0, 0.2, 1, 0.3, -0.7], src_tz)
+    assert seq(activ_infer()) == vctr_of(src_tz, [0, 0, 0.2, 1.0, 0.3, 0])
+    assert seq(input(activ_infer)) == vctr_of(src_tz, [0, 0, 0.2, 1.0, 0.3, 0])
+    assert seq(output(activ_infer)) == vctr_of(src_tz, [0, 0, 0.2, 1.0, 0.3, 0])
+    transfer([-0.5, 0, 0.2, 1, 0.3, -0.7], src_tz)
+    dnn.forward(activ_train)
+    assert seq(input(activ_train)) == vctr_of(src_tz, [-0.5, 0, 0.2, 1, 0.3, -0.7])
+    assert seq(output(activ_train)) == vctr_of(src_tz, [0, 0, 0.2, 1.0, 0.3, 0])
+    transfer([-0.1, 0.1, 1, 2, 7, -0.6], dnn.diff_input(activ_train))
+    dnn.backward(activ_train)
+    assert seq(dnn.diff_output(activ_train)) == vctr_of(src_tz, [0, 0, 1, 2, 7.0, 0])
+
+
+def test_activation_sigmoid(fact):
+    """dt :56-82"""
+    src_tz = tensor(fact, [1, 1, 1, 1], "float", "nchw")
+    activ_bluep = dnn.activation(fact, src_tz, "sigmoid")
+    activ_infer = activ_bluep(src_tz)
+    activ_train = activ_bluep(src_tz, src_tz)
+    transfer([0.7], src_tz)
+    assert abs(seq(activ_infer())[0] - 0.6681877374649048) < 1e-6
+    assert abs(seq(input(activ_infer))[0] - 0.6681877374649048) < 1e-6
+    transfer([-0.5], src_tz)
+    dnn.forward(activ_train)
+    assert seq(input(activ_train)) == vctr_of(src_tz, [-0.5])
+    assert abs(seq(output(activ_train))[0] - 0.3775407) < 1e-6
+    transfer([-0.1], dnn.diff_input(activ_train))
+    dnn.backward(activ_train)
+    assert abs(seq(input(activ_train))[0] - (-0.02350037172436714)) < 1e-8
+
+
+def test_activation_linear_tanh_elu(fact):
+    """Activation kinds the shared suite does not exercise: layers against the C-level oracle."""
+    import oracle
+    x = [-1.5, -0.2, 0.0, 0.4, 2.0, 5.0]
+    g = [1.0, -2.0, 0.5, 3.0, -1.0, 0.25]
+    for kind, args in (("tanh", None), ("elu", {"alpha": 1.0}), ("linear", {"alpha": 2.0, "beta": 0.5})):
+        src = tensor(fact, [1, 6, 1, 1], "float", "nchw")
+        dsrc = tensor(fact, [1, 6, 1, 1], "float", "nchw")
+        layer = dnn.activation(fact, src, kind, args)(src, dsrc)
+        transfer(x, src)
+        dnn.forward(layer)
+        xa, ga = np.array(x, np.float32), np.array(g, np.float32)
+        if kind == "linear":   # the cuDNN-style linear training layer is a pair of copies
+            assert seq(output(layer)) == x
+        else:
+            want = oracle.eltwise_fwd(kind, xa, np.zeros(6, np.float32), coef=(args or {}).get("alpha", 0.0))
+            assert np.allclose(seq(output(layer)), want, rtol=3e-7, atol=0)
+        transfer(g, dnn.diff_input(layer))
+        dnn.backward(layer)
+        if kind == "linear":
+            assert seq(dnn.diff_output(layer)) == g
+        else:
+            wantb = oracle.eltwise_bwd(kind, xa, ga, np.zeros(6, np.float32), coef=(args or {}).get("alpha", 0.0))
+            assert np.allclose(seq(dnn.diff_output(layer)), wantb, rtol=3e-7, atol=0)
+
+
+def test_sum(fact):
+    """dt :855-874"""
+    input0_tz = tensor(fact, [1, 2, 1, 1], "float", "nchw")
+    input1_tz = tensor(fact, [1, 2, 1, 1], "float", "nchw")
+    sum_bluep = dnn.sum(fact, [input0_tz, input1_tz])
+    sum_train = sum_bluep([input0_tz, input1_tz], True, None)
+    transfer([1, 2], input0_tz)
+    transfer([3, 4], input1_tz)
+    assert dnn.forward(sum_train, None) is sum_train
+    assert seq(output(sum_train)) == [4.0, 6.0]
+    transfer([0, 0], input1_tz)
+    assert seq(input1_tz) == [0.0, 0.0]
+    assert dnn.backward(sum_train, None) is sum_train
+    assert seq(input0_tz) == [2.0, 3.0] and seq(input1_tz) == [2.0, 3.0]
+
+
+def test_blas_generics_on_tensors(fact):
+    """axpy! / scal! / copy! / nrm2 / amax on tensors: the TensorEngine of cudnn/factory.clj:161-196."""
+    x = tensor(fact, [2, 3, 1, 1], "float", "nchw")
+    y = tensor(fact, [2, 3, 1, 1], "float", "nchw")
+    bias = tensor(fact, [1, 3, 1, 1], "float", "nchw")
+    transfer([1, 2, 3, 4, 5, 6], x)
+    transfer([10, 20, 30], bias)
+    T.copy(x, y)
+    T.axpy(2.0, x, y)
+    assert seq(y) == [3.0, 6.0, 9.0, 12.0, 15.0, 18.0]
+    T.axpy(1.0, bias, y)                     # bias broadcast over the batch
+    assert seq(y) == [13.0, 26.0, 39.0, 22.0, 35.0, 48.0]
+    T.scal(0.5, y)
+    assert seq(y) == [6.5, 13.0, 19.5, 11.0, 17.5, 24.0]
+    T.axpby(1.0, x, -1.0, y)
+    assert seq(y) == [-5.5, -11.0, -16.5, -7.0, -12.5, -18.0]
+    assert abs(T.nrm2(x) - np.sqrt(91.0)) < 1e-5 and T.amax(y) == 18.0 and T.sum(x) == 21.0

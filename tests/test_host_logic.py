@@ -1,0 +1,147 @@
+"""CPU-only checks: the C-ABI library loads and exports every symbol the header declares, the host
+logic (layout keywords, descriptors, argument validation that needs no device) behaves like the
+reference's, and the multi-rank logic of the sharded reduce agrees with a single-rank reduce
+(world size 2 over gloo).  No kernel is launched here.
+"""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from deep_diamond_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "dd_b200.h")).read()
+    declared = set(re.findall(r"DD_API\s+[\w\s\*]+?\b(dd[A-Z]\w+)\s*\(", header))
+    assert len(declared) >= 45
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    missing = [name for name in sorted(declared) if not hasattr(lib, name)]
+    assert not missing, missing
+    assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
+    assert lib.ddGetVersion() == 100
+
+
+def test_error_strings_and_descriptor_calls_without_a_device():
+    from deep_diamond_b200 import _lib, core
+    from deep_diamond_b200._lib import DiamondError
+    assert _lib.lib.ddGetErrorString(3) == b"DD_STATUS_BAD_PARAM"
+    assert _lib.lib.ddGetErrorString(0) == b"DD_STATUS_SUCCESS"
+    d = core.tensor_descriptor([3, 2, 2, 1], "float", "nhwc")
+    assert core.strides(d) == [4, 1, 2, 2] and core.dims(d) == [3, 2, 2, 1] and core.data_type(d) == "float"
+    assert core.bytesize(d) == 48
+    assert core.bytesize(core.tensor_descriptor([2, 2, 3, 2], "float", [48, 100, 8, 3])) == (1 + 48 + 100 + 16 + 3) * 4
+    assert core.equal_desc(d, core.tensor_descriptor([3, 2, 2, 1], "float", [4, 1, 2, 2]))
+    assert not core.equal_desc(d, core.tensor_descriptor([3, 2, 2, 1], "int", "nhwc"))
+    # cudnn core_test.clj:30-36: rank-3 descriptors are native here (no padding to 4)
+    tnc = core.tensor_descriptor([2, 3, 4], "float", [12, 4, 1])
+    assert core.dims(tnc) == [2, 3, 4] and core.strides(tnc) == [12, 4, 1]
+    for bad in (([2, 3], "f128", [3, 1]), ([1, 1], "byte", "xxx"), ([2, -1, 1, 1], "float", "nchw"),
+                ([2, 3], "float", [3])):
+        with pytest.raises(DiamondError):
+            core.tensor_descriptor(*bad)
+    ad = core.activation_descriptor("relu", True, 42.0)
+    assert core.activation_descriptor(ad) == {"mode": "relu", "relu-nan-opt": True, "coef": 42.0}
+    assert core.activation_descriptor(core.activation_descriptor("sigmoid", True, 42.0))["mode"] == "logistic"
+    with pytest.raises(DiamondError):
+        core.activation_descriptor("softsign")
+    with pytest.raises(DiamondError):
+        core.reduce_tensor_descriptor("median")
+    with pytest.raises(DiamondError):
+        core.reduce_tensor_descriptor("add", "half")
+
+
+def test_layout_keywords():
+    from deep_diamond_b200.constants import default_strides, layout_strides
+    assert layout_strides([2, 3, 4, 5], "nchw") == [60, 20, 5, 1]
+    assert layout_strides([2, 3, 4, 5], "nhwc") == [60, 1, 15, 3]
+    assert layout_strides([2, 7, 1], "tnc") == [7, 1, 1]
+    assert layout_strides([2, 7, 1], "ntc") == [1, 2, 1]
+    assert layout_strides([2, 3], "nc") == [3, 1] and layout_strides([2, 3], "cn") == [1, 2]
+    assert layout_strides([2, 3, 4, 5, 6], "ncdhw") == default_strides([2, 3, 4, 5, 6])
+    assert layout_strides([4], "x") == [1]
+    assert default_strides([2, 3, 4, 5]) == [60, 20, 5, 1] and default_strides([]) == []
+
+
+def test_general_descriptor_and_the_no_fallback_rule():
+    from deep_diamond_b200 import tensor as T
+    from deep_diamond_b200._lib import DiamondError
+    d = T.desc([2, 3, 2, 4], "nhwc")
+    assert (d.shape, d.data_type, d.layout) == ([2, 3, 2, 4], None, "nhwc")
+    assert T.desc([2, 3], "float", "nc").data_type == "float"
+    assert T.default_desc([2, 3, 4], "float").layout == [12, 4, 1]
+    with pytest.raises(DiamondError):
+        T.desc([2, 3], "float", "nchw")
+    import torch
+    if not torch.cuda.is_available():
+        from deep_diamond_b200 import b200_factory
+        with pytest.raises(DiamondError):   # no device: the factory refuses, nothing falls back to the CPU
+            b200_factory()
+
+
+def test_shard_arithmetic():
+    from deep_diamond_b200 import sharded
+    from deep_diamond_b200._lib import DiamondError
+    assert sharded.shard_range(64, 8, 3) == (24, 32)
+    assert sharded.shard_shape([2048, 256, 28, 28], 8) == [256, 256, 28, 28]
+    assert sharded.spans_sharded_dim([8, 1024, 32, 32], [1, 1024, 1, 1])
+    assert not sharded.spans_sharded_dim([8, 1024, 32, 32], [8, 1, 32, 32])
+    with pytest.raises(DiamondError):
+        sharded.shard_range(10, 4, 0)
+
+
+_WORKER = r'''
+import os, sys
+import numpy as np
+import torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+import oracle
+from deep_diamond_b200 import sharded
+
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%s" % sys.argv[2], rank=int(sys.argv[3]), world_size=2)
+rank, world = dist.get_rank(), dist.get_world_size()
+full = oracle.gen_signed_lognormal([8, 6, 5, 4], 5)
+lo, hi = sharded.shard_range(full.shape[0], world, rank)
+mine = np.ascontiguousarray(full[lo:hi])
+ok = True
+for op, pre in (("add", "add"), ("avg", "add"), ("norm2", None), ("max", "max"), ("norm1", "norm1")):
+    yshape = (1, 6, 1, 1)
+    # local pre-finish partial: sum, sum|x|, sum x^2 or max over this rank's slice
+    if op == "norm2":
+        part = (mine.astype(np.float64) ** 2).sum(axis=(0, 2, 3), keepdims=True)
+    else:
+        part = np.zeros(yshape, np.float32)
+        oracle.reduce(pre, mine, part)
+    gathered = [None, None]
+    dist.all_gather_object(gathered, np.asarray(part, dtype=np.float64))
+    got = sharded.combine_partials_host(op, gathered, mine.size // 6, world)
+    want = np.zeros(yshape, np.float32)
+    _, truth = oracle.reduce(op, full, want, want_truth=True)
+    ok = ok and np.allclose(got, truth, rtol=1e-5, atol=1e-5)
+flags = [None, None]
+dist.all_gather_object(flags, bool(ok))
+dist.barrier()
+dist.destroy_process_group()
+sys.exit(0 if all(flags) else 1)
+'''
+
+
+def test_sharded_reduce_logic_world_size_2_gloo(tmp_path):
+    """Two CPU ranks each hold half the batch; local partial + combine + finish equals the reduce of
+    the whole tensor for sum, mean, norm2, max, norm1 (the arithmetic ddShardedReduceTensor runs with
+    NCCL in place of the gather)."""
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, str(port), str(r)]) for r in range(2)]
+    codes = [p.wait(timeout=180) for p in procs]
+    assert codes == [0, 0]
