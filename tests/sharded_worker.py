@@ -1,0 +1,81 @@
+"""One rank of the multi-GPU reduce test (launched by tests/test_gpu_sharded.py under
+torch.distributed.run).  Every rank builds the same full tensor from a seed, keeps its own batch
+slice on its GPU, runs ddShardedReduceTensor, and checks the (replicated) result against the CPU
+oracle's reduction of the whole tensor."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import oracle
+    from deep_diamond_b200 import b200_factory, core, sharded
+    fact = b200_factory(local)
+    sh = sharded.create_from_torch_distributed(fact)
+    assert sh.check()
+    full_shape = [4 * world, 64, 16, 16]
+    full = oracle.gen_signed_lognormal(full_shape, 5)
+    lo, hi = sharded.shard_range(full_shape[0], world, rank)
+    mine = np.ascontiguousarray(full[lo:hi])
+    x = torch.from_numpy(mine).to(fact.device)
+    shard_shape = list(mine.shape)
+    xd = core.tensor_descriptor(shard_shape, "float", "nchw")
+    failures = []
+    for op in ("add", "avg", "norm2", "norm1", "max", "min", "amax"):
+        for alpha, beta in ((1.0, 0.0), (2.0, 0.5)):
+            yshape = [1, 64, 1, 1]
+            y0 = np.linspace(-1, 1, 64, dtype=np.float32)
+            want = y0.copy().reshape(yshape)
+            _, truth = oracle.reduce(op, full, want, alpha=alpha, beta=beta, want_truth=True)
+            y = torch.from_numpy(y0.copy()).to(fact.device)
+            yd = core.tensor_descriptor(yshape, "float", "nchw")
+            sh.reduce_tensor(core.reduce_tensor_descriptor(op, "float"), alpha, xd, x, beta, yd, y)
+            fact.synchronize()
+            got = y.cpu().numpy().reshape(yshape)
+            if op in ("max", "min", "amax") and beta == 0.0:
+                ok = np.array_equal(got, want)
+            else:
+                scale = np.abs(full.astype(np.float64)).sum(axis=(0, 2, 3), keepdims=True)
+                ok = bool((np.abs(got - want) <= np.maximum(1e-5 * np.abs(want), 16 * 6e-8 * abs(alpha) * scale)).all())
+            if not ok:
+                failures.append((op, alpha, beta, float(np.abs(got - want).max())))
+    # a reduction that keeps the sharded dim needs no exchange: result stays sharded
+    yshape = [shard_shape[0], 1, 16, 16]
+    want = np.zeros(yshape, np.float32)
+    oracle.reduce("max", mine, want)
+    y = torch.zeros(int(np.prod(yshape)), device=fact.device)
+    sh.reduce_tensor(core.reduce_tensor_descriptor("max", "float"), 1.0, xd, x, 0.0,
+                     core.tensor_descriptor(yshape, "float", "nchw"), y)
+    fact.synchronize()
+    if not np.array_equal(y.cpu().numpy().reshape(yshape), want):
+        failures.append(("max over C (local)",))
+    # all ranks must hold identical bits for the replicated results
+    y = torch.zeros(64, device=fact.device)
+    sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0, xd, x, 0.0,
+                     core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y)
+    gathered = [torch.zeros_like(y) for _ in range(world)]
+    dist.all_gather(gathered, y)
+    if any(not torch.equal(g, gathered[0]) for g in gathered):
+        failures.append(("replicas differ",))
+    flag = torch.tensor([len(failures)], device=fact.device)
+    dist.all_reduce(flag)
+    sh.release()
+    fact.release()
+    dist.destroy_process_group()
+    if failures:
+        print("rank", rank, "failures:", failures, flush=True)
+    sys.exit(1 if int(flag.item()) else 0)
+
+
+if __name__ == "__main__":
+    main()
