@@ -247,13 +247,15 @@ def op_row(name, cfg, nbytes, ms, peak, elems):
             "Gelem/s": round(elems / (med * 1e-3) / 1e9, 2)}
 
 
-def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
+def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_only=False, c5_batch=None):
     """Every other configuration's ops, each timed alone: launches captured in a CUDA graph and
     replayed between CUDA events (see graph_ms).  Small tensors rotate through enough distinct
-    buffers to exceed L2, so every launch is cold."""
+    buffers to exceed L2, so every launch is cold.  With `profile_only` each op is just launched
+    three times (a short, fixed launch list for a profiler) and nothing is timed."""
     rows = []
     h, dev, stream = fact.handle, fact.device, fact.stream
     L2 = 126 << 20
+    it = [0]
 
     def dbuf(nbytes):
         return torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
@@ -261,7 +263,19 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
     def put(arr):
         return torch.from_numpy(np.ascontiguousarray(arr).reshape(-1).view(np.uint8)).to(dev)
 
-    # C1: fp32 [32,64,56,56] nchw -> nhwc (25.7 MB each way: rotate 12 buffer pairs)
+    def measure(name, cfg, nbytes, elems, fn, per_graph, replays, graph=True):
+        if profile_only:
+            for _ in range(3):
+                fn()
+            stream.synchronize()
+            rows.append({"op": name, "config": cfg, "kernel": h.last_kernel()})
+            return
+        ms = graph_ms(torch, fact, fn, per_graph, replays) if graph else event_ms(torch, fn, stream, 100, 10)
+        row = op_row(name, cfg, nbytes, ms, peak, elems)
+        row["kernel"] = h.last_kernel()
+        rows.append(row)
+
+    # C1: fp32 [32,64,56,56] nchw -> nhwc (25.7 MB each way: rotate buffer pairs past L2)
     shp = [32, 64, 56, 56]
     n = int(np.prod(shp))
     xd = core.tensor_descriptor(shp, "float", "nchw")
@@ -270,19 +284,16 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
     sets = max(2, (2 * L2) // (n * 8) + 1)
     xs = [x0] + [x0.clone() for _ in range(sets - 1)]
     ys = [dbuf(n * 4) for _ in range(sets)]
-    it = [0]
 
     def c1():
         i = it[0] % sets
         it[0] += 1
         core.transform_tensor(h, 1.0, xd, xs[i], 0.0, yd, ys[i])
-    rows.append(op_row("reorder f32 nchw->nhwc", "C1 [32,64,56,56], cold L2 (rotating %d buffer pairs)" % sets,
-                       n * 8, graph_ms(torch, fact, c1, 4 * sets, 20), peak, n))
 
     def c1w():
         core.transform_tensor(h, 1.0, xd, xs[0], 0.0, yd, ys[0])
-    rows.append(op_row("reorder f32 nchw->nhwc (warm L2)", "C1 [32,64,56,56], same buffers every launch",
-                       n * 8, graph_ms(torch, fact, c1w, 24, 20), peak, n))
+    measure("reorder f32 nchw->nhwc", "C1 [32,64,56,56], cold L2 (rotating %d buffer pairs)" % sets, n * 8, n, c1, 4 * sets, 20)
+    measure("reorder f32 nchw->nhwc (warm L2)", "C1 [32,64,56,56], same buffers every launch", n * 8, n, c1w, 24, 20)
     del xs, ys
 
     # C3: broadcast op-tensor on [128,512,14,14]
@@ -306,10 +317,8 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
         i = it[0] % sets
         it[0] += 1
         core.op_tensor(h, "mul", 1.0, xd, xs[i], 1.0, bd, scale, 0.0, xd, outs[i])
-    rows.append(op_row("op-tensor a*x + b*bias[c]", "C3 [128,512,14,14], a=1 b=0.5, cold L2", n * 8 + 2048,
-                       graph_ms(torch, fact, c3add, 4 * sets, 20), peak, n))
-    rows.append(op_row("op-tensor x * scale[c]", "C3 [128,512,14,14], cold L2", n * 8 + 2048,
-                       graph_ms(torch, fact, c3mul, 4 * sets, 20), peak, n))
+    measure("op-tensor a*x + b*bias[c]", "C3 [128,512,14,14], a=1 b=0.5, cold L2", n * 8 + 2048, n, c3add, 4 * sets, 20)
+    measure("op-tensor x * scale[c]", "C3 [128,512,14,14], cold L2", n * 8 + 2048, n, c3mul, 4 * sets, 20)
     del xs, outs
 
     # C4: reductions on [64,1024,32,32] (268 MB: larger than L2).  With world > 1 each rank holds
@@ -324,20 +333,19 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
         yd = core.tensor_descriptor(yshape, "float", "nchw")
         y = dbuf(int(np.prod(yshape)) * 4)
         rtd = core.reduce_tensor_descriptor(op, "float")
-        if sharded is not None and yshape[0] == 1:
+        spans = sharded is not None and yshape[0] == 1
+        if spans:
             fn = lambda rtd=rtd, yd=yd, y=y: sharded.reduce_tensor(rtd, 1.0, xd, x, 0.0, yd, y, spans=True)  # noqa: E731
-            tag = "C4 shard [%d,1024,32,32] + 4 KB ncclAllReduce" % shp[0]
+            tag = "C4 shard [%d,1024,32,32] + 4 KB ncclAllReduce (un-captured launches)" % shp[0]
         else:
             fn = lambda rtd=rtd, yd=yd, y=y: core.reduce_tensor(h, rtd, 1.0, xd, x, 0.0, yd, y)  # noqa: E731
             tag = "C4 [%d,1024,32,32]" % shp[0]
-        ms = event_ms(torch, fn, stream, 100, 10) if (sharded is not None and yshape[0] == 1) else \
-            graph_ms(torch, fact, fn, 10, 20)
-        rows.append(op_row("reduce " + label, tag, n * 4 + int(np.prod(yshape)) * 4, ms, peak, n))
+        measure("reduce " + label, tag, n * 4 + int(np.prod(yshape)) * 4, n, fn, 10, 20, graph=not spans)
     del x
 
     # C5: [2048/world,256,28,28] f32 nchw -> bf16 nhwc, then s8 nchw -> s8 nhwc
     full = [2048, 256, 28, 28]
-    shp = [full[0] // world] + full[1:]
+    shp = [c5_batch or full[0] // world] + full[1:]
     n = int(np.prod(shp))
     xd = core.tensor_descriptor(shp, "float", "nchw")
     yd = core.tensor_descriptor(shp, "bf16", "nhwc")
@@ -349,11 +357,26 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1):
     y = dbuf(n * 2)
     q = torch.clamp(torch.round(x * 127.0), -128, 127).to(torch.int8)
     z = dbuf(n)
-    rows.append(op_row("reorder+convert f32 nchw -> bf16 nhwc", "C5 [%d,256,28,28]" % shp[0], n * 6,
-                       graph_ms(torch, fact, lambda: core.transform_tensor(h, 1.0, xd, x, 0.0, yd, y), 5, 10), peak, n))
-    rows.append(op_row("reorder s8 nchw -> nhwc", "C5 [%d,256,28,28]" % shp[0], n * 2,
-                       graph_ms(torch, fact, lambda: core.transform_tensor(h, 1.0, qd, q, 0.0, zd, z), 5, 10), peak, n))
+    measure("reorder+convert f32 nchw -> bf16 nhwc", "C5 [%d,256,28,28]" % shp[0], n * 6, n,
+            lambda: core.transform_tensor(h, 1.0, xd, x, 0.0, yd, y), 5, 10)
+    measure("reorder s8 nchw -> nhwc", "C5 [%d,256,28,28]" % shp[0], n * 2, n,
+            lambda: core.transform_tensor(h, 1.0, qd, q, 0.0, zd, z), 5, 10)
     return rows
+
+
+def run_profile_ops(args):
+    """`--profile-ops`: launches every op of the per-op table three times on cuda:0 and prints the
+    kernel family each call chose.  A short fixed launch list for ncu; the large reorder runs on a
+    per-GPU shard ([256,256,28,28], what one of 8 GPUs holds) to keep the capture small."""
+    import torch
+    import oracle
+    from deep_diamond_b200 import b200_factory, core
+    torch.cuda.set_device(0)
+    oracle.build()
+    fact = b200_factory(0)
+    rows = ops_table(torch, fact, core, oracle, peaks()[0], None, 1, profile_only=True, c5_batch=256)
+    print(json.dumps({"profile_ops": rows}))
+    fact.release()
 
 
 # ------------------------------------------------------------------ main GPU arm ---------------
@@ -370,6 +393,7 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     import oracle
@@ -561,8 +585,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table of the other configurations")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for profiler captures)")
+    ap.add_argument("--profile-ops", action="store_true",
+                    help="launch each op of the per-op table three times and exit (for profiler captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_ops:
+        run_profile_ops(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
