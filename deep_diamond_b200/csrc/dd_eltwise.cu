@@ -124,9 +124,10 @@ __device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef) {
   }
 }
 
+// alpha*v + beta*old.  Multiplying by exactly 1 is exact, so alpha is applied unconditionally.
 template <typename C>
 __device__ __forceinline__ C dd_blend(C alpha, C v, C beta, C old, bool useOld) {
-  C t = dd_scale(alpha, v);
+  C t = dd_mul_rn(alpha, v);
   return useOld ? dd_add_rn(t, dd_mul_rn(beta, old)) : t;
 }
 
@@ -140,8 +141,9 @@ struct ddEltFlatParams {
   int vec;
 };
 
-template <typename T, typename C, int MODE, bool BWD>
-__global__ void __launch_bounds__(256) dd_elt_flat_kernel(ddEltFlatParams p) {
+// PLAIN: alpha == 1 and beta == 0 (what every layer passes): no blend arithmetic at all.
+template <typename T, typename C, int MODE, bool BWD, bool PLAIN>
+__global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) {
   constexpr int V = 16 / sizeof(T);
   const T *x = (const T *)p.x;
   const T *dy = (const T *)p.dy;
@@ -156,7 +158,8 @@ __global__ void __launch_bounds__(256) dd_elt_flat_kernel(ddEltFlatParams p) {
     for (int64_t i = tid; i < nv; i += nthreads) {
       uint4 xin = *(const uint4 *)(x + i * V);
       uint4 din = BWD ? *(const uint4 *)(dy + i * V) : make_uint4(0, 0, 0, 0);
-      uint4 oin = useOld ? *(const uint4 *)(out + i * V) : make_uint4(0, 0, 0, 0);
+      uint4 oin = make_uint4(0, 0, 0, 0);
+      if (!PLAIN && useOld) oin = *(const uint4 *)(out + i * V);
       uint4 res;
       const T *xv = (const T *)&xin, *dv = (const T *)&din, *ov = (const T *)&oin;
       T *rv = (T *)&res;
@@ -165,7 +168,7 @@ __global__ void __launch_bounds__(256) dd_elt_flat_kernel(ddEltFlatParams p) {
         C xc = dd_load<C, T>(xv[k]);
         C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dv[k]), coef)
                   : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
-        rv[k] = dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
+        rv[k] = PLAIN ? dd_store<T, C>(v) : dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
       }
       *(uint4 *)(out + i * V) = res;
     }
@@ -224,8 +227,9 @@ static ddStatus_t launch_elt(ddHandle_t h, const ddCanon &c, const void *x, cons
     uintptr_t bits = (uintptr_t)x | (uintptr_t)out | (BWD ? (uintptr_t)dy : 0);
     p.vec = (bits & 15) == 0;
     constexpr int V = 16 / sizeof(T);
-    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
-    dd_elt_flat_kernel<T, C, MODE, BWD><<<grid, 256, 0, h->stream>>>(p);
+    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 8);
+    if (alpha == 1.0 && beta == 0.0) dd_elt_flat_kernel<T, C, MODE, BWD, true><<<grid, 256, 0, h->stream>>>(p);
+    else dd_elt_flat_kernel<T, C, MODE, BWD, false><<<grid, 256, 0, h->stream>>>(p);
     DD_LAUNCHED(h, BWD ? "activation-bwd/flat" : "activation-fwd/flat");
   } else {
     ddEltStridedParams p;

@@ -23,6 +23,12 @@ __device__ __forceinline__ C dd_binop(int op, C a, C b) {
   }
 }
 
+// Multiplying by a factor of exactly 1 is exact, so the hot loops multiply unconditionally
+// (one instruction) instead of testing the factor per element; the result is the same bits as
+// "a factor of exactly 1 is skipped".
+template <typename C>
+__device__ __forceinline__ C dd_times(C alpha, C v) { return dd_mul_rn(alpha, v); }
+
 struct ddOpFlatParams {
   const void *A;
   const void *B;
@@ -49,15 +55,16 @@ __device__ __forceinline__ int64_t dd_channel_of(const ddOpFlatParams &p, int64_
   return (e / p.inner) % p.channels;
 }
 
-template <typename T, typename C>
-__global__ void __launch_bounds__(256) dd_op_flat_kernel(ddOpFlatParams p) {
+// OP < 0: the op comes from p.op at run time (the less common ops share one instantiation).
+template <typename T, typename C, int OP, int BMODE>
+__global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
   constexpr int V = 16 / sizeof(T);
   const T *A = (const T *)p.A;
   const T *B = (const T *)p.B;
   T *Cp = (T *)p.C;
   const C a1 = (C)p.alpha1, a2 = (C)p.alpha2, beta = (C)p.beta;
   const bool useOld = p.beta != 0.0, readA = p.readA != 0;
-  const int op = p.op;
+  const int op = OP < 0 ? p.op : OP;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   int64_t done = 0;
@@ -65,23 +72,23 @@ __global__ void __launch_bounds__(256) dd_op_flat_kernel(ddOpFlatParams p) {
     const int64_t nv = p.n / V;
     for (int64_t i = tid; i < nv; i += nthreads) {
       const int64_t e0 = i * V;
-      uint4 ain = readA ? *(const uint4 *)(A + e0) : make_uint4(0, 0, 0, 0);
-      uint4 oin = useOld ? *(const uint4 *)(Cp + e0) : make_uint4(0, 0, 0, 0);
-      uint4 bin;
+      uint4 ain = make_uint4(0, 0, 0, 0), oin = make_uint4(0, 0, 0, 0), bin = make_uint4(0, 0, 0, 0);
+      if (readA) ain = *(const uint4 *)(A + e0);
+      if (useOld) oin = *(const uint4 *)(Cp + e0);
       C bs = (C)0;
-      if (p.bmode == 0) {
+      if (BMODE == 0) {
         bin = *(const uint4 *)(B + e0);
       } else {  // inner % V == 0: the whole vector shares one channel
         const int64_t ch = dd_channel_of(p, e0);
-        bs = dd_scale(a2, dd_load<C, T>(__ldg(B + ch * p.sB)));
+        bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch * p.sB)));
       }
       uint4 res;
       const T *av = (const T *)&ain, *bv = (const T *)&bin, *ov = (const T *)&oin;
       T *rv = (T *)&res;
 #pragma unroll
       for (int k = 0; k < V; k++) {
-        C a = readA ? dd_scale(a1, dd_load<C, T>(av[k])) : (C)0;
-        C b = p.bmode == 0 ? dd_scale(a2, dd_load<C, T>(bv[k])) : bs;
+        C a = dd_times(a1, dd_load<C, T>(av[k]));  // readA == 0: a1 == 0 and av == 0, the term is +0
+        C b = BMODE == 0 ? dd_times(a2, dd_load<C, T>(bv[k])) : bs;
         C r = dd_binop<C>(op, a, b);
         if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
         rv[k] = dd_store<T, C>(r);
@@ -92,7 +99,7 @@ __global__ void __launch_bounds__(256) dd_op_flat_kernel(ddOpFlatParams p) {
   }
   for (int64_t i = done + tid; i < p.n; i += nthreads) {
     C a = readA ? dd_scale(a1, dd_load<C, T>(A[i])) : (C)0;
-    C b = p.bmode == 0 ? dd_load<C, T>(B[i]) : dd_load<C, T>(B[dd_channel_of(p, i) * p.sB]);
+    C b = BMODE == 0 ? dd_load<C, T>(B[i]) : dd_load<C, T>(B[dd_channel_of(p, i) * p.sB]);
     C r = dd_binop<C>(op, a, dd_scale(a2, b));
     if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(Cp[i])));
     Cp[i] = dd_store<T, C>(r);
@@ -198,8 +205,14 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
       p.fdInner = dd_fastdiv((uint32_t)inner);
       p.fdChannels = dd_fastdiv((uint32_t)channels);
     }
-    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
-    dd_op_flat_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
+    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 8);
+    // add and mul (bias, per-channel scale, axpy, sum) get their own instantiations
+    if (op == DD_OP_TENSOR_ADD && bmode == 0) dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 0><<<grid, 256, 0, h->stream>>>(p);
+    else if (op == DD_OP_TENSOR_ADD) dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 1><<<grid, 256, 0, h->stream>>>(p);
+    else if (op == DD_OP_TENSOR_MUL && bmode == 0) dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 0><<<grid, 256, 0, h->stream>>>(p);
+    else if (op == DD_OP_TENSOR_MUL) dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 1><<<grid, 256, 0, h->stream>>>(p);
+    else if (bmode == 0) dd_op_flat_kernel<T, C, -1, 0><<<grid, 256, 0, h->stream>>>(p);
+    else dd_op_flat_kernel<T, C, -1, 1><<<grid, 256, 0, h->stream>>>(p);
     DD_LAUNCHED(h, bmode == 0 ? "optensor/flat" : "optensor/flat-bcast");
     return DD_STATUS_SUCCESS;
   }

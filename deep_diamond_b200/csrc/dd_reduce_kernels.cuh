@@ -29,6 +29,10 @@ __device__ __forceinline__ float dd_abs(float v) { return fabsf(v); }
 __device__ __forceinline__ double dd_abs(double v) { return fabs(v); }
 __device__ __forceinline__ float dd_fma(float a, float b, float c) { return fmaf(a, b, c); }
 __device__ __forceinline__ double dd_fma(double a, double b, double c) { return fma(a, b, c); }
+__device__ __forceinline__ float dd_fmax(float a, float b) { return fmaxf(a, b); }
+__device__ __forceinline__ double dd_fmax(double a, double b) { return fmax(a, b); }
+__device__ __forceinline__ float dd_fmin(float a, float b) { return fminf(a, b); }
+__device__ __forceinline__ double dd_fmin(double a, double b) { return fmin(a, b); }
 __device__ __forceinline__ float dd_sqrt(float v) { return __fsqrt_rn(v); }
 __device__ __forceinline__ double dd_sqrt(double v) { return __dsqrt_rn(v); }
 __device__ __forceinline__ float dd_div(float a, float b) { return __fdiv_rn(a, b); }
@@ -56,12 +60,14 @@ struct dd_red {
   static __device__ __forceinline__ C comb(C a, C b, bool nanProp) {
     if (OPC == DD_OPC_SUM || OPC == DD_OPC_SUMABS || OPC == DD_OPC_SUMSQ) return dd_add_rn(a, b);
     if (OPC == DD_OPC_PROD || OPC == DD_OPC_PRODNZ) return dd_mul_rn(a, b);
-    C r;
-    if (OPC == DD_OPC_MIN) r = a < b ? a : b;
-    else r = a > b ? a : b;  // MAX, AMAX
-    if (a != a) r = nanProp ? a : b;
-    if (b != b) r = nanProp ? b : (a != a ? b : a);
-    return r;
+    // propagate: a NaN on either side wins (b beats a only when it compares so or is NaN; a NaN in a
+    // survives because every comparison with it is false).  Otherwise IEEE maxNum/minNum: the number wins.
+    if (nanProp) {
+      if (OPC == DD_OPC_MIN) return (b < a || b != b) ? b : a;
+      return (b > a || b != b) ? b : a;
+    }
+    if (OPC == DD_OPC_MIN) return dd_fmin(a, b);
+    return dd_fmax(a, b);
   }
 };
 

@@ -359,14 +359,14 @@ def test_activation_linear_tanh_elu(fact):
         dnn.forward(layer)
         xa, ga = np.array(x, np.float32), np.array(g, np.float32)
         if kind == "linear":   # the cuDNN-style linear training layer is a pair of copies
-            assert seq(output(layer)) == x
+            assert seq(output(layer)) == vctr_of(src, x)
         else:
             want = oracle.eltwise_fwd(kind, xa, np.zeros(6, np.float32), coef=(args or {}).get("alpha", 0.0))
             assert np.allclose(seq(output(layer)), want, rtol=3e-7, atol=0)
         transfer(g, dnn.diff_input(layer))
         dnn.backward(layer)
         if kind == "linear":
-            assert seq(dnn.diff_output(layer)) == g
+            assert seq(dnn.diff_output(layer)) == vctr_of(src, g)
         else:
             wantb = oracle.eltwise_bwd(kind, xa, ga, np.zeros(6, np.float32), coef=(args or {}).get("alpha", 0.0))
             assert np.allclose(seq(dnn.diff_output(layer)), wantb, rtol=3e-7, atol=0)
