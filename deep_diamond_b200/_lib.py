@@ -64,6 +64,9 @@ _SIGS = {
     "ddTransformTensor": [_vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "ddGatherTransform": [_vp, _int, _i64p, _i64p, _vp, _vp, _vp, _vp],
     "ddTensorEquals": [_vp, _vp, _vp, _vp, _vp, _vp],
+    "ddMultiTransform": [_vp, _int, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
+                         ctypes.POINTER(_vp)],
+    "ddCostDiff": [_vp, _int, _vp, _vp, _vp, _vp, _vp],
     "ddCreateActivationDescriptor": [ctypes.POINTER(_vp)],
     "ddDestroyActivationDescriptor": [_vp],
     "ddSetActivationDescriptor": [_vp, _int, _int, _dbl],

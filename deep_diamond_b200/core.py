@@ -240,6 +240,29 @@ def gather_transform(handle, src_offsets, dst_offsets, desc_x, buf_x, desc_y, bu
     return handle
 
 
+def multi_transform(handle, pairs):
+    """All the sub-tensor copies of a branch / concatenate pass in one launch.  `pairs` is a list of
+    (x, y) tensors (anything with ``desc`` and a device address); the reference runs one
+    transform-tensor per pair (cudnn/directed.clj:1331-1333, 1402-1409)."""
+    n = len(pairs)
+    xd = (ctypes.c_void_p * n)(*[desc(x).ptr.value for x, _ in pairs])
+    yd = (ctypes.c_void_p * n)(*[desc(y).ptr.value for _, y in pairs])
+    xp = (ctypes.c_void_p * n)(*[_ptr(x).value for x, _ in pairs])
+    yp = (ctypes.c_void_p * n)(*[_ptr(y).value for _, y in pairs])
+    check(lib.ddMultiTransform(handle.ptr, n, xd, xp, yd, yp), handle.ptr, "ddMultiTransform")
+    return handle
+
+
+COST_KIND = {"quadratic": 0, "mean-absolute": 1}
+
+
+def cost_diff(handle, kind, desc_a, a, y, d, cost):
+    """d = a - y and its cost in one pass (`cost`: one device element)."""
+    check(lib.ddCostDiff(handle.ptr, enc_keyword(COST_KIND, kind, "cost"), desc(desc_a).ptr, _ptr(a), _ptr(y),
+                         _ptr(d), _ptr(cost)), handle.ptr, "ddCostDiff")
+    return handle
+
+
 def tensor_equals(handle, desc_x, x, desc_y, y, device_flag):
     check(lib.ddTensorEquals(handle.ptr, desc(desc_x).ptr, _ptr(x), desc(desc_y).ptr, _ptr(y),
                              _ptr(device_flag)), handle.ptr, "ddTensorEquals")

@@ -199,7 +199,7 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
     // ddCreate, reset by the kernels); a context without them (counterSlots == 0) or a reduction with
     // more counters than fit falls back to the separate finishing kernel
     const int64_t nctr = pl.kind == DD_RED_ROW ? pl.nout : pl.p.K1 * pl.p.tilesK2;
-    if (h->counterSlots > 0 && nctr <= h->counterSlots) counters = (unsigned *)h->scratch;
+    if (h->counterSlots > 0 && nctr < h->counterSlots) counters  /* the last slot belongs to ddCostDiff */ = (unsigned *)h->scratch;
     if (!ws) {
       ws = (char *)h->scratch + h->counterSlots * sizeof(unsigned);
       wsBytes = h->scratchBytes - h->counterSlots * sizeof(unsigned);

@@ -283,3 +283,283 @@ def diff_input(layer):
 
 def diff_output(layer):
     return layer.diff_output()
+
+
+# ====================== branch / concatenate / split ============================================
+# Counterparts of cudnn/directed.clj:1289-1549 (branch, concat) and :1553-1710 (split).  Where the
+# reference invokes one transformer per sub-tensor, a pass here is ONE ddMultiTransform launch.
+
+def concat_offsets(split_dim, sub_shapes):
+    """``concat-offsets`` (deep-diamond-base/src/uncomplicate/diamond/internal/utils.clj:88-92)."""
+    acc = [0]
+    for s in sub_shapes:
+        acc.append(acc[-1] + int(s[split_dim]))
+    return acc[:-1]
+
+
+def concat_dst_shape(conc_dim, src_shapes):
+    """``concat-dst-shape`` (utils.clj:98-100)."""
+    out = list(src_shapes[0])
+    out[conc_dim] = builtins_sum(int(s[conc_dim]) for s in src_shapes)
+    return out
+
+
+import builtins as _builtins  # noqa: E402
+
+builtins_sum = _builtins.sum
+
+
+class _Pairs:
+    """A list of (source, destination) tensor pairs copied by one launch."""
+
+    def __init__(self, fact, pairs):
+        self.fact, self.pairs = fact, pairs
+
+    def __call__(self):
+        core.multi_transform(self.fact.handle, self.pairs)
+
+
+class B200Branch:
+    """``CUDnnBranchInference`` / ``CUDnnBranchTraining`` (:1289-1404) for both branch (one source
+    cut along `dim` into several destinations) and concatenate (the mirror image)."""
+
+    def __init__(self, fact, bluep, is_branch, data_tz, diff_data, fwd_pairs, bwd_pairs, prop_diff):
+        self.fact, self.bluep, self.is_branch, self.data_tz, self.diff_data = fact, bluep, is_branch, data_tz, diff_data
+        self.fwd, self.bwd, self.prop_diff = _Pairs(fact, fwd_pairs), (_Pairs(fact, bwd_pairs) if bwd_pairs else None), prop_diff
+        self._fwd_pairs, self._bwd_pairs = fwd_pairs, bwd_pairs
+
+    def input(self):
+        return self.data_tz if self.is_branch else [x for x, _ in self._fwd_pairs]
+
+    def output(self):
+        return [y for _, y in self._fwd_pairs] if self.is_branch else self.data_tz
+
+    def diff_input(self):
+        return [x for x, _ in self._bwd_pairs] if self.is_branch else self.data_tz
+
+    def diff_output(self):
+        return self.diff_data if self.is_branch else [y for _, y in self._bwd_pairs]
+
+    def parameters(self):
+        return []
+
+    def forward(self, _=None):
+        self.fwd()
+        return self
+
+    def backward(self, _=None):
+        if self.prop_diff and self.bwd is not None:
+            self.bwd()
+        return self
+
+    def __call__(self):
+        self.fwd()
+        return self.output()
+
+    def release(self):
+        return True
+
+
+def _sub_views(tz, dim, sub_shapes):
+    """Sub-tensors of `tz` laid end to end along `dim` (same strides, element offsets of
+    ``concat-offsets`` times the stride of `dim`)."""
+    views = []
+    for shp, off in zip(sub_shapes, concat_offsets(dim, sub_shapes)):
+        v = tz.view()
+        v.offset(off * tz.layout[dim])
+        views.append(v.view_tz(_t.desc(list(shp), tz.data_type, tz.layout)))
+    return views
+
+
+class B200BranchBlueprint:
+    """``CUDnnBranchBlueprint`` (:1406-1466)."""
+
+    def __init__(self, fact, src_desc, branch_dim, dst_descs):
+        self.fact, self.branch_dim = fact, int(branch_dim)
+        self.src_desc = fact.create_tensor_desc(src_desc)
+        self.dst_descs = [fact.create_tensor_desc(d) if not isinstance(d, _t.TensorDescriptorImpl) or d.data_type
+                          else fact.create_tensor_desc(d.shape, self.src_desc.dtype_code, d.layout) for d in dst_descs]
+        self.dst_dims = [list(d.shape) for d in self.dst_descs]
+
+    @property
+    def shape(self):
+        return [d.shape for d in self.dst_descs]
+
+    def diamond_factory(self):
+        return self.fact
+
+    def __call__(self, prev_layer, prop_diff=None, _=None):
+        src_tz = _t.output(prev_layer)
+        dst_tzs = [self.fact.create_tensor(d.view(), 0, True) for d in self.dst_descs]
+        fwd = list(zip(_sub_views(src_tz, self.branch_dim, self.dst_dims), dst_tzs))
+        if prop_diff is None:
+            return B200Branch(self.fact, self, True, src_tz, None, fwd, None, False)
+        diff_src_tz = prev_layer.diff_input() if hasattr(prev_layer, "diff_input") else src_tz
+        bwd = list(zip(dst_tzs, _sub_views(diff_src_tz, self.branch_dim, self.dst_dims)))
+        return B200Branch(self.fact, self, True, src_tz, diff_src_tz, fwd, bwd, prop_diff)
+
+    def release(self):
+        return True
+
+
+class B200ConcatBlueprint:
+    """``CUDnnConcatBlueprint`` (:1468-1549): destination has default strides."""
+
+    def __init__(self, fact, src_descs, conc_dim, dst_type=None):
+        self.fact, self.conc_dim = fact, int(conc_dim)
+        self.src_descs = [fact.create_tensor_desc(d) for d in src_descs]
+        self.src_dims = [list(d.shape) for d in self.src_descs]
+        dst_shape = concat_dst_shape(self.conc_dim, self.src_dims)
+        from .constants import default_strides
+        self.dst_desc = fact.create_tensor_desc(dst_shape, dst_type or self.src_descs[0].dtype_code,
+                                                default_strides(dst_shape))
+
+    @property
+    def shape(self):
+        return self.dst_desc.shape
+
+    def diamond_factory(self):
+        return self.fact
+
+    def __call__(self, prev_layer, prop_diff=None, _=None):
+        src_tzs = [_t.output(p).view() for p in prev_layer]
+        dst_tz = self.fact.create_tensor(self.dst_desc.view(), 0, True)
+        subs = _sub_views(dst_tz, self.conc_dim, self.src_dims)
+        fwd = list(zip(src_tzs, subs))
+        if prop_diff is None:
+            return B200Branch(self.fact, self, False, dst_tz, None, fwd, None, False)
+        diff_src_tzs = [(p.diff_input() if hasattr(p, "diff_input") else _t.output(p)).view() for p in prev_layer]
+        bwd = list(zip(subs, diff_src_tzs))
+        return B200Branch(self.fact, self, False, dst_tz, diff_src_tzs, fwd, bwd, prop_diff)
+
+    def release(self):
+        return True
+
+
+class B200Split:
+    """``CUDnnSplitInference`` / ``CUDnnSplitTraining`` (:1553-1660): forward hands out the source n
+    times; backward = mean of the n incoming gradients, here one n-ary sum launch (the reference
+    zero-fills and runs n ``axpy!`` passes, :1649-1653)."""
+
+    def __init__(self, fact, bluep, n, src_tz, diff_tzs, prop_diff):
+        self.fact, self.bluep, self.n, self.src_tz, self.diff_tzs, self.prop_diff = fact, bluep, n, src_tz, diff_tzs, prop_diff
+
+    def input(self):
+        return self.src_tz
+
+    def output(self):
+        return [self.src_tz] * self.n
+
+    def diff_input(self):
+        return self.diff_tzs
+
+    def diff_output(self):
+        return self.src_tz
+
+    def parameters(self):
+        return []
+
+    def forward(self, _=None):
+        return self
+
+    def backward(self, _=None):
+        if self.prop_diff and self.diff_tzs:
+            core.sum_tensors(self.fact.handle, [1.0 / self.n] * self.n, [t.desc for t in self.diff_tzs],
+                             self.diff_tzs, self.src_tz.desc, self.src_tz)
+        return self
+
+    def __call__(self):
+        return self.output()
+
+    def release(self):
+        return True
+
+
+class B200SplitBlueprint:
+    """``CUDnnSplitBlueprint`` (:1662-1710)."""
+
+    def __init__(self, fact, src_desc, n):
+        self.fact, self.n = fact, int(n)
+        self.src_desc = fact.create_tensor_desc(src_desc)
+
+    def diamond_factory(self):
+        return self.fact
+
+    def __call__(self, prev_layer, prop_diff=None, _=None):
+        src_tz = _t.output(prev_layer)
+        if prop_diff is None:
+            return B200Split(self.fact, self, self.n, src_tz, None, False)
+        diffs = [self.fact.create_tensor(self.src_desc.view(), 0, True) for _ in range(self.n)]
+        return B200Split(self.fact, self, self.n, src_tz, diffs, prop_diff)
+
+    def release(self):
+        return True
+
+
+def branch(fact, src_desc, branch_dim, dst_descs):
+    """``branch`` (dnn.clj:477-508)."""
+    return B200BranchBlueprint(fact.diamond_factory(), src_desc, branch_dim, dst_descs)
+
+
+def concatenate(fact, conc_dim, src_descs, dst_type=None):
+    """``concatenate`` (dnn.clj:411-443)."""
+    return B200ConcatBlueprint(fact.diamond_factory(), src_descs, conc_dim, dst_type)
+
+
+def split(fact, src_desc, n):
+    """``split`` (dnn.clj:510-535)."""
+    return B200SplitBlueprint(fact.diamond_factory(), src_desc, n)
+
+
+# ====================== cost ====================================================================
+
+class B200Cost:
+    """``CUDnnUniversalCost`` (cudnn/directed.clj:367-412) for :quadratic and :mean-absolute
+    (base/internal/cost.clj:20-34).  Invoking it writes a - y into the previous layer's diff-input and
+    returns the cost, both from ONE kernel; the reference runs connector + ``axpy! -1`` + ``nrm2``."""
+
+    def __init__(self, prev_layer, train_tz, kind):
+        import torch
+        self.prev_layer, self.train_tz, self.kind = prev_layer, train_tz, kind
+        self.fact = train_tz.fact
+        self.a = _t.output(prev_layer)
+        self.a_y = prev_layer.diff_input() if hasattr(prev_layer, "diff_input") else self.a
+        if not (core.equal_desc(self.a.desc, train_tz.desc) and core.equal_desc(self.a_y.desc, train_tz.desc)):
+            raise DiamondError("The B200 cost needs the output, its gradient and the target in one layout.",
+                               {"output": repr(self.a), "target": repr(train_tz)})
+        self._cost = torch.zeros(1, dtype=torch.float64, device=self.fact.device)
+
+    def input(self):
+        return self.a
+
+    def output(self):
+        return self.a
+
+    def diff_input(self):
+        return self.train_tz
+
+    def diff_output(self):
+        return self.a_y
+
+    def forward(self):
+        return self
+
+    def backward(self):
+        core.cost_diff(self.fact.handle, self.kind, self.train_tz.desc, self.a, self.train_tz, self.a_y, self._cost)
+        if hasattr(self.prev_layer, "backward"):
+            self.prev_layer.backward()
+        return self
+
+    def __call__(self):
+        import torch
+        core.cost_diff(self.fact.handle, self.kind, self.train_tz.desc, self.a, self.train_tz, self.a_y, self._cost)
+        with torch.cuda.stream(self.fact.stream):
+            view = self._cost.view(torch.float32) if self.train_tz.desc.dtype_code == 0 else self._cost
+            return float(view[0].item())
+
+
+def cost(layer, train_tz, cost_kw="quadratic"):
+    """``cost`` (dnn.clj:559-581); :crossentropy is outside this engine."""
+    if cost_kw not in core.COST_KIND:
+        raise DiamondError("This cost function is not supported.", {"cost": cost_kw})
+    return B200Cost(layer, train_tz, cost_kw)

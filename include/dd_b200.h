@@ -221,6 +221,23 @@ DD_API ddStatus_t ddGatherTransform(ddHandle_t handle, int count, const int64_t 
 DD_API ddStatus_t ddTensorEquals(ddHandle_t handle, ddTensorDescriptor_t xDesc, const void *x,
                           ddTensorDescriptor_t yDesc, const void *y, int *deviceFlag);
 
+/* Up to 8 independent reorder/convert copies y_i = convert(x_i) in ONE launch (all items share one
+ * source and one destination data type; each item has its own dims and strides).  Replaces the
+ * per-sub-tensor transformer loops of the branch and concatenate layers,
+ * `(doseq [ft fwd-trans] (ft))`, cudnn/directed.clj:1289-1549 (blueprints :1455-1549).
+ * xDescs/xs/yDescs/ys are HOST arrays of `count` entries. */
+DD_API ddStatus_t ddMultiTransform(ddHandle_t handle, int count, const ddTensorDescriptor_t *xDescs,
+                                   const void *const *xs, const ddTensorDescriptor_t *yDescs,
+                                   void *const *ys);
+
+/* d = a - y and, in the same pass, cost[0] = sum (a-y)^2 / (2n) (kind 0, quadratic) or
+ * sum |a-y| / n (kind 1, mean absolute); a, y, d dense tensors of one descriptor, d may be NULL or
+ * alias a.  `cost` is one DEVICE element of the tensor's data type (float or double).  Replaces the
+ * cost glue `axpy! -1.0 y a-y` + `nrm2`/`asum` (cudnn/directed.clj:367-458 with
+ * deep-diamond-base/src/uncomplicate/diamond/internal/cost.clj:20-34). */
+DD_API ddStatus_t ddCostDiff(ddHandle_t handle, int kind, ddTensorDescriptor_t desc, const void *a,
+                             const void *y, void *d, void *cost);
+
 /* ---------------------------------------------------------------- activation ---------------- */
 
 /* Replace cudnnCreate/Set/Get/DestroyActivationDescriptor (cudnn/impl.clj:206-221,
@@ -302,7 +319,7 @@ DD_API ddStatus_t ddReduceTensor(ddHandle_t handle, ddReduceTensorDescriptor_t r
  * count of that device; make that first call outside any stream capture.
  * Results are identical to ddReduceTensor's (same plan, same kernels).
  * `errbuf` (may be NULL) receives a NUL-terminated reason when the status is not success. */
-#define DD_NOALLOC_SCRATCH_BYTES (512u << 10)
+#define DD_NOALLOC_SCRATCH_BYTES (64u << 10)
 DD_API ddStatus_t ddReduceTensorNoAlloc(void *stream, ddReduceTensorOp_t op, ddNanPropagation_t nanOpt,
                                         const void *alpha, ddTensorDescriptor_t xDesc, const void *x,
                                         const void *beta, ddTensorDescriptor_t yDesc, void *y,

@@ -405,3 +405,101 @@ def test_blas_generics_on_tensors(fact):
     T.axpby(1.0, x, -1.0, y)
     assert seq(y) == [-5.5, -11.0, -16.5, -7.0, -12.5, -18.0]
     assert abs(T.nrm2(x) - np.sqrt(91.0)) < 1e-5 and T.amax(y) == 18.0 and T.sum(x) == 21.0
+
+
+def test_concatenate(fact):
+    """dt :657-684"""
+    input0_tz = tensor(fact, [1, 1, 2, 2], "float", "nchw")
+    input1_tz = tensor(fact, [1, 2, 2, 2], "float", "nchw")
+    concat_bluep = dnn.concatenate(fact, 1, [input0_tz, input1_tz, input0_tz], None)
+    concat_inf = concat_bluep([input0_tz, input1_tz, input0_tz])
+    concat_train = concat_bluep([input0_tz, input1_tz, input0_tz], True, None)
+    transfer(range(4), input0_tz)
+    transfer(range(10, 90, 10), input1_tz)
+    want = [0.0, 1.0, 2.0, 3.0, 10.0, 20.0, 30.0, 40.0, 50.0, 60.0, 70.0, 80.0, 0.0, 1.0, 2.0, 3.0]
+    n0 = fact.handle.launch_count()
+    assert seq(concat_inf()) == want
+    assert fact.handle.launch_count() - n0 == 1 and fact.handle.last_kernel().startswith("multi-transform")
+    assert dnn.forward(concat_train, None) is concat_train
+    assert seq(output(concat_train)) == want
+    transfer(itertools.repeat(0.0), input0_tz)
+    transfer(itertools.repeat(0.0), input1_tz)
+    assert seq(input0_tz) == [0.0] * 4
+    assert dnn.backward(concat_train, None) is concat_train
+    assert seq(input0_tz) == [0.0, 1.0, 2.0, 3.0]
+    assert seq(input1_tz) == [10.0, 20.0, 30.0, 40.0, 50.0, 60.0, 70.0, 80.0]
+
+
+def test_branch(fact):
+    """dt :686-710"""
+    dst0_desc = desc([1, 1, 2, 2], "float", "nchw")
+    dst1_desc = desc([1, 2, 2, 2], "float", "nchw")
+    input_tz = tensor(fact, [1, 3, 2, 2], "float", "nchw")
+    branch_bluep = dnn.branch(fact, input_tz, 1, [dst0_desc, dst1_desc])
+    branch_inf = branch_bluep(input_tz)
+    branch_train = branch_bluep(input_tz, True, None)
+    data = [0.0, 1.0, 2.0, 3.0, 10.0, 20.0, 30.0, 40.0, 50.0, 60.0, 70.0, 80.0]
+    transfer(data, input_tz)
+    assert [seq(t) for t in branch_inf()] == [data[:4], data[4:]]
+    assert dnn.forward(branch_train, None) is branch_train
+    assert [seq(t) for t in output(branch_train)] == [data[:4], data[4:]]
+    transfer(itertools.repeat(0.0), input_tz)
+    assert seq(input_tz) == [0.0] * 12
+    assert dnn.backward(branch_train, None) is branch_train
+    assert seq(input_tz) == data
+
+
+def test_split(fact):
+    """dt :876-898"""
+    input_tz = tensor(fact, [1, 2, 1, 1], "float", "nchw")
+    split_bluep = dnn.split(fact, input_tz, 2)
+    split_inf = split_bluep(input_tz)
+    split_train = split_bluep(input_tz, True, None)
+    transfer([1.0, 2.0], input_tz)
+    assert [seq(t) for t in split_inf()] == [[1.0, 2.0], [1.0, 2.0]]
+    assert dnn.forward(split_train, None) is split_train
+    assert [seq(t) for t in output(split_train)] == [[1.0, 2.0], [1.0, 2.0]]
+    transfer(itertools.repeat(0.0), input_tz)
+    transfer([1.0, 2.0], dnn.diff_input(split_train)[0])
+    transfer([3.0, 4.0], dnn.diff_input(split_train)[1])
+    assert dnn.backward(split_train, None) is split_train
+    assert seq(input_tz) == [2.0, 3.0]
+
+
+def test_quadratic_and_mean_absolute_cost(fact):
+    """dt :321-334 (the cost numbers; the network in front of it is outside this engine, so the cost
+    sits directly on an output tensor): quadratic 0.68625, gradient [0.15 -1.65]."""
+    out_tz = tensor(fact, [2, 1], "float", "nc")
+    train_tz = tensor(fact, [2, 1], "float", "nc")
+    quad = dnn.cost(out_tz, train_tz, "quadratic")
+    transfer([0.25, 0.35], train_tz)
+    transfer([0.4, -1.3], out_tz)
+    assert abs(quad() - 0.6862499438341274) < 1e-6
+    assert np.allclose(seq(out_tz), [0.15, -1.65], rtol=1e-6)      # a - y lands in the diff-input
+    transfer([0.4, -1.3], out_tz)
+    mae = dnn.cost(out_tz, train_tz, "mean-absolute")
+    assert abs(mae() - (0.15 + 1.65) / 2) < 1e-6
+    with pytest.raises(DiamondError):
+        dnn.cost(out_tz, train_tz, "crossentropy")
+
+
+def test_branch_concat_large_against_oracle(fact, dev):
+    """Branch then concatenate of a [8, 96, 14, 14] tensor cut 32/48/16 along channels, against the
+    oracle's per-sub-tensor reorders: the 16-byte path of the multi-copy kernel."""
+    import oracle
+    shape = [8, 96, 14, 14]
+    parts = [[8, 32, 14, 14], [8, 48, 14, 14], [8, 16, 14, 14]]
+    x = oracle.gen_uniform(shape, -1, 1, 3).reshape(-1)
+    src = tensor(fact, shape, "float", "nchw")
+    transfer(x, src)
+    br = dnn.branch(fact, src, 1, [desc(p, "float", "nchw") for p in parts])(src)
+    outs = br()
+    assert fact.handle.last_kernel() == "multi-transform/vec"
+    xv = x.reshape(shape)
+    c0 = 0
+    for p, t in zip(parts, outs):
+        want = np.ascontiguousarray(xv[:, c0:c0 + p[1]]).reshape(-1)
+        c0 += p[1]
+        assert np.array_equal(np.asarray(seq(t), np.float32), want)
+    cat = dnn.concatenate(fact, 1, outs)(outs)
+    assert np.array_equal(np.asarray(seq(cat()), np.float32), x)

@@ -61,14 +61,14 @@ def test_matches_the_handle_entry_point_on_consecutive_calls(fact, dev):
 
 
 def test_refuses_what_does_not_fit(fact, dev):
-    shape, yshape = [64, 72000], [1, 72000]
-    xd = core.tensor_descriptor(shape, "float", [72000, 1])
-    yd = core.tensor_descriptor(yshape, "float", [72000, 1])
+    shape, yshape = [256, 20000], [1, 20000]
+    xd = core.tensor_descriptor(shape, "float", [20000, 1])
+    yd = core.tensor_descriptor(yshape, "float", [20000, 1])
     rtd = core.reduce_tensor_descriptor("add", "float")
     need = core.reduction_workspace_size(fact.handle, rtd, xd, yd)
-    assert need > (512 << 10)
-    tx = dev.empty(64 * 72000 * 4, fill=0)
-    ty = dev.empty(72000 * 4, fill=0)
+    assert need > (64 << 10)
+    tx = dev.empty(256 * 20000 * 4, fill=0)
+    ty = dev.empty(20000 * 4, fill=0)
     st, msg = no_alloc_reduce(fact, "add", xd, tx, yd, ty)
     assert st == 9 and "scratch" in msg and str(need) in msg     # DD_STATUS_NOT_SUPPORTED
     st, msg = no_alloc_reduce(fact, "add", xd, None, yd, ty)
