@@ -24,8 +24,10 @@ __device__ __forceinline__ float dd_rcp_approx(float x) {
 }
 
 // exp(x) = (p + pl) * 2^n for x in [-104, 0] (callers clamp): p in [0.7, 1.43] is the rounded
-// mantissa part, pl its rounding error, n in [-150, 0].
-__device__ __forceinline__ void dd_exp_neg_raw(float x, float &p, float &pl, int &n) {
+// mantissa part, pl its rounding error, n in [-150, 0].  `nbits` is the raw bit pattern of the
+// rounding helper, 0x4B400000 + n: shifted left by 23 it is n << 23 (every set bit of 0x4B400000
+// falls off the top), which is how the callers build 2^(n+k) in two integer instructions.
+__device__ __forceinline__ void dd_exp_neg_raw(float x, float &p, float &pl, int &nbits) {
   // n = rint(x * log2 e) by the add-a-big-constant trick: both the rounded float and the integer
   // come out of one FMA (no round / float-to-int conversions, which run on the quarter-rate unit)
   const float big = fmaf(x, DD_LOG2E, 12582912.0f);  // 1.5 * 2^23: the sum's low mantissa bits are n
@@ -41,11 +43,13 @@ __device__ __forceinline__ void dd_exp_neg_raw(float x, float &p, float &pl, int
   const float t = fmaf(__fmul_rn(r, r), g, r);  // exp(r) - 1, |t| <= 0.43
   p = __fadd_rn(1.0f, t);
   pl = __fsub_rn(t, __fsub_rn(p, 1.0f));        // exact: 1 + t = p + pl
-  n = __float_as_int(big) - 0x4B400000;
+  nbits = __float_as_int(big);
 }
 
-// 2^n as a float, n in [-126, 127].
-__device__ __forceinline__ float dd_pow2(int n) { return __int_as_float((n + 127) << 23); }
+// 2^(n + k) as a float from nbits = 0x4B400000 + n; n + k must be in [-126, 127].
+__device__ __forceinline__ float dd_pow2_from_bits(int nbits, int k) {
+  return __int_as_float((int)(((unsigned)nbits << 23) + ((unsigned)(127 + k) << 23)));
+}
 
 // exp(x) for x in [-104, 0] reaches 2^-150, below the normal range.  To stay branch-free the kernels
 // carry E = exp(x) * 2^64 (always a normal float, scaled exactly by one factor) wherever exp(x) is a
@@ -56,9 +60,9 @@ __device__ __forceinline__ float dd_pow2(int n) { return __int_as_float((n + 127
 
 __device__ __forceinline__ void dd_exp_neg_biased(float x, float &Eh, float &El) {
   float p, pl;
-  int n;
-  dd_exp_neg_raw(x, p, pl, n);
-  const float sc = dd_pow2(n + DD_EXP_BIAS);
+  int nbits;
+  dd_exp_neg_raw(x, p, pl, nbits);
+  const float sc = dd_pow2_from_bits(nbits, DD_EXP_BIAS);
   Eh = __fmul_rn(p, sc);
   El = __fmul_rn(pl, sc);
 }
@@ -78,13 +82,20 @@ __device__ __forceinline__ void dd_one_plus(float eh, float el, float &dh, float
   dl = __fadd_rn(__fadd_rn(__fsub_rn(1.0f, dh), eh), el);
 }
 
+// The same from the biased pair E = e * 2^64: the un-biasing multiplications ride inside FMAs
+// (fma(Eh, 2^-64, 1) rounds 1 + eh once, exactly like the addition above).
+__device__ __forceinline__ void dd_one_plus_biased(float Eh, float El, float &dh, float &dl) {
+  dh = fmaf(Eh, DD_UNBIAS, 1.0f);
+  dl = fmaf(El, DD_UNBIAS, fmaf(Eh, DD_UNBIAS, __fsub_rn(1.0f, dh)));
+}
+
 __device__ __forceinline__ float dd_sigmoid_f32(float x) {
   float Eh, El, dh, dl;
   dd_exp_neg_biased(fmaxf(-fabsf(x), -104.0f), Eh, El);
-  dd_one_plus(__fmul_rn(Eh, DD_UNBIAS), __fmul_rn(El, DD_UNBIAS), dh, dl);
+  dd_one_plus_biased(Eh, El, dh, dl);
   const bool pos = x >= 0.0f;
-  float s = dd_quot(pos ? 1.0f : Eh, pos ? 0.0f : El, dh, dl);  // 1/(1+e) or (e/(1+e)) * 2^64
-  s = pos ? s : __fmul_rn(s, DD_UNBIAS);
+  // numerator 1 (as 2^64) or e (as E = e * 2^64); one exact un-biasing multiplication at the end
+  const float s = __fmul_rn(dd_quot(pos ? 18446744073709551616.0f : Eh, pos ? 0.0f : El, dh, dl), DD_UNBIAS);
   return x != x ? x : s;
 }
 
@@ -94,7 +105,7 @@ template <int K>
 __device__ __forceinline__ float dd_e_over_one_plus_e_sq(float xneg) {
   float Eh, El, dh, dl;
   dd_exp_neg_biased(xneg, Eh, El);
-  dd_one_plus(__fmul_rn(Eh, DD_UNBIAS), __fmul_rn(El, DD_UNBIAS), dh, dl);
+  dd_one_plus_biased(Eh, El, dh, dl);
   const float nh = Eh * (float)(1 << K), nl = El * (float)(1 << K);  // exact
   const float r0 = dd_rcp_approx(dh);
   const float rr = __fmul_rn(r0, r0);
@@ -111,18 +122,18 @@ __device__ __forceinline__ float dd_e_over_one_plus_e_sq(float xneg) {
 
 // tanh(x) = (1 - e) / (1 + e), e = exp(-2|x|).  No separate small-|x| branch: 1 - e is formed from
 // the hi/lo pair, and for |x| < 0.17 (n == 0) that difference is exactly -(exp(r) - 1), which the
-// exp kernel computed without cancellation.  Here e only ever meets 1, so its scale factor is simply
-// clamped at 2^-126 (for |x| > 43.6, where tanh is 1 to the last bit anyway).
+// exp kernel computed without cancellation.  Here e only ever meets 1, so the argument is clamped at
+// -87 (n >= -126: 2^n stays a normal float; tanh is 1 to the last bit from |x| = 9.1 on anyway).
 __device__ __forceinline__ float dd_tanh_f32(float x) {
   float p, pl, dh, dl;
-  int n;
-  dd_exp_neg_raw(fmaxf(-2.0f * fabsf(x), -104.0f), p, pl, n);
-  const float sc = dd_pow2(max(n, -126));
+  int nbits;
+  dd_exp_neg_raw(fmaxf(-2.0f * fabsf(x), -87.0f), p, pl, nbits);
+  const float sc = dd_pow2_from_bits(nbits, 0);
   const float eh = __fmul_rn(p, sc), el = __fmul_rn(pl, sc);
   dd_one_plus(eh, el, dh, dl);
-  const float nh = __fsub_rn(1.0f, eh);                                    // 1 - e as a pair
-  const float nl = __fsub_rn(__fsub_rn(__fsub_rn(1.0f, nh), eh), el);
-  const float t = copysignf(dd_quot(nh, nl, dh, dl), x);
+  // 1 - e = 2 - (1 + e) exactly: 2 - dh is exact (dh in [1, 2]) and the low word just changes sign.
+  // The pair is not normalised, which dd_quot does not need: its residual is formed exactly.
+  const float t = copysignf(dd_quot(__fsub_rn(2.0f, dh), -dl, dh, dl), x);
   return x != x ? x : t;
 }
 
