@@ -25,6 +25,7 @@ template <typename C> struct dd_math;
 template <> struct dd_math<float> {
   static __device__ __forceinline__ float exp(float x) { return expf(x); }
   static __device__ __forceinline__ float expm1(float x) { return expm1f(x); }
+  static __device__ __forceinline__ float expm1_neg(float x) { return dd_expm1_neg(x); }
   static __device__ __forceinline__ float tanh(float x) { return tanhf(x); }
   static __device__ __forceinline__ float abs(float x) { return fabsf(x); }
   static __device__ __forceinline__ float fma(float a, float b, float c) { return fmaf(a, b, c); }
@@ -48,6 +49,7 @@ template <> struct dd_math<float> {
 template <> struct dd_math<double> {
   static __device__ __forceinline__ double exp(double x) { return ::exp(x); }
   static __device__ __forceinline__ double expm1(double x) { return ::expm1(x); }
+  static __device__ __forceinline__ double expm1_neg(double x) { return ::expm1(x); }
   static __device__ __forceinline__ double tanh(double x) { return ::tanh(x); }
   static __device__ __forceinline__ double abs(double x) { return ::fabs(x); }
   static __device__ __forceinline__ double fma(double a, double b, double c) { return ::fma(a, b, c); }
@@ -92,7 +94,7 @@ __device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp) {
   } else if (MODE == DD_ACTIVATION_TANH) {
     return M::tanh_(x);
   } else if (MODE == DD_ACTIVATION_ELU) {
-    return x > (C)0 ? x : dd_mul_rn(coef, M::expm1(x));
+    return x > (C)0 ? x : dd_mul_rn(coef, M::expm1_neg(x));
   } else if (MODE == DD_ACTIVATION_LINEAR) {
     return M::fma(coef, x, shift);
   } else if (MODE == DD_ACTIVATION_CLIPPED_RELU) {

@@ -143,3 +143,15 @@ __device__ __forceinline__ float dd_exp_neg_rounded(float x) {
   dd_exp_neg_biased(fmaxf(x, -104.0f), Eh, El);
   return x != x ? x : __fmul_rn(__fadd_rn(Eh, El), DD_UNBIAS);
 }
+
+// exp(x) - 1 for x <= 0 (elu forward): (eh - 1) + el.  For |x| < 0.35 the reduction has n = 0, so
+// eh - 1 is exact and the sum is the cancellation-free exp(r) - 1 the exp kernel produced; further
+// out exp(x) <= 0.71 and the subtraction does not cancel.
+__device__ __forceinline__ float dd_expm1_neg(float x) {
+  float p, pl;
+  int nbits;
+  dd_exp_neg_raw(fmaxf(x, -87.0f), p, pl, nbits);  // exp(-87) - 1 is already -1 to the last bit
+  const float sc = dd_pow2_from_bits(nbits, 0);
+  const float r = __fadd_rn(__fsub_rn(__fmul_rn(p, sc), 1.0f), __fmul_rn(pl, sc));
+  return x != x ? x : r;
+}

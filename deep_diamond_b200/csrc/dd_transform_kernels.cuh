@@ -206,6 +206,41 @@ __global__ void __launch_bounds__((dd_tile_geom<S, D>::NT)) dd_tile_kernel(ddTil
   }
 }
 
+// Scalar tile: the same A/B transposition for tensors whose rows are not 16-byte aligned (odd
+// spatial sizes, odd channel counts, unaligned bases).  32 x 32 elements per CTA through a padded
+// shared-memory tile: warps read 32 consecutive elements along A and write 32 consecutive elements
+// along B, so both global sides stay coalesced (at element, not 16-byte, granularity).
+template <typename S, typename D, typename C, bool RAW>
+__global__ void __launch_bounds__(256) dd_tile_scalar_kernel(ddTileParams p) {
+  __shared__ D tile[32][33];
+  uint32_t id = blockIdx.x, ta, tb;
+  dd_divmod(id, p.fdA, id, ta);
+  dd_divmod(id, p.fdB, id, tb);
+  int64_t offx = 0, offy = 0;
+  for (int d = p.nb - 1; d >= 0; d--) {
+    uint32_t r;
+    dd_divmod(id, p.fdBatch[d], id, r);
+    offx += (int64_t)r * p.bsx[d];
+    offy += (int64_t)r * p.bsy[d];
+  }
+  const S *xb = (const S *)p.x + offx;
+  D *yb = (D *)p.y + offy;
+  const int64_t a0 = (int64_t)ta * 32, b0 = (int64_t)tb * 32;
+  const C alpha = (C)p.alpha;
+  const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const int64_t b = b0 + ly + 8 * k, a = a0 + lx;
+    if (a < p.LA && b < p.LB) tile[ly + 8 * k][lx] = dd_cvt<S, D, C, RAW>::f(xb[b * p.sxB + a], alpha);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const int64_t a = a0 + ly + 8 * k, b = b0 + lx;
+    if (a < p.LA && b < p.LB) yb[a * p.syA + b] = tile[lx][ly + 8 * k];
+  }
+}
+
 // ------------------------------------------------------------------ strided ------------------
 
 struct ddStridedXformParams {
@@ -284,27 +319,30 @@ static ddStatus_t dd_launch_flat(ddHandle_t h, const ddXformPlan &pl) {
   return DD_STATUS_SUCCESS;
 }
 
-// Fills tile parameters if the canonical space fits the tile kernel; returns false otherwise.
+// Fills tile parameters if the canonical space fits a tile kernel; returns 0 if not, 1 for the
+// 16-byte vector tile kernel, 2 for the scalar tile kernel (rows not 16-byte aligned).
 template <typename S, typename D>
-static bool dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
+static int dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
   typedef dd_tile_geom<S, D> G;
   const ddCanon &c = pl.canon;
-  if (pl.beta != 0.0 || c.nd < 2) return false;
+  if (pl.beta != 0.0 || c.nd < 2) return 0;
   const int B = c.nd - 1;
-  if (c.st[1][B] != 1) return false;
+  if (c.st[1][B] != 1) return 0;
   int A = -1;
   for (int i = 0; i < c.nd - 1; i++)
     if (c.st[0][i] == 1) A = i;
-  if (A < 0) return false;
-  if (c.nd - 2 > DD_TILE_BATCH_DIMS) return false;
-  if ((((uintptr_t)pl.x) | ((uintptr_t)pl.y)) & 15) return false;
-  if (c.dims[A] % G::VS || c.dims[B] % G::VD) return false;
+  if (A < 0) return 0;
+  if (c.nd - 2 > DD_TILE_BATCH_DIMS) return 0;
+  bool vec = ((((uintptr_t)pl.x) | ((uintptr_t)pl.y)) & 15) == 0;
+  if (c.dims[A] % G::VS || c.dims[B] % G::VD) vec = false;
   for (int i = 0; i < c.nd; i++) {
-    if (i != A && (c.st[0][i] % G::VS)) return false;
-    if (i != B && (c.st[1][i] % G::VD)) return false;
+    if (i != A && (c.st[0][i] % G::VS)) vec = false;
+    if (i != B && (c.st[1][i] % G::VD)) vec = false;
   }
-  // a tile that is mostly padding wastes the machine: leave short dims to the strided kernel
-  if (c.dims[A] < G::VS * 2 || c.dims[B] < G::VD * 2) return false;
+  // a tile that is mostly padding wastes the machine: leave short dims to the other kernels
+  if (c.dims[A] < G::VS * 2 || c.dims[B] < G::VD * 2) vec = false;
+  const int TAe = vec ? G::TA : 32, TBe = vec ? G::TB : 32;
+  if (!vec && (c.dims[A] < 8 || c.dims[B] < 8)) return 0;  // too thin to be worth a tile
   tp->x = pl.x;
   tp->y = pl.y;
   tp->LA = c.dims[A];
@@ -319,26 +357,31 @@ static bool dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
     tp->bsy[tp->nb] = c.st[1][i];
     tp->nb++;
   }
-  tp->tilesA = (tp->LA + G::TA - 1) / G::TA;
-  tp->tilesB = (tp->LB + G::TB - 1) / G::TB;
+  tp->tilesA = (tp->LA + TAe - 1) / TAe;
+  tp->tilesB = (tp->LB + TBe - 1) / TBe;
   int64_t tiles = tp->tilesA * tp->tilesB;
   for (int i = 0; i < tp->nb; i++) tiles *= tp->bdims[i];
-  if (tiles >= 0x7fffffffLL) return false;
+  if (tiles >= 0x7fffffffLL) return 0;
   tp->fdA = dd_fastdiv((uint32_t)tp->tilesA);
   tp->fdB = dd_fastdiv((uint32_t)tp->tilesB);
   for (int i = 0; i < tp->nb; i++) tp->fdBatch[i] = dd_fastdiv((uint32_t)tp->bdims[i]);
   tp->alpha = pl.alpha;
-  return true;
+  return vec ? 1 : 2;
 }
 
 template <typename S, typename D, typename C, bool RAW>
-static ddStatus_t dd_launch_tile(ddHandle_t h, const ddTileParams &tp) {
+static ddStatus_t dd_launch_tile(ddHandle_t h, const ddTileParams &tp, int kind) {
   typedef dd_tile_geom<S, D> G;
   int64_t tiles = tp.tilesA * tp.tilesB;
   for (int i = 0; i < tp.nb; i++) tiles *= tp.bdims[i];
   if (tiles > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "transform/tile: too many tiles");
-  dd_tile_kernel<S, D, C, RAW><<<(unsigned)tiles, G::NT, 0, h->stream>>>(tp);
-  DD_LAUNCHED(h, "transform/tile");
+  if (kind == 1) {
+    dd_tile_kernel<S, D, C, RAW><<<(unsigned)tiles, G::NT, 0, h->stream>>>(tp);
+    DD_LAUNCHED(h, "transform/tile");
+  } else {
+    dd_tile_scalar_kernel<S, D, C, RAW><<<(unsigned)tiles, 256, 0, h->stream>>>(tp);
+    DD_LAUNCHED(h, "transform/tile-scalar");
+  }
   return DD_STATUS_SUCCESS;
 }
 
@@ -364,7 +407,7 @@ static ddStatus_t dd_xform_typed(ddHandle_t h, const ddXformPlan &pl) {
   const ddCanon &c = pl.canon;
   if (c.nd == 1 && c.st[0][0] == 1 && c.st[1][0] == 1) return dd_launch_flat<S, D, C, RAW>(h, pl);
   ddTileParams tp;
-  if (dd_tile_plan<S, D>(pl, &tp)) return dd_launch_tile<S, D, C, RAW>(h, tp);
+  if (int kind = dd_tile_plan<S, D>(pl, &tp)) return dd_launch_tile<S, D, C, RAW>(h, tp, kind);
   return dd_launch_strided<S, D, C, RAW>(h, pl);
 }
 

@@ -110,6 +110,24 @@ def test_nchw_nhwc_both_ways(fact, dev, oracle, shape, pair):
     run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=5)
 
 
+def test_unaligned_transposes_use_the_scalar_tile(fact, dev, oracle):
+    # rows not 16-byte aligned: odd spatial sizes (7x7, 13x13), odd channel counts, every type width
+    for shape in ([3, 24, 7, 7], [2, 33, 13, 13], [5, 9, 3, 11], [1, 100, 1, 37]):
+        for sdt, ddt in (("float", "float"), ("float", "bf16"), ("byte", "byte"), ("half", "float"), ("double", "float")):
+            run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), sdt, ddt, seed=31, expect="transform/tile-scalar")
+            run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=32, expect="transform/tile-scalar")
+    # an unaligned base pointer demotes an otherwise aligned reorder to the scalar tile
+    shape = [2, 32, 8, 16]
+    xs = make_values(np.random.default_rng(33), 1 + int(np.prod(shape)), "float")
+    want = np.zeros(int(np.prod(shape)), np.float32)
+    oracle.reorder(oracle.as_layout(xs, shape, nchw(shape), offset=1), oracle.as_layout(want, shape, nhwc(shape)))
+    tx, ty = dev.put(xs), dev.put(np.zeros_like(want))
+    core.transform_tensor(fact.handle, 1.0, core.tensor_descriptor(shape, "float", nchw(shape)), tx.data_ptr() + 4,
+                          0.0, core.tensor_descriptor(shape, "float", nhwc(shape)), ty)
+    assert fact.handle.last_kernel() == "transform/tile-scalar"
+    assert np.array_equal(dev.get(ty, np.float32), want)
+
+
 def test_tile_ragged_edges(fact, dev, oracle):
     # extents that are vector-aligned but not tile-aligned, in both tiled dims, with batch dims
     for shape in ([3, 72, 5, 12], [2, 200, 3, 28], [7, 8, 2, 68]):
