@@ -87,7 +87,9 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
     const int64_t want = desired * gpb;
     if (nout < want) {
       int64_t units = p.R1 * p.cpr;
-      int64_t S = (want + nout - 1) / nout;
+      // once splitting, aim at one full wave of the 4-CTA-per-SM residency (64 registers/thread)
+      int64_t S = ((int64_t)h->smCount * 4 * gpb) / nout;
+      if (S < 2) S = 2;
       if (S > units / 4) S = units / 4;
       if (S > 1024) S = 1024;
       if (S > 1) {
@@ -98,8 +100,6 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
         } else {
           p.splitR1 = 0;
           if (S > p.cpr) S = p.cpr;
-          int64_t per = (p.cpr + S - 1) / S;
-          S = (p.cpr + per - 1) / per;
         }
       }
       p.S = S < 1 ? 1 : (int)S;

@@ -86,7 +86,7 @@ struct ddRedParams {
   int G;             // row: threads per group (32 or 256)
   int64_t CH;        // row: elements of r2 covered per group iteration (G * V)
   int64_t cpr;       // row: chunks per r2 run
-  int splitR1;       // row: 1 = splits partition r1, 0 = splits partition the chunks of r2
+  int splitR1;       // row: 1 = splits partition r1, 0 = splits interleave the chunks of r2
   int TX;            // col: lanes along k2
   int64_t tilesK2;   // col: tiles along k2
   double alpha, beta, count;
@@ -154,20 +154,22 @@ __global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
     s = (int)(g - out * p.S);
     k1 = out / p.K2;
     k2 = out - k1 * p.K2;
-    int64_t r1lo = 0, r1hi = p.R1, jlo = 0, jhi = p.cpr;
+    // splits either partition r1 (each takes whole runs) or interleave the chunks of every run
+    // (split s takes chunks s, s + S, ...): concurrently running splits of one output then read
+    // neighbouring 16-byte-vector rows, like one flat stream
+    int64_t r1lo = 0, r1hi = p.R1, jlo = 0, jstep = 1;
     if (p.S > 1) {
       if (p.splitR1) {
         int64_t per = (p.R1 + p.S - 1) / p.S;
         r1lo = s * per;
         r1hi = r1lo + per < p.R1 ? r1lo + per : p.R1;
       } else {
-        int64_t per = (p.cpr + p.S - 1) / p.S;
-        jlo = s * per;
-        jhi = jlo + per < p.cpr ? jlo + per : p.cpr;
+        jlo = s;
+        jstep = p.S;
       }
     }
     const T *xb = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2;
-    const int64_t nj = jhi - jlo;
+    const int64_t nj = jlo < p.cpr ? (p.cpr - jlo + jstep - 1) / jstep : 0;
     const int64_t iters = (r1hi > r1lo && nj > 0) ? (r1hi - r1lo) * nj : 0;
     int64_t r1 = r1lo, j = jlo;
     for (int64_t it = 0; it < iters; it += U) {
@@ -188,8 +190,8 @@ __global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
             vals[q][0] = dd_load<C, T>(*ptr);
           }
         }
-        j++;
-        if (j == jhi) { j = jlo; r1++; }
+        j += jstep;
+        if (j >= p.cpr) { j = jlo; r1++; }
       }
 #pragma unroll
       for (int q = 0; q < U; q++) {
@@ -226,7 +228,7 @@ __global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
 // col: CTA = TX lanes along k2 (V elements each, TX a power of two <= 256) x TY = 256/TX row
 // groups striding over r1.
 template <typename T, typename C, int OPC, bool VEC>
-__global__ void __launch_bounds__(256) dd_reduce_col_kernel(ddRedParams p) {
+__global__ void __launch_bounds__(256, 8) dd_reduce_col_kernel(ddRedParams p) {
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;
   __shared__ C smem[256 * V];
