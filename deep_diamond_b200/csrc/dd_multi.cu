@@ -76,7 +76,7 @@ extern "C" ddStatus_t ddMultiTransform(ddHandle_t h, int count, const ddTensorDe
   if (!h) return DD_STATUS_BAD_PARAM;
   if (count < 1 || count > DD_MULTI_MAX) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddMultiTransform: count must be in 1..%d", DD_MULTI_MAX);
   if (!xDescs || !xs || !yDescs || !ys) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddMultiTransform: null pointer");
-  static ddMultiParams p;  // 3 KB: kept off the stack; a handle is driven by one thread
+  static thread_local ddMultiParams p;  // 3 KB: kept off the stack, one per calling thread
   memset(&p, 0, sizeof(p));
   p.count = count;
   const ddDataType_t st = xDescs[0] ? xDescs[0]->dtype : DD_DATA_FLOAT, dt = yDescs[0] ? yDescs[0]->dtype : DD_DATA_FLOAT;

@@ -5,6 +5,7 @@
 #include "dd_internal.cuh"
 
 #include <dlfcn.h>
+#include <mutex>
 #include <new>
 
 // The handful of NCCL declarations used, spelled out so the build needs no NCCL header.  They
@@ -28,8 +29,10 @@ struct ddNccl {
 };
 
 static ddNccl g_nccl;
+static std::mutex g_nccl_mu;
 
 static bool load_nccl() {
+  std::lock_guard<std::mutex> lock(g_nccl_mu);
   if (g_nccl.lib) return true;
   void *lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
   if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);

@@ -421,7 +421,7 @@ struct ddGatherPlan {
 
 template <typename S, typename D, typename C, bool RAW>
 static ddStatus_t dd_gather_typed(ddHandle_t h, const ddGatherPlan &pl) {
-  static ddGatherParams p;  // 8 KB: kept off the stack; a handle is driven by one thread
+  static thread_local ddGatherParams p;  // 8 KB: kept off the stack, one per calling thread
   for (int base = 0; base < pl.count; base += DD_GATHER_CHUNK) {
     int n = pl.count - base < DD_GATHER_CHUNK ? pl.count - base : DD_GATHER_CHUNK;
     p.x = pl.x;

@@ -6,6 +6,8 @@ deep-diamond-cuda/src/clojure/uncomplicate/diamond/internal/cudnn/directed.clj (
 :352-363; sum :1722-1833).  A blueprint is called with source tensors to make a layer; a layer has
 ``forward`` / ``backward`` and the Transfer / DiffTransfer accessors.
 """
+import builtins as _builtins
+
 from . import core
 from . import tensor as _t
 from ._lib import DiamondError
@@ -300,13 +302,8 @@ def concat_offsets(split_dim, sub_shapes):
 def concat_dst_shape(conc_dim, src_shapes):
     """``concat-dst-shape`` (utils.clj:98-100)."""
     out = list(src_shapes[0])
-    out[conc_dim] = builtins_sum(int(s[conc_dim]) for s in src_shapes)
+    out[conc_dim] = _builtins.sum(int(s[conc_dim]) for s in src_shapes)  # this module defines its own `sum`
     return out
-
-
-import builtins as _builtins  # noqa: E402
-
-builtins_sum = _builtins.sum
 
 
 class _Pairs:

@@ -11,6 +11,15 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    # the library and the oracle are built artefacts (kept out of git): build them when a fresh
+    # checkout runs the tests before anything else did (nvcc cross-compiles without a GPU)
+    lib = os.path.join(ROOT, "deep_diamond_b200", "libdd_b200.so")
+    if not os.path.exists(lib):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("dd_b200_build", os.path.join(ROOT, "deep_diamond_b200", "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build(verbose=False)
 
 
 @pytest.fixture(scope="session")
