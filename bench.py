@@ -158,6 +158,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    oracle.set_num_threads(os.cpu_count() or 1)  # all host threads, whatever the launcher exported
     n_batch = 32
     vals = []
     for _ in range(args.warmup):
@@ -270,7 +271,10 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_on
             stream.synchronize()
             rows.append({"op": name, "config": cfg, "kernel": h.last_kernel()})
             return
-        ms = graph_ms(torch, fact, fn, per_graph, replays) if graph else event_ms(torch, fn, stream, 100, 10)
+        if graph:
+            ms = graph_ms(torch, fact, fn, per_graph, replays)
+        else:
+            ms = event_ms(torch, fn, stream, 100, 10)
         row = op_row(name, cfg, nbytes, ms, peak, elems)
         row["kernel"] = h.last_kernel()
         rows.append(row)
@@ -543,6 +547,7 @@ def run_ours(args):
 
     cpu = None
     if rank == 0 and world == 1:
+        oracle.set_num_threads(os.cpu_count() or 1)
         gbs, dt, elems = cpu_sample(oracle, 32, 3)
         cpu = {"value": round(gbs, 3), "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
                "Gelem/s": round(elems * len(ACTS) * 2 / dt / 1e9, 4),

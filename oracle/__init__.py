@@ -221,6 +221,12 @@ def num_threads():
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n):
+    """Overrides OMP_NUM_THREADS (launchers such as torch.distributed.run set it to 1)."""
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 # ---------------------------------------------------------------- synthetic inputs ------------
 # Seeded generators for the benchmark configurations (shapes, value distributions and seeds as
 # BASELINE.json states them).  Shared by the GPU and CPU legs so both see identical inputs.

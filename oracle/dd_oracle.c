@@ -631,6 +631,14 @@ int oracle_equals(int t, int nd, const int64_t *dims, const int64_t *xst, const 
   return !diff;
 }
 
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
   int n = 1;
 #ifdef _OPENMP
