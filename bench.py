@@ -152,6 +152,34 @@ def cpu_sample(oracle, n_batch, reps):
     return nbytes / dt / 1e9, dt, x.size
 
 
+def onednn_forward_sample(n_batch=32, reps=3):
+    """Real oneDNN (the build inside PyTorch, through mkldnn tensors) on the host cores for the three
+    forward activations it exposes: elements/s and GB/s on a [n_batch,256,28,28] slice.  It has no
+    elu, no backward and no nhwc reorder through this route, so it complements the oracle's number
+    rather than replacing it."""
+    try:
+        import torch
+        torch.set_num_threads(os.cpu_count() or 1)
+        import oracle
+        shape = [n_batch] + SHAPE_C2[1:]
+        x = torch.from_numpy(oracle.gen_normal(shape, 2.0, 1)).to_mkldnn()
+        out = {}
+        for name, fn in (("relu", torch.relu), ("logistic", torch.sigmoid), ("tanh", torch.tanh)):
+            fn(x)
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn(x)
+            dt = (time.perf_counter() - t0) / reps
+            n = int(np.prod(shape))
+            out[name] = {"Gelem/s": round(n / dt / 1e9, 3), "GB/s": round(n * 8 / dt / 1e9, 2)}
+        ver = [ln.strip(" -") for ln in torch.__config__.show().splitlines() if "MKL-DNN" in ln]
+        out["library"] = ver[0] if ver else "oneDNN (version unknown)"
+        out["threads"] = torch.get_num_threads()
+        return out
+    except Exception as e:  # mkldnn tensors unavailable: report that, the oracle number stands
+        return {"unavailable": str(e)[:200]}
+
+
 def run_reference(args):
     import oracle
     oracle.build()
@@ -176,7 +204,7 @@ def run_reference(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
-                         "sample": sample},
+                         "sample": sample, "onednn_forward_via_torch": onednn_forward_sample()},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference is Clojure on the JVM calling oneDNN; no JVM on this box, so this arm "
                 "times oracle/ (the CPU restatement of its DNNL path, OpenMP, all host threads)",
@@ -551,7 +579,8 @@ def run_ours(args):
         gbs, dt, elems = cpu_sample(oracle, 32, 3)
         cpu = {"value": round(gbs, 3), "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
                "Gelem/s": round(elems * len(ACTS) * 2 / dt / 1e9, 4),
-               "sample": "the 8 eltwise ops on a [32,256,28,28] slice (1/8 of the batch), 3 repetitions, oracle/ (C + OpenMP)"}
+               "sample": "the 8 eltwise ops on a [32,256,28,28] slice (1/8 of the batch), 3 repetitions, oracle/ (C + OpenMP)",
+               "onednn_forward_via_torch": onednn_forward_sample()}
 
     if rank == 0:
         line = {
