@@ -72,6 +72,33 @@ class HostTensor:
                                                              self.values()[:16])
 
 
+class ZeroDescriptor:
+    """Descriptor of a tensor with a zero extent.  The C library (like cuDNN) only takes positive
+    extents, so such tensors never reach it: the reference keeps a general descriptor for them too
+    (cudnn/tensor.clj:119-122) and turns their transformers into no-ops (:204-207)."""
+
+    ptr = None
+
+    def __init__(self, shape, dtype_code, strides):
+        self.dims, self.dtype_code, self.strides = [int(d) for d in shape], dtype_code, [int(s) for s in strides]
+        self.data_type = DATA_TYPE_NAME[dtype_code]
+
+    shape = property(lambda self: list(self.dims))
+    layout = property(lambda self: list(self.strides))
+
+    def __eq__(self, other):
+        return (isinstance(other, ZeroDescriptor) and self.dims == other.dims
+                and self.dtype_code == other.dtype_code and self.strides == other.strides)
+
+    __hash__ = None
+
+    def view(self):
+        return self
+
+    def release(self):
+        return True
+
+
 # ====================== Tensor ==================================================
 
 class B200Tensor:
@@ -91,7 +118,7 @@ class B200Tensor:
         self.n_index = int(n_index)
         self.master = master
         self.width = DATA_TYPE_WIDTH[tdesc.dtype_code]
-        self.storage_elems = _span(tdesc.dims, tdesc.strides)
+        self.storage_elems = _span(tdesc.dims, tdesc.strides) if self.nc > 0 else 0
 
     # --- protocols ---------------------------------------------------------------
     @property
@@ -470,19 +497,23 @@ class B200Factory:
     def create_tensor_desc(self, shape, dtype=None, fmt=None):
         if dtype is None and fmt is None and not isinstance(shape, (list, tuple)):
             tdesc = shape
-            if isinstance(tdesc, core.TensorDescriptor):
+            if isinstance(tdesc, (core.TensorDescriptor, ZeroDescriptor)):
                 return tdesc
-            if hasattr(tdesc, "desc") and isinstance(tdesc.desc, core.TensorDescriptor):
+            if hasattr(tdesc, "desc") and isinstance(tdesc.desc, (core.TensorDescriptor, ZeroDescriptor)):
                 return tdesc.desc
             shape, dtype, fmt = _shape_of(tdesc), _dtype_of(tdesc), _layout_of(tdesc)
         shape = [int(d) for d in shape]
         if any(d < 0 for d in shape):
             raise DiamondError("Tensor dimensions must not be negative.", {"shape": shape})
+        if any(d == 0 for d in shape):
+            from .constants import layout_strides
+            code = dtype if isinstance(dtype, int) else enc_keyword(DATA_TYPE, dtype if dtype is not None else "float", "data type")
+            return ZeroDescriptor(shape, code, layout_strides([max(d, 1) for d in shape], fmt))
         return core.tensor_descriptor(shape, dtype if dtype is not None else "float", fmt)
 
     def create_tensor(self, tensor_desc, batch_index=0, init=True):
         td = self.create_tensor_desc(tensor_desc)
-        nbytes = max(1, core.bytesize(td))
+        nbytes = 1 if isinstance(td, ZeroDescriptor) else max(1, core.bytesize(td))
         with torch.cuda.stream(self.stream):
             alloc = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         tz = B200Tensor(self, alloc, 0, nbytes // DATA_TYPE_WIDTH[td.dtype_code], td, batch_index, True)
@@ -563,6 +594,8 @@ class B200Factory:
 
     def copy(self, x, y):
         """``copy`` (:166-168): transform-tensor with alpha 1, beta 0."""
+        if x.nc == 0 and y.nc == 0:
+            return y
         core.transform_tensor(self.handle, 1.0, x.desc, x, 0.0, y.desc, y)
         return y
 
@@ -701,6 +734,9 @@ def transfer(source, destination):
 
     if isinstance(source, B200Tensor) and isinstance(destination, B200Tensor):
         source.fact.copy(source, destination)  # :542-544
+        return destination
+
+    if isinstance(source, B200Tensor) and source.nc == 0:
         return destination
 
     if isinstance(destination, B200Tensor):

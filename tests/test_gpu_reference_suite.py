@@ -503,3 +503,15 @@ def test_branch_concat_large_against_oracle(fact, dev):
         assert np.array_equal(np.asarray(seq(t), np.float32), want)
     cat = dnn.concatenate(fact, 1, outs)(outs)
     assert np.array_equal(np.asarray(seq(cat()), np.float32), x)
+
+
+def test_zero_sized_tensors(fact):
+    """Zero extents never reach the C library: descriptors stay general, transformers are no-ops
+    (cudnn/tensor.clj:119-122, 204-207) and transfers do nothing (:584, :598)."""
+    z = tensor(fact, [0, 3, 2, 2], "float", "nchw")
+    w = tensor(fact, [0, 3, 2, 2], "float", "nhwc")
+    assert T.dim(z) == 0 and T.shape(z) == [0, 3, 2, 2] and asum(z) == 0.0
+    assert transformer(z, w)() is not None
+    assert transfer([1, 2, 3], z) is z
+    assert transfer(z, w) is w
+    assert entry_(z, 1.0) is z
