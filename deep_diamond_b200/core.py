@@ -253,7 +253,7 @@ def multi_transform(handle, pairs):
     return handle
 
 
-COST_KIND = {"quadratic": 0, "mean-absolute": 1}
+COST_KIND = {"quadratic": 0, "mean-absolute": 1, "crossentropy": 2}
 
 
 def cost_diff(handle, kind, desc_a, a, y, d, cost):

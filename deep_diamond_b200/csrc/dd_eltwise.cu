@@ -25,26 +25,24 @@ template <typename C> struct dd_math;
 template <> struct dd_math<float> {
   static __device__ __forceinline__ float exp(float x) { return expf(x); }
   static __device__ __forceinline__ float expm1(float x) { return expm1f(x); }
-  static __device__ __forceinline__ float expm1_neg(float x) { return dd_expm1_neg(x); }
+  static __device__ __forceinline__ float expm1_neg(float x) { return dd_expm1_neg<float>(x); }
   static __device__ __forceinline__ float tanh(float x) { return tanhf(x); }
   static __device__ __forceinline__ float abs(float x) { return fabsf(x); }
   static __device__ __forceinline__ float fma(float a, float b, float c) { return fmaf(a, b, c); }
   static __device__ __forceinline__ float max(float a, float b) { return fmaxf(a, b); }
   static __device__ __forceinline__ float min(float a, float b) { return fminf(a, b); }
   static __device__ __forceinline__ float div(float a, float b) { return __fdiv_rn(a, b); }
-  static __device__ __forceinline__ float sigmoid(float x) { return dd_sigmoid_f32(x); }
+  static __device__ __forceinline__ float sigmoid(float x) { return dd_sigmoid<float>(x); }
   // s*(1-s) = e/(1+e)^2 with e = exp(-|x|)
   static __device__ __forceinline__ float dsigmoid(float x) {
-    float d = dd_e_over_one_plus_e_sq<0>(fmaxf(-fabsf(x), -104.0f));
-    return x != x ? x : d;
+    return dd_e_over_one_plus_e_sq<float, 0>(dd_lane<float>::neg_abs_clamped<1>(x, -104.0f));
   }
-  static __device__ __forceinline__ float tanh_(float x) { return dd_tanh_f32(x); }
+  static __device__ __forceinline__ float tanh_(float x) { return dd_tanh<float>(x); }
   // 1 - tanh^2 = 4e/(1+e)^2 with e = exp(-2|x|)
   static __device__ __forceinline__ float dtanh(float x) {
-    float d = dd_e_over_one_plus_e_sq<2>(fmaxf(-2.0f * fabsf(x), -104.0f));
-    return x != x ? x : d;
+    return dd_e_over_one_plus_e_sq<float, 2>(dd_lane<float>::neg_abs_clamped<2>(x, -104.0f));
   }
-  static __device__ __forceinline__ float exp_neg(float x) { return dd_exp_neg_rounded(x); }
+  static __device__ __forceinline__ float exp_neg(float x) { return dd_exp_neg_rounded<float>(x); }
 };
 template <> struct dd_math<double> {
   static __device__ __forceinline__ double exp(double x) { return ::exp(x); }
@@ -126,6 +124,31 @@ __device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef) {
   }
 }
 
+// The transcendental modes on TWO fp32 elements at a time (packed f32x2 arithmetic): the same
+// formulas as above, lane for lane, with identical results.
+template <int MODE> struct dd_act_packed { static constexpr bool value = false; };
+template <> struct dd_act_packed<DD_ACTIVATION_SIGMOID> { static constexpr bool value = true; };
+template <> struct dd_act_packed<DD_ACTIVATION_TANH> { static constexpr bool value = true; };
+template <> struct dd_act_packed<DD_ACTIVATION_ELU> { static constexpr bool value = true; };
+
+template <int MODE>
+__device__ __forceinline__ float2 dd_act_fwd2(float2 x, float coef) {
+  typedef dd_lane<float2> L;
+  if (MODE == DD_ACTIVATION_SIGMOID) return dd_sigmoid<float2>(x);
+  if (MODE == DD_ACTIVATION_TANH) return dd_tanh<float2>(x);
+  return L::sel_pos(x, x, L::mul(L::bc(coef), dd_expm1_neg<float2>(x)));  // ELU
+}
+
+template <int MODE>
+__device__ __forceinline__ float2 dd_act_bwd2(float2 x, float2 dy, float coef) {
+  typedef dd_lane<float2> L;
+  if (MODE == DD_ACTIVATION_SIGMOID)
+    return L::mul(dy, dd_e_over_one_plus_e_sq<float2, 0>(L::neg_abs_clamped<1>(x, -104.0f)));
+  if (MODE == DD_ACTIVATION_TANH)
+    return L::mul(dy, dd_e_over_one_plus_e_sq<float2, 2>(L::neg_abs_clamped<2>(x, -104.0f)));
+  return L::sel_pos(x, dy, L::mul(dy, L::mul(L::bc(coef), dd_exp_neg_rounded<float2>(x))));  // ELU
+}
+
 // alpha*v + beta*old.  Multiplying by exactly 1 is exact, so alpha is applied unconditionally.
 template <typename C>
 __device__ __forceinline__ C dd_blend(C alpha, C v, C beta, C old, bool useOld) {
@@ -165,12 +188,24 @@ __global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) 
       uint4 res;
       const T *xv = (const T *)&xin, *dv = (const T *)&din, *ov = (const T *)&oin;
       T *rv = (T *)&res;
+      if constexpr (sizeof(C) == 4 && dd_act_packed<MODE>::value) {
 #pragma unroll
-      for (int k = 0; k < V; k++) {
-        C xc = dd_load<C, T>(xv[k]);
-        C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dv[k]), coef)
-                  : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
-        rv[k] = PLAIN ? dd_store<T, C>(v) : dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
+        for (int k = 0; k < V; k += 2) {
+          const float2 xc = make_float2(dd_load<float, T>(xv[k]), dd_load<float, T>(xv[k + 1]));
+          float2 v;
+          if (BWD) v = dd_act_bwd2<MODE>(xc, make_float2(dd_load<float, T>(dv[k]), dd_load<float, T>(dv[k + 1])), coef);
+          else v = dd_act_fwd2<MODE>(xc, coef);
+          rv[k] = PLAIN ? dd_store<T, float>(v.x) : dd_store<T, float>(dd_blend(alpha, v.x, beta, dd_load<float, T>(ov[k]), useOld));
+          rv[k + 1] = PLAIN ? dd_store<T, float>(v.y) : dd_store<T, float>(dd_blend(alpha, v.y, beta, dd_load<float, T>(ov[k + 1]), useOld));
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < V; k++) {
+          C xc = dd_load<C, T>(xv[k]);
+          C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dv[k]), coef)
+                    : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+          rv[k] = PLAIN ? dd_store<T, C>(v) : dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
+        }
       }
       *(uint4 *)(out + i * V) = res;
     }

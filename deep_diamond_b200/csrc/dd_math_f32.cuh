@@ -10,6 +10,14 @@
 //                  exp(r) - 1 = r + r^2*g(r), g a degree-5 polynomial fitted by least squares on
 //                  Chebyshev nodes over |r| <= 1.02*ln2/2 (max error 1.6e-9 in g, 2e-10 in exp);
 //                  result = (1 + t) * 2^n with the rounding error of 1 + t kept as the low word.
+//
+// Every function is written once over a lane type F: `float` (one element) or `float2` (two
+// elements in a 64-bit register pair).  On sm_100 the float2 form issues the packed
+// fma/add/mul.rn.f32x2 instructions, one per TWO elements; each lane of a packed instruction is the
+// same IEEE round-to-nearest operation as its scalar twin, so both forms return identical bits.
+// Only what has no packed form stays per lane: the clamp, the reciprocal seed, the exponent
+// integer arithmetic and the selects.  Subtractions are written as fma(u, -1, t) or as additions of
+// negated constants so that no separate negation is needed on a packed operand.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -23,135 +31,208 @@ __device__ __forceinline__ float dd_rcp_approx(float x) {
   return r;
 }
 
-// exp(x) = (p + pl) * 2^n for x in [-104, 0] (callers clamp): p in [0.7, 1.43] is the rounded
-// mantissa part, pl its rounding error, n in [-150, 0].  `nbits` is the raw bit pattern of the
-// rounding helper, 0x4B400000 + n: shifted left by 23 it is n << 23 (every set bit of 0x4B400000
-// falls off the top), which is how the callers build 2^(n+k) in two integer instructions.
-__device__ __forceinline__ void dd_exp_neg_raw(float x, float &p, float &pl, int &nbits) {
-  // n = rint(x * log2 e) by the add-a-big-constant trick: both the rounded float and the integer
-  // come out of one FMA (no round / float-to-int conversions, which run on the quarter-rate unit)
-  const float big = fmaf(x, DD_LOG2E, 12582912.0f);  // 1.5 * 2^23: the sum's low mantissa bits are n
-  const float fn = __fsub_rn(big, 12582912.0f);
-  float r = fmaf(fn, -DD_LN2_HI, x);
-  r = fmaf(fn, -DD_LN2_LO, r);
-  float g = 0.00019901622727047652f;
-  g = fmaf(g, r, 0.0013935454189777374f);
-  g = fmaf(g, r, 0.008333295583724976f);
-  g = fmaf(g, r, 0.04166644811630249f);
-  g = fmaf(g, r, 0.1666666716337204f);
-  g = fmaf(g, r, 0.5f);
-  const float t = fmaf(__fmul_rn(r, r), g, r);  // exp(r) - 1, |t| <= 0.43
-  p = __fadd_rn(1.0f, t);
-  pl = __fsub_rn(t, __fsub_rn(p, 1.0f));        // exact: 1 + t = p + pl
-  nbits = __float_as_int(big);
+// max(a, b) that returns NaN when a is NaN (fmaxf would return b): lets a NaN input run through
+// the arithmetic below and come out as NaN without a select at the end.
+__device__ __forceinline__ float dd_max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
 }
 
-// 2^(n + k) as a float from nbits = 0x4B400000 + n; n + k must be in [-126, 127].
-__device__ __forceinline__ float dd_pow2_from_bits(int nbits, int k) {
-  return __int_as_float((int)(((unsigned)nbits << 23) + ((unsigned)(127 + k) << 23)));
+// 2^(n + k) as a float from the rounding helper big = 1.5*2^23 + n (bit pattern 0x4B400000 + n):
+// shifted left by 23 it is n << 23 (every set bit of 0x4B400000 falls off the top); n + k must be
+// in [-126, 127].
+__device__ __forceinline__ float dd_pow2_from_big(float big, int k) {
+  return __int_as_float((int)(((unsigned)__float_as_int(big) << 23) + ((unsigned)(127 + k) << 23)));
+}
+
+template <typename F> struct dd_lane;
+
+template <> struct dd_lane<float> {
+  static __device__ __forceinline__ float bc(float c) { return c; }
+  static __device__ __forceinline__ float fma(float a, float b, float c) { return fmaf(a, b, c); }
+  static __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+  static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+  static __device__ __forceinline__ float nrcp(float a) { return dd_rcp_approx(-a); }  // about -1/a
+  // max(-S*|x|, lo); NaN stays NaN
+  template <int S> static __device__ __forceinline__ float neg_abs_clamped(float x, float lo) {
+    return dd_max_nan(S == 1 ? -fabsf(x) : -(float)S * fabsf(x), lo);
+  }
+  static __device__ __forceinline__ float clamped(float x, float lo) { return dd_max_nan(x, lo); }
+  static __device__ __forceinline__ float pow2(float big, int k) { return dd_pow2_from_big(big, k); }
+  static __device__ __forceinline__ float sel_nonneg(float x, float a, float b) { return x >= 0.0f ? a : b; }
+  static __device__ __forceinline__ float sel_pos(float x, float a, float b) { return x > 0.0f ? a : b; }
+  static __device__ __forceinline__ float copysign(float m, float sgn) { return copysignf(m, sgn); }
+};
+
+template <> struct dd_lane<float2> {
+  typedef dd_lane<float> S1;
+  static __device__ __forceinline__ float2 bc(float c) { return make_float2(c, c); }
+  static __device__ __forceinline__ float2 fma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+  static __device__ __forceinline__ float2 add(float2 a, float2 b) { return __fadd2_rn(a, b); }
+  static __device__ __forceinline__ float2 mul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+  static __device__ __forceinline__ float2 nrcp(float2 a) { return make_float2(S1::nrcp(a.x), S1::nrcp(a.y)); }
+  template <int S> static __device__ __forceinline__ float2 neg_abs_clamped(float2 x, float lo) {
+    return make_float2(S1::neg_abs_clamped<S>(x.x, lo), S1::neg_abs_clamped<S>(x.y, lo));
+  }
+  static __device__ __forceinline__ float2 clamped(float2 x, float lo) {
+    return make_float2(dd_max_nan(x.x, lo), dd_max_nan(x.y, lo));
+  }
+  static __device__ __forceinline__ float2 pow2(float2 big, int k) {
+    return make_float2(dd_pow2_from_big(big.x, k), dd_pow2_from_big(big.y, k));
+  }
+  static __device__ __forceinline__ float2 sel_nonneg(float2 x, float2 a, float2 b) {
+    return make_float2(x.x >= 0.0f ? a.x : b.x, x.y >= 0.0f ? a.y : b.y);
+  }
+  static __device__ __forceinline__ float2 sel_pos(float2 x, float2 a, float2 b) {
+    return make_float2(x.x > 0.0f ? a.x : b.x, x.y > 0.0f ? a.y : b.y);
+  }
+  static __device__ __forceinline__ float2 copysign(float2 m, float2 sgn) {
+    return make_float2(copysignf(m.x, sgn.x), copysignf(m.y, sgn.y));
+  }
+};
+
+// exp(x) = (p + pl) * 2^n for x in [-104, 0] (callers clamp): p in [0.7, 1.43] is the rounded
+// mantissa part, pl its rounding error, n in [-150, 0] sits in the low mantissa bits of `big`.
+template <typename F>
+__device__ __forceinline__ void dd_exp_neg_raw(F x, F &p, F &pl, F &big) {
+  typedef dd_lane<F> L;
+  // n = rint(x * log2 e) by the add-a-big-constant trick: both the rounded float and the integer
+  // come out of one FMA (no round / float-to-int conversions, which run on the quarter-rate unit)
+  big = L::fma(x, L::bc(DD_LOG2E), L::bc(12582912.0f));  // 1.5 * 2^23: the sum's low mantissa bits are n
+  const F fn = L::add(big, L::bc(-12582912.0f));
+  F r = L::fma(fn, L::bc(-DD_LN2_HI), x);
+  r = L::fma(fn, L::bc(-DD_LN2_LO), r);
+  F g = L::bc(0.00019901622727047652f);
+  g = L::fma(g, r, L::bc(0.0013935454189777374f));
+  g = L::fma(g, r, L::bc(0.008333295583724976f));
+  g = L::fma(g, r, L::bc(0.04166644811630249f));
+  g = L::fma(g, r, L::bc(0.1666666716337204f));
+  g = L::fma(g, r, L::bc(0.5f));
+  const F t = L::fma(L::mul(r, r), g, r);  // exp(r) - 1, |t| <= 0.43
+  p = L::add(L::bc(1.0f), t);
+  pl = L::fma(L::add(p, L::bc(-1.0f)), L::bc(-1.0f), t);  // t - (p - 1), exact: 1 + t = p + pl
 }
 
 // exp(x) for x in [-104, 0] reaches 2^-150, below the normal range.  To stay branch-free the kernels
 // carry E = exp(x) * 2^64 (always a normal float, scaled exactly by one factor) wherever exp(x) is a
 // NUMERATOR and multiply the final quotient by 2^-64 (exact unless the result is denormal, where it
-// is the single rounding), and the plain e = E * 2^-64 only where it is added to 1.
+// is the single rounding), and the plain e = E * 2^-64 only where it is added to 1.  KX extra powers
+// of two can ride in the same scale factor (the derivative kernels want 2^K * e).
 #define DD_EXP_BIAS 64
 #define DD_UNBIAS 5.421010862427522e-20f  // 2^-64
 
-__device__ __forceinline__ void dd_exp_neg_biased(float x, float &Eh, float &El) {
-  float p, pl;
-  int nbits;
-  dd_exp_neg_raw(x, p, pl, nbits);
-  const float sc = dd_pow2_from_bits(nbits, DD_EXP_BIAS);
-  Eh = __fmul_rn(p, sc);
-  El = __fmul_rn(pl, sc);
+template <typename F, int KX = 0>
+__device__ __forceinline__ void dd_exp_neg_biased(F x, F &Eh, F &El) {
+  typedef dd_lane<F> L;
+  F p, pl, big;
+  dd_exp_neg_raw<F>(x, p, pl, big);
+  const F sc = L::pow2(big, DD_EXP_BIAS + KX);
+  Eh = L::mul(p, sc);
+  El = L::mul(pl, sc);
 }
 
-// (nh + nl) / (dh + dl) with dh in [1, 2]: approximate quotient + one residual correction.
-__device__ __forceinline__ float dd_quot(float nh, float nl, float dh, float dl) {
-  const float r0 = dd_rcp_approx(dh);
-  const float q = __fmul_rn(nh, r0);
-  float res = fmaf(-dh, q, nh);  // exact remainder of the leading terms
-  res = __fadd_rn(fmaf(-dl, q, res), nl);
-  return fmaf(res, r0, q);
+// MINUS (nh + nl) / (dh + dl) with dh in [1, 2]: approximate quotient + one residual correction,
+// carried negated (nr0 is about -1/dh) so that every step is a plain fma; callers fold the sign into
+// their last operation.  Each step is the exact mirror image of the positive form, so the magnitude
+// has the same bits.
+template <typename F>
+__device__ __forceinline__ F dd_neg_quot(F nh, F nl, F dh, F dl) {
+  typedef dd_lane<F> L;
+  const F nr0 = L::nrcp(dh);
+  const F nq = L::mul(nh, nr0);
+  F res = L::fma(dh, nq, nh);  // exact remainder of the leading terms
+  res = L::add(L::fma(dl, nq, res), nl);
+  return L::fma(res, nr0, nq);
 }
 
 // 1 + e as an exact pair (e = eh + el in [0, 1])
-__device__ __forceinline__ void dd_one_plus(float eh, float el, float &dh, float &dl) {
-  dh = __fadd_rn(1.0f, eh);
-  dl = __fadd_rn(__fadd_rn(__fsub_rn(1.0f, dh), eh), el);
+template <typename F>
+__device__ __forceinline__ void dd_one_plus(F eh, F el, F &dh, F &dl) {
+  typedef dd_lane<F> L;
+  dh = L::add(L::bc(1.0f), eh);
+  dl = L::add(L::add(L::fma(dh, L::bc(-1.0f), L::bc(1.0f)), eh), el);
 }
 
-// The same from the biased pair E = e * 2^64: the un-biasing multiplications ride inside FMAs
-// (fma(Eh, 2^-64, 1) rounds 1 + eh once, exactly like the addition above).
-__device__ __forceinline__ void dd_one_plus_biased(float Eh, float El, float &dh, float &dl) {
-  dh = fmaf(Eh, DD_UNBIAS, 1.0f);
-  dl = fmaf(El, DD_UNBIAS, fmaf(Eh, DD_UNBIAS, __fsub_rn(1.0f, dh)));
+// The same from the biased pair E = e / unb: the un-biasing multiplications ride inside FMAs
+// (fma(Eh, unb, 1) rounds 1 + eh once, exactly like the addition above).
+template <typename F>
+__device__ __forceinline__ void dd_one_plus_biased(F Eh, F El, float unb, F &dh, F &dl) {
+  typedef dd_lane<F> L;
+  dh = L::fma(Eh, L::bc(unb), L::bc(1.0f));
+  dl = L::fma(El, L::bc(unb), L::fma(Eh, L::bc(unb), L::fma(dh, L::bc(-1.0f), L::bc(1.0f))));
 }
 
-__device__ __forceinline__ float dd_sigmoid_f32(float x) {
-  float Eh, El, dh, dl;
-  dd_exp_neg_biased(fmaxf(-fabsf(x), -104.0f), Eh, El);
-  dd_one_plus_biased(Eh, El, dh, dl);
-  const bool pos = x >= 0.0f;
+// logistic(x) = 1 / (1 + e) for x >= 0, e / (1 + e) for x < 0, e = exp(-|x|).  NaN in, NaN out.
+template <typename F>
+__device__ __forceinline__ F dd_sigmoid(F x) {
+  typedef dd_lane<F> L;
+  F Eh, El, dh, dl;
+  dd_exp_neg_biased<F>(L::template neg_abs_clamped<1>(x, -104.0f), Eh, El);
+  dd_one_plus_biased<F>(Eh, El, DD_UNBIAS, dh, dl);
   // numerator 1 (as 2^64) or e (as E = e * 2^64); one exact un-biasing multiplication at the end
-  const float s = __fmul_rn(dd_quot(pos ? 18446744073709551616.0f : Eh, pos ? 0.0f : El, dh, dl), DD_UNBIAS);
-  return x != x ? x : s;
+  const F nh = L::sel_nonneg(x, L::bc(18446744073709551616.0f), Eh);
+  const F nl = L::sel_nonneg(x, L::bc(0.0f), El);
+  return L::mul(dd_neg_quot<F>(nh, nl, dh, dl), L::bc(-DD_UNBIAS));
 }
 
 // 2^K * e / (1 + e)^2 for e = exp(xneg), xneg in [-104, 0]: the derivative kernel of both logistic
 // (K = 0, e = exp(-|x|): s*(1-s)) and tanh (K = 2, e = exp(-2|x|): 1 - tanh^2).
-template <int K>
-__device__ __forceinline__ float dd_e_over_one_plus_e_sq(float xneg) {
-  float Eh, El, dh, dl;
-  dd_exp_neg_biased(xneg, Eh, El);
-  dd_one_plus_biased(Eh, El, dh, dl);
-  const float nh = Eh * (float)(1 << K), nl = El * (float)(1 << K);  // exact
-  const float r0 = dd_rcp_approx(dh);
-  const float rr = __fmul_rn(r0, r0);
-  const float q = __fmul_rn(nh, rr);
+template <typename F, int K>
+__device__ __forceinline__ F dd_e_over_one_plus_e_sq(F xneg) {
+  typedef dd_lane<F> L;
+  constexpr float unb = DD_UNBIAS / (float)(1 << K);  // the numerator carries 2^(64+K)
+  F nh, nl, dh, dl;
+  dd_exp_neg_biased<F, K>(xneg, nh, nl);
+  dd_one_plus_biased<F>(nh, nl, unb, dh, dl);
+  const F ndh = L::mul(dh, L::bc(-1.0f));
+  const F r0 = L::nrcp(dh);
+  const F rr = L::mul(r0, r0);
+  const F q = L::mul(nh, rr);
   // residual nh + nl - q*(dh+dl)^2, with w = q*dh split into a rounded part and its error
-  const float w = __fmul_rn(q, dh);
-  const float wl = fmaf(q, dh, -w);
-  float res = fmaf(-w, dh, nh);
-  res = fmaf(-wl, dh, res);
-  res = fmaf(-2.0f * w, dl, res);
-  res = __fadd_rn(res, nl);
-  return __fmul_rn(fmaf(res, rr, q), DD_UNBIAS);
+  const F nw = L::mul(q, ndh);           // -w
+  const F wl = L::fma(q, dh, nw);
+  F res = L::fma(nw, dh, nh);
+  res = L::fma(wl, ndh, res);
+  res = L::fma(L::mul(nw, L::bc(2.0f)), dl, res);
+  res = L::add(res, nl);
+  return L::mul(L::fma(res, rr, q), L::bc(DD_UNBIAS));
 }
 
 // tanh(x) = (1 - e) / (1 + e), e = exp(-2|x|).  No separate small-|x| branch: 1 - e is formed from
 // the hi/lo pair, and for |x| < 0.17 (n == 0) that difference is exactly -(exp(r) - 1), which the
 // exp kernel computed without cancellation.  Here e only ever meets 1, so the argument is clamped at
 // -87 (n >= -126: 2^n stays a normal float; tanh is 1 to the last bit from |x| = 9.1 on anyway).
-__device__ __forceinline__ float dd_tanh_f32(float x) {
-  float p, pl, dh, dl;
-  int nbits;
-  dd_exp_neg_raw(fmaxf(-2.0f * fabsf(x), -87.0f), p, pl, nbits);
-  const float sc = dd_pow2_from_bits(nbits, 0);
-  const float eh = __fmul_rn(p, sc), el = __fmul_rn(pl, sc);
-  dd_one_plus(eh, el, dh, dl);
+template <typename F>
+__device__ __forceinline__ F dd_tanh(F x) {
+  typedef dd_lane<F> L;
+  F p, pl, big, dh, dl;
+  dd_exp_neg_raw<F>(L::template neg_abs_clamped<2>(x, -87.0f), p, pl, big);
+  const F sc = L::pow2(big, 0);
+  dd_one_plus<F>(L::mul(p, sc), L::mul(pl, sc), dh, dl);
   // 1 - e = 2 - (1 + e) exactly: 2 - dh is exact (dh in [1, 2]) and the low word just changes sign.
-  // The pair is not normalised, which dd_quot does not need: its residual is formed exactly.
-  const float t = copysignf(dd_quot(__fsub_rn(2.0f, dh), -dl, dh, dl), x);
-  return x != x ? x : t;
+  // The pair is not normalised, which the quotient does not need: its residual is formed exactly.
+  const F q = dd_neg_quot<F>(L::fma(dh, L::bc(-1.0f), L::bc(2.0f)), L::mul(dl, L::bc(-1.0f)), dh, dl);
+  return L::copysign(q, x);  // the quotient's own sign (negated form) is replaced by x's
 }
 
 // exp(x) rounded once, for x <= 0 (elu backward)
-__device__ __forceinline__ float dd_exp_neg_rounded(float x) {
-  float Eh, El;
-  dd_exp_neg_biased(fmaxf(x, -104.0f), Eh, El);
-  return x != x ? x : __fmul_rn(__fadd_rn(Eh, El), DD_UNBIAS);
+template <typename F>
+__device__ __forceinline__ F dd_exp_neg_rounded(F x) {
+  typedef dd_lane<F> L;
+  F Eh, El;
+  dd_exp_neg_biased<F>(L::clamped(x, -104.0f), Eh, El);
+  return L::mul(L::add(Eh, El), L::bc(DD_UNBIAS));
 }
 
 // exp(x) - 1 for x <= 0 (elu forward): (eh - 1) + el.  For |x| < 0.35 the reduction has n = 0, so
 // eh - 1 is exact and the sum is the cancellation-free exp(r) - 1 the exp kernel produced; further
 // out exp(x) <= 0.71 and the subtraction does not cancel.
-__device__ __forceinline__ float dd_expm1_neg(float x) {
-  float p, pl;
-  int nbits;
-  dd_exp_neg_raw(fmaxf(x, -87.0f), p, pl, nbits);  // exp(-87) - 1 is already -1 to the last bit
-  const float sc = dd_pow2_from_bits(nbits, 0);
-  const float r = __fadd_rn(__fsub_rn(__fmul_rn(p, sc), 1.0f), __fmul_rn(pl, sc));
-  return x != x ? x : r;
+template <typename F>
+__device__ __forceinline__ F dd_expm1_neg(F x) {
+  typedef dd_lane<F> L;
+  F p, pl, big;
+  dd_exp_neg_raw<F>(L::clamped(x, -87.0f), p, pl, big);  // exp(-87) - 1 is already -1 to the last bit
+  const F sc = L::pow2(big, 0);
+  return L::add(L::add(L::mul(p, sc), L::bc(-1.0f)), L::mul(pl, sc));
 }

@@ -151,11 +151,33 @@ struct ddCostParams {
   double *part;     // per-CTA partial sums (handle scratch, after the counters)
   unsigned *counter;
   int64_t n;
-  int kind;         // 0 quadratic: sum (a-y)^2 / (2n); 1 mean absolute: sum |a-y| / n
+  int64_t divisor;  // n for the mean absolute cost, the batch extent for the cross-entropy
   int vec;
 };
 
-template <typename T>
+// One element's contribution.  KIND 2 follows the reference's vector steps one rounding at a time:
+// y*log(a), (y-1), log(1.0000001 - a), their product, the difference (cost.clj:34-38).
+template <typename T, int KIND>
+__device__ __forceinline__ T dd_cost_term(T a, T y, T t, T acc) {
+  if constexpr (KIND == 0) {
+    if constexpr (sizeof(T) == 4) return fmaf(t, t, acc);
+    else return fma(t, t, acc);
+  } else if constexpr (KIND == 1) {
+    return dd_add_rn(acc, t < (T)0 ? -t : t);
+  } else {
+    if constexpr (sizeof(T) == 4) {
+      const float ylna = __fmul_rn(y, logf(a));
+      const float h = __fadd_rn(__fmul_rn(__fadd_rn(y, -1.0f), logf(__fadd_rn(1.0000001f, -a))), -ylna);
+      return __fadd_rn(acc, fabsf(h));
+    } else {
+      const double ylna = __dmul_rn(y, log(a));
+      const double h = __dadd_rn(__dmul_rn(__dadd_rn(y, -1.0), log(__dadd_rn(1.0000001, -a))), -ylna);
+      return __dadd_rn(acc, fabs(h));
+    }
+  }
+}
+
+template <typename T, int KIND>
 __global__ void __launch_bounds__(256) dd_cost_kernel(ddCostParams p) {
   constexpr int V = 16 / sizeof(T);
   const T *a = (const T *)p.a;
@@ -175,17 +197,17 @@ __global__ void __launch_bounds__(256) dd_cost_kernel(ddCostParams p) {
       for (int k = 0; k < V; k++) {
         T t = dd_add_rn(ap[k], -yp[k]);
         dp[k] = t;
-        acc = p.kind == 0 ? (sizeof(T) == 4 ? (T)fmaf((float)t, (float)t, (float)acc) : (T)fma((double)t, (double)t, (double)acc))
-                          : dd_add_rn(acc, t < (T)0 ? -t : t);
+        acc = dd_cost_term<T, KIND>(ap[k], yp[k], t, acc);
       }
       if (d) *(uint4 *)(d + i * V) = dv;
     }
     done = nv * V;
   }
   for (int64_t i = done + tid; i < p.n; i += nthreads) {
-    T t = dd_add_rn(a[i], -y[i]);
+    const T av = a[i], yv = y[i];
+    T t = dd_add_rn(av, -yv);
     if (d) d[i] = t;
-    acc = p.kind == 0 ? t * t + acc : acc + (t < (T)0 ? -t : t);
+    acc = dd_cost_term<T, KIND>(av, yv, t, acc);
   }
   // CTA tree in double, then the last CTA to arrive folds the per-CTA partials in index order
   __shared__ double smem[8];
@@ -207,7 +229,7 @@ __global__ void __launch_bounds__(256) dd_cost_kernel(ddCostParams p) {
     __threadfence();
     double tot = 0;
     for (unsigned b = 0; b < gridDim.x; b++) tot += __ldcg(p.part + b);
-    tot = p.kind == 0 ? tot / (2.0 * (double)p.n) : tot / (double)p.n;
+    tot = KIND == 0 ? tot / (2.0 * (double)p.n) : tot / (double)p.divisor;
     *(T *)p.cost = (T)tot;
     *p.counter = 0;
   }
@@ -219,7 +241,8 @@ extern "C" ddStatus_t ddCostDiff(ddHandle_t h, int kind, ddTensorDescriptor_t de
   ddStatus_t st = dd_check_desc(h, desc, "ddCostDiff");
   if (st != DD_STATUS_SUCCESS) return st;
   if (!a || !y || !cost) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddCostDiff: null pointer");
-  if (kind != 0 && kind != 1) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddCostDiff: kind must be 0 (quadratic) or 1 (mean absolute)");
+  if (kind < 0 || kind > 2)
+    DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddCostDiff: kind must be 0 (quadratic), 1 (mean absolute) or 2 (cross-entropy)");
   if (desc->dtype != DD_DATA_FLOAT && desc->dtype != DD_DATA_DOUBLE)
     DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddCostDiff: float and double only");
   int64_t strides[1][DD_DIM_MAX];
@@ -236,12 +259,21 @@ extern "C" ddStatus_t ddCostDiff(ddHandle_t h, int kind, ddTensorDescriptor_t de
   p.counter = (unsigned *)h->scratch + (h->counterSlots - 1);  // the last arrival counter is this kernel's
   p.part = (double *)((char *)h->scratch + h->counterSlots * sizeof(unsigned));
   p.n = c.total;
-  p.kind = kind;
+  p.divisor = kind == 2 ? desc->dims[0] : c.total;
   p.vec = ((((uintptr_t)a) | ((uintptr_t)y) | ((uintptr_t)d)) & 15) == 0;
   const int V = 16 / dd_type_size(desc->dtype);
   unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 8);
-  if (desc->dtype == DD_DATA_FLOAT) dd_cost_kernel<float><<<grid, 256, 0, h->stream>>>(p);
-  else dd_cost_kernel<double><<<grid, 256, 0, h->stream>>>(p);
+  const bool f = desc->dtype == DD_DATA_FLOAT;
+  if (kind == 0) {
+    if (f) dd_cost_kernel<float, 0><<<grid, 256, 0, h->stream>>>(p);
+    else dd_cost_kernel<double, 0><<<grid, 256, 0, h->stream>>>(p);
+  } else if (kind == 1) {
+    if (f) dd_cost_kernel<float, 1><<<grid, 256, 0, h->stream>>>(p);
+    else dd_cost_kernel<double, 1><<<grid, 256, 0, h->stream>>>(p);
+  } else {
+    if (f) dd_cost_kernel<float, 2><<<grid, 256, 0, h->stream>>>(p);
+    else dd_cost_kernel<double, 2><<<grid, 256, 0, h->stream>>>(p);
+  }
   DD_LAUNCHED(h, "cost-diff/flat");
   return DD_STATUS_SUCCESS;
 }

@@ -555,8 +555,47 @@ class B200Cost:
             return float(view[0].item())
 
 
+class B200CustomCost(B200Cost):
+    """``CUDnnCustomCost`` (cudnn/directed.clj:413-458) with ``crossentropy-cost!``
+    (base/internal/cost.clj:34-40).  Invoking it only reads: the cost of (y, a) comes from one pass
+    where the reference runs two logs, two linear-fracs, two products, an axpy and an asum.
+    ``backward`` writes a - y into the previous layer's gradient after its linear part (``diff-z``:
+    the activation layer's diff-output here) and, like the reference, does not call the previous
+    layer's backward."""
+
+    def __init__(self, prev_layer, train_tz, kind):
+        import torch
+        self.prev_layer, self.train_tz, self.kind = prev_layer, train_tz, kind
+        self.fact = train_tz.fact
+        self.a = _t.output(prev_layer)
+        if hasattr(prev_layer, "diff_z"):
+            self.a_y = prev_layer.diff_z()
+        elif hasattr(prev_layer, "diff_output"):
+            self.a_y = prev_layer.diff_output()
+        else:
+            self.a_y = _t.tensor(self.fact, train_tz.desc)
+        if not (core.equal_desc(self.a.desc, train_tz.desc) and core.equal_desc(self.a_y.desc, train_tz.desc)):
+            raise DiamondError("The B200 cost needs the output, its gradient and the target in one layout.",
+                               {"output": repr(self.a), "target": repr(train_tz)})
+        self._cost = torch.zeros(1, dtype=torch.float64, device=self.fact.device)
+
+    def backward(self):
+        core.cost_diff(self.fact.handle, "mean-absolute", self.train_tz.desc, self.a, self.train_tz, self.a_y,
+                       self._cost)
+        return self
+
+    def __call__(self):
+        import torch
+        core.cost_diff(self.fact.handle, self.kind, self.train_tz.desc, self.a, self.train_tz, None, self._cost)
+        with torch.cuda.stream(self.fact.stream):
+            view = self._cost.view(torch.float32) if self.train_tz.desc.dtype_code == 0 else self._cost
+            return float(view[0].item())
+
+
 def cost(layer, train_tz, cost_kw="quadratic"):
-    """``cost`` (dnn.clj:559-581); :crossentropy is outside this engine."""
+    """``cost`` (dnn.clj:559-581)."""
     if cost_kw not in core.COST_KIND:
         raise DiamondError("This cost function is not supported.", {"cost": cost_kw})
+    if cost_kw == "crossentropy":
+        return B200CustomCost(layer, train_tz, cost_kw)
     return B200Cost(layer, train_tz, cost_kw)

@@ -231,10 +231,12 @@ DD_API ddStatus_t ddMultiTransform(ddHandle_t handle, int count, const ddTensorD
                                    void *const *ys);
 
 /* d = a - y and, in the same pass, cost[0] = sum (a-y)^2 / (2n) (kind 0, quadratic) or
- * sum |a-y| / n (kind 1, mean absolute); a, y, d dense tensors of one descriptor, d may be NULL or
- * alias a.  `cost` is one DEVICE element of the tensor's data type (float or double).  Replaces the
- * cost glue `axpy! -1.0 y a-y` + `nrm2`/`asum` (cudnn/directed.clj:367-458 with
- * deep-diamond-base/src/uncomplicate/diamond/internal/cost.clj:20-34). */
+ * sum |a-y| / n (kind 1, mean absolute) or sum |(y-1) log(1.0000001-a) - y log(a)| / dims[0]
+ * (kind 2, cross-entropy; the divisor is the batch extent); a, y, d dense tensors of one
+ * descriptor, d may be NULL or alias a.  `cost` is one DEVICE element of the tensor's data type
+ * (float or double).  Replaces the cost glue `axpy! -1.0 y a-y` + `nrm2`/`asum`, and the six
+ * vector-math passes of the cross-entropy (cudnn/directed.clj:367-458 with
+ * deep-diamond-base/src/uncomplicate/diamond/internal/cost.clj:20-40). */
 DD_API ddStatus_t ddCostDiff(ddHandle_t handle, int kind, ddTensorDescriptor_t desc, const void *a,
                              const void *y, void *d, void *cost);
 

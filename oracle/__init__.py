@@ -217,6 +217,25 @@ def equals(x, y, tag=None):
     return bool(lib().oracle_equals(code_of(x, tag), len(x.shape), dims, xs, xp, ys, yp))
 
 
+COST = {"quadratic": 0, "mean-absolute": 1, "crossentropy": 2}
+
+
+def cost(kind, a, y, batch=None, want_diff=False):
+    """(cost, truth[, a - y]) of dense float32 arrays per base/internal/cost.clj:20-40; ``batch`` is
+    the divisor of the cross-entropy (the extent of the batch dim), default ``a.shape[0]``."""
+    a32 = np.ascontiguousarray(a, dtype=np.float32)
+    y32 = np.ascontiguousarray(y, dtype=np.float32)
+    assert a32.shape == y32.shape
+    d = np.empty(a32.size, dtype=np.float32) if want_diff else None
+    c, t = ctypes.c_double(), ctypes.c_double()
+    rc = lib().oracle_cost(COST[kind], ctypes.c_int64(a32.size),
+                           ctypes.c_int64(a32.shape[0] if batch is None else batch),
+                           ctypes.c_void_p(a32.ctypes.data), ctypes.c_void_p(y32.ctypes.data),
+                           ctypes.c_void_p(d.ctypes.data if want_diff else 0), ctypes.byref(c), ctypes.byref(t))
+    assert rc == 0
+    return (c.value, t.value, d.reshape(a32.shape)) if want_diff else (c.value, t.value)
+
+
 def num_threads():
     return int(lib().oracle_num_threads())
 

@@ -631,6 +631,52 @@ int oracle_equals(int t, int nd, const int64_t *dims, const int64_t *xst, const 
   return !diff;
 }
 
+/* Cost functions over dense vectors of n floats, following
+ * deep-diamond-base/src/uncomplicate/diamond/internal/cost.clj step by step, every vector
+ * operation rounding to float as Neanderthal's float vectors do:
+ *   kind 0 (:20-25)  a_y = a - y;  (nrm2 a_y)^2 / (2 n)
+ *   kind 1 (:27-32)  a_y = a - y;  (asum a_y) / n
+ *   kind 2 (:34-40)  asum( (y - 1) * log(1.0000001 - a) - y * log(a) ) / batch
+ * d (may be NULL) receives a - y.  The sums are accumulated in double (the reference's nrm2/asum
+ * are BLAS calls whose order is not specified); *truth gets the same quantity with every
+ * elementwise step in double. */
+int oracle_cost(int kind, int64_t n, int64_t batch, const float *a, const float *y, float *d,
+                double *cost, double *truth) {
+  double acc = 0, tacc = 0;
+  for (int64_t i = 0; i < n; i++) {
+    const float t = a[i] - y[i];
+    if (d) d[i] = t;
+    if (kind == 0) {
+      acc += (double)t * (double)t;
+      tacc += ((double)a[i] - (double)y[i]) * ((double)a[i] - (double)y[i]);
+    } else if (kind == 1) {
+      acc += fabs((double)t);
+      tacc += fabs((double)a[i] - (double)y[i]);
+    } else {
+      const float lna = (float)log((double)a[i]);
+      const float ylna = y[i] * lna;
+      const float y1 = y[i] - 1.0f;
+      const float om = 1.0000001f - a[i];
+      const float l1 = (float)log((double)om);
+      const float h = y1 * l1 - ylna;
+      acc += fabs((double)h);
+      tacc += fabs(((double)y[i] - 1.0) * log(1.0000001 - (double)a[i]) - (double)y[i] * log((double)a[i]));
+    }
+  }
+  if (kind == 0) {
+    /* the reference squares the float norm: (sqr (nrm2 a-y)) / (* 2 n) */
+    *cost = acc / (2.0 * (double)n);
+    if (truth) *truth = tacc / (2.0 * (double)n);
+  } else if (kind == 1) {
+    *cost = acc / (double)n;
+    if (truth) *truth = tacc / (double)n;
+  } else {
+    *cost = acc / (double)batch;
+    if (truth) *truth = tacc / (double)batch;
+  }
+  return 0;
+}
+
 void oracle_set_num_threads(int n) {
 #ifdef _OPENMP
   if (n > 0) omp_set_num_threads(n);

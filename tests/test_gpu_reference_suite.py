@@ -480,7 +480,59 @@ def test_quadratic_and_mean_absolute_cost(fact):
     mae = dnn.cost(out_tz, train_tz, "mean-absolute")
     assert abs(mae() - (0.15 + 1.65) / 2) < 1e-6
     with pytest.raises(DiamondError):
-        dnn.cost(out_tz, train_tz, "crossentropy")
+        dnn.cost(out_tz, train_tz, "hinge")
+
+
+def test_crossentropy_cost(fact):
+    """dt :335-346: y = [0.25 0.65], a = [0.4 0.1] -> 1.0728740692138672; invoking the cost leaves
+    the output alone, backward leaves a - y in the gradient after the linear part."""
+    out_tz = tensor(fact, [2, 1], "float", "nc")
+    train_tz = tensor(fact, [2, 1], "float", "nc")
+    ce = dnn.cost(out_tz, train_tz, "crossentropy")
+    transfer([0.25, 0.65], train_tz)
+    transfer([0.4, 0.1], out_tz)
+    assert abs(ce() - 1.0728740692138672) < 2e-7
+    assert seq(out_tz) == vctr_of(out_tz, [0.4, 0.1])
+    assert ce.backward() is ce
+    assert np.allclose(seq(dnn.diff_output(ce)), [0.15, -0.55], rtol=1e-6)
+    # behind a sigmoid layer the gradient lands in the layer's diff-output (its diff-z)
+    src_tz = tensor(fact, [2, 1], "float", "nc")
+    dsrc_tz = tensor(fact, [2, 1], "float", "nc")
+    layer = dnn.activation(fact, src_tz, "sigmoid")(src_tz, dsrc_tz)
+    transfer([-0.4054651, -2.1972246], src_tz)                 # logit(0.4), logit(0.1)
+    layer.forward()
+    ce2 = dnn.cost(layer, train_tz, "crossentropy")
+    assert abs(ce2() - 1.0728740692138672) < 1e-6
+    ce2.backward()
+    assert np.allclose(seq(dnn.diff_output(layer)), [0.15, -0.55], atol=1e-6)
+
+
+def test_costs_against_oracle(fact):
+    """All three costs on [64, 1000] outputs against the oracle's float restatement and its double
+    truth (1e-5 relative), a - y bit-exact; float and double tensors."""
+    import oracle
+    rng = np.random.default_rng(77)
+    a = rng.uniform(0.001, 0.999, (64, 1000)).astype(np.float32)
+    y = (rng.random((64, 1000)) < 0.1).astype(np.float32) * 0.9 + 0.05
+    for dt, npt in (("float", np.float32), ("double", np.float64)):
+        for kind in ("quadratic", "mean-absolute", "crossentropy"):
+            out_tz = tensor(fact, [64, 1000], dt, "nc")
+            train_tz = tensor(fact, [64, 1000], dt, "nc")
+            transfer(a.astype(npt).reshape(-1), out_tz)
+            transfer(y.astype(npt).reshape(-1), train_tz)
+            c = dnn.cost(out_tz, train_tz, kind)
+            got = c()
+            want, truth, diff = oracle.cost(kind, a, y, want_diff=True)
+            assert abs(got - truth) <= 1e-5 * abs(truth), (dt, kind, got, truth)
+            assert abs(got - want) <= 1e-5 * abs(want), (dt, kind, got, want)
+            if kind == "crossentropy":      # invoking it only reads; backward writes a - y
+                assert np.array_equal(np.array(seq(out_tz), dtype=npt), a.astype(npt).reshape(-1))
+                c.backward()
+            d = np.array(seq(dnn.diff_output(c)), dtype=npt)
+            if dt == "float":
+                assert np.array_equal(d.astype(np.float32), diff.reshape(-1)), (dt, kind)
+            else:
+                assert np.array_equal(d, (a.astype(np.float64) - y.astype(np.float64)).reshape(-1)), (dt, kind)
 
 
 def test_branch_concat_large_against_oracle(fact, dev):

@@ -337,3 +337,17 @@ def test_equals(oracle):
     assert oracle.equals(lay(oracle, x, d, NCHW(oracle, d)), lay(oracle, y, d, NHWC(oracle, d)))
     y[3] += 1
     assert not oracle.equals(lay(oracle, x, d, NCHW(oracle, d)), lay(oracle, y, d, NHWC(oracle, d)))
+
+
+def test_cost_known_answers(oracle):
+    """deep-diamond-test/src/uncomplicate/diamond/dnn_test.clj:321-346: quadratic cost of
+    a = [0.4 -1.3], y = [0.25 0.35] is 0.6862499438341274 with a - y = [0.15 -1.65]; sigmoid
+    cross-entropy of a = [0.4 0.1], y = [0.25 0.65] is 1.0728740692138672 (float results)."""
+    c, t, d = oracle.cost("quadratic", np.array([[0.4], [-1.3]]), np.array([[0.25], [0.35]]), want_diff=True)
+    assert abs(c - 0.6862499438341274) < 1e-7 and abs(t - c) < 1e-7
+    assert np.array_equal(d.reshape(-1), np.array([0.4, -1.3], np.float32) - np.array([0.25, 0.35], np.float32))
+    c, t = oracle.cost("crossentropy", np.array([[0.4], [0.1]]), np.array([[0.25], [0.65]]))
+    assert np.float32(c) == np.float32(1.0728740692138672)
+    assert abs(t - c) < 1e-7
+    c, _ = oracle.cost("mean-absolute", np.array([[0.4], [-1.3]]), np.array([[0.25], [0.35]]))
+    assert abs(c - 0.9) < 1e-7
