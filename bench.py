@@ -366,13 +366,23 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_on
         y = dbuf(int(np.prod(yshape)) * 4)
         rtd = core.reduce_tensor_descriptor(op, "float")
         spans = sharded is not None and yshape[0] == 1
+        nb = n * 4 + int(np.prod(yshape)) * 4
         if spans:
             fn = lambda rtd=rtd, yd=yd, y=y: sharded.reduce_tensor(rtd, 1.0, xd, x, 0.0, yd, y, spans=True)  # noqa: E731
-            tag = "C4 shard [%d,1024,32,32] + 4 KB ncclAllReduce (un-captured launches)" % shp[0]
+            if sharded.peer_attached:
+                sharded.peer_configure(use_peer=True)
+                measure("reduce " + label, "C4 shard [%d,1024,32,32] + 4 KB peer-exchange kernel over NVLink" % shp[0],
+                        nb, n, fn, 10, 20)
+                sharded.peer_status()
+            if op == "add" or not sharded.peer_attached:
+                sharded.peer_configure(use_peer=False)
+                measure("reduce " + label + " (NCCL)",
+                        "C4 shard [%d,1024,32,32] + 4 KB ncclAllReduce + finish kernel (un-captured launches)" % shp[0],
+                        nb, n, fn, 10, 20, graph=False)
+                sharded.peer_configure(use_peer=True)
         else:
             fn = lambda rtd=rtd, yd=yd, y=y: core.reduce_tensor(h, rtd, 1.0, xd, x, 0.0, yd, y)  # noqa: E731
-            tag = "C4 [%d,1024,32,32]" % shp[0]
-        measure("reduce " + label, tag, n * 4 + int(np.prod(yshape)) * 4, n, fn, 10, 20, graph=not spans)
+            measure("reduce " + label, "C4 [%d,1024,32,32]" % shp[0], nb, n, fn, 10, 20)
     del x
 
     # C5: [2048/world,256,28,28] f32 nchw -> bf16 nhwc, then s8 nchw -> s8 nhwc

@@ -89,6 +89,10 @@ _SIGS = {
     "ddShardedDestroy": [_vp],
     "ddShardedReduceTensor": [_vp, _vp, _int, _vp, _vp, _vp, _vp, _vp, _vp],
     "ddShardedCheck": [_vp],
+    "ddShardedPeerExport": [_vp, _vp],
+    "ddShardedPeerAttach": [_vp, _vp],
+    "ddShardedPeerConfigure": [_vp, _int, _dbl],
+    "ddShardedPeerStatus": [_vp, ctypes.POINTER(_int)],
 }
 for _name, _args in _SIGS.items():
     _f = getattr(lib, _name)

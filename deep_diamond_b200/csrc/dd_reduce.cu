@@ -245,6 +245,28 @@ ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, 
   DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
 }
 
+ddStatus_t dd_reduce_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,
+                                   double count, double alpha, double beta, const ddTensorStruct *xd,
+                                   const ddTensorStruct *yd, void *y) {
+  ddRedPlan pl;
+  ddStatus_t st = dd_reduce_plan(h, red, xd, (const void *)0, yd, &pl);
+  if (st != DD_STATUS_SUCCESS) return st;
+  if (pl.kind == DD_RED_GENERIC)
+    DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
+  pl.p.y = y;
+  pl.p.alpha = alpha;
+  pl.p.beta = beta;
+  pl.p.count = count;
+  switch (xd->dtype) {
+    case DD_DATA_FLOAT: return dd_reduce_exchange_launch<float, float>(h, pl, *peer);
+    case DD_DATA_DOUBLE: return dd_reduce_exchange_launch<double, double>(h, pl, *peer);
+    case DD_DATA_HALF: return dd_reduce_exchange_launch<__half, float>(h, pl, *peer);
+    case DD_DATA_BFLOAT16: return dd_reduce_exchange_launch<__nv_bfloat16, float>(h, pl, *peer);
+    default: break;
+  }
+  DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
+}
+
 // ------------------------------------------------------------------ no-allocation entry ------
 //
 // ddReduceTensorNoAlloc: the same planning and the same kernels as ddReduceTensor, for callers

@@ -334,6 +334,160 @@ __global__ void __launch_bounds__(256) dd_reduce_finish_kernel(ddRedParams p, co
   }
 }
 
+// ------------------------------------------------------------------ cross-GPU exchange --------
+//
+// One process per GPU, every rank holding the raw accumulators of its own shard (nout values of C).
+// Each rank owns an exchange buffer that all ranks of the box have mapped (CUDA IPC over NVLink):
+//
+//   [0, 256)                  control words, touched by the owner only:
+//                             [0] number of the last finished call, [1] CTA arrivals, [2] status
+//   [DD_PEER_SLOTS_OFF, ...)  slots[parity][sender][DD_PEER_SLOT_BYTES]: 8-byte cells, each one
+//                             32-bit word of an accumulator paired with the number of the call that
+//                             wrote it
+//
+// A call is one kernel per rank.  Every thread PUSHES the words of its outputs' accumulators into
+// slot [parity][own rank] of every other rank, each as ONE 8-byte store {word, call number} to peer
+// memory.  An aligned 8-byte store arrives whole, so a cell whose tag equals this call's number
+// holds this call's word: no fence and no separate flag are needed, and a value crosses NVLink once.
+// The thread then polls its outputs' cells in its OWN memory until every sender's tag matches,
+// combines the world's values in rank order (its own straight from the local buffer; every rank
+// computes bit-identical results) and finishes (divide / sqrt / alpha / beta) into y.
+// Two parities alternate between calls: a rank can be at most one call ahead of the slowest one,
+// because finishing call k+1 needs every rank's cells for k+1, which they send only after call k.
+// The call number lives in the buffer (read at the start, advanced by the last CTA to finish), so
+// a captured launch can be replayed.
+//
+// Every wait is bounded (wall-clock limit and an iteration cap): when it runs out the thread
+// records 1 + the rank it waited for in the status word, skips its output and returns.  No thread
+// waits on another thread of the same GPU.
+#define DD_PEER_MAX 8
+#define DD_PEER_GRID_MAX 128
+#define DD_PEER_SLOT_BYTES (2u << 20)
+#define DD_PEER_SLOTS_OFF 8192u
+#define DD_PEER_BYTES (DD_PEER_SLOTS_OFF + 2u * DD_PEER_MAX * DD_PEER_SLOT_BYTES)
+
+struct ddPeerParams {
+  unsigned char *base[DD_PEER_MAX];  // every rank's exchange buffer as mapped here; base[rank] is the own one
+  const void *partial;               // this rank's accumulators
+  int world, rank;
+  unsigned long long waitNs;         // wall-clock limit of one wait
+};
+
+__device__ __forceinline__ void dd_st_cell(uint2 *p, unsigned word, unsigned tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 dd_ld_cell(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long dd_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <typename C> struct dd_words;
+template <> struct dd_words<float> {
+  static constexpr int N = 1;
+  static __device__ __forceinline__ void split(float v, unsigned *w) { w[0] = __float_as_uint(v); }
+  static __device__ __forceinline__ float join(const unsigned *w) { return __uint_as_float(w[0]); }
+};
+template <> struct dd_words<double> {
+  static constexpr int N = 2;
+  static __device__ __forceinline__ void split(double v, unsigned *w) {
+    w[0] = (unsigned)__double2loint(v);
+    w[1] = (unsigned)__double2hiint(v);
+  }
+  static __device__ __forceinline__ double join(const unsigned *w) { return __hiloint2double((int)w[1], (int)w[0]); }
+};
+
+template <typename T, typename C, int OPC>
+__global__ void __launch_bounds__(256) dd_reduce_exchange_kernel(ddRedParams p, ddPeerParams q) {
+  constexpr int NW = dd_words<C>::N;
+  const bool nanProp = p.nanProp != 0;
+  const int64_t nout = p.K1 * p.K2;
+  unsigned char *mine = q.base[q.rank];
+  unsigned *ctl = (unsigned *)mine;
+  const unsigned call = __ldcg(ctl) + 1u;  // published by the previous launch's last CTA
+  const unsigned par = call & 1u;
+  const int W = q.world;
+  const C *part = (const C *)q.partial;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t parOff = DD_PEER_SLOTS_OFF + (size_t)par * DD_PEER_MAX * DD_PEER_SLOT_BYTES;
+
+  for (int64_t o = first; o < nout; o += nthreads) {
+    unsigned w[NW];
+    dd_words<C>::split(part[o], w);
+    for (int r = 0; r < W; r++) {
+      if (r == q.rank) continue;
+      uint2 *cell = (uint2 *)(q.base[r] + parOff + (size_t)q.rank * DD_PEER_SLOT_BYTES) + o * NW;
+#pragma unroll
+      for (int k = 0; k < NW; k++) dd_st_cell(cell + k, w[k], call);
+    }
+  }
+
+  const unsigned long long t0 = dd_globaltimer();
+  for (int64_t o = first; o < nout; o += nthreads) {
+    uint2 v[DD_PEER_MAX][NW];
+    unsigned spins = 0;
+    int late = -1;
+    for (;;) {
+      late = -1;
+#pragma unroll
+      for (int r = 0; r < DD_PEER_MAX; r++) {
+        if (r < W && r != q.rank) {
+          const uint2 *cell = (const uint2 *)(mine + parOff + (size_t)r * DD_PEER_SLOT_BYTES) + o * NW;
+#pragma unroll
+          for (int k = 0; k < NW; k++) v[r][k] = dd_ld_cell(cell + k);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < DD_PEER_MAX; r++) {
+        if (r < W && r != q.rank) {
+#pragma unroll
+          for (int k = 0; k < NW; k++)
+            if (v[r][k].y != call) late = r;
+        }
+      }
+      if (late < 0) break;
+      if (++spins > (1u << 24) || ((spins & 63u) == 0 && dd_globaltimer() - t0 > q.waitNs)) break;
+    }
+    if (late >= 0) {
+      atomicExch((int *)ctl + 2, 1 + late);
+      continue;
+    }
+    C acc = (C)0;
+#pragma unroll
+    for (int r = 0; r < DD_PEER_MAX; r++) {
+      if (r < W) {
+        C val;
+        if (r == q.rank) {
+          val = part[o];
+        } else {
+          unsigned w[NW];
+#pragma unroll
+          for (int k = 0; k < NW; k++) w[k] = v[r][k].x;
+          val = dd_words<C>::join(w);
+        }
+        acc = r == 0 ? val : dd_red<C, OPC>::comb(acc, val, nanProp);
+      }
+    }
+    const int64_t k1 = o / p.K2;
+    dd_red_finish<T, C>(p, k1, o - k1 * p.K2, acc);
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {
+      ctl[1] = 0;
+      __stcg(ctl, call);
+    }
+  }
+}
+
 // generic: one thread per output, serial walk over the reduced dims.
 struct ddRedGenericParams {
   const void *x;
@@ -405,9 +559,12 @@ template <typename T, typename C>
 ddStatus_t dd_reduce_launch(ddHandle_t h, const ddRedPlan &pl);
 template <typename T, typename C>
 ddStatus_t dd_reduce_finish_launch(ddHandle_t h, const ddRedPlan &pl, const void *part);
+template <typename T, typename C>
+ddStatus_t dd_reduce_exchange_launch(ddHandle_t h, const ddRedPlan &pl, const ddPeerParams &q);
 #define DD_REDUCE_DECLARE(T, C)                                                   \
   template <> ddStatus_t dd_reduce_launch<T, C>(ddHandle_t, const ddRedPlan &);   \
-  template <> ddStatus_t dd_reduce_finish_launch<T, C>(ddHandle_t, const ddRedPlan &, const void *);
+  template <> ddStatus_t dd_reduce_finish_launch<T, C>(ddHandle_t, const ddRedPlan &, const void *); \
+  template <> ddStatus_t dd_reduce_exchange_launch<T, C>(ddHandle_t, const ddRedPlan &, const ddPeerParams &);
 DD_REDUCE_DECLARE(float, float)
 DD_REDUCE_DECLARE(double, double)
 DD_REDUCE_DECLARE(__half, float)
@@ -445,6 +602,31 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
     dd_reduce_finish_kernel<T, C, OPC><<<fg, 256, 0, h->stream>>>(p, part);                        \
     DD_LAUNCHED(h, "reduce/finish");                                                               \
     return DD_STATUS_SUCCESS;                                                                      \
+  }                                                                                                \
+  template <int OPC>                                                                               \
+  static ddStatus_t exchange_opc_##T(ddHandle_t h, const ddRedPlan &pl, const ddPeerParams &q) {   \
+    ddRedParams p = pl.p;                                                                          \
+    p.S = 1;                                                                                       \
+    p.partialOnly = 0;                                                                             \
+    int64_t g = (pl.nout + 255) / 256;                                                             \
+    unsigned grid = (unsigned)(g < 1 ? 1 : (g > DD_PEER_GRID_MAX ? DD_PEER_GRID_MAX : g));         \
+    dd_reduce_exchange_kernel<T, C, OPC><<<grid, 256, 0, h->stream>>>(p, q);                       \
+    DD_LAUNCHED(h, "reduce/peer-exchange");                                                        \
+    return DD_STATUS_SUCCESS;                                                                      \
+  }                                                                                                \
+  template <>                                                                                      \
+  ddStatus_t dd_reduce_exchange_launch<T, C>(ddHandle_t h, const ddRedPlan &pl, const ddPeerParams &q) { \
+    switch (pl.opc) {                                                                              \
+      case DD_OPC_SUM: return exchange_opc_##T<DD_OPC_SUM>(h, pl, q);                              \
+      case DD_OPC_SUMABS: return exchange_opc_##T<DD_OPC_SUMABS>(h, pl, q);                        \
+      case DD_OPC_SUMSQ: return exchange_opc_##T<DD_OPC_SUMSQ>(h, pl, q);                          \
+      case DD_OPC_PROD: return exchange_opc_##T<DD_OPC_PROD>(h, pl, q);                            \
+      case DD_OPC_PRODNZ: return exchange_opc_##T<DD_OPC_PRODNZ>(h, pl, q);                        \
+      case DD_OPC_MIN: return exchange_opc_##T<DD_OPC_MIN>(h, pl, q);                              \
+      case DD_OPC_MAX: return exchange_opc_##T<DD_OPC_MAX>(h, pl, q);                              \
+      case DD_OPC_AMAX: return exchange_opc_##T<DD_OPC_AMAX>(h, pl, q);                            \
+    }                                                                                              \
+    return DD_STATUS_INTERNAL_ERROR;                                                               \
   }                                                                                                \
   template <>                                                                                      \
   ddStatus_t dd_reduce_launch<T, C>(ddHandle_t h, const ddRedPlan &pl) {                           \

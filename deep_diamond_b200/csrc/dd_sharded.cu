@@ -1,8 +1,16 @@
 // Multi-GPU reduce: one process per GPU, tensors sharded along the batch dim.  A reduction that
-// spans the sharded dim = local partial reduce -> ncclAllReduce of the partial buffer on the
-// handle's stream -> finishing kernel.  NCCL is looked up at run time so that single-GPU users of
-// the library never need it.
+// spans the sharded dim = local partial reduce, then the partial results (a few KB) are combined
+// across the ranks and finished.  Two ways to combine:
+//
+//   peer exchange   ONE kernel per rank that pushes its accumulators into every rank's exchange
+//                   buffer over NVLink (CUDA IPC mappings) as tagged 8-byte cells, polls its own
+//                   buffer for the others' and finishes (dd_reduce_exchange_kernel).  Needs ddShardedPeerExport/Attach; up to
+//                   DD_PEER_MAX ranks of one box.
+//   NCCL            ncclAllReduce of the partial buffer on the handle's stream, then the finishing
+//                   kernel.  NCCL is looked up at run time so that single-GPU users of the library
+//                   never need it.
 #include "dd_internal.cuh"
+#include "dd_reduce_kernels.cuh"
 
 #include <dlfcn.h>
 #include <mutex>
@@ -56,10 +64,19 @@ static bool load_nccl() {
 
 struct ddShardedStruct {
   ddHandle_t h;
-  ncclComm_t comm;
+  ncclComm_t comm;  // NULL: created without an id, peer exchange only
   int nRanks, rank;
-  void *partial;  // DD_PARTIAL_BYTES of device memory for the all-reduced accumulators
+  void *partial;    // DD_PARTIAL_BYTES of device memory for the local (NCCL: all-reduced) accumulators
+  unsigned char *xbuf;                   // this rank's exchange buffer (DD_PEER_BYTES), NULL until exported
+  unsigned char *peerBase[DD_PEER_MAX];  // every rank's exchange buffer as mapped here
+  bool peerOpened[DD_PEER_MAX];          // mapped with cudaIpcOpenMemHandle (to be closed)
+  bool attached;
+  int usePeer;                           // 1: combine over the peer exchange when attached
+  unsigned long long waitNs;
 };
+
+static_assert(DD_PEER_SLOT_BYTES == 2 * DD_PARTIAL_BYTES, "one slot holds one partial buffer as 8-byte {word, tag} cells");
+static_assert(sizeof(cudaIpcMemHandle_t) == DD_PEER_HANDLE_BYTES, "IPC handle size");
 
 extern "C" {
 
@@ -74,10 +91,10 @@ ddStatus_t ddShardedGetUniqueId(void *id128) {
 
 ddStatus_t ddShardedCreate(ddShardedHandle_t *out, ddHandle_t h, int nRanks, int rank,
                            const void *id128) {
-  if (!out || !h || !id128) return DD_STATUS_BAD_PARAM;
+  if (!out || !h) return DD_STATUS_BAD_PARAM;
   *out = nullptr;
   if (nRanks < 1 || rank < 0 || rank >= nRanks) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddShardedCreate: bad rank %d of %d", rank, nRanks);
-  if (!load_nccl()) DD_FAIL(h, DD_STATUS_NOT_INITIALIZED, "ddShardedCreate: libnccl.so.2 not found: %s", dlerror());
+  if (id128 && !load_nccl()) DD_FAIL(h, DD_STATUS_NOT_INITIALIZED, "ddShardedCreate: libnccl.so.2 not found: %s", dlerror());
   ddShardedStruct *s = new (std::nothrow) ddShardedStruct();
   if (!s) return DD_STATUS_ALLOC_FAILED;
   s->h = h;
@@ -85,33 +102,142 @@ ddStatus_t ddShardedCreate(ddShardedHandle_t *out, ddHandle_t h, int nRanks, int
   s->rank = rank;
   s->comm = nullptr;
   s->partial = nullptr;
+  s->xbuf = nullptr;
+  for (int i = 0; i < DD_PEER_MAX; i++) {
+    s->peerBase[i] = nullptr;
+    s->peerOpened[i] = false;
+  }
+  s->attached = false;
+  s->usePeer = 1;
+  s->waitNs = 2000000000ull;  // 2 s
   if (cudaMalloc(&s->partial, DD_PARTIAL_BYTES) != cudaSuccess) {
     cudaGetLastError();
     delete s;
     DD_FAIL(h, DD_STATUS_ALLOC_FAILED, "ddShardedCreate: cudaMalloc failed");
   }
-  ncclUniqueId id;
-  memcpy(&id, id128, sizeof(id));
-  ncclResult_t r = g_nccl.CommInitRank(&s->comm, nRanks, id, rank);
-  if (r != 0) {
-    cudaFree(s->partial);
-    delete s;
-    DD_FAIL(h, DD_STATUS_COMM_FAILED, "ncclCommInitRank: %s", g_nccl.GetErrorString(r));
+  if (id128) {
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    ncclResult_t r = g_nccl.CommInitRank(&s->comm, nRanks, id, rank);
+    if (r != 0) {
+      cudaFree(s->partial);
+      delete s;
+      DD_FAIL(h, DD_STATUS_COMM_FAILED, "ncclCommInitRank: %s", g_nccl.GetErrorString(r));
+    }
   }
   *out = s;
   return DD_STATUS_SUCCESS;
 }
 
+static void peer_detach(ddShardedStruct *s) {
+  for (int i = 0; i < DD_PEER_MAX; i++) {
+    if (s->peerOpened[i] && s->peerBase[i]) cudaIpcCloseMemHandle(s->peerBase[i]);
+    s->peerBase[i] = nullptr;
+    s->peerOpened[i] = false;
+  }
+  s->attached = false;
+}
+
 ddStatus_t ddShardedDestroy(ddShardedHandle_t s) {
   if (!s) return DD_STATUS_BAD_PARAM;
+  if (s->h) cudaStreamSynchronize(s->h->stream);  // no exchange of this rank may still be in flight
+  peer_detach(s);
   if (s->comm) g_nccl.CommDestroy(s->comm);
+  if (s->xbuf) cudaFree(s->xbuf);
   if (s->partial) cudaFree(s->partial);
+  cudaGetLastError();
   delete s;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddShardedPeerExport(ddShardedHandle_t s, void *handle64) {
+  if (!s || !handle64) return DD_STATUS_BAD_PARAM;
+  ddHandle_t h = s->h;
+  if (s->nRanks > DD_PEER_MAX)
+    DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddShardedPeerExport: the peer exchange covers up to %d ranks", DD_PEER_MAX);
+  if (!s->xbuf) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, DD_PEER_BYTES) != cudaSuccess) {
+      cudaGetLastError();
+      DD_FAIL(h, DD_STATUS_ALLOC_FAILED, "ddShardedPeerExport: cudaMalloc failed");
+    }
+    // control words and every cell's tag start at zero (no call has number 0); finished before
+    // anyone can learn the handle
+    if (cudaMemset(p, 0, DD_PEER_BYTES) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(p);
+      DD_FAIL(h, DD_STATUS_EXECUTION_FAILED, "ddShardedPeerExport: clearing the exchange buffer failed");
+    }
+    s->xbuf = (unsigned char *)p;
+  }
+  cudaIpcMemHandle_t ipc;
+  cudaError_t e = cudaIpcGetMemHandle(&ipc, s->xbuf);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    DD_FAIL(h, DD_STATUS_MAPPING_ERROR, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle64, &ipc, sizeof(ipc));
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddShardedPeerAttach(ddShardedHandle_t s, const void *handles) {
+  if (!s || !handles) return DD_STATUS_BAD_PARAM;
+  ddHandle_t h = s->h;
+  if (!s->xbuf) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddShardedPeerAttach: call ddShardedPeerExport first");
+  if (s->attached) peer_detach(s);
+  cudaIpcMemHandle_t own;
+  if (cudaIpcGetMemHandle(&own, s->xbuf) != cudaSuccess) {
+    cudaGetLastError();
+    DD_FAIL(h, DD_STATUS_MAPPING_ERROR, "ddShardedPeerAttach: cudaIpcGetMemHandle failed");
+  }
+  for (int r = 0; r < s->nRanks; r++) {
+    cudaIpcMemHandle_t ipc;
+    memcpy(&ipc, (const char *)handles + (size_t)r * sizeof(ipc), sizeof(ipc));
+    // an entry that names this rank's own buffer (its own position always does) needs no mapping
+    if (r == s->rank || memcmp(&ipc, &own, sizeof(ipc)) == 0) {
+      s->peerBase[r] = s->xbuf;
+      continue;
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, ipc, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      peer_detach(s);
+      DD_FAIL(h, DD_STATUS_MAPPING_ERROR, "cudaIpcOpenMemHandle (rank %d): %s", r, cudaGetErrorString(e));
+    }
+    s->peerBase[r] = (unsigned char *)p;
+    s->peerOpened[r] = true;
+  }
+  s->attached = true;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddShardedPeerConfigure(ddShardedHandle_t s, int usePeer, double waitSeconds) {
+  if (!s) return DD_STATUS_BAD_PARAM;
+  if (usePeer >= 0) s->usePeer = usePeer ? 1 : 0;
+  if (waitSeconds > 0) s->waitNs = (unsigned long long)(waitSeconds * 1e9);
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddShardedPeerStatus(ddShardedHandle_t s, int *status) {
+  if (!s || !status) return DD_STATUS_BAD_PARAM;
+  *status = 0;
+  if (!s->xbuf) return DD_STATUS_SUCCESS;
+  ddHandle_t h = s->h;
+  cudaError_t e = cudaMemcpyAsync(status, s->xbuf + 2 * sizeof(unsigned), sizeof(int), cudaMemcpyDeviceToHost, h->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    DD_FAIL(h, DD_STATUS_EXECUTION_FAILED, "ddShardedPeerStatus: %s", cudaGetErrorString(e));
+  }
+  if (*status != 0)
+    DD_FAIL(h, DD_STATUS_TIMEOUT, "peer exchange: the wait for rank %d ran out; the exchange buffers are out of step, create a new sharded handle", *status - 1);
   return DD_STATUS_SUCCESS;
 }
 
 ddStatus_t ddShardedCheck(ddShardedHandle_t s) {
   if (!s) return DD_STATUS_BAD_PARAM;
+  if (!s->comm) return DD_STATUS_SUCCESS;
   ncclResult_t async = 0;
   ncclResult_t r = g_nccl.CommGetAsyncError(s->comm, &async);
   if (r != 0) DD_FAIL(s->h, DD_STATUS_COMM_FAILED, "ncclCommGetAsyncError: %s", g_nccl.GetErrorString(r));
@@ -147,8 +273,21 @@ ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t
     default: ncclOp = DD_NCCL_MAX; break;  // MAX, AMAX
   }
   double a = dd_read_scalar(alpha, xd->dtype), b = dd_read_scalar(beta, yd->dtype);
+  const bool peer = s->attached && s->usePeer;
+  if (!peer && !s->comm)
+    DD_FAIL(h, DD_STATUS_NOT_INITIALIZED, "ddShardedReduceTensor: no NCCL communicator and no peer exchange attached");
   ddStatus_t st = dd_reduce_impl(h, red, nullptr, 0, 1.0, xd, x, 0.0, yd, y, true, s->partial);
   if (st != DD_STATUS_SUCCESS) return st;
+  if (peer) {
+    ddPeerParams q;
+    for (int i = 0; i < DD_PEER_MAX; i++) q.base[i] = s->peerBase[i];
+    q.partial = s->partial;
+    q.world = s->nRanks;
+    q.rank = s->rank;
+    q.waitNs = s->waitNs;
+    // equal shards: the global count is nRanks times the local one
+    return dd_reduce_exchange_impl(h, red, &q, (double)nredLocal * s->nRanks, a, b, xd, yd, y);
+  }
   ncclResult_t r = g_nccl.AllReduce(s->partial, s->partial, (size_t)nout, dbl ? DD_NCCL_FLOAT64 : DD_NCCL_FLOAT32,
                                     ncclOp, s->comm, h->stream);
   if (r != 0) DD_FAIL(h, DD_STATUS_COMM_FAILED, "ncclAllReduce: %s", g_nccl.GetErrorString(r));

@@ -6,7 +6,9 @@ arithmetic `shard_range` repeats.
 
 Reorder, eltwise and broadcast op-tensor need no communication: every rank just runs the
 single-GPU call on its slice.  Only a reduction that spans the sharded dim exchanges data: the
-local partial result (a few KB) is all-reduced over NCCL on the compute stream, then finished.
+local partial results (a few KB) are combined across the ranks and finished, either by the
+library's own peer exchange (one kernel per rank pushing into every rank's buffer over NVLink) or
+by an NCCL all-reduce on the compute stream followed by a finishing kernel.
 """
 import ctypes
 
@@ -16,6 +18,8 @@ from . import core
 from ._lib import DiamondError, check, lib
 
 UNIQUE_ID_BYTES = 128
+PEER_HANDLE_BYTES = 64
+PEER_MAX_RANKS = 8
 
 
 def shard_range(n, world_size, rank):
@@ -46,15 +50,17 @@ def get_unique_id():
 
 
 class ShardedHandle:
-    """The library's communicator for one rank (wraps ddShardedCreate)."""
+    """The library's communicator for one rank (wraps ddShardedCreate).  ``unique_id=None`` makes a
+    handle without NCCL that can only combine over the peer exchange."""
 
     def __init__(self, fact, world_size, rank, unique_id):
         self.fact, self.world_size, self.rank = fact, world_size, rank
         h = ctypes.c_void_p()
-        idbuf = (ctypes.c_ubyte * UNIQUE_ID_BYTES).from_buffer_copy(unique_id)
+        idbuf = (ctypes.c_ubyte * UNIQUE_ID_BYTES).from_buffer_copy(unique_id) if unique_id is not None else None
         check(lib.ddShardedCreate(ctypes.byref(h), fact.handle.ptr, world_size, rank, idbuf),
               fact.handle.ptr, "ddShardedCreate")
         self.ptr = h
+        self.peer_attached = False
 
     def reduce_tensor(self, rtd, alpha, desc_x, x, beta, desc_y, y, spans=None):
         dx, dy = core.desc(desc_x), core.desc(desc_y)
@@ -65,6 +71,36 @@ class ShardedHandle:
                                         core._ptr(x), ctypes.byref(b), dy.ptr, core._ptr(y)),
               self.fact.handle.ptr, "ddShardedReduceTensor")
         return y
+
+    def peer_export(self):
+        """This rank's exchange-buffer handle (64 bytes) for the other processes of the box."""
+        buf = (ctypes.c_ubyte * PEER_HANDLE_BYTES)()
+        check(lib.ddShardedPeerExport(self.ptr, buf), self.fact.handle.ptr, "ddShardedPeerExport")
+        return bytes(buf)
+
+    def peer_attach(self, handles):
+        """`handles`: every rank's exported handle, in rank order."""
+        if len(handles) != self.world_size or any(len(hd) != PEER_HANDLE_BYTES for hd in handles):
+            raise DiamondError("One 64-byte handle per rank is needed.",
+                               {"world-size": self.world_size, "handles": len(handles)})
+        blob = b"".join(handles)
+        buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+        check(lib.ddShardedPeerAttach(self.ptr, buf), self.fact.handle.ptr, "ddShardedPeerAttach")
+        self.peer_attached = True
+        return self
+
+    def peer_configure(self, use_peer=None, wait_seconds=None):
+        check(lib.ddShardedPeerConfigure(self.ptr, -1 if use_peer is None else int(bool(use_peer)),
+                                         0.0 if wait_seconds is None else float(wait_seconds)),
+              self.fact.handle.ptr, "ddShardedPeerConfigure")
+        return self
+
+    def peer_status(self):
+        """Synchronises the stream; raises DiamondError (type timeout) when a bounded wait of the
+        exchange ran out, else returns 0."""
+        st = ctypes.c_int(0)
+        check(lib.ddShardedPeerStatus(self.ptr, ctypes.byref(st)), self.fact.handle.ptr, "ddShardedPeerStatus")
+        return st.value
 
     def check(self):
         check(lib.ddShardedCheck(self.ptr), self.fact.handle.ptr, "ddShardedCheck")
@@ -77,16 +113,44 @@ class ShardedHandle:
         return True
 
 
-def create_from_torch_distributed(fact):
+def gather_in_rank_order(payload, all_gather_object, world_size):
+    """Every rank's `payload` as a list indexed by rank, through any all-gather of Python objects
+    (``torch.distributed.all_gather_object`` over gloo or nccl)."""
+    out = [None] * world_size
+    all_gather_object(out, payload)
+    return out
+
+
+def create_from_torch_distributed(fact, peer=True, nccl=True):
     """Builds the library communicator for this rank from an initialised torch.distributed group:
-    rank 0 makes the id, the group broadcasts it (any transport: gloo or nccl)."""
+    rank 0 makes the NCCL id, the group broadcasts it (any transport: gloo or nccl); with `peer`
+    the ranks also swap exchange-buffer handles and attach the peer exchange (boxes of up to 8
+    GPUs), which then carries the reductions."""
     import torch
     import torch.distributed as dist
     world, rank = dist.get_world_size(), dist.get_rank()
-    payload = [get_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(payload, src=0)
+    payload = [None]
+    if nccl:
+        payload = [get_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(payload, src=0)
     with torch.cuda.device(fact.device):
-        return ShardedHandle(fact, world, rank, payload[0])
+        sh = ShardedHandle(fact, world, rank, payload[0])
+        if peer and world <= PEER_MAX_RANKS:
+            handles = gather_in_rank_order(sh.peer_export(), dist.all_gather_object, world)
+            try:
+                sh.peer_attach(handles)
+                mine = None
+            except DiamondError as e:       # e.g. no peer access between two of the GPUs
+                mine = str(e)
+            errors = gather_in_rank_order(mine, dist.all_gather_object, world)
+            if any(errors):
+                # the exchange needs every rank: all fall back to NCCL together, or fail together
+                sh.peer_attached = False
+                sh.peer_configure(use_peer=False)
+                if not nccl:
+                    raise DiamondError("The peer exchange could not be attached on every rank.",
+                                       {"errors": [e for e in errors if e]})
+        return sh
 
 
 def combine_partials_host(op, partials, local_count, world_size):

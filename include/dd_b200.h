@@ -331,9 +331,10 @@ DD_API ddStatus_t ddReduceTensorNoAlloc(void *stream, ddReduceTensorOp_t op, ddN
 
 /* No counterpart in the reference (it has no multi-device code).  One process per GPU; a tensor is
  * sharded along its batch dim, each rank holding `x` = its own slice.  A reduction that spans the
- * sharded dim runs the local partial reduce, one ncclAllReduce of the (small) partial result on the
- * handle's stream, and the finishing kernel (sqrt / divide / alpha-beta).  The NCCL library is
- * located at run time (libnccl.so.2); nothing else in this header needs it.
+ * sharded dim runs the local partial reduce, then combines the (small) partial results across the
+ * ranks and finishes (sqrt / divide / alpha-beta): by one ncclAllReduce on the handle's stream plus
+ * a finishing kernel, or by the peer exchange below.  The NCCL library is located at run time
+ * (libnccl.so.2); nothing else in this header needs it.
  *
  * ddShardedGetUniqueId fills a 128-byte id on one rank; the caller ships it to the other ranks by
  * any means; every rank then calls ddShardedCreate (collective, blocks until all ranks join or the
@@ -350,6 +351,23 @@ DD_API ddStatus_t ddShardedReduceTensor(ddShardedHandle_t sharded, ddReduceTenso
                                  int spansShardedDim, const void *alpha,
                                  ddTensorDescriptor_t xDesc, const void *x, const void *beta,
                                  ddTensorDescriptor_t yDesc, void *y);
+/* Peer exchange: the combine step as ONE kernel per rank over NVLink instead of the NCCL call
+ * (no counterpart in the reference).  Every rank calls ddShardedPeerExport (allocates its
+ * exchange buffer once and returns a DD_PEER_HANDLE_BYTES handle for other processes of the same
+ * box), the caller gathers all ranks' handles in rank order by any transport, and every rank calls
+ * ddShardedPeerAttach with the nRanks * DD_PEER_HANDLE_BYTES bytes; from then on
+ * ddShardedReduceTensor uses the exchange.  Up to 8 ranks.  ddShardedCreate accepts a NULL id for
+ * a handle that only ever uses the peer exchange (no NCCL needed).
+ * ddShardedPeerConfigure: usePeer 0/1 switches between NCCL and the exchange (-1: leave), and
+ * waitSeconds > 0 sets the limit of the kernel's bounded waits (default 2 s).
+ * ddShardedPeerStatus synchronises the handle's stream and reports whether a wait ran out
+ * (*status = 1 + the rank waited for, return DD_STATUS_TIMEOUT); the kernel that gave up wrote no
+ * result, returned normally, and the CUDA context stays usable. */
+#define DD_PEER_HANDLE_BYTES 64
+DD_API ddStatus_t ddShardedPeerExport(ddShardedHandle_t sharded, void *handle64);
+DD_API ddStatus_t ddShardedPeerAttach(ddShardedHandle_t sharded, const void *allHandles);
+DD_API ddStatus_t ddShardedPeerConfigure(ddShardedHandle_t sharded, int usePeer, double waitSeconds);
+DD_API ddStatus_t ddShardedPeerStatus(ddShardedHandle_t sharded, int *status);
 /* Non-blocking health check of the communicator (wraps ncclCommGetAsyncError). */
 DD_API ddStatus_t ddShardedCheck(ddShardedHandle_t sharded);
 

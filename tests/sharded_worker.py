@@ -1,7 +1,8 @@
 """One rank of the multi-GPU reduce test (launched by tests/test_gpu_sharded.py under
 torch.distributed.run).  Every rank builds the same full tensor from a seed, keeps its own batch
-slice on its GPU, runs ddShardedReduceTensor, and checks the (replicated) result against the CPU
-oracle's reduction of the whole tensor."""
+slice on its GPU, runs ddShardedReduceTensor over both combine paths (the library's peer exchange
+and NCCL), and checks the (replicated) result against the CPU oracle's reduction of the whole
+tensor."""
 import os
 import sys
 
@@ -13,6 +14,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
+def within(got, want, full, alpha, axes):
+    scale = np.abs(full.astype(np.float64)).sum(axis=axes, keepdims=True)
+    return bool((np.abs(got - want) <= np.maximum(1e-5 * np.abs(want), 16 * 6e-8 * abs(alpha) * scale)).all())
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -22,7 +28,7 @@ def main():
     from deep_diamond_b200 import b200_factory, core, sharded
     fact = b200_factory(local)
     sh = sharded.create_from_torch_distributed(fact)
-    assert sh.check()
+    assert sh.check() and sh.peer_attached
     full_shape = [4 * world, 64, 16, 16]
     full = oracle.gen_signed_lognormal(full_shape, 5)
     lo, hi = sharded.shard_range(full_shape[0], world, rank)
@@ -31,24 +37,84 @@ def main():
     shard_shape = list(mine.shape)
     xd = core.tensor_descriptor(shard_shape, "float", "nchw")
     failures = []
-    for op in ("add", "avg", "norm2", "norm1", "max", "min", "amax"):
-        for alpha, beta in ((1.0, 0.0), (2.0, 0.5)):
-            yshape = [1, 64, 1, 1]
-            y0 = np.linspace(-1, 1, 64, dtype=np.float32)
-            want = y0.copy().reshape(yshape)
-            _, truth = oracle.reduce(op, full, want, alpha=alpha, beta=beta, want_truth=True)
-            y = torch.from_numpy(y0.copy()).to(fact.device)
-            yd = core.tensor_descriptor(yshape, "float", "nchw")
-            sh.reduce_tensor(core.reduce_tensor_descriptor(op, "float"), alpha, xd, x, beta, yd, y)
-            fact.synchronize()
-            got = y.cpu().numpy().reshape(yshape)
-            if op in ("max", "min", "amax") and beta == 0.0:
-                ok = np.array_equal(got, want)
-            else:
-                scale = np.abs(full.astype(np.float64)).sum(axis=(0, 2, 3), keepdims=True)
-                ok = bool((np.abs(got - want) <= np.maximum(1e-5 * np.abs(want), 16 * 6e-8 * abs(alpha) * scale)).all())
-            if not ok:
-                failures.append((op, alpha, beta, float(np.abs(got - want).max())))
+    for path in ("peer", "nccl"):
+        sh.peer_configure(use_peer=(path == "peer"))
+        for op in ("add", "avg", "norm2", "norm1", "max", "min", "amax"):
+            for alpha, beta in ((1.0, 0.0), (2.0, 0.5)):
+                yshape = [1, 64, 1, 1]
+                y0 = np.linspace(-1, 1, 64, dtype=np.float32)
+                want = y0.copy().reshape(yshape)
+                oracle.reduce(op, full, want, alpha=alpha, beta=beta)
+                y = torch.from_numpy(y0.copy()).to(fact.device)
+                yd = core.tensor_descriptor(yshape, "float", "nchw")
+                sh.reduce_tensor(core.reduce_tensor_descriptor(op, "float"), alpha, xd, x, beta, yd, y)
+                fact.synchronize()
+                want_kernel = "reduce/peer-exchange" if path == "peer" else "reduce/finish"
+                if fact.handle.last_kernel() != want_kernel:
+                    failures.append((path, "kernel", fact.handle.last_kernel()))
+                got = y.cpu().numpy().reshape(yshape)
+                if op in ("max", "min", "amax") and beta == 0.0:
+                    ok = np.array_equal(got, want)
+                else:
+                    ok = within(got, want, full, alpha, (0, 2, 3))
+                if not ok:
+                    failures.append((path, op, alpha, beta, float(np.abs(got - want).max())))
+        # all ranks must hold identical bits for the replicated results
+        y = torch.zeros(64, device=fact.device)
+        sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0, xd, x, 0.0,
+                         core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y)
+        gathered = [torch.zeros_like(y) for _ in range(world)]
+        dist.all_gather(gathered, y)
+        if any(not torch.equal(g, gathered[0]) for g in gathered):
+            failures.append((path, "replicas differ"))
+    sh.peer_configure(use_peer=True)
+
+    # many outputs (several CTAs of the exchange kernel, each with its own flags): sum over N only
+    yshape = [1, 64, 16, 16]
+    want = np.zeros(yshape, np.float32)
+    oracle.reduce("add", full, want)
+    y = torch.zeros(int(np.prod(yshape)), device=fact.device)
+    yd = core.tensor_descriptor(yshape, "float", "nchw")
+    rtd = core.reduce_tensor_descriptor("add", "float")
+    for _ in range(5):          # calls in a row alternate the exchange's two parities
+        y.zero_()
+        sh.reduce_tensor(rtd, 1.0, xd, x, 0.0, yd, y)
+    fact.synchronize()
+    if not within(y.cpu().numpy().reshape(yshape), want, full, 1.0, (0,)):
+        failures.append(("sum over N, 16384 outputs",))
+
+    # a captured launch replayed: the call number lives on the device, so replays stay in step
+    side = torch.cuda.Stream(device=fact.device)
+    side.wait_stream(fact.stream)
+    fact.handle.set_stream(side)
+    with torch.cuda.stream(side):
+        sh.reduce_tensor(rtd, 1.0, xd, x, 0.0, yd, y)
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(3):
+                sh.reduce_tensor(rtd, 1.0, xd, x, 0.0, yd, y)
+        for _ in range(4):
+            y.zero_()
+            g.replay()
+        side.synchronize()
+    fact.handle.set_stream(fact.stream)
+    if not within(y.cpu().numpy().reshape(yshape), want, full, 1.0, (0,)):
+        failures.append(("graph replay",))
+
+    # double precision accumulators through the exchange
+    fulld = full.astype(np.float64)
+    xdbl = torch.from_numpy(np.ascontiguousarray(fulld[lo:hi])).to(fact.device)
+    wantd = np.zeros([1, 64, 1, 1], np.float64)
+    oracle.reduce("norm2", fulld, wantd)
+    yd64 = torch.zeros(64, dtype=torch.float64, device=fact.device)
+    sh.reduce_tensor(core.reduce_tensor_descriptor("norm2", "double"), 1.0,
+                     core.tensor_descriptor(shard_shape, "double", "nchw"), xdbl, 0.0,
+                     core.tensor_descriptor([1, 64, 1, 1], "double", "nchw"), yd64)
+    fact.synchronize()
+    if not np.allclose(yd64.cpu().numpy().reshape(wantd.shape), wantd, rtol=1e-12):
+        failures.append(("norm2 double",))
+
     # a reduction that keeps the sharded dim needs no exchange: result stays sharded
     yshape = [shard_shape[0], 1, 16, 16]
     want = np.zeros(yshape, np.float32)
@@ -59,16 +125,12 @@ def main():
     fact.synchronize()
     if not np.array_equal(y.cpu().numpy().reshape(yshape), want):
         failures.append(("max over C (local)",))
-    # all ranks must hold identical bits for the replicated results
-    y = torch.zeros(64, device=fact.device)
-    sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0, xd, x, 0.0,
-                     core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y)
-    gathered = [torch.zeros_like(y) for _ in range(world)]
-    dist.all_gather(gathered, y)
-    if any(not torch.equal(g, gathered[0]) for g in gathered):
-        failures.append(("replicas differ",))
+
+    if sh.peer_status() != 0:
+        failures.append(("peer status",))
     flag = torch.tensor([len(failures)], device=fact.device)
     dist.all_reduce(flag)
+    dist.barrier()
     sh.release()
     fact.release()
     dist.destroy_process_group()

@@ -19,7 +19,7 @@ def test_library_exports_every_declared_symbol():
     from deep_diamond_b200 import _lib
     header = open(os.path.join(ROOT, "include", "dd_b200.h")).read()
     declared = set(re.findall(r"DD_API\s+[\w\s\*]+?\b(dd[A-Z]\w+)\s*\(", header))
-    assert len(declared) >= 45
+    assert len(declared) >= 49
     lib = ctypes.CDLL(_lib.LIB_PATH)
     missing = [name for name in sorted(declared) if not hasattr(lib, name)]
     assert not missing, missing
@@ -123,6 +123,9 @@ for op, pre in (("add", "add"), ("avg", "add"), ("norm2", None), ("max", "max"),
     want = np.zeros(yshape, np.float32)
     _, truth = oracle.reduce(op, full, want, want_truth=True)
     ok = ok and np.allclose(got, truth, rtol=1e-5, atol=1e-5)
+# the handle swap of the peer exchange: every rank ends up with all handles in rank order
+handles = sharded.gather_in_rank_order(bytes([rank + 1]) * sharded.PEER_HANDLE_BYTES, dist.all_gather_object, world)
+ok = ok and handles == [bytes([1]) * 64, bytes([2]) * 64]
 flags = [None, None]
 dist.all_gather_object(flags, bool(ok))
 dist.barrier()
