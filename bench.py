@@ -607,8 +607,8 @@ def run_ours(args):
                          "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                          # dram__bytes_read.sum + dram__bytes_write.sum per backward launch, mean of the four
                          # activations in profiles/eltwise_flat_kernel_ncu_full.md (reads 411.1 MB = the
-                         # algorithmic input; writes 173 MB: the tail of dx is still in L2 at kernel end)
-                         "traffic": 584.5e6, "traffic_source": "ncu capture, profiles/eltwise_flat_kernel_ncu_full.md",
+                         # algorithmic input; writes 173.8 MB: the tail of dx is still in L2 at kernel end)
+                         "traffic": 584.8e6, "traffic_source": "ncu capture, profiles/eltwise_flat_kernel_ncu_full.md",
                          "avg_launch_ms": round(bwd_avg_ms, 5),
                          "algorithmic_bytes_per_launch": bwd_bytes},
             "per_kernel": per_kernel,
