@@ -169,6 +169,7 @@ struct ddEltFlatParams {
 // PLAIN: alpha == 1 and beta == 0 (what every layer passes): no blend arithmetic at all.
 template <typename T, typename C, int MODE, bool BWD, bool PLAIN>
 __global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) {
+  dd_pdl_prologue();
   constexpr int V = 16 / sizeof(T);
   const T *x = (const T *)p.x;
   const T *dy = (const T *)p.dy;
@@ -265,8 +266,8 @@ static ddStatus_t launch_elt(ddHandle_t h, const ddCanon &c, const void *x, cons
     p.vec = (bits & 15) == 0;
     constexpr int V = 16 / sizeof(T);
     unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
-    if (alpha == 1.0 && beta == 0.0) dd_elt_flat_kernel<T, C, MODE, BWD, true><<<grid, 256, 0, h->stream>>>(p);
-    else dd_elt_flat_kernel<T, C, MODE, BWD, false><<<grid, 256, 0, h->stream>>>(p);
+    if (alpha == 1.0 && beta == 0.0) dd_launch_pdl(dd_elt_flat_kernel<T, C, MODE, BWD, true>, grid, 256, h->stream, p);
+    else dd_launch_pdl(dd_elt_flat_kernel<T, C, MODE, BWD, false>, grid, 256, h->stream, p);
     DD_LAUNCHED(h, BWD ? "activation-bwd/flat" : "activation-fwd/flat");
   } else {
     ddEltStridedParams p;

@@ -61,6 +61,33 @@ struct ddContext {
       DD_FAIL(h, DD_STATUS_EXECUTION_FAILED, "%s: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched with dd_launch_pdl may be scheduled while the
+// previous kernel of the stream is still draining, which takes the launch latency out of
+// back-to-back calls.  Such a kernel MUST call dd_pdl_prologue() before its first access to global
+// memory: it holds the thread until the previous kernel has completed and its writes are visible,
+// then lets the NEXT kernel of the stream be scheduled early in turn.  Launched the ordinary way,
+// the prologue returns at once.
+__device__ __forceinline__ void dd_pdl_prologue() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename P>
+static inline void dd_launch_pdl(void (*kernel)(P), unsigned grid, unsigned block, cudaStream_t stream,
+                                 const P &params) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, params);  // a failure is picked up by DD_LAUNCHED's cudaGetLastError
+}
+
 static inline int dd_type_size(ddDataType_t t) {
   switch (t) {
     case DD_DATA_FLOAT: return 4;

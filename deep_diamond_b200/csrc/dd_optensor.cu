@@ -58,6 +58,7 @@ __device__ __forceinline__ int64_t dd_channel_of(const ddOpFlatParams &p, int64_
 // OP < 0: the op comes from p.op at run time (the less common ops share one instantiation).
 template <typename T, typename C, int OP, int BMODE>
 __global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
+  dd_pdl_prologue();
   constexpr int V = 16 / sizeof(T);
   const T *A = (const T *)p.A;
   const T *B = (const T *)p.B;
@@ -207,12 +208,12 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
     }
     unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 8);
     // add and mul (bias, per-channel scale, axpy, sum) get their own instantiations
-    if (op == DD_OP_TENSOR_ADD && bmode == 0) dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 0><<<grid, 256, 0, h->stream>>>(p);
-    else if (op == DD_OP_TENSOR_ADD) dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 1><<<grid, 256, 0, h->stream>>>(p);
-    else if (op == DD_OP_TENSOR_MUL && bmode == 0) dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 0><<<grid, 256, 0, h->stream>>>(p);
-    else if (op == DD_OP_TENSOR_MUL) dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 1><<<grid, 256, 0, h->stream>>>(p);
-    else if (bmode == 0) dd_op_flat_kernel<T, C, -1, 0><<<grid, 256, 0, h->stream>>>(p);
-    else dd_op_flat_kernel<T, C, -1, 1><<<grid, 256, 0, h->stream>>>(p);
+    if (op == DD_OP_TENSOR_ADD && bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 0>, grid, 256, h->stream, p);
+    else if (op == DD_OP_TENSOR_ADD) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 1>, grid, 256, h->stream, p);
+    else if (op == DD_OP_TENSOR_MUL && bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 0>, grid, 256, h->stream, p);
+    else if (op == DD_OP_TENSOR_MUL) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 1>, grid, 256, h->stream, p);
+    else if (bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 0>, grid, 256, h->stream, p);
+    else dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 1>, grid, 256, h->stream, p);
     DD_LAUNCHED(h, bmode == 0 ? "optensor/flat" : "optensor/flat-bcast");
     return DD_STATUS_SUCCESS;
   }

@@ -145,6 +145,7 @@ __global__ void __launch_bounds__((dd_tile_geom<S, D>::NT)) dd_tile_kernel(ddTil
   typedef dd_tile_geom<S, D> G;
   constexpr int VS = G::VS, VD = G::VD, NA = G::NA, NB = G::NB, TA = G::TA, TB = G::TB;
   __shared__ uint4 tile[TA * NB];
+  dd_pdl_prologue();
 
   // tile id -> (batch index, tile along B, tile along A); A varies fastest
   uint32_t id = blockIdx.x, ta, tb;
@@ -376,7 +377,7 @@ static ddStatus_t dd_launch_tile(ddHandle_t h, const ddTileParams &tp, int kind)
   for (int i = 0; i < tp.nb; i++) tiles *= tp.bdims[i];
   if (tiles > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "transform/tile: too many tiles");
   if (kind == 1) {
-    dd_tile_kernel<S, D, C, RAW><<<(unsigned)tiles, G::NT, 0, h->stream>>>(tp);
+    dd_launch_pdl(dd_tile_kernel<S, D, C, RAW>, (unsigned)tiles, (unsigned)G::NT, h->stream, tp);
     DD_LAUNCHED(h, "transform/tile");
   } else {
     dd_tile_scalar_kernel<S, D, C, RAW><<<(unsigned)tiles, 256, 0, h->stream>>>(tp);
