@@ -232,7 +232,7 @@ def event_ms(torch, fn, stream, reps, warm):
     return t[len(t) // 2], t[max(0, len(t) // 10)], t[min(len(t) - 1, (9 * len(t)) // 10)]
 
 
-def graph_ms(torch, fact, fn, per_graph, replays, warm=3):
+def graph_ms(torch, fact, fn, per_graph, replays, warm=20):
     """Per-launch device time of `fn` (one library call = one kernel) with the host taken out of the
     loop: `per_graph` calls are captured into a CUDA graph on a side stream, the graph is replayed
     `replays` times with an event pair around each replay, and the median replay time is divided by

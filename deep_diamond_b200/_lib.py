@@ -83,6 +83,7 @@ _SIGS = {
     "ddGetReductionIndicesSize": [_vp, _vp, _vp, _vp, ctypes.POINTER(_sz)],
     "ddGetReductionWorkspaceSize": [_vp, _vp, _vp, _vp, ctypes.POINTER(_sz)],
     "ddReduceTensor": [_vp, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ddConvolutionBackwardBias": [_vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "ddReduceTensorNoAlloc": [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_char_p, _sz],
     "ddShardedGetUniqueId": [_vp],
     "ddShardedCreate": [ctypes.POINTER(_vp), _vp, _int, _int, _vp],

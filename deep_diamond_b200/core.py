@@ -379,6 +379,15 @@ def reduce_tensor(handle, rtd, *args):
     return handle
 
 
+def convolution_bwd_bias(handle, alpha, desc_dy, buf_dy, beta, desc_db, buf_db):
+    """``convolution-bwd-bias`` (cudnn/core.clj:344-350): db = alpha * sum(dy over N,H,W) + beta * db."""
+    ddy, ddb = desc(desc_dy), desc(desc_db)
+    a, b = _scalar(alpha, ddy.dtype_code), _scalar(beta, ddb.dtype_code)
+    check(lib.ddConvolutionBackwardBias(handle.ptr, ctypes.byref(a), ddy.ptr, _ptr(buf_dy), ctypes.byref(b),
+                                        ddb.ptr, _ptr(buf_db)), handle.ptr, "ddConvolutionBackwardBias")
+    return handle
+
+
 def data_type_width(dt):
     """``data-type-width`` (cudnn/constants.clj:126-148)."""
     return DATA_TYPE_WIDTH[enc_keyword(DATA_TYPE, dt, "data type") if not isinstance(dt, int) else dt]

@@ -511,4 +511,23 @@ ddStatus_t ddReduceTensor(ddHandle_t h, ddReduceTensorDescriptor_t red, void *in
                         dd_read_scalar(beta, yd->dtype), yd, y, false, nullptr);
 }
 
+// db = alpha * sum of dy over every dim where db's extent is 1 (N, H, W for a [1,C,1,1] bias)
+// + beta * db: the (N,H,W) sum of ddReduceTensor under the name the convolution layers call.
+ddStatus_t ddConvolutionBackwardBias(ddHandle_t h, const void *alpha, ddTensorDescriptor_t dyd,
+                                     const void *dy, const void *beta, ddTensorDescriptor_t dbd, void *db) {
+  DD_CHECK_HANDLE(h);
+  DD_CHECK(dd_check_desc(h, dyd, "ddConvolutionBackwardBias dy"));
+  DD_CHECK(dd_check_desc(h, dbd, "ddConvolutionBackwardBias db"));
+  if (!dy || !db || !alpha || !beta) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddConvolutionBackwardBias: null pointer");
+  DD_CHECK(check_reduce_shapes(h, dyd, dbd));
+  if (!dd_type_is_float(dyd->dtype) || !dd_type_is_float(dbd->dtype))
+    DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddConvolutionBackwardBias: data types must be floating point");
+  ddReduceTensorStruct red;
+  red.op = DD_REDUCE_TENSOR_ADD;
+  red.comp = dyd->dtype == DD_DATA_DOUBLE ? DD_DATA_DOUBLE : DD_DATA_FLOAT;
+  red.nan = DD_PROPAGATE_NAN;
+  return dd_reduce_impl(h, &red, nullptr, 0, dd_read_scalar(alpha, dyd->dtype), dyd, dy,
+                        dd_read_scalar(beta, dbd->dtype), dbd, db, false, nullptr);
+}
+
 }  // extern "C"

@@ -302,6 +302,14 @@ DD_API ddStatus_t ddReduceTensor(ddHandle_t handle, ddReduceTensorDescriptor_t r
 
 /* ---------------------------------------------------------------- no-allocation reduce ------- */
 
+/* db = alpha * (sum of dy over the dims where db's extent is 1) + beta * db: the bias gradient of
+ * the convolution and fully connected layers, here the (N,H,W) sum of ddReduceTensor under its
+ * cuDNN name.  Replaces convolution-bwd-bias*, cudnn/impl.clj:470-475 (core.clj:344-350, called
+ * from cudnn/directed.clj:591). */
+DD_API ddStatus_t ddConvolutionBackwardBias(ddHandle_t handle, const void *alpha,
+                                            ddTensorDescriptor_t dyDesc, const void *dy,
+                                            const void *beta, ddTensorDescriptor_t dbDesc, void *db);
+
 /* No counterpart in the reference.  ddReduceTensor for callers that cannot allocate device memory:
  * code running where cudaMalloc is off limits (inside a real-time or latency-critical loop, under a
  * memory pool that owns the whole device, in a plugin whose host forbids allocations after start-up).

@@ -170,3 +170,28 @@ def test_nan_propagation(fact, dev):
     assert np.isnan(dev.get(ty, np.float32)[0])
     core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor("max", "float", False), 1.0, d_x, tx, 0.0, d_y, ty)
     assert dev.get(ty, np.float32)[0] == 6.0
+
+
+def test_convolution_bwd_bias(fact, dev, oracle):
+    """The bias gradient (cudnn/core.clj:344-350) is the (N,H,W) sum: db = alpha * sum(dy) + beta * db."""
+    shape, bshape = [16, 48, 9, 7], [1, 48, 1, 1]
+    dy = oracle.gen_normal(shape, 1.0, 11)
+    db0 = np.linspace(-2, 2, 48, dtype=np.float32)
+    for alpha, beta in ((1.0, 0.0), (0.5, 2.0)):
+        want = db0.copy().reshape(bshape)
+        oracle.reduce("add", dy, want, alpha=alpha, beta=beta)
+        tdy, tdb = dev.put(dy), dev.put(db0)
+        core.convolution_bwd_bias(fact.handle, alpha, core.tensor_descriptor(shape, "float", "nchw"), tdy, beta,
+                                  core.tensor_descriptor(bshape, "float", "nchw"), tdb)
+        got = dev.get(tdb, np.float32).reshape(bshape)
+        scale = np.abs(dy.astype(np.float64)).sum(axis=(0, 2, 3), keepdims=True)
+        assert (np.abs(got - want) <= np.maximum(1e-5 * np.abs(want), 12 * 6e-8 * abs(alpha) * scale)).all()
+    # nhwc gradient, same result layout
+    dyn = np.ascontiguousarray(dy.transpose(0, 2, 3, 1))
+    want = np.zeros(bshape, np.float32)
+    oracle.reduce("add", dy, want)
+    tdy, tdb = dev.put(dyn), dev.put(np.zeros(48, np.float32))
+    core.convolution_bwd_bias(fact.handle, 1.0, core.tensor_descriptor(shape, "float", "nhwc"), tdy, 0.0,
+                              core.tensor_descriptor(bshape, "float", "nchw"), tdb)
+    got = dev.get(tdb, np.float32).reshape(bshape)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-4)
