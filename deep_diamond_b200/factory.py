@@ -454,6 +454,38 @@ class B200Shuffler:
 
 # ====================== Factory =================================================
 
+class CapturedCalls:
+    """A CUDA graph of library calls on a factory's tensors (see ``B200Factory.capture``).  The capture
+    runs on a side stream the factory's handle is switched to for its duration; replays are enqueued
+    on the factory's own stream, in order with everything else on it."""
+
+    def __init__(self, fact, fn, warmup=1):
+        self.fact = fact
+        side = torch.cuda.Stream(device=fact.device)
+        side.wait_stream(fact.stream)
+        fact.handle.set_stream(side)
+        try:
+            with torch.cuda.stream(side):
+                for _ in range(max(0, int(warmup))):
+                    fn()
+                side.synchronize()
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, stream=side):
+                    fn()
+        finally:
+            fact.handle.set_stream(fact.stream)
+        fact.stream.wait_stream(side)
+
+    def __call__(self):
+        with torch.cuda.stream(self.fact.stream):
+            self.graph.replay()
+        return self
+
+    def release(self):
+        self.graph = None
+        return True
+
+
 class B200Factory:
     """``CUDnnFactory`` (cudnn/factory.clj:324-431): creates descriptors, tensors, transformers,
     batchers, shufflers and layer blueprints, and carries the tensor engine (:161-322)."""
@@ -492,6 +524,14 @@ class B200Factory:
 
     def synchronize(self):
         self.stream.synchronize()
+
+    def capture(self, fn, warmup=1):
+        """Records the library calls `fn` makes (layer forwards / backwards, transformers, reductions
+        on fixed tensors) into a CUDA graph and returns a ``CapturedCalls`` whose call replays them
+        with one launch.  A Python + ctypes call costs 10-20 us of host time, more than the smaller
+        kernels run; a replayed graph keeps a chain of them launch-bound no longer.  `fn` must only
+        enqueue work on this factory (no host reads, no allocation of new tensors)."""
+        return CapturedCalls(self, fn, warmup)
 
     # TensorFactory (base/internal/protocols.clj:36-52)
     def create_tensor_desc(self, shape, dtype=None, fmt=None):
@@ -542,14 +582,44 @@ class B200Factory:
         from . import dnn
         return dnn.B200SumBlueprint(self, [self.create_tensor_desc(d).view() for d in src_descs])
 
+    def activ_op_blueprint(self, src_desc, activ, alpha, beta):
+        """The operation-level blueprint is the layer-level one here: an activation is one kernel."""
+        return self.activ_blueprint(src_desc, activ, alpha, beta)
+
+    def concat_blueprint(self, src_descs, conc_dim, dst_type=None):
+        from . import dnn
+        return dnn.B200ConcatBlueprint(self, src_descs, conc_dim, dst_type)
+
+    def branch_blueprint(self, src_desc, split_dim, dst_descs):
+        from . import dnn
+        return dnn.B200BranchBlueprint(self, src_desc, split_dim, dst_descs)
+
+    def split_blueprint(self, src_desc, n):
+        from . import dnn
+        return dnn.B200SplitBlueprint(self, src_desc, n)
+
     def create_workspace(self, byte_size):
         return torch.empty(max(1, int(byte_size)), dtype=torch.uint8, device=self.device)
+
+    # CostFactory (base/internal/protocols.clj:125-129)
+    def quadratic_cost(self, last_layer, train_tz):
+        from . import dnn
+        return dnn.B200Cost(last_layer, train_tz, "quadratic")
+
+    def mean_absolute_cost(self, last_layer, train_tz):
+        from . import dnn
+        return dnn.B200Cost(last_layer, train_tz, "mean-absolute")
+
+    def crossentropy_cost(self, last_layer, train_tz):
+        from . import dnn
+        return dnn.B200CustomCost(last_layer, train_tz, "crossentropy")
 
     def inner_product_blueprint(self, *_):
         raise DiamondError("The B200 engine covers the tensor hot path only; use another factory "
                            "for contractions.", {"type": "not-supported"})
 
     fc_blueprint = convolution_blueprint = pooling_blueprint = batch_norm_blueprint = inner_product_blueprint
+    gaussian_dropout_blueprint = rnn_op_blueprint = rnn_blueprint = abbreviate_blueprint = inner_product_blueprint
 
     # ------------------------------------------------------------------ host <-> device -------
     def upload(self, host_array, tz):

@@ -567,3 +567,58 @@ def test_zero_sized_tensors(fact):
     assert transfer([1, 2, 3], z) is z
     assert transfer(z, w) is w
     assert entry_(z, 1.0) is z
+
+
+def test_factory_protocol_surface(fact):
+    """The factory answers every DnnFactory / CostFactory method of base/internal/protocols.clj:68-129:
+    the hot-path ones build blueprints, the contraction ones refuse like the cuDNN factory's
+    missing pieces."""
+    src = tensor(fact, [2, 4, 1, 1], "float", "nchw")
+    f = fact.diamond_factory()
+    assert f.activ_op_blueprint(src, "relu", 0.0, 0.0) is not None
+    assert f.split_blueprint(src, 2)(src)() is not None
+    parts = [desc([2, 1, 1, 1], "float", "nchw"), desc([2, 3, 1, 1], "float", "nchw")]
+    transfer(range(8), src)
+    outs = f.branch_blueprint(src, 1, parts)(src)()
+    assert [seq(t) for t in outs] == [[0.0, 4.0], [1.0, 2.0, 3.0, 5.0, 6.0, 7.0]]
+    cat = f.concat_blueprint(parts, 1)(outs)
+    assert seq(cat()) == [float(i) for i in range(8)]
+    train = tensor(fact, [2, 4, 1, 1], "float", "nchw")
+    for make in (f.quadratic_cost, f.mean_absolute_cost, f.crossentropy_cost):
+        assert callable(make(src, train))
+    for name in ("inner_product_blueprint", "fc_blueprint", "convolution_blueprint", "pooling_blueprint",
+                 "batch_norm_blueprint", "gaussian_dropout_blueprint", "rnn_op_blueprint", "rnn_blueprint",
+                 "abbreviate_blueprint"):
+        with pytest.raises(DiamondError):
+            getattr(f, name)(src)
+
+
+def test_captured_layer_chain_replays(fact):
+    """A chain of layers recorded once with ``capture`` and replayed as one graph launch gives the
+    same bits as the calls made one by one, also after the inputs change."""
+    rng = np.random.default_rng(5)
+    shape = [4, 8, 6, 6]
+    src = tensor(fact, shape, "float", "nchw")
+    dsrc = tensor(fact, shape, "float", "nchw")
+    nhwc = tensor(fact, shape, "float", "nhwc")
+    layer = dnn.activation(fact, src, "tanh")(src, dsrc)
+    tr = transformer(dsrc, nhwc)
+
+    def step():                     # the gradient fed back is the output itself (same buffer for tanh)
+        layer.forward()
+        layer.backward()
+        tr()
+
+    calls = fact.capture(step)
+    for seed in (1, 2):
+        x = rng.standard_normal(int(np.prod(shape))).astype(np.float32)
+        transfer(x, src)
+        step()
+        want = seq(nhwc)
+        transfer(x, src)
+        transfer(itertools.repeat(0.0), nhwc)
+        n0 = fact.handle.launch_count()
+        calls()
+        assert fact.handle.launch_count() == n0          # no library call on the host: one graph launch
+        assert seq(nhwc) == want
+    calls.release()
