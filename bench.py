@@ -373,6 +373,12 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_on
                 sharded.peer_configure(use_peer=True)
                 measure("reduce " + label, "C4 shard [%d,1024,32,32] + 4 KB peer-exchange kernel over NVLink" % shp[0],
                         nb, n, fn, 10, 20)
+                if op == "add":
+                    sharded.peer_configure(use_peer=True, fused=True)
+                    measure("reduce " + label + " (exchange fused into the reduce kernel)",
+                            "C4 shard [%d,1024,32,32] + 4 KB pushed over NVLink from inside the reduce kernel" % shp[0],
+                            nb, n, fn, 10, 20)
+                    sharded.peer_configure(use_peer=True)
                 sharded.peer_status()
             if op == "add" or not sharded.peer_attached:
                 sharded.peer_configure(use_peer=False)

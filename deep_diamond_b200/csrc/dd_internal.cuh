@@ -376,6 +376,10 @@ ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, 
                                  const ddTensorStruct *yd, void *y);
 // The same finish, fed by the cross-GPU exchange of dd_reduce_kernels.cuh instead of a local buffer.
 struct ddPeerParams;
+ddStatus_t dd_reduce_fused_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,
+                                         double count, double alpha, const ddTensorStruct *xd, const void *x,
+                                         double beta, const ddTensorStruct *yd, void *y, void *partialOut,
+                                         bool *fused);
 ddStatus_t dd_reduce_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,
                                    double count, double alpha, double beta, const ddTensorStruct *xd,
                                    const ddTensorStruct *yd, void *y);

@@ -215,6 +215,9 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
   pl.p.alpha = alpha;
   pl.p.beta = beta;
   pl.p.partialOnly = partialOnly ? 1 : 0;
+  for (int i = 0; i < DD_PEER_MAX; i++) pl.p.peerBase[i] = nullptr;
+  pl.p.peerWorld = pl.p.peerRank = 0;
+  pl.p.peerWaitNs = 0;
   pl.g.y = y;
   pl.g.partOut = partialOut;
   pl.g.alpha = alpha;
@@ -243,6 +246,44 @@ ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, 
     default: break;
   }
   DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
+}
+
+// Fused form: ONE kernel reduces the local shard, pushes each accumulator to the peers as soon as it
+// is final and lets its last CTA collect and finish.  *fused = false (nothing launched) when the plan
+// does not allow it: many outputs, or splits that a second kernel would have to combine.
+#define DD_PEER_FUSED_MAX_OUT 4096
+ddStatus_t dd_reduce_fused_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,
+                                         double count, double alpha, const ddTensorStruct *xd, const void *x,
+                                         double beta, const ddTensorStruct *yd, void *y, void *partialOut,
+                                         bool *fused) {
+  *fused = false;
+  ddRedPlan pl;
+  ddStatus_t st = dd_reduce_plan(h, red, xd, x, yd, &pl);
+  if (st != DD_STATUS_SUCCESS) return st;
+  if (pl.kind == DD_RED_GENERIC || pl.nout > DD_PEER_FUSED_MAX_OUT) return DD_STATUS_SUCCESS;
+  unsigned *counters = nullptr;
+  void *ws = nullptr;
+  if (pl.wsBytes > 0) {
+    const int64_t nctr = pl.kind == DD_RED_ROW ? pl.nout : pl.p.K1 * pl.p.tilesK2;
+    if (!(h->counterSlots > 0 && nctr < h->counterSlots)) return DD_STATUS_SUCCESS;
+    counters = (unsigned *)h->scratch;
+    ws = (char *)h->scratch + h->counterSlots * sizeof(unsigned);
+    if (h->scratchBytes - h->counterSlots * sizeof(unsigned) < pl.wsBytes) return DD_STATUS_SUCCESS;
+  }
+  pl.p.y = y;
+  pl.p.part = ws;
+  pl.p.partOut = partialOut;
+  pl.p.counters = counters;
+  pl.p.alpha = alpha;
+  pl.p.beta = beta;
+  pl.p.count = count;
+  pl.p.partialOnly = 2;
+  for (int i = 0; i < DD_PEER_MAX; i++) pl.p.peerBase[i] = peer->base[i];
+  pl.p.peerWorld = peer->world;
+  pl.p.peerRank = peer->rank;
+  pl.p.peerWaitNs = peer->waitNs;
+  *fused = true;
+  return launch_by_type(h, xd->dtype, pl);
 }
 
 ddStatus_t dd_reduce_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,

@@ -71,6 +71,49 @@ struct dd_red {
   }
 };
 
+// ---- cross-GPU exchange: constants and cell helpers (the protocol is described further down) ----
+#define DD_PEER_MAX 8
+#define DD_PEER_GRID_MAX 128
+#define DD_PEER_SLOT_BYTES (2u << 20)
+#define DD_PEER_SLOTS_OFF 8192u
+#define DD_PEER_BYTES (DD_PEER_SLOTS_OFF + 2u * DD_PEER_MAX * DD_PEER_SLOT_BYTES)
+
+struct ddPeerParams {
+  unsigned char *base[DD_PEER_MAX];  // every rank's exchange buffer as mapped here; base[rank] is the own one
+  const void *partial;               // this rank's accumulators
+  int world, rank;
+  unsigned long long waitNs;         // wall-clock limit of one wait
+};
+
+__device__ __forceinline__ void dd_st_cell(uint2 *p, unsigned word, unsigned tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 dd_ld_cell(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long dd_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <typename C> struct dd_words;
+template <> struct dd_words<float> {
+  static constexpr int N = 1;
+  static __device__ __forceinline__ void split(float v, unsigned *w) { w[0] = __float_as_uint(v); }
+  static __device__ __forceinline__ float join(const unsigned *w) { return __uint_as_float(w[0]); }
+};
+template <> struct dd_words<double> {
+  static constexpr int N = 2;
+  static __device__ __forceinline__ void split(double v, unsigned *w) {
+    w[0] = (unsigned)__double2loint(v);
+    w[1] = (unsigned)__double2hiint(v);
+  }
+  static __device__ __forceinline__ double join(const unsigned *w) { return __hiloint2double((int)w[1], (int)w[0]); }
+};
+
 struct ddRedParams {
   const void *x;
   void *y;
@@ -93,14 +136,16 @@ struct ddRedParams {
   int post;
   int nanProp;
   int partialOnly;   // 1: store the raw accumulator into partOut[out] and leave y alone
+                     // 2: the same, and push it to the other ranks; the last CTA of the grid then
+                     //    combines the world's accumulators and finishes into y (fused exchange)
+  unsigned char *peerBase[DD_PEER_MAX];  // partialOnly == 2: every rank's exchange buffer
+  int peerWorld, peerRank;
+  unsigned long long peerWaitNs;
 };
 
+// post-processing + alpha/beta + store of one finished output
 template <typename T, typename C>
-__device__ __forceinline__ void dd_red_finish(const ddRedParams &p, int64_t k1, int64_t k2, C acc) {
-  if (p.partialOnly) {
-    ((C *)p.partOut)[k1 * p.K2 + k2] = acc;
-    return;
-  }
+__device__ __forceinline__ void dd_red_output(const ddRedParams &p, int64_t k1, int64_t k2, C acc) {
   C v = acc;
   if (p.post == DD_POST_AVG) v = dd_div(v, (C)p.count);
   if (p.post == DD_POST_SQRT) v = dd_sqrt(v);
@@ -108,6 +153,120 @@ __device__ __forceinline__ void dd_red_finish(const ddRedParams &p, int64_t k1, 
   T *yp = (T *)p.y + k1 * p.syK1 + k2 * p.syK2;
   if (p.beta != 0.0) v = dd_add_rn(v, dd_mul_rn((C)p.beta, dd_load<C, T>(*yp)));
   *yp = dd_store<T, C>(v);
+}
+
+// partialOnly == 2: this rank's accumulator of output o goes to the other ranks as tagged cells
+template <typename C>
+__device__ __forceinline__ void dd_peer_push(const ddRedParams &p, int64_t o, C acc) {
+  constexpr int NW = dd_words<C>::N;
+  const unsigned call = __ldcg((const unsigned *)p.peerBase[p.peerRank]) + 1u;
+  const size_t off = DD_PEER_SLOTS_OFF + ((size_t)(call & 1u) * DD_PEER_MAX + p.peerRank) * DD_PEER_SLOT_BYTES;
+  unsigned w[NW];
+  dd_words<C>::split(acc, w);
+  for (int r = 0; r < p.peerWorld; r++) {
+    if (r == p.peerRank) continue;
+    uint2 *cell = (uint2 *)(p.peerBase[r] + off) + o * NW;
+#pragma unroll
+    for (int k = 0; k < NW; k++) dd_st_cell(cell + k, w[k], call);
+  }
+}
+
+template <typename T, typename C, bool PEER = false>
+__device__ __forceinline__ void dd_red_finish(const ddRedParams &p, int64_t k1, int64_t k2, C acc) {
+  if (p.partialOnly) {
+    const int64_t o = k1 * p.K2 + k2;
+    ((C *)p.partOut)[o] = acc;
+    if constexpr (PEER) dd_peer_push<C>(p, o, acc);
+    return;
+  }
+  dd_red_output<T, C>(p, k1, k2, acc);
+}
+
+// Polls this rank's own exchange buffer for the other ranks' accumulators of output o (bounded),
+// combines the world's values in rank order (own value `mineVal`) and finishes into y.  Returns
+// false when the wait ran out (status word set, output skipped).
+template <typename T, typename C, int OPC>
+__device__ __forceinline__ bool dd_peer_collect(const ddRedParams &p, unsigned char *mine, unsigned call,
+                                                int W, int rank, unsigned long long t0,
+                                                unsigned long long waitNs, int64_t o, C mineVal) {
+  constexpr int NW = dd_words<C>::N;
+  const bool nanProp = p.nanProp != 0;
+  const size_t parOff = DD_PEER_SLOTS_OFF + (size_t)(call & 1u) * DD_PEER_MAX * DD_PEER_SLOT_BYTES;
+  uint2 v[DD_PEER_MAX][NW];
+  unsigned spins = 0;
+  int late = -1;
+  for (;;) {
+    late = -1;
+#pragma unroll
+    for (int r = 0; r < DD_PEER_MAX; r++) {
+      if (r < W && r != rank) {
+        const uint2 *cell = (const uint2 *)(mine + parOff + (size_t)r * DD_PEER_SLOT_BYTES) + o * NW;
+#pragma unroll
+        for (int k = 0; k < NW; k++) v[r][k] = dd_ld_cell(cell + k);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < DD_PEER_MAX; r++) {
+      if (r < W && r != rank) {
+#pragma unroll
+        for (int k = 0; k < NW; k++)
+          if (v[r][k].y != call) late = r;
+      }
+    }
+    if (late < 0) break;
+    if (++spins > (1u << 24) || ((spins & 63u) == 0 && dd_globaltimer() - t0 > waitNs)) break;
+  }
+  if (late >= 0) {
+    atomicExch((int *)mine + 2, 1 + late);
+    return false;
+  }
+  C acc = (C)0;
+#pragma unroll
+  for (int r = 0; r < DD_PEER_MAX; r++) {
+    if (r < W) {
+      C val;
+      if (r == rank) {
+        val = mineVal;
+      } else {
+        unsigned w[NW];
+#pragma unroll
+        for (int k = 0; k < NW; k++) w[k] = v[r][k].x;
+        val = dd_words<C>::join(w);
+      }
+      acc = r == 0 ? val : dd_red<C, OPC>::comb(acc, val, nanProp);
+    }
+  }
+  const int64_t k1 = o / p.K2;
+  dd_red_output<T, C>(p, k1, o - k1 * p.K2, acc);
+  return true;
+}
+
+// partialOnly == 2, called by every thread at the end of a reduce kernel: the CTA that arrives last
+// (all local accumulators are in partOut and on their way to the peers by then) collects the other
+// ranks' values for every output and finishes; it then publishes the call number.  Only this one
+// CTA ever waits, and only on other GPUs.
+template <typename T, typename C, int OPC>
+__device__ __forceinline__ void dd_peer_tail(const ddRedParams &p) {
+  __shared__ int lastFlag;
+  unsigned char *mine = p.peerBase[p.peerRank];
+  unsigned *ctl = (unsigned *)mine;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) lastFlag = atomicAdd(ctl + 1, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!lastFlag) return;
+  __threadfence();
+  const unsigned call = __ldcg(ctl) + 1u;
+  const int64_t nout = p.K1 * p.K2;
+  const unsigned long long t0 = dd_globaltimer();
+  for (int64_t o = threadIdx.x; o < nout; o += blockDim.x)
+    dd_peer_collect<T, C, OPC>(p, mine, call, p.peerWorld, p.peerRank, t0, p.peerWaitNs, o,
+                               __ldcg((const C *)p.partOut + o));
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ctl[1] = 0;
+    __stcg(ctl, call);
+  }
 }
 
 // Tree over the G threads of a group (G = 32: one warp; G = 256: the CTA).  Result valid in lane 0
@@ -134,8 +293,10 @@ __device__ __forceinline__ C dd_group_reduce(C acc, int G, bool nanProp, C *smem
   return acc;
 }
 
-template <typename T, typename C, int OPC, bool VEC>
-__global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
+// PEER: the fused exchange (partialOnly == 2), its own instantiation so that the plain kernels keep
+// their register budget.
+template <typename T, typename C, int OPC, bool VEC, bool PEER>
+__global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedParams p) {
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;  // independent loads in flight per thread
   __shared__ C smem[8];
@@ -205,7 +366,7 @@ __global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
   acc = dd_group_reduce<C, OPC>(acc, G, nanProp, smem);
   if (live && lane == 0) {
     if (p.S == 1) {
-      dd_red_finish<T, C>(p, k1, k2, acc);
+      dd_red_finish<T, C, PEER>(p, k1, k2, acc);
     } else {
       C *part = (C *)p.part + out * p.S;
       part[s] = acc;
@@ -217,18 +378,19 @@ __global__ void __launch_bounds__(256) dd_reduce_row_kernel(ddRedParams p) {
           __threadfence();
           C a = __ldcg(part);
           for (int i = 1; i < p.S; i++) a = dd_red<C, OPC>::comb(a, __ldcg(part + i), nanProp);
-          dd_red_finish<T, C>(p, k1, k2, a);
+          dd_red_finish<T, C, PEER>(p, k1, k2, a);
           p.counters[out] = 0;
         }
       }
     }
   }
+  if constexpr (PEER) dd_peer_tail<T, C, OPC>(p);
 }
 
 // col: CTA = TX lanes along k2 (V elements each, TX a power of two <= 256) x TY = 256/TX row
 // groups striding over r1.
-template <typename T, typename C, int OPC, bool VEC>
-__global__ void __launch_bounds__(256, 8) dd_reduce_col_kernel(ddRedParams p) {
+template <typename T, typename C, int OPC, bool VEC, bool PEER>
+__global__ void __launch_bounds__(256, PEER ? 4 : 8) dd_reduce_col_kernel(ddRedParams p) {
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;
   __shared__ C smem[256 * V];
@@ -290,7 +452,7 @@ __global__ void __launch_bounds__(256, 8) dd_reduce_col_kernel(ddRedParams p) {
     for (int r = 1; r < TY; r++) a = dd_red<C, OPC>::comb(a, smem[r * (TX * V) + col], nanProp);
     const int64_t kk = tk * TX * V + col;
     if (kk < p.K2) {
-      if (p.S == 1) dd_red_finish<T, C>(p, k1, kk, a);
+      if (p.S == 1) dd_red_finish<T, C, PEER>(p, k1, kk, a);
       else ((C *)p.part)[(k1 * p.K2 + kk) * p.S + s] = a;
     }
   }
@@ -310,12 +472,13 @@ __global__ void __launch_bounds__(256, 8) dd_reduce_col_kernel(ddRedParams p) {
           const C *pp = (const C *)p.part + (k1 * p.K2 + kk) * p.S;
           C a = __ldcg(pp);
           for (int i = 1; i < p.S; i++) a = dd_red<C, OPC>::comb(a, __ldcg(pp + i), nanProp);
-          dd_red_finish<T, C>(p, k1, kk, a);
+          dd_red_finish<T, C, PEER>(p, k1, kk, a);
         }
       }
       if (threadIdx.x == 0) *ctr = 0;
     }
   }
+  if constexpr (PEER) dd_peer_tail<T, C, OPC>(p);
 }
 
 // Combines the S partials of each output in index order and finishes.  `part` may be an
@@ -360,52 +523,16 @@ __global__ void __launch_bounds__(256) dd_reduce_finish_kernel(ddRedParams p, co
 // Every wait is bounded (wall-clock limit and an iteration cap): when it runs out the thread
 // records 1 + the rank it waited for in the status word, skips its output and returns.  No thread
 // waits on another thread of the same GPU.
-#define DD_PEER_MAX 8
-#define DD_PEER_GRID_MAX 128
-#define DD_PEER_SLOT_BYTES (2u << 20)
-#define DD_PEER_SLOTS_OFF 8192u
-#define DD_PEER_BYTES (DD_PEER_SLOTS_OFF + 2u * DD_PEER_MAX * DD_PEER_SLOT_BYTES)
-
-struct ddPeerParams {
-  unsigned char *base[DD_PEER_MAX];  // every rank's exchange buffer as mapped here; base[rank] is the own one
-  const void *partial;               // this rank's accumulators
-  int world, rank;
-  unsigned long long waitNs;         // wall-clock limit of one wait
-};
-
-__device__ __forceinline__ void dd_st_cell(uint2 *p, unsigned word, unsigned tag) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 dd_ld_cell(const uint2 *p) {
-  uint2 v;
-  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned long long dd_globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-template <typename C> struct dd_words;
-template <> struct dd_words<float> {
-  static constexpr int N = 1;
-  static __device__ __forceinline__ void split(float v, unsigned *w) { w[0] = __float_as_uint(v); }
-  static __device__ __forceinline__ float join(const unsigned *w) { return __uint_as_float(w[0]); }
-};
-template <> struct dd_words<double> {
-  static constexpr int N = 2;
-  static __device__ __forceinline__ void split(double v, unsigned *w) {
-    w[0] = (unsigned)__double2loint(v);
-    w[1] = (unsigned)__double2hiint(v);
-  }
-  static __device__ __forceinline__ double join(const unsigned *w) { return __hiloint2double((int)w[1], (int)w[0]); }
-};
-
+//
+// Two forms.  FUSED (few outputs): the reduce kernel itself pushes each output's accumulator the
+// moment it is final (dd_peer_push from dd_red_finish), so the transfers overlap the rest of the
+// local pass, and the CTA that finishes last collects and finishes (dd_peer_tail): one kernel for
+// reduce + exchange.  SEPARATE (many outputs, or a plan whose splits are combined by a second
+// kernel): the local pass writes its accumulators to a buffer and dd_reduce_exchange_kernel below
+// does push + collect with all its CTAs.
 template <typename T, typename C, int OPC>
 __global__ void __launch_bounds__(256) dd_reduce_exchange_kernel(ddRedParams p, ddPeerParams q) {
   constexpr int NW = dd_words<C>::N;
-  const bool nanProp = p.nanProp != 0;
   const int64_t nout = p.K1 * p.K2;
   unsigned char *mine = q.base[q.rank];
   unsigned *ctl = (unsigned *)mine;
@@ -429,54 +556,8 @@ __global__ void __launch_bounds__(256) dd_reduce_exchange_kernel(ddRedParams p, 
   }
 
   const unsigned long long t0 = dd_globaltimer();
-  for (int64_t o = first; o < nout; o += nthreads) {
-    uint2 v[DD_PEER_MAX][NW];
-    unsigned spins = 0;
-    int late = -1;
-    for (;;) {
-      late = -1;
-#pragma unroll
-      for (int r = 0; r < DD_PEER_MAX; r++) {
-        if (r < W && r != q.rank) {
-          const uint2 *cell = (const uint2 *)(mine + parOff + (size_t)r * DD_PEER_SLOT_BYTES) + o * NW;
-#pragma unroll
-          for (int k = 0; k < NW; k++) v[r][k] = dd_ld_cell(cell + k);
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < DD_PEER_MAX; r++) {
-        if (r < W && r != q.rank) {
-#pragma unroll
-          for (int k = 0; k < NW; k++)
-            if (v[r][k].y != call) late = r;
-        }
-      }
-      if (late < 0) break;
-      if (++spins > (1u << 24) || ((spins & 63u) == 0 && dd_globaltimer() - t0 > q.waitNs)) break;
-    }
-    if (late >= 0) {
-      atomicExch((int *)ctl + 2, 1 + late);
-      continue;
-    }
-    C acc = (C)0;
-#pragma unroll
-    for (int r = 0; r < DD_PEER_MAX; r++) {
-      if (r < W) {
-        C val;
-        if (r == q.rank) {
-          val = part[o];
-        } else {
-          unsigned w[NW];
-#pragma unroll
-          for (int k = 0; k < NW; k++) w[k] = v[r][k].x;
-          val = dd_words<C>::join(w);
-        }
-        acc = r == 0 ? val : dd_red<C, OPC>::comb(acc, val, nanProp);
-      }
-    }
-    const int64_t k1 = o / p.K2;
-    dd_red_finish<T, C>(p, k1, o - k1 * p.K2, acc);
-  }
+  for (int64_t o = first; o < nout; o += nthreads)
+    dd_peer_collect<T, C, OPC>(p, mine, call, W, q.rank, t0, q.waitNs, o, part[o]);
 
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -573,13 +654,25 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
 #define DD_REDUCE_DEFINE(T, C)                                                                     \
   template <int OPC>                                                                               \
   static ddStatus_t launch_opc_##T(ddHandle_t h, const ddRedPlan &pl) {                            \
+    if (pl.p.partialOnly == 2) { /* fused exchange: row or col only, no second kernel */           \
+      if (pl.kind == DD_RED_ROW) {                                                                 \
+        if (pl.vec) dd_reduce_row_kernel<T, C, OPC, true, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);  \
+        else dd_reduce_row_kernel<T, C, OPC, false, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
+        DD_LAUNCHED(h, "reduce/row+peer-exchange");                                                \
+      } else {                                                                                     \
+        if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);  \
+        else dd_reduce_col_kernel<T, C, OPC, false, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
+        DD_LAUNCHED(h, "reduce/col+peer-exchange");                                                \
+      }                                                                                            \
+      return DD_STATUS_SUCCESS;                                                                    \
+    }                                                                                              \
     if (pl.kind == DD_RED_ROW) {                                                                   \
-      if (pl.vec) dd_reduce_row_kernel<T, C, OPC, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);     \
-      else dd_reduce_row_kernel<T, C, OPC, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);           \
+      if (pl.vec) dd_reduce_row_kernel<T, C, OPC, true, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
+      else dd_reduce_row_kernel<T, C, OPC, false, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);    \
       DD_LAUNCHED(h, "reduce/row");                                                                \
     } else if (pl.kind == DD_RED_COL) {                                                            \
-      if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);     \
-      else dd_reduce_col_kernel<T, C, OPC, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);           \
+      if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
+      else dd_reduce_col_kernel<T, C, OPC, false, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);    \
       DD_LAUNCHED(h, "reduce/col");                                                                \
     } else {                                                                                       \
       dd_reduce_generic_kernel<T, C, OPC><<<pl.grid, 256, 0, h->stream>>>(pl.g);                   \

@@ -72,6 +72,9 @@ struct ddShardedStruct {
   bool peerOpened[DD_PEER_MAX];          // mapped with cudaIpcOpenMemHandle (to be closed)
   bool attached;
   int usePeer;                           // 1: combine over the peer exchange when attached
+  int fuse;                              // 1: reduce + exchange in one kernel where the plan allows (measured
+                                         // slightly slower than the two-kernel form for a 4 KB result, so off
+                                         // by default)
   unsigned long long waitNs;
 };
 
@@ -109,6 +112,7 @@ ddStatus_t ddShardedCreate(ddShardedHandle_t *out, ddHandle_t h, int nRanks, int
   }
   s->attached = false;
   s->usePeer = 1;
+  s->fuse = 0;
   s->waitNs = 2000000000ull;  // 2 s
   if (cudaMalloc(&s->partial, DD_PARTIAL_BYTES) != cudaSuccess) {
     cudaGetLastError();
@@ -214,7 +218,10 @@ ddStatus_t ddShardedPeerAttach(ddShardedHandle_t s, const void *handles) {
 
 ddStatus_t ddShardedPeerConfigure(ddShardedHandle_t s, int usePeer, double waitSeconds) {
   if (!s) return DD_STATUS_BAD_PARAM;
-  if (usePeer >= 0) s->usePeer = usePeer ? 1 : 0;
+  if (usePeer >= 0) {
+    s->usePeer = usePeer ? 1 : 0;
+    s->fuse = usePeer == 2 ? 1 : 0;  // 2: push from inside the reduce kernel where the plan allows
+  }
   if (waitSeconds > 0) s->waitNs = (unsigned long long)(waitSeconds * 1e9);
   return DD_STATUS_SUCCESS;
 }
@@ -276,8 +283,7 @@ ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t
   const bool peer = s->attached && s->usePeer;
   if (!peer && !s->comm)
     DD_FAIL(h, DD_STATUS_NOT_INITIALIZED, "ddShardedReduceTensor: no NCCL communicator and no peer exchange attached");
-  ddStatus_t st = dd_reduce_impl(h, red, nullptr, 0, 1.0, xd, x, 0.0, yd, y, true, s->partial);
-  if (st != DD_STATUS_SUCCESS) return st;
+  ddStatus_t st;
   if (peer) {
     ddPeerParams q;
     for (int i = 0; i < DD_PEER_MAX; i++) q.base[i] = s->peerBase[i];
@@ -286,8 +292,18 @@ ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t
     q.rank = s->rank;
     q.waitNs = s->waitNs;
     // equal shards: the global count is nRanks times the local one
-    return dd_reduce_exchange_impl(h, red, &q, (double)nredLocal * s->nRanks, a, b, xd, yd, y);
+    const double count = (double)nredLocal * s->nRanks;
+    if (s->fuse) {
+      bool fused = false;
+      st = dd_reduce_fused_exchange_impl(h, red, &q, count, a, xd, x, b, yd, y, s->partial, &fused);
+      if (st != DD_STATUS_SUCCESS || fused) return st;
+    }
+    st = dd_reduce_impl(h, red, nullptr, 0, 1.0, xd, x, 0.0, yd, y, true, s->partial);
+    if (st != DD_STATUS_SUCCESS) return st;
+    return dd_reduce_exchange_impl(h, red, &q, count, a, b, xd, yd, y);
   }
+  st = dd_reduce_impl(h, red, nullptr, 0, 1.0, xd, x, 0.0, yd, y, true, s->partial);
+  if (st != DD_STATUS_SUCCESS) return st;
   ncclResult_t r = g_nccl.AllReduce(s->partial, s->partial, (size_t)nout, dbl ? DD_NCCL_FLOAT64 : DD_NCCL_FLOAT32,
                                     ncclOp, s->comm, h->stream);
   if (r != 0) DD_FAIL(h, DD_STATUS_COMM_FAILED, "ncclAllReduce: %s", g_nccl.GetErrorString(r));

@@ -89,9 +89,12 @@ class ShardedHandle:
         self.peer_attached = True
         return self
 
-    def peer_configure(self, use_peer=None, wait_seconds=None):
-        check(lib.ddShardedPeerConfigure(self.ptr, -1 if use_peer is None else int(bool(use_peer)),
-                                         0.0 if wait_seconds is None else float(wait_seconds)),
+    def peer_configure(self, use_peer=None, wait_seconds=None, fused=False):
+        """use_peer False: NCCL; True: the peer exchange as a kernel of its own after the local
+        pass (`fused=True`: pushed from inside the reduce kernel where the plan allows); None:
+        leave as is."""
+        mode = -1 if use_peer is None else (0 if not use_peer else (2 if fused else 1))
+        check(lib.ddShardedPeerConfigure(self.ptr, mode, 0.0 if wait_seconds is None else float(wait_seconds)),
               self.fact.handle.ptr, "ddShardedPeerConfigure")
         return self
 

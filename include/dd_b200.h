@@ -366,7 +366,12 @@ DD_API ddStatus_t ddShardedReduceTensor(ddShardedHandle_t sharded, ddReduceTenso
  * ddShardedPeerAttach with the nRanks * DD_PEER_HANDLE_BYTES bytes; from then on
  * ddShardedReduceTensor uses the exchange.  Up to 8 ranks.  ddShardedCreate accepts a NULL id for
  * a handle that only ever uses the peer exchange (no NCCL needed).
- * ddShardedPeerConfigure: usePeer 0/1 switches between NCCL and the exchange (-1: leave), and
+ * The exchange is a small kernel of its own after the local pass.  A fused form exists as well
+ * (few outputs, <= 4096: the reduce kernel pushes each result the moment it is final and its last
+ * CTA collects and finishes, ONE kernel for reduce + exchange); it measured about 2 us slower per
+ * call than the two-kernel form on a 4 KB result, so it is opt-in.
+ * ddShardedPeerConfigure: usePeer 0 = NCCL, 1 = the exchange kernel, 2 = the fused form where the
+ * plan allows, -1 = leave as is; and
  * waitSeconds > 0 sets the limit of the kernel's bounded waits (default 2 s).
  * ddShardedPeerStatus synchronises the handle's stream and reports whether a wait ran out
  * (*status = 1 + the rank waited for, return DD_STATUS_TIMEOUT); the kernel that gave up wrote no

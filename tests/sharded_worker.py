@@ -37,8 +37,8 @@ def main():
     shard_shape = list(mine.shape)
     xd = core.tensor_descriptor(shard_shape, "float", "nchw")
     failures = []
-    for path in ("peer", "nccl"):
-        sh.peer_configure(use_peer=(path == "peer"))
+    for path in ("fused", "peer", "nccl"):
+        sh.peer_configure(use_peer=(path != "nccl"), fused=(path == "fused"))
         for op in ("add", "avg", "norm2", "norm1", "max", "min", "amax"):
             for alpha, beta in ((1.0, 0.0), (2.0, 0.5)):
                 yshape = [1, 64, 1, 1]
@@ -49,7 +49,8 @@ def main():
                 yd = core.tensor_descriptor(yshape, "float", "nchw")
                 sh.reduce_tensor(core.reduce_tensor_descriptor(op, "float"), alpha, xd, x, beta, yd, y)
                 fact.synchronize()
-                want_kernel = "reduce/peer-exchange" if path == "peer" else "reduce/finish"
+                want_kernel = {"fused": "reduce/row+peer-exchange", "peer": "reduce/peer-exchange",
+                               "nccl": "reduce/finish"}[path]
                 if fact.handle.last_kernel() != want_kernel:
                     failures.append((path, "kernel", fact.handle.last_kernel()))
                 got = y.cpu().numpy().reshape(yshape)
@@ -67,9 +68,31 @@ def main():
         dist.all_gather(gathered, y)
         if any(not torch.equal(g, gathered[0]) for g in gathered):
             failures.append((path, "replicas differ"))
+    sh.peer_configure(use_peer=True, fused=True)
+
+    # the fused form through the col kernel (sum over N only, 4096 outputs) and with split rows
+    # (few outputs, long ranges: the per-output arrival counters feed the push)
+    for fshape, yshape, axes in (([4 * world, 16, 16, 16], [1, 16, 16, 16], (0,)),
+                                 ([2 * world, 2, 64, 64], [1, 2, 1, 1], (0, 2, 3))):
+        ffull = oracle.gen_signed_lognormal(fshape, 9)
+        flo, fhi = sharded.shard_range(fshape[0], world, rank)
+        fx = torch.from_numpy(np.ascontiguousarray(ffull[flo:fhi])).to(fact.device)
+        want = np.zeros(yshape, np.float32)
+        oracle.reduce("add", ffull, want)
+        y = torch.zeros(int(np.prod(yshape)), device=fact.device)
+        for _ in range(3):
+            sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0,
+                             core.tensor_descriptor([fhi - flo] + fshape[1:], "float", "nchw"), fx, 0.0,
+                             core.tensor_descriptor(yshape, "float", "nchw"), y)
+        fact.synchronize()
+        if not fact.handle.last_kernel().endswith("+peer-exchange"):
+            failures.append(("fused kernel expected", fshape, fact.handle.last_kernel()))
+        if not within(y.cpu().numpy().reshape(yshape), want, ffull, 1.0, axes):
+            failures.append(("fused", fshape))
+
     sh.peer_configure(use_peer=True)
 
-    # many outputs (several CTAs of the exchange kernel, each with its own flags): sum over N only
+    # many outputs (several CTAs of the exchange kernel): sum over N only
     yshape = [1, 64, 16, 16]
     want = np.zeros(yshape, np.float32)
     oracle.reduce("add", full, want)

@@ -40,18 +40,20 @@ def test_peer_exchange_wait_runs_out(fact, dev):
     try:
         own = sh.peer_export()
         sh.peer_attach([own, own])                            # "rank 1" is this rank's own buffer: nobody signals for it
-        sh.peer_configure(wait_seconds=0.05)
         shape = [4, 64, 16, 16]
         x = dev.put(np.ones(shape, np.float32))
         y0 = np.full(64, -7.0, np.float32)
         y = dev.put(y0)
-        sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0,
-                         core.tensor_descriptor(shape, "float", "nchw"), x, 0.0,
-                         core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y, spans=True)
-        with pytest.raises(DiamondError) as e:
-            sh.peer_status()
-        assert e.value.data["type"] == "timeout" and "rank 1" in str(e.value)
-        assert np.array_equal(dev.get(y, np.float32), y0)     # the kernel that gave up wrote nothing
+        for fused, kernel in ((True, "reduce/row+peer-exchange"), (False, "reduce/peer-exchange")):
+            sh.peer_configure(use_peer=True, wait_seconds=0.05, fused=fused)
+            sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0,
+                             core.tensor_descriptor(shape, "float", "nchw"), x, 0.0,
+                             core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y, spans=True)
+            assert fact.handle.last_kernel() == kernel
+            with pytest.raises(DiamondError) as e:
+                sh.peer_status()
+            assert e.value.data["type"] == "timeout" and "rank 1" in str(e.value)
+            assert np.array_equal(dev.get(y, np.float32), y0)     # the kernel that gave up wrote nothing
         # the context is still usable
         z = dev.put(np.zeros(64, np.float32))
         core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor("add", "float"), 1.0,
