@@ -412,6 +412,114 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_on
     return rows
 
 
+class _View:
+    """A (descriptor, device address) pair for the entry points that take tensor-like arguments."""
+
+    def __init__(self, desc, buf, byte_offset=0):
+        self.desc, self.buf, self.off = desc, buf, int(byte_offset)
+
+    def device_ptr(self):
+        return self.buf.data_ptr() + self.off
+
+
+def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
+    """The callers either side of the path, each timed alone like the per-op table: shuffler gather,
+    branch / concatenate copies, n-ary sum, cost, equality, same-layout convert, fill and scale.
+    Every tensor is [256,256,28,28]-sized (205 MB in f32) or larger than L2 in total, so launches
+    stream from HBM."""
+    rows = []
+    h, dev, stream = fact.handle, fact.device, fact.stream
+
+    def dbuf(nbytes):
+        return torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
+
+    def measure(name, cfg, nbytes, elems, fn, per_graph=5, replays=10):
+        if profile_only:
+            for _ in range(3):
+                fn()
+            stream.synchronize()
+            rows.append({"op": name, "config": cfg, "kernel": h.last_kernel()})
+            return
+        row = op_row(name, cfg, nbytes, graph_ms(torch, fact, fn, per_graph, replays), peak, elems)
+        row["kernel"] = h.last_kernel()
+        rows.append(row)
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    shp = [256, 256, 28, 28]
+    n = int(np.prod(shp))
+    x = torch.randn(n, dtype=torch.float32, device=dev, generator=g)
+    y = torch.empty(n, dtype=torch.float32, device=dev)
+    z = torch.randn(n, dtype=torch.float32, device=dev, generator=g)
+    d4 = core.tensor_descriptor(shp, "float", "nchw")
+
+    # same-layout convert f32 -> bf16 (flat stream)
+    yb = dbuf(n * 2)
+    measure("convert f32 -> bf16, same layout", "[256,256,28,28] nchw", n * 6, n,
+            lambda: core.transform_tensor(h, 1.0, d4, x, 0.0, core.tensor_descriptor(shp, "bf16", "nchw"), yb))
+
+    # shuffler: 8192 of 16384 rows of [16384,64,8,8] f32 picked at random into [8192,64,8,8]
+    rows_src, rows_dst, row_elems = 16384, 8192, 64 * 8 * 8
+    src = torch.randn(rows_src * row_elems, dtype=torch.float32, device=dev, generator=g)
+    dst = torch.empty(rows_dst * row_elems, dtype=torch.float32, device=dev)
+    perm = np.random.default_rng(8).permutation(rows_src)[:rows_dst]
+    sub = core.tensor_descriptor([1, 64, 8, 8], "float", "nchw")
+    so, do = [int(i) * row_elems for i in perm], [i * row_elems for i in range(rows_dst)]
+
+    def shuffle():
+        for k in range(0, rows_dst, 4096):      # the entry point takes up to 4096 items per call
+            core.gather_transform(h, so[k:k + 4096], do[k:k + 4096], sub, src, sub, dst)
+    measure("shuffler gather", "8192 random rows of [16384,64,8,8] f32 (16 KB each), 2 calls", rows_dst * row_elems * 8,
+            rows_dst * row_elems, shuffle, 2, 10)
+    del src, dst
+
+    # branch: [256,256,28,28] cut 64/128/64 along channels, one launch; concatenate is the inverse
+    parts, pairs, c0 = [64, 128, 64], [], 0
+    outs = []
+    for c in parts:
+        pshape = [256, c, 28, 28]
+        pd_src = core.tensor_descriptor(pshape, "float", [256 * 784, 784, 28, 1])   # a channel window of x
+        pd_dst = core.tensor_descriptor(pshape, "float", "nchw")
+        o = torch.empty(int(np.prod(pshape)), dtype=torch.float32, device=dev)
+        outs.append((pd_dst, o))
+        pairs.append((_View(pd_src, x, c0 * 784 * 4), _View(pd_dst, o)))
+        c0 += c
+    measure("branch (3 sub-tensor copies, one launch)", "[256,256,28,28] f32 -> 64/128/64 channels", n * 8, n,
+            lambda: core.multi_transform(h, pairs))
+    back = [(b, a) for a, b in pairs]
+    measure("concatenate (3 sub-tensor copies, one launch)", "64/128/64 channels -> [256,256,28,28] f32", n * 8, n,
+            lambda: core.multi_transform(h, back))
+    del outs, pairs, back
+
+    # n-ary sum: y = x + 0.5*z + 0.25*y0 in one pass (3 sources)
+    w = torch.randn(n, dtype=torch.float32, device=dev, generator=g)
+    measure("sum of 3 tensors, one pass", "[256,256,28,28] f32, scales 1, 0.5, 0.25", n * 16, n,
+            lambda: core.sum_tensors(h, [1.0, 0.5, 0.25], [d4, d4, d4], [x, z, w], d4, y))
+    del w
+
+    # cost: d = a - y with the quadratic cost / the cross-entropy in the same pass
+    cost = torch.zeros(1, dtype=torch.float64, device=dev)
+    a01 = torch.rand(n, dtype=torch.float32, device=dev, generator=g) * 0.98 + 0.01
+    t01 = (torch.rand(n, dtype=torch.float32, device=dev, generator=g) < 0.1).to(torch.float32)
+    d2 = core.tensor_descriptor([256, 256 * 784], "float", "nc")
+    measure("cost: a - y and quadratic cost, one pass", "[256, 200704] f32", n * 12, n,
+            lambda: core.cost_diff(h, "quadratic", d2, a01, t01, y, cost))
+    measure("cost: cross-entropy (no gradient written)", "[256, 200704] f32", n * 8, n,
+            lambda: core.cost_diff(h, "crossentropy", d2, a01, t01, None, cost))
+    del a01, t01
+
+    # equality of two tensors
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    y.copy_(x)
+    measure("tensor equality", "[256,256,28,28] f32 vs an equal copy", n * 8, n,
+            lambda: core.tensor_equals(h, d4, x, d4, y, flag))
+
+    # fill and scale
+    measure("set-tensor (fill)", "[256,256,28,28] f32", n * 4, n, lambda: core.set_tensor(h, d4, y, 0.5))
+    measure("scale-tensor", "[256,256,28,28] f32", n * 8, n, lambda: core.scale_tensor(h, 1.0009765625, d4, y))
+    return rows
+
+
 def run_profile_ops(args):
     """`--profile-ops`: launches every op of the per-op table three times on cuda:0 and prints the
     kernel family each call chose.  A short fixed launch list for ncu; the large reorder runs on a
@@ -422,7 +530,10 @@ def run_profile_ops(args):
     torch.cuda.set_device(0)
     oracle.build()
     fact = b200_factory(0)
-    rows = ops_table(torch, fact, core, oracle, peaks()[0], None, 1, profile_only=True, c5_batch=256)
+    if args.profile_next:
+        rows = next_rows_table(torch, fact, core, oracle, peaks()[0], profile_only=True)
+    else:
+        rows = ops_table(torch, fact, core, oracle, peaks()[0], None, 1, profile_only=True, c5_batch=256)
     print(json.dumps({"profile_ops": rows}))
     fact.release()
 
@@ -592,7 +703,7 @@ def run_ours(args):
            "api": "tensor.transfer (pinned numpy -> device), dnn.activation layers forward/backward, tensor.transfer back"}
     del layers, tz_x, tz_dx, pin_x, pin_dy, pin_y, pin_dx
 
-    ops = None
+    ops = ops_next = None
     if not args.no_ops:
         sh = shd.create_from_torch_distributed(fact) if world > 1 else None
         del x, dy, y, dx
@@ -600,6 +711,8 @@ def run_ours(args):
         ops = ops_table(torch, fact, core, oracle, peak, sh, world)
         if sh is not None:
             sh.release()
+        torch.cuda.empty_cache()
+        ops_next = next_rows_table(torch, fact, core, oracle, peak) if world == 1 else None
 
     cpu = None
     if rank == 0 and world == 1:
@@ -636,6 +749,7 @@ def run_ours(args):
             "clocks": clocks,
             "parity_spot_check": parity,
             "ops": ops,
+            "ops_next": ops_next,
         }
         print(json.dumps(line))
     fact.release()
@@ -651,10 +765,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table of the other configurations")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for profiler captures)")
+    ap.add_argument("--profile-next", action="store_true",
+                    help="like --profile-ops for the table of the path's callers (shuffler, branch, sum, cost ...)")
     ap.add_argument("--profile-ops", action="store_true",
                     help="launch each op of the per-op table three times and exit (for profiler captures)")
     args = ap.parse_args()
-    if args.profile_ops:
+    if args.profile_ops or args.profile_next:
         run_profile_ops(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -178,7 +178,7 @@ __device__ __forceinline__ T dd_cost_term(T a, T y, T t, T acc) {
 }
 
 template <typename T, int KIND>
-__global__ void __launch_bounds__(256) dd_cost_kernel(ddCostParams p) {
+__global__ void __launch_bounds__(256, KIND == 2 ? 4 : 6) dd_cost_kernel(ddCostParams p) {
   constexpr int V = 16 / sizeof(T);
   const T *a = (const T *)p.a;
   const T *y = (const T *)p.y;
@@ -225,10 +225,20 @@ __global__ void __launch_bounds__(256) dd_cost_kernel(ddCostParams p) {
     lastFlag = atomicAdd(p.counter, 1u) == gridDim.x - 1;
   }
   __syncthreads();
-  if (lastFlag && threadIdx.x == 0) {
-    __threadfence();
+  if (!lastFlag) return;
+  // the last CTA folds the per-CTA partials: every thread takes a strided share, then the same
+  // fixed tree as above (the order depends only on the grid size, so results repeat run to run)
+  __threadfence();
+  double mine = 0;
+  for (unsigned b = threadIdx.x; b < gridDim.x; b += blockDim.x) mine += __ldcg(p.part + b);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_down_sync(0xffffffffu, mine, o);
+  __syncthreads();  // smem is reused
+  if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
     double tot = 0;
-    for (unsigned b = 0; b < gridDim.x; b++) tot += __ldcg(p.part + b);
+    for (int w = 0; w < 8; w++) tot += smem[w];
     tot = KIND == 0 ? tot / (2.0 * (double)p.n) : tot / (double)p.divisor;
     *(T *)p.cost = (T)tot;
     *p.counter = 0;
@@ -262,7 +272,8 @@ extern "C" ddStatus_t ddCostDiff(ddHandle_t h, int kind, ddTensorDescriptor_t de
   p.divisor = kind == 2 ? desc->dims[0] : c.total;
   p.vec = ((((uintptr_t)a) | ((uintptr_t)y) | ((uintptr_t)d)) & 15) == 0;
   const int V = 16 / dd_type_size(desc->dtype);
-  unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 8);
+  // one resident wave: 6 CTAs per SM for the two subtract-and-accumulate kinds, 4 for the cross-entropy
+  unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, kind == 2 ? 4 : 6);
   const bool f = desc->dtype == DD_DATA_FLOAT;
   if (kind == 0) {
     if (f) dd_cost_kernel<float, 0><<<grid, 256, 0, h->stream>>>(p);

@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(256) dd_strided_kernel(ddStridedXformParams p)
 
 // Gather form: `count` items, item k starts at element offsets so[k] / do_[k]; inside an item the
 // walk is the strided one.  Offsets travel in the kernel parameters (no device scratch).
-#define DD_GATHER_CHUNK 512
+#define DD_GATHER_CHUNK 1024
 struct ddGatherParams {
   const void *x;
   void *y;
@@ -291,6 +291,52 @@ __global__ void __launch_bounds__(256) dd_gather_kernel(const __grid_constant__ 
     int64_t off[2];
     dd_offsets<2, int64_t>(p.sp, r, off);
     y[p.do_[k] + off[1]] = dd_cvt<S, D, C, RAW>::f(x[p.so[k] + off[0]], (C)1);
+  }
+}
+
+// Dense gather: every item is one contiguous run on both sides, the destinations follow one
+// another at a fixed step (what a shuffler or batcher produces), and the source offsets are
+// multiples of one unit.  Up to 4096 items then fit the parameters of ONE launch as 32-bit indices,
+// and the copy runs as a flat stream: a multiply-shift division finds the item of each 16-byte
+// vector, consecutive threads copy consecutive vectors.
+#define DD_GATHER_SEQ_MAX 4096
+struct ddGatherSeqParams {
+  const void *x;
+  void *y;
+  uint32_t total;    // count * vpi
+  uint32_t vpi;      // accesses (16-byte vectors or single elements) per item
+  ddFastDiv fdVpi;
+  int64_t unit;      // source offset of item k: so[k] * unit elements
+  int64_t d0, dstep; // destination offset of item k: d0 + k * dstep elements
+  uint32_t so[DD_GATHER_SEQ_MAX];
+};
+
+template <typename S, typename D, typename C, bool RAW, bool VEC>
+__global__ void __launch_bounds__(256) dd_gather_dense_kernel(const __grid_constant__ ddGatherSeqParams p) {
+  static_assert(!VEC || sizeof(S) == sizeof(D), "the vector form copies equal-width elements");
+  constexpr int V = VEC ? 16 / (int)sizeof(S) : 1;
+  const S *x = (const S *)p.x;
+  D *y = (D *)p.y;
+  const uint32_t nthreads = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += nthreads) {
+    uint32_t k, r;
+    dd_divmod(i, p.fdVpi, k, r);
+    const S *src = x + (int64_t)p.so[k] * p.unit + (int64_t)r * V;
+    D *dst = y + p.d0 + (int64_t)k * p.dstep + (int64_t)r * V;
+    if (VEC) {
+      uint4 v = *(const uint4 *)src;
+      if (!RAW) {
+        uint4 o;
+        const S *sv = (const S *)&v;
+        D *dv = (D *)&o;
+#pragma unroll
+        for (int e = 0; e < V; e++) dv[e] = dd_cvt<S, D, C, RAW>::f(sv[e], (C)1);
+        v = o;
+      }
+      *(uint4 *)dst = v;
+    } else {
+      *dst = dd_cvt<S, D, C, RAW>::f(*src, (C)1);
+    }
   }
 }
 
@@ -420,9 +466,72 @@ struct ddGatherPlan {
   const int64_t *so, *do_;
 };
 
+static inline int64_t dd_gcd64(int64_t a, int64_t b) {
+  while (b) {
+    int64_t t = a % b;
+    a = b;
+    b = t;
+  }
+  return a;
+}
+
+// Tries the dense single-launch form; returns false (nothing launched) when the items are not
+// dense runs, the destinations are not evenly spaced or the indices do not fit 32 bits.
+template <typename S, typename D, typename C, bool RAW>
+static bool dd_gather_dense(ddHandle_t h, const ddGatherPlan &pl) {
+  const ddCanon &c = pl.canon;
+  if (!(c.nd == 1 && c.st[0][0] == 1 && c.st[1][0] == 1) || pl.count > DD_GATHER_SEQ_MAX) return false;
+  const int64_t per = c.total;
+  const int64_t d0 = pl.do_[0], dstep = pl.count > 1 ? pl.do_[1] - pl.do_[0] : 0;
+  int64_t unit = 0;
+  for (int k = 0; k < pl.count; k++) {
+    if (pl.do_[k] != d0 + (int64_t)k * dstep) return false;
+    unit = dd_gcd64(unit, pl.so[k]);
+  }
+  if (unit == 0) unit = 1;  // every source offset is 0
+  for (int k = 0; k < pl.count; k++)
+    if (pl.so[k] / unit > 0xffffffffLL) return false;
+  constexpr int V = sizeof(S) == sizeof(D) ? 16 / (int)sizeof(S) : 1;
+  bool vec = false;
+  if (sizeof(S) == sizeof(D)) {
+    const uintptr_t bytes = (uintptr_t)pl.x | (uintptr_t)pl.y | (uintptr_t)(unit * (int64_t)sizeof(S)) |
+                            (uintptr_t)(d0 * (int64_t)sizeof(D)) | (uintptr_t)(dstep * (int64_t)sizeof(D)) |
+                            (uintptr_t)(per * (int64_t)sizeof(S));
+    vec = (bytes & 15) == 0;
+  }
+  const int64_t vpi = vec ? per / V : per;
+  if (vpi <= 0 || vpi * pl.count >= 0x7fffffffLL) return false;
+  static thread_local ddGatherSeqParams p;  // 16 KB: kept off the stack, one per calling thread
+  p.x = pl.x;
+  p.y = pl.y;
+  p.total = (uint32_t)(vpi * pl.count);
+  p.vpi = (uint32_t)vpi;
+  p.fdVpi = dd_fastdiv((uint32_t)vpi);
+  p.unit = unit;
+  p.d0 = d0;
+  p.dstep = dstep;
+  for (int k = 0; k < pl.count; k++) p.so[k] = (uint32_t)(pl.so[k] / unit);
+  unsigned grid = dd_flat_grid(h, p.total, 256, 16);
+  if (vec) {
+    if constexpr (sizeof(S) == sizeof(D)) dd_gather_dense_kernel<S, D, C, RAW, true><<<grid, 256, 0, h->stream>>>(p);
+    h->launches++;
+    h->lastKernel = "transform/gather-dense-vec";
+  } else {
+    dd_gather_dense_kernel<S, D, C, RAW, false><<<grid, 256, 0, h->stream>>>(p);
+    h->launches++;
+    h->lastKernel = "transform/gather-dense";
+  }
+  return true;
+}
+
 template <typename S, typename D, typename C, bool RAW>
 static ddStatus_t dd_gather_typed(ddHandle_t h, const ddGatherPlan &pl) {
-  static thread_local ddGatherParams p;  // 8 KB: kept off the stack, one per calling thread
+  if (dd_gather_dense<S, D, C, RAW>(h, pl)) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) DD_FAIL(h, DD_STATUS_EXECUTION_FAILED, "transform/gather-dense: %s", cudaGetErrorString(e));
+    return DD_STATUS_SUCCESS;
+  }
+  static thread_local ddGatherParams p;  // 16 KB: kept off the stack, one per calling thread
   for (int base = 0; base < pl.count; base += DD_GATHER_CHUNK) {
     int n = pl.count - base < DD_GATHER_CHUNK ? pl.count - base : DD_GATHER_CHUNK;
     p.x = pl.x;

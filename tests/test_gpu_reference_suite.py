@@ -239,7 +239,7 @@ def test_shuffler(fact):
     assert seq(tz_y) == [0.0] * 6
     shuff([0, 2, 1])
     assert seq(tz_y) == [1.0, 5.0, 3.0, 2.0, 6.0, 4.0]
-    assert fact.handle.last_kernel() == "transform/gather"
+    assert fact.handle.last_kernel().startswith("transform/gather")
     with pytest.raises(DiamondError):
         shuff([0, 2, 1, 1])
     with pytest.raises(DiamondError):
