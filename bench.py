@@ -458,6 +458,17 @@ def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
     measure("convert f32 -> bf16, same layout", "[256,256,28,28] nchw", n * 6, n,
             lambda: core.transform_tensor(h, 1.0, d4, x, 0.0, core.tensor_descriptor(shp, "bf16", "nchw"), yb))
 
+    # a channel window of a wider tensor copied out (what view-tz + transformer do): rows kernel
+    wide = torch.randn(256 * 320 * 784, dtype=torch.float32, device=dev, generator=g)
+    wd = core.tensor_descriptor(shp, "float", [320 * 784, 784, 28, 1])
+    measure("sub-tensor copy (256 of 320 channels)", "[256,256,28,28] f32 window of [256,320,28,28]", n * 8, n,
+            lambda: core.transform_tensor(h, 1.0, wd, wide, 0.0, d4, y))
+    del wide
+    # N and C swapped (nchw -> cnhw): rows of 784 elements
+    measure("reorder nchw -> cnhw", "[256,256,28,28] f32", n * 8, n,
+            lambda: core.transform_tensor(h, 1.0, d4, x, 0.0,
+                                          core.tensor_descriptor(shp, "float", [784, 256 * 784, 28, 1]), y))
+
     # shuffler: 8192 of 16384 rows of [16384,64,8,8] f32 picked at random into [8192,64,8,8]
     rows_src, rows_dst, row_elems = 16384, 8192, 64 * 8 * 8
     src = torch.randn(rows_src * row_elems, dtype=torch.float32, device=dev, generator=g)

@@ -267,6 +267,38 @@ __global__ void __launch_bounds__(256) dd_strided_kernel(ddStridedXformParams p)
   }
 }
 
+// Rows: the innermost dim has stride 1 on both sides (sub-tensor windows, swapped outer dims,
+// padded outer strides), so the walk is the strided one over 16-byte vectors instead of elements.
+// `sp` counts the innermost dim in vectors of V elements (extent / V, stride V).
+template <typename S, typename D, typename C, bool RAW>
+__global__ void __launch_bounds__(256) dd_rows_kernel(ddStridedXformParams p) {
+  constexpr int MINW = sizeof(S) < sizeof(D) ? sizeof(S) : sizeof(D);
+  constexpr int V = 16 / MINW;
+  const S *x = (const S *)p.x;
+  D *y = (D *)p.y;
+  const C alpha = (C)p.alpha, beta = (C)p.beta;
+  const bool blend = p.beta != 0.0;
+  const uint32_t total = (uint32_t)p.sp.total, nthreads = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+    int64_t off[2];
+    dd_offsets<2, uint32_t>(p.sp, i, off);
+    dd_vec<V * sizeof(S)> in = dd_vload<V * sizeof(S)>(x + off[0]);
+    dd_vec<V * sizeof(D)> out;
+    const S *sv = (const S *)&in;
+    D *dv = (D *)&out;
+    if (blend) {
+      dd_vec<V * sizeof(D)> old = dd_vload<V * sizeof(D)>(y + off[1]);
+      const D *ov = (const D *)&old;
+#pragma unroll
+      for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::blend(sv[k], alpha, beta, ov[k]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::f(sv[k], alpha);
+    }
+    dd_vstore<V * sizeof(D)>(y + off[1], out);
+  }
+}
+
 // Gather form: `count` items, item k starts at element offsets so[k] / do_[k]; inside an item the
 // walk is the strided one.  Offsets travel in the kernel parameters (no device scratch).
 #define DD_GATHER_CHUNK 1024
@@ -449,12 +481,46 @@ static ddStatus_t dd_launch_strided(ddHandle_t h, const ddXformPlan &pl) {
   return DD_STATUS_SUCCESS;
 }
 
+// Rows form: innermost dim contiguous on both sides, every vector start 16-byte aligned.
+template <typename S, typename D, typename C, bool RAW>
+static bool dd_launch_rows(ddHandle_t h, const ddXformPlan &pl) {
+  constexpr int MINW = sizeof(S) < sizeof(D) ? sizeof(S) : sizeof(D);
+  constexpr int V = 16 / MINW;
+  const ddCanon &c = pl.canon;
+  const int last = c.nd - 1;
+  if (c.nd < 2 || c.st[0][last] != 1 || c.st[1][last] != 1 || c.dims[last] % V != 0) return false;
+  if ((((uintptr_t)pl.x | (uintptr_t)pl.y) & 15) != 0 || c.total / V >= 0x7fffffffLL) return false;
+  for (int i = 0; i < last; i++)
+    if ((c.st[0][i] * (int64_t)sizeof(S)) % 16 != 0 || (c.st[1][i] * (int64_t)sizeof(D)) % 16 != 0) return false;
+  ddCanon v = c;
+  v.dims[last] = c.dims[last] / V;
+  v.st[0][last] = V;
+  v.st[1][last] = V;
+  v.total = c.total / V;
+  ddStridedXformParams p;
+  p.x = pl.x;
+  p.y = pl.y;
+  p.sp = dd_strided_params<2>(v);
+  p.alpha = pl.alpha;
+  p.beta = pl.beta;
+  unsigned grid = dd_flat_grid(h, v.total, 256, 16);
+  dd_rows_kernel<S, D, C, RAW><<<grid, 256, 0, h->stream>>>(p);
+  h->launches++;
+  h->lastKernel = "transform/rows";
+  return true;
+}
+
 template <typename S, typename D, typename C, bool RAW>
 static ddStatus_t dd_xform_typed(ddHandle_t h, const ddXformPlan &pl) {
   const ddCanon &c = pl.canon;
   if (c.nd == 1 && c.st[0][0] == 1 && c.st[1][0] == 1) return dd_launch_flat<S, D, C, RAW>(h, pl);
   ddTileParams tp;
   if (int kind = dd_tile_plan<S, D>(pl, &tp)) return dd_launch_tile<S, D, C, RAW>(h, tp, kind);
+  if (dd_launch_rows<S, D, C, RAW>(h, pl)) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) DD_FAIL(h, DD_STATUS_EXECUTION_FAILED, "transform/rows: %s", cudaGetErrorString(e));
+    return DD_STATUS_SUCCESS;
+  }
   return dd_launch_strided<S, D, C, RAW>(h, pl);
 }
 

@@ -100,6 +100,26 @@ def test_every_type_pair_flat_tile_strided(fact, dev, oracle, sdt, ddt):
              expect="transform/strided")
 
 
+@pytest.mark.parametrize("sdt,ddt", [("float", "float"), ("float", "bf16"), ("half", "float"), ("byte", "byte"),
+                                     ("double", "float"), ("byte", "double"), ("int", "float")])
+def test_rows_kernel(fact, dev, oracle, sdt, ddt):
+    """Innermost dim contiguous on both sides but not one flat run: a channel window of a wider
+    tensor, swapped outer dims, padded outer strides -- 16-byte vectors through the strided walk."""
+    shape = [4, 6, 8, 16]
+    window = [10 * 128, 128, 16, 1]                       # channels 0..5 of a [4,10,8,16] parent
+    run_case(fact, dev, oracle, shape, window, nchw(shape), sdt, ddt, seed=41, expect="transform/rows")
+    run_case(fact, dev, oracle, shape, nchw(shape), window, sdt, ddt, seed=42, expect="transform/rows")
+    cnhw = [8 * 16, 4 * 8 * 16, 16, 1]                    # N and C swapped
+    run_case(fact, dev, oracle, shape, nchw(shape), cnhw, sdt, ddt, seed=43, expect="transform/rows")
+    padded = [6 * 8 * 32 + 64, 8 * 32, 32, 1]             # rows of 16 in a pitch of 32
+    run_case(fact, dev, oracle, shape, padded, nchw(shape), sdt, ddt, seed=44, expect="transform/rows")
+    if sdt == "float":
+        run_case(fact, dev, oracle, shape, window, cnhw, sdt, ddt, alpha=2.0, beta=0.5, seed=45, expect="transform/rows")
+    # a row length that is not a whole number of vectors stays with the element-wise walk
+    odd = [4, 5, 7, 15]
+    run_case(fact, dev, oracle, odd, [10 * 105, 105, 15, 1], nchw(odd), sdt, ddt, seed=46, expect="transform/strided")
+
+
 @pytest.mark.parametrize("shape", [[2, 2, 3, 2], [1, 64, 56, 56], [4, 64, 8, 8], [2, 256, 28, 28],
                                    [3, 48, 4, 20], [2, 96, 1, 132], [5, 16, 3, 24], [1, 512, 2, 2]])
 @pytest.mark.parametrize("pair", [("float", "float"), ("float", "bf16"), ("byte", "byte"),
