@@ -167,21 +167,47 @@ __global__ void __launch_bounds__((dd_tile_geom<S, D>::NT)) dd_tile_kernel(ddTil
   {  // load 16-byte vectors along A for VD consecutive rows of B, convert, transpose in registers
     const int ma = t % NA, mb = t / NA;
     const int64_t a = a0 + ma * VS;
+    // one 64-bit multiplication per thread: the rows follow at a fixed step, and what is left of
+    // the tensor below this thread's first row fits an int
+    const int64_t bFirst = b0 + mb * VD;
+    const int64_t left = p.LB - bFirst;
+    const int rows = a < p.LA ? (left < VD ? (left > 0 ? (int)left : 0) : VD) : 0;
+    const S *src = xb + bFirst * p.sxB + a;
     uint4 in[VD];
 #pragma unroll
     for (int j = 0; j < VD; j++) {
-      const int64_t b = b0 + mb * VD + j;
-      if (a < p.LA && b < p.LB)
-        in[j] = *(const uint4 *)(xb + b * p.sxB + a);
-      else
-        in[j] = make_uint4(0, 0, 0, 0);
+      in[j] = j < rows ? *(const uint4 *)src : make_uint4(0, 0, 0, 0);
+      src += p.sxB;
     }
     __align__(16) D reg[VS][VD];
+    if constexpr (RAW && sizeof(S) == 1 && sizeof(D) == 1) {
+      // 16 x 16 bytes as sixteen 4 x 4 byte blocks, each transposed with 8 byte permutes: word w of
+      // rows 4jj..4jj+3 becomes word jj of columns 4w..4w+3
+      uint4 *outv = (uint4 *)&reg[0][0];
 #pragma unroll
-    for (int j = 0; j < VD; j++) {
-      const S *sv = (const S *)&in[j];
+      for (int w = 0; w < 4; w++) {
+        uint32_t c[4][4];
 #pragma unroll
-      for (int i = 0; i < VS; i++) reg[i][j] = dd_cvt<S, D, C, RAW>::f(sv[i], alpha);
+        for (int jj = 0; jj < 4; jj++) {
+          const uint32_t r0 = (&in[4 * jj + 0].x)[w], r1 = (&in[4 * jj + 1].x)[w];
+          const uint32_t r2 = (&in[4 * jj + 2].x)[w], r3 = (&in[4 * jj + 3].x)[w];
+          const uint32_t t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r0, r1, 0x7362);
+          const uint32_t t2 = __byte_perm(r2, r3, 0x5140), t3 = __byte_perm(r2, r3, 0x7362);
+          c[0][jj] = __byte_perm(t0, t2, 0x5410);
+          c[1][jj] = __byte_perm(t0, t2, 0x7632);
+          c[2][jj] = __byte_perm(t1, t3, 0x5410);
+          c[3][jj] = __byte_perm(t1, t3, 0x7632);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) outv[4 * w + k] = make_uint4(c[k][0], c[k][1], c[k][2], c[k][3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < VD; j++) {
+        const S *sv = (const S *)&in[j];
+#pragma unroll
+        for (int i = 0; i < VS; i++) reg[i][j] = dd_cvt<S, D, C, RAW>::f(sv[i], alpha);
+      }
     }
     // row = index along A inside the tile; 16-byte chunk index along B swizzled by the row's
     // micro-block number so that the 8 lanes of a quarter warp hit 8 different bank groups
@@ -195,14 +221,18 @@ __global__ void __launch_bounds__((dd_tile_geom<S, D>::NT)) dd_tile_kernel(ddTil
   {  // write rows of the tile: NB consecutive lanes cover one contiguous run along B
     const int rb = t % NB, ra = t / NB;
     const int64_t b = b0 + rb * VD;
+    const int64_t leftA = p.LA - a0;
+    const int rowsA = b < p.LB ? (leftA < TA ? (int)leftA : TA) : 0;  // rows of this tile inside the tensor
+    D *dst = yb + (a0 + ra) * p.syA + b;
+    const int64_t step = (int64_t)NA * p.syA;
 #pragma unroll
     for (int k = 0; k < VS; k++) {
       const int row = ra + k * NA;
-      const int64_t a = a0 + row;
-      if (a < p.LA && b < p.LB) {
+      if (row < rowsA) {
         uint4 v = tile[row * NB + (rb ^ ((row / VS) & 7))];
-        *(uint4 *)(yb + a * p.syA + b) = v;
+        *(uint4 *)dst = v;
       }
+      dst += step;
     }
   }
 }
