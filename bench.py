@@ -464,6 +464,12 @@ def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
     measure("sub-tensor copy (256 of 320 channels)", "[256,256,28,28] f32 window of [256,320,28,28]", n * 8, n,
             lambda: core.transform_tensor(h, 1.0, wd, wide, 0.0, d4, y))
     del wide
+    # relu forward on the same kind of window, into a dense tensor
+    ad = core.activation_descriptor("relu", True, 0.0)
+    wide = torch.randn(256 * 320 * 784, dtype=torch.float32, device=dev, generator=g)
+    measure("relu forward on a sub-tensor view", "[256,256,28,28] f32 window of [256,320,28,28] -> dense", n * 8, n,
+            lambda: core.activation_forward(h, ad, 1.0, wd, wide, 0.0, d4, y))
+    del wide
     # N and C swapped (nchw -> cnhw): rows of 784 elements
     measure("reorder nchw -> cnhw", "[256,256,28,28] f32", n * 8, n,
             lambda: core.transform_tensor(h, 1.0, d4, x, 0.0,

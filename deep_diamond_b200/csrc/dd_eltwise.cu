@@ -249,6 +249,56 @@ __global__ void __launch_bounds__(256) dd_elt_strided_kernel(ddEltStridedParams 
   }
 }
 
+// Rows: views whose innermost dim is contiguous for every operand (a channel window, a batch slice
+// with its own pitch): the strided walk over 16-byte vectors.  `sp` counts the innermost dim in
+// vectors of V elements (extent / V, stride V).
+template <typename T, typename C, int MODE, bool BWD>
+__global__ void __launch_bounds__(256) dd_elt_rows_kernel(ddEltStridedParams p) {
+  constexpr int V = 16 / sizeof(T);
+  const T *x = (const T *)p.x;
+  const T *dy = (const T *)p.dy;
+  T *out = (T *)p.out;
+  const C alpha = (C)p.alpha, beta = (C)p.beta, coef = (C)p.act.coef, shift = (C)p.act.shift;
+  const bool useOld = p.beta != 0.0, nanProp = p.act.nanProp != 0;
+  const uint32_t total = (uint32_t)p.sp.total, nthreads = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+    int64_t off[3];
+    dd_offsets32<3>(p.sp, i, off);
+    uint4 xin = *(const uint4 *)(x + off[0]);
+    uint4 din = BWD ? *(const uint4 *)(dy + off[1]) : make_uint4(0, 0, 0, 0);
+    uint4 oin = make_uint4(0, 0, 0, 0);
+    if (useOld) oin = *(const uint4 *)(out + off[2]);
+    uint4 res;
+    const T *xv = (const T *)&xin, *dv = (const T *)&din, *ov = (const T *)&oin;
+    T *rv = (T *)&res;
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+      C xc = dd_load<C, T>(xv[k]);
+      C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dv[k]), coef)
+                : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+      rv[k] = dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
+    }
+    *(uint4 *)(out + off[2]) = res;
+  }
+}
+
+// True when every operand's innermost dim is contiguous and every vector start is 16-byte aligned.
+template <typename T, bool BWD>
+static bool dd_elt_rows_ok(const ddCanon &c, const void *x, const void *dy, const void *out) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int last = c.nd - 1;
+  if (c.nd < 2 || c.dims[last] % V != 0 || c.total / V >= 0x7fffffffLL) return false;
+  uintptr_t bits = (uintptr_t)x | (uintptr_t)out | (BWD ? (uintptr_t)dy : 0);
+  if (bits & 15) return false;
+  for (int o = 0; o < 3; o++) {
+    if (o == 1 && !BWD) continue;
+    if (c.st[o][last] != 1) return false;
+    for (int i = 0; i < last; i++)
+      if ((c.st[o][i] * (int64_t)sizeof(T)) % 16 != 0) return false;
+  }
+  return true;
+}
+
 template <typename T, typename C, int MODE, bool BWD>
 static ddStatus_t launch_elt(ddHandle_t h, const ddCanon &c, const void *x, const void *dy, void *out,
                              double alpha, double beta, const ddActArgs &act) {
@@ -269,6 +319,24 @@ static ddStatus_t launch_elt(ddHandle_t h, const ddCanon &c, const void *x, cons
     if (alpha == 1.0 && beta == 0.0) dd_launch_pdl(dd_elt_flat_kernel<T, C, MODE, BWD, true>, grid, 256, h->stream, p);
     else dd_launch_pdl(dd_elt_flat_kernel<T, C, MODE, BWD, false>, grid, 256, h->stream, p);
     DD_LAUNCHED(h, BWD ? "activation-bwd/flat" : "activation-fwd/flat");
+  } else if (dd_elt_rows_ok<T, BWD>(c, x, dy, out)) {
+    constexpr int V = 16 / (int)sizeof(T);
+    ddCanon v = c;
+    const int last = c.nd - 1;
+    v.dims[last] = c.dims[last] / V;
+    for (int o = 0; o < 3; o++) v.st[o][last] = V;
+    v.total = c.total / V;
+    ddEltStridedParams p;
+    p.x = x;
+    p.dy = dy;
+    p.out = out;
+    p.sp = dd_strided_params<3>(v);
+    p.alpha = alpha;
+    p.beta = beta;
+    p.act = act;
+    unsigned grid = dd_flat_grid(h, v.total, 256, 16);
+    dd_elt_rows_kernel<T, C, MODE, BWD><<<grid, 256, 0, h->stream>>>(p);
+    DD_LAUNCHED(h, BWD ? "activation-bwd/rows" : "activation-fwd/rows");
   } else {
     ddEltStridedParams p;
     p.x = x;

@@ -136,6 +136,57 @@ __global__ void __launch_bounds__(256) dd_op_strided_kernel(ddOpStridedParams p)
   }
 }
 
+// Rows: A and C contiguous along the innermost dim (any outer strides), B contiguous or constant
+// along it: the strided walk over 16-byte vectors.  `sp` counts the innermost dim in vectors of V
+// elements; bInner is B's stride along it (0 or 1).
+template <typename T, typename C>
+__global__ void __launch_bounds__(256) dd_op_rows_kernel(ddOpStridedParams p, int bInner) {
+  constexpr int V = 16 / sizeof(T);
+  const T *A = (const T *)p.A;
+  const T *B = (const T *)p.B;
+  T *Cp = (T *)p.C;
+  const C a1 = (C)p.alpha1, a2 = (C)p.alpha2, beta = (C)p.beta;
+  const bool useOld = p.beta != 0.0, readA = p.readA != 0;
+  const uint32_t total = (uint32_t)p.sp.total, nthreads = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+    int64_t off[3];
+    dd_offsets32<3>(p.sp, i, off);
+    uint4 ain = make_uint4(0, 0, 0, 0), oin = make_uint4(0, 0, 0, 0), bin = make_uint4(0, 0, 0, 0);
+    if (readA) ain = *(const uint4 *)(A + off[0]);
+    if (useOld) oin = *(const uint4 *)(Cp + off[2]);
+    C bs = (C)0;
+    if (bInner) bin = *(const uint4 *)(B + off[1]);
+    else bs = dd_times(a2, dd_load<C, T>(__ldg(B + off[1])));
+    uint4 res;
+    const T *av = (const T *)&ain, *bv = (const T *)&bin, *ov = (const T *)&oin;
+    T *rv = (T *)&res;
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+      C a = dd_times(a1, dd_load<C, T>(av[k]));
+      C b = bInner ? dd_times(a2, dd_load<C, T>(bv[k])) : bs;
+      C r = dd_binop<C>(p.op, a, b);
+      if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
+      rv[k] = dd_store<T, C>(r);
+    }
+    *(uint4 *)(Cp + off[2]) = res;
+  }
+}
+
+template <typename T>
+static bool dd_op_rows_ok(const ddCanon &c, const void *A, const void *B, const void *Cp, int readA) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int last = c.nd - 1;
+  if (c.nd < 2 || c.dims[last] % V != 0 || c.total / V >= 0x7fffffffLL) return false;
+  if (c.st[0][last] != 1 || c.st[2][last] != 1 || (c.st[1][last] != 0 && c.st[1][last] != 1)) return false;
+  uintptr_t bits = (uintptr_t)Cp | (readA ? (uintptr_t)A : 0) | (c.st[1][last] == 1 ? (uintptr_t)B : 0);
+  if (bits & 15) return false;
+  for (int i = 0; i < last; i++) {
+    if ((c.st[0][i] * (int64_t)sizeof(T)) % 16 != 0 || (c.st[2][i] * (int64_t)sizeof(T)) % 16 != 0) return false;
+    if (c.st[1][last] == 1 && (c.st[1][i] * (int64_t)sizeof(T)) % 16 != 0) return false;
+  }
+  return true;
+}
+
 template <typename T, typename C>
 static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
                                  const ddTensorStruct *ad, const void *A, double alpha2,
@@ -221,12 +272,27 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
   p.A = A;
   p.B = B;
   p.C = Cp;
-  p.sp = dd_strided_params<3>(c);
   p.op = (int)op;
   p.readA = readA;
   p.alpha1 = alpha1;
   p.alpha2 = alpha2;
   p.beta = beta;
+  if (dd_op_rows_ok<T>(c, A, B, Cp, readA)) {
+    const int last = c.nd - 1;
+    const int bInner = c.st[1][last] == 1;
+    ddCanon v = c;
+    v.dims[last] = c.dims[last] / V;
+    v.st[0][last] = V;
+    v.st[1][last] = bInner ? V : 0;
+    v.st[2][last] = V;
+    v.total = c.total / V;
+    p.sp = dd_strided_params<3>(v);
+    unsigned grid = dd_flat_grid(h, v.total, 256, 16);
+    dd_op_rows_kernel<T, C><<<grid, 256, 0, h->stream>>>(p, bInner);
+    DD_LAUNCHED(h, "optensor/rows");
+    return DD_STATUS_SUCCESS;
+  }
+  p.sp = dd_strided_params<3>(c);
   unsigned grid = dd_flat_grid(h, c.total, 256, 16);
   dd_op_strided_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
   DD_LAUNCHED(h, "optensor/strided");

@@ -183,6 +183,44 @@ def test_strided_views(fact, dev, oracle):
     assert np.array_equal(dev.get(ty, np.float32), w)
 
 
+@pytest.mark.parametrize("mode", ["relu", "tanh", "logistic", "elu", "abs"])
+def test_rows_views(fact, dev, oracle, mode):
+    """Activation forward and backward on a channel window of a wider tensor (rows contiguous,
+    16-byte aligned): the vectorised walk over views; untouched channels keep their bits."""
+    shape, parent = [4, 6, 8, 16], [4, 10, 8, 16]
+    st = [10 * 128, 128, 16, 1]
+    rng = np.random.default_rng(12)
+    xs = (rng.standard_normal(int(np.prod(parent))) * 2).astype(np.float32)
+    gs = rng.standard_normal(int(np.prod(parent))).astype(np.float32)
+    coef = COEF[mode]
+    off = 2 * 128                                           # channels 2..7
+    want = np.full(xs.size, 7.0, np.float32)
+    oracle.eltwise_fwd(mode, oracle.as_layout(xs, shape, st, offset=off), oracle.as_layout(want, shape, st, offset=off), coef=coef)
+    tx, ty = dev.put(xs), dev.put(np.full(xs.size, 7.0, np.float32))
+    d = core.tensor_descriptor(shape, "float", st)
+    ad = core.activation_descriptor(mode, True, coef)
+    core.activation_forward(fact.handle, ad, 1.0, d, tx.data_ptr() + off * 4, 0.0, d, ty.data_ptr() + off * 4)
+    assert fact.handle.last_kernel() == "activation-fwd/rows"
+    got = dev.get(ty, np.float32)
+    if mode in EXACT:
+        assert np.array_equal(got, want)
+    else:
+        assert ulp_diff_f32(got, want).max() <= 2
+    wantb = np.full(xs.size, -3.0, np.float32)
+    oracle.eltwise_bwd(mode, oracle.as_layout(xs, shape, st, offset=off), oracle.as_layout(gs, shape, st, offset=off),
+                       oracle.as_layout(wantb, shape, st, offset=off), coef=coef)
+    tg, tdx = dev.put(gs), dev.put(np.full(xs.size, -3.0, np.float32))
+    core.activation_backward(fact.handle, ad, 1.0, d, None, d, tg.data_ptr() + off * 4, d, tx.data_ptr() + off * 4,
+                             0.0, d, tdx.data_ptr() + off * 4)
+    assert fact.handle.last_kernel() == "activation-bwd/rows"
+    gotb = dev.get(tdx, np.float32)
+    if mode in EXACT:
+        assert np.array_equal(gotb, wantb)
+    else:
+        ok = (ulp_diff_f32(gotb, wantb) <= 2) | (np.abs(gotb.astype(np.float64) - wantb) <= 4 * 2.0 ** -24 * np.abs(gs))
+        assert ok.all()
+
+
 def _ordered(t):
     """float32 tensor -> int64 keys that are monotone in the float order (ulp distance = key diff)."""
     import torch

@@ -42,6 +42,30 @@ def test_op_tensor_broadcast(fact, dev, oracle, shape, bshape, op):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (op, a1, a2, beta)
 
 
+@pytest.mark.parametrize("op", ["add", "mul", "max"])
+@pytest.mark.parametrize("bshape", [[1, 6, 1, 1], [4, 6, 8, 16], [1, 1, 1, 16], [4, 1, 8, 1]])
+def test_op_tensor_rows_views(fact, dev, oracle, op, bshape):
+    """A and C are channel windows of wider tensors (rows contiguous and 16-byte aligned), B a bias,
+    a same-shape tensor, a row vector or a per-(n,h) scalar: the vectorised walk over views."""
+    shape = [4, 6, 8, 16]
+    win = [10 * 128, 128, 16, 1]                          # channels of a [4,10,8,16] parent
+    span = oracle.span(shape, win)
+    a, c0 = rnd([span], 11), rnd([span], 12)
+    bst = oracle.default_strides(bshape)
+    b = rnd(bshape, 13, 0.5, 1.5)
+    for (a1, a2, beta) in ((1.0, 1.0, 0.0), (0.75, -2.0, 0.5)):
+        want = c0.copy()
+        oracle.binary(op, oracle.as_layout(a, shape, win), oracle.as_layout(b, bshape, bst),
+                      oracle.as_layout(want, shape, win), alpha1=a1, alpha2=a2, beta=beta)
+        ta, tb, tc = dev.put(a), dev.put(b), dev.put(c0)
+        core.op_tensor(fact.handle, op, a1, core.tensor_descriptor(shape, "float", win), ta, a2,
+                       core.tensor_descriptor(bshape, "float", bst), tb, beta,
+                       core.tensor_descriptor(shape, "float", win), tc)
+        assert fact.handle.last_kernel() == "optensor/rows", bshape
+        got = dev.get(tc, np.float32)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (op, bshape, a1, a2, beta)
+
+
 def test_add_tensor_bias_form_and_kernel_choice(fact, dev, oracle):
     shape, bshape = [8, 64, 14, 14], [1, 64, 1, 1]
     x, bias = rnd(shape, 4), rnd(bshape, 5, -0.1, 0.1)
