@@ -236,3 +236,37 @@ __device__ __forceinline__ F dd_expm1_neg(F x) {
   const F sc = L::pow2(big, 0);
   return L::add(L::add(L::mul(p, sc), L::bc(-1.0f)), L::mul(pl, sc));
 }
+
+// log(x) for two positive, normal, finite inputs at once (the cross-entropy cost needs log(a) and
+// log(1 - a) of every element).  x = m * 2^e with m in [sqrt(1/2), sqrt(2)); t = m - 1 exactly;
+// log(m) = t - t^2/2 + t^3 * P(t) with P a degree-7 polynomial fitted by least squares on Chebyshev
+// nodes (0.84 ulp of log(m) in a float32 emulation over 2 million points); the result is assembled
+// small terms first as e*ln2_hi + (t + (t^3*P - t^2/2 + e*ln2_lo)), e*ln2_hi being exact.  Anything
+// else (zero, negative, denormal, infinite, NaN) takes the library's logf for that lane.
+__device__ __forceinline__ float2 dd_log_pair(float2 x) {
+  typedef dd_lane<float2> L;
+  const int ix = __float_as_int(x.x), iy = __float_as_int(x.y);
+  const int ex = (ix - 0x3f3504f3) >> 23, ey = (iy - 0x3f3504f3) >> 23;
+  const float2 m = make_float2(__int_as_float(ix - (ex << 23)), __int_as_float(iy - (ey << 23)));
+  // e as a float without an integer-to-float conversion (an eighth-rate instruction): 1.5*2^23 + e
+  // has e in its low mantissa bits, and subtracting 1.5*2^23 is exact
+  const float2 fe = L::add(make_float2(__int_as_float(0x4B400000 + ex), __int_as_float(0x4B400000 + ey)),
+                           L::bc(-12582912.0f));
+  const float2 t = L::add(m, L::bc(-1.0f));
+  float2 P = L::bc(-0.0733518898487091f);
+  P = L::fma(P, t, L::bc(0.12697939574718475f));
+  P = L::fma(P, t, L::bc(-0.13257159292697906f));
+  P = L::fma(P, t, L::bc(0.1422044187784195f));
+  P = L::fma(P, t, L::bc(-0.16613943874835968f));
+  P = L::fma(P, t, L::bc(0.1999974548816681f));
+  P = L::fma(P, t, L::bc(-0.25001105666160583f));
+  P = L::fma(P, t, L::bc(0.3333336412906647f));
+  const float2 t2 = L::mul(t, t);
+  float2 s = L::fma(L::bc(-0.5f), t2, L::mul(L::mul(t2, t), P));
+  s = L::fma(fe, L::bc(DD_LN2_LO), s);
+  float2 r = L::fma(fe, L::bc(DD_LN2_HI), L::add(t, s));
+  // 0x00800000 <= bits < 0x7f800000: positive, normal, finite
+  if ((unsigned)(ix - 0x00800000) >= 0x7f000000u) r.x = logf(x.x);
+  if ((unsigned)(iy - 0x00800000) >= 0x7f000000u) r.y = logf(x.y);
+  return r;
+}

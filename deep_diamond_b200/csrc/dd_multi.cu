@@ -12,6 +12,7 @@
 // Both are HBM-bound streams.  Algorithmic bytes per element: multi-transform sizeof(S)+sizeof(D);
 // cost-diff 3*sizeof(T).
 #include "dd_internal.cuh"
+#include "dd_math_f32.cuh"
 
 #define DD_MULTI_MAX 8
 
@@ -166,8 +167,9 @@ __device__ __forceinline__ T dd_cost_term(T a, T y, T t, T acc) {
     return dd_add_rn(acc, t < (T)0 ? -t : t);
   } else {
     if constexpr (sizeof(T) == 4) {
-      const float ylna = __fmul_rn(y, logf(a));
-      const float h = __fadd_rn(__fmul_rn(__fadd_rn(y, -1.0f), logf(__fadd_rn(1.0000001f, -a))), -ylna);
+      const float2 lg = dd_log_pair(make_float2(a, __fadd_rn(1.0000001f, -a)));  // log(a), log(1.0000001 - a)
+      const float ylna = __fmul_rn(y, lg.x);
+      const float h = __fadd_rn(__fmul_rn(__fadd_rn(y, -1.0f), lg.y), -ylna);
       return __fadd_rn(acc, fabsf(h));
     } else {
       const double ylna = __dmul_rn(y, log(a));
@@ -178,7 +180,7 @@ __device__ __forceinline__ T dd_cost_term(T a, T y, T t, T acc) {
 }
 
 template <typename T, int KIND>
-__global__ void __launch_bounds__(256, KIND == 2 ? 4 : 6) dd_cost_kernel(ddCostParams p) {
+__global__ void __launch_bounds__(256, 6) dd_cost_kernel(ddCostParams p) {
   constexpr int V = 16 / sizeof(T);
   const T *a = (const T *)p.a;
   const T *y = (const T *)p.y;
@@ -272,8 +274,8 @@ extern "C" ddStatus_t ddCostDiff(ddHandle_t h, int kind, ddTensorDescriptor_t de
   p.divisor = kind == 2 ? desc->dims[0] : c.total;
   p.vec = ((((uintptr_t)a) | ((uintptr_t)y) | ((uintptr_t)d)) & 15) == 0;
   const int V = 16 / dd_type_size(desc->dtype);
-  // one resident wave: 6 CTAs per SM for the two subtract-and-accumulate kinds, 4 for the cross-entropy
-  unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, kind == 2 ? 4 : 6);
+  // one resident wave: 6 CTAs per SM
+  unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 6);
   const bool f = desc->dtype == DD_DATA_FLOAT;
   if (kind == 0) {
     if (f) dd_cost_kernel<float, 0><<<grid, 256, 0, h->stream>>>(p);

@@ -10,7 +10,7 @@ import itertools
 import numpy as np
 import pytest
 
-from deep_diamond_b200 import dnn
+from deep_diamond_b200 import core, dnn
 from deep_diamond_b200 import tensor as T
 from deep_diamond_b200._lib import DiamondError
 from deep_diamond_b200.tensor import (asum, batcher, connector, desc, entry, entry_, input, native, offset_,
@@ -622,3 +622,40 @@ def test_captured_layer_chain_replays(fact):
         assert fact.handle.launch_count() == n0          # no library call on the host: one graph launch
         assert seq(nhwc) == want
     calls.release()
+
+
+def test_crossentropy_log_accuracy(fact, dev):
+    """The cross-entropy kernel's own log (two at a time, packed arithmetic), element by element:
+    with y = 1 the cost of a one-element tensor is |log(a)|, with y = 0 it is |log(1.0000001 - a)|.
+    4000 values from the smallest normal float up to 1, dense near 1 where log cancels: within
+    2 ulp of the double-precision log; zero and denormal inputs take the library path."""
+    import torch
+    from conftest import ulp_diff_f32
+    rng = np.random.default_rng(3)
+    a = np.concatenate([
+        np.exp(rng.uniform(np.log(1.2e-38), 0.0, 2000)),
+        1.0 - np.exp(rng.uniform(np.log(1e-7), np.log(0.5), 1500)),
+        np.array([0.5, 0.25, 0.70710677, 0.70710683, 0.9999999, 1.0, 1e-40, 3e-39]),
+    ]).astype(np.float32)
+    n = a.size
+    ta = dev.put(a)
+    ones, zeros = dev.put(np.ones(n, np.float32)), dev.put(np.zeros(n, np.float32))
+    out = torch.zeros(2 * n, dtype=torch.float32, device=fact.device)
+    d = core_desc([1, 1])
+    for i in range(n):
+        core.cost_diff(fact.handle, "crossentropy", d, ta.data_ptr() + 4 * i, ones.data_ptr() + 4 * i, None,
+                       out.data_ptr() + 4 * i)
+        core.cost_diff(fact.handle, "crossentropy", d, ta.data_ptr() + 4 * i, zeros.data_ptr() + 4 * i, None,
+                       out.data_ptr() + 4 * (n + i))
+    fact.synchronize()
+    got = out.cpu().numpy()
+    want_log = np.abs(np.log(a.astype(np.float64))).astype(np.float32)
+    assert ulp_diff_f32(got[:n], want_log).max() <= 2
+    one_minus = (np.float32(1.0000001) - a).astype(np.float32)          # formed in float like the kernel
+    want_l1 = np.abs(np.log(one_minus.astype(np.float64))).astype(np.float32)
+    assert ulp_diff_f32(got[n:], want_l1).max() <= 2
+
+
+def core_desc(shape):
+    from deep_diamond_b200 import core as _core
+    return _core.tensor_descriptor(shape, "float", "nc")
