@@ -454,6 +454,30 @@ class B200Shuffler:
 
 # ====================== Factory =================================================
 
+class Pending:
+    """A host<->device copy in flight on one of the factory's copy streams (``transfer_async``)."""
+
+    def __init__(self, fact, event, result):
+        self.fact, self.event, self.result = fact, event, result
+
+    def wait(self):
+        """Blocks the host until the copy has finished; returns what was copied into."""
+        if self.event is not None:
+            self.event.synchronize()
+        return self.result
+
+    def done(self):
+        return self.event is None or self.event.query()
+
+    def before_overwrite(self):
+        """Makes the factory's stream wait for this copy without blocking the host: call it right
+        before the call that overwrites the SOURCE of a device -> host copy (uploads issued after
+        it wait too, since an upload starts behind what the factory's stream holds)."""
+        if self.event is not None:
+            self.fact.stream.wait_event(self.event)
+        return self
+
+
 class CapturedCalls:
     """A CUDA graph of library calls on a factory's tensors (see ``B200Factory.capture``).  The capture
     runs on a side stream the factory's handle is switched to for its duration; replays are enqueued
@@ -501,6 +525,7 @@ class B200Factory:
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scalar = torch.zeros(2, dtype=torch.float64, device=self.device)
         self._reduce_desc = {}
+        self._h2d = self._d2h = None   # copy streams of transfer_async, made on first use
         self.master = True
 
     # DiamondFactoryProvider / FlowProvider
@@ -648,6 +673,44 @@ class B200Factory:
             dst.copy_(self._bytes(tz), non_blocking=False)
         return host_array
 
+    def _copy_streams(self):
+        if self._h2d is None:
+            self._h2d = torch.cuda.Stream(device=self.device)
+            self._d2h = torch.cuda.Stream(device=self.device)
+
+    def upload_async(self, host_array, tz):
+        """Raw storage copy pinned host -> device on the factory's upload stream.  The copy starts once
+        the work already given to the factory's stream is done (the destination may still be in
+        use) and everything given to it afterwards waits for the copy; a download in flight on the
+        other copy stream is NOT waited for, so both directions of the link run at once."""
+        self._copy_streams()
+        n = tz.storage_elems
+        arr = np.ascontiguousarray(host_array).reshape(-1)
+        if arr.size < n:
+            raise DiamondError(DOES_NOT_FIT_MSG, {"source": arr.size, "destination": n})
+        src = torch.from_numpy(arr[:n].view(np.uint8))
+        self._h2d.wait_stream(self.stream)
+        with torch.cuda.stream(self._h2d):
+            self._bytes(tz).copy_(src, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self._h2d)
+        self.stream.wait_stream(self._h2d)
+        return Pending(self, ev, tz)
+
+    def download_async(self, tz, host_array):
+        """Raw storage copy device -> a caller-owned pinned numpy array on the factory's download
+        stream, after the work already given to the factory's stream.  Later work does not wait
+        for it: use ``Pending.wait`` before reading the array and ``Pending.before_overwrite``
+        before anything writes `tz` again."""
+        self._copy_streams()
+        dst = torch.from_numpy(host_array.reshape(-1)[:tz.storage_elems].view(np.uint8))
+        self._d2h.wait_stream(self.stream)
+        with torch.cuda.stream(self._d2h):
+            dst.copy_(self._bytes(tz), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self._d2h)
+        return Pending(self, ev, host_array)
+
     def _bytes(self, tz):
         start = tz.base + tz.position * tz.width
         return tz.alloc[start:start + tz.storage_elems * tz.width]
@@ -760,6 +823,25 @@ def b200_factory(device=None, stream=None):
 
 
 # ====================== transfer! ===============================================
+
+def transfer_async(source, destination):
+    """``transfer!`` without blocking the host, for the two raw-copy cases (a C-contiguous numpy array
+    of the tensor's own data type, ideally pinned, to or from a contiguous device tensor): the copy
+    runs on a copy stream of its own, uploads and downloads on different ones, and a ``Pending`` is
+    returned.  Every other combination is done at once by ``transfer`` and comes back finished.
+    The reference has no counterpart (its ``transfer!`` is synchronous, cudnn/tensor.clj:546-608)."""
+    if (isinstance(destination, B200Tensor) and isinstance(source, np.ndarray) and destination.is_contiguous()
+            and source.dtype == NUMPY_TYPE[destination.desc.dtype_code] and destination.desc.dtype_code != 9
+            and source.flags["C_CONTIGUOUS"] and source.size >= destination.nc and destination.nc > 0):
+        return destination.fact.upload_async(source, destination)
+    if (isinstance(source, B200Tensor) and isinstance(destination, np.ndarray) and source.is_contiguous()
+            and destination.dtype == NUMPY_TYPE[source.desc.dtype_code] and source.desc.dtype_code != 9
+            and destination.flags["C_CONTIGUOUS"] and destination.size >= source.nc and source.nc > 0):
+        return source.fact.download_async(source, destination)
+    result = transfer(source, destination)
+    fact = destination.fact if isinstance(destination, B200Tensor) else getattr(source, "fact", None)
+    return Pending(fact, None, result)
+
 
 def _host_values(source, n, dtype_code):
     """`n` values from a host sequence in the storage dtype of `dtype_code`; a numpy array that already

@@ -218,6 +218,13 @@ def transfer(source, destination):
 
 
 
+def transfer_async(source, destination):
+    """``transfer`` on the factory's copy streams: returns a ``Pending`` (see factory.transfer_async)."""
+    src = source.tz if isinstance(source, VectorView) else source
+    dst = destination.tz if isinstance(destination, VectorView) else destination
+    return _f.transfer_async(src, dst)
+
+
 def native(x):
     if isinstance(x, (_f.HostTensor, np.ndarray, list)):
         return x

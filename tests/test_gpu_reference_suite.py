@@ -659,3 +659,32 @@ def test_crossentropy_log_accuracy(fact, dev):
 def core_desc(shape):
     from deep_diamond_b200 import core as _core
     return _core.tensor_descriptor(shape, "float", "nc")
+
+
+def test_transfer_async_pipeline(fact):
+    """Uploads and downloads on the factory's copy streams: results equal the synchronous path, a
+    download started before its source is overwritten still delivers the old contents once
+    ``before_overwrite`` guards the overwrite, and mixed cases fall back to ``transfer``."""
+    import torch
+    shape = [8, 16, 32, 32]
+    n = int(np.prod(shape))
+    rng = np.random.default_rng(9)
+    src = tensor(fact, shape, "float", "nchw")
+    dst = tensor(fact, shape, "float", "nchw")
+    layer = dnn.activation(fact, src, "relu")(src, dst)
+    hx = [torch.from_numpy(rng.standard_normal(n).astype(np.float32)).pin_memory() for _ in range(3)]
+    hy = [torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(3)]
+    pend = []
+    for i in range(3):
+        T.transfer_async(hx[i].numpy(), src)
+        if pend:
+            pend[-1].before_overwrite()               # the previous result is still being read
+        layer.forward()
+        pend.append(T.transfer_async(layer.output(), hy[i].numpy()))
+    for i, p in enumerate(pend):
+        assert p.wait() is not None and p.done()
+        assert np.array_equal(hy[i].numpy(), np.maximum(hx[i].numpy(), 0.0)), i
+    # a list source is not a raw copy: done at once, returned finished
+    p = T.transfer_async([1.0] * n, src)
+    assert p.done() and p.wait() is src
+    assert seq(src)[:3] == [1.0, 1.0, 1.0]
