@@ -470,6 +470,15 @@ def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
     measure("relu forward on a sub-tensor view", "[256,256,28,28] f32 window of [256,320,28,28] -> dense", n * 8, n,
             lambda: core.activation_forward(h, ad, 1.0, wd, wide, 0.0, d4, y))
     del wide
+    # activations on 16-bit tensors (arithmetic in float): relu and tanh forward on bf16
+    db = core.tensor_descriptor(shp, "bf16", "nchw")
+    xb = (x.view(torch.int32) >> 16).to(torch.int16)          # the bf16 bit patterns of x (truncated)
+    yb16 = dbuf(n * 2)
+    for mode in ("relu", "tanh"):
+        adm = core.activation_descriptor(mode, True, 0.0)
+        measure("%s forward, bf16 tensors" % mode, "[256,256,28,28] bf16", n * 4, n,
+                lambda adm=adm: core.activation_forward(h, adm, 1.0, db, xb, 0.0, db, yb16))
+    del xb, yb16
     # N and C swapped (nchw -> cnhw): rows of 784 elements
     measure("reorder nchw -> cnhw", "[256,256,28,28] f32", n * 8, n,
             lambda: core.transform_tensor(h, 1.0, d4, x, 0.0,

@@ -78,9 +78,21 @@ struct ddActArgs {
   int nanProp;
 };
 
-template <typename C, int MODE>
+// The result of a 16-bit element type takes the special-function-unit forms of dd_math_f32.cuh for
+// the transcendental modes (at most one unit of the 16-bit type off).
+// LIGHT: 0 = full float accuracy, 1 = f16 result, 2 = bf16 result
+template <typename T> struct dd_light { static constexpr int value = 0; };
+template <> struct dd_light<__half> { static constexpr int value = 1; };
+template <> struct dd_light<__nv_bfloat16> { static constexpr int value = 2; };
+
+template <typename C, int MODE, int LIGHT = 0>
 __device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp) {
   typedef dd_math<C> M;
+  if constexpr (LIGHT != 0 && sizeof(C) == 4) {
+    if (MODE == DD_ACTIVATION_SIGMOID) return dd_sigmoid_light(x);
+    if (MODE == DD_ACTIVATION_TANH) return LIGHT == 2 ? dd_tanh_sfu(x) : dd_tanh_light(x);
+    if (MODE == DD_ACTIVATION_ELU) return x > 0.0f ? x : dd_mul_rn(coef, dd_expm1_neg_light(x));
+  }
   if (MODE == DD_ACTIVATION_RELU) {
     if (coef == (C)0) {
       if (nanProp && x != x) return x;
@@ -104,9 +116,14 @@ __device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp) {
 }
 
 // returns act'(x) * dy
-template <typename C, int MODE>
+template <typename C, int MODE, int LIGHT = 0>
 __device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef) {
   typedef dd_math<C> M;
+  if constexpr (LIGHT != 0 && sizeof(C) == 4) {
+    if (MODE == DD_ACTIVATION_SIGMOID) return dd_mul_rn(dy, dd_dsigmoid_light(x));
+    if (MODE == DD_ACTIVATION_TANH) return dd_mul_rn(dy, dd_dtanh_light(x));
+    if (MODE == DD_ACTIVATION_ELU) return x > 0.0f ? dy : dd_mul_rn(dy, dd_mul_rn(coef, dd_exp_neg_light(x)));
+  }
   if (MODE == DD_ACTIVATION_RELU) {
     return x > (C)0 ? dy : dd_mul_rn(coef, dy);
   } else if (MODE == DD_ACTIVATION_SIGMOID) {
@@ -189,7 +206,7 @@ __global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) 
       uint4 res;
       const T *xv = (const T *)&xin, *dv = (const T *)&din, *ov = (const T *)&oin;
       T *rv = (T *)&res;
-      if constexpr (sizeof(C) == 4 && dd_act_packed<MODE>::value) {
+      if constexpr (sizeof(C) == 4 && sizeof(T) == 4 && dd_act_packed<MODE>::value) {
 #pragma unroll
         for (int k = 0; k < V; k += 2) {
           const float2 xc = make_float2(dd_load<float, T>(xv[k]), dd_load<float, T>(xv[k + 1]));
@@ -203,8 +220,8 @@ __global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) 
 #pragma unroll
         for (int k = 0; k < V; k++) {
           C xc = dd_load<C, T>(xv[k]);
-          C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dv[k]), coef)
-                    : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+          C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef)
+                    : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
           rv[k] = PLAIN ? dd_store<T, C>(v) : dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
         }
       }
@@ -214,8 +231,8 @@ __global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) 
   }
   for (int64_t i = done + tid; i < p.n; i += nthreads) {
     C xc = dd_load<C, T>(x[i]);
-    C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dy[i]), coef)
-              : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+    C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dy[i]), coef)
+              : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
     C old = useOld ? dd_load<C, T>(out[i]) : (C)0;
     out[i] = dd_store<T, C>(dd_blend(alpha, v, beta, old, useOld));
   }
@@ -242,8 +259,8 @@ __global__ void __launch_bounds__(256) dd_elt_strided_kernel(ddEltStridedParams 
     int64_t off[3];
     dd_offsets<3, int64_t>(p.sp, i, off);
     C xc = dd_load<C, T>(x[off[0]]);
-    C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dy[off[1]]), coef)
-              : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+    C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dy[off[1]]), coef)
+              : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
     C old = useOld ? dd_load<C, T>(out[off[2]]) : (C)0;
     out[off[2]] = dd_store<T, C>(dd_blend(alpha, v, beta, old, useOld));
   }
@@ -274,8 +291,8 @@ __global__ void __launch_bounds__(256) dd_elt_rows_kernel(ddEltStridedParams p) 
 #pragma unroll
     for (int k = 0; k < V; k++) {
       C xc = dd_load<C, T>(xv[k]);
-      C v = BWD ? dd_act_bwd<C, MODE>(xc, dd_load<C, T>(dv[k]), coef)
-                : dd_act_fwd<C, MODE>(xc, coef, shift, nanProp);
+      C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef)
+                : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
       rv[k] = dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
     }
     *(uint4 *)(out + off[2]) = res;

@@ -270,3 +270,64 @@ __device__ __forceinline__ float2 dd_log_pair(float2 x) {
   if ((unsigned)(iy - 0x00800000) >= 0x7f000000u) r.y = logf(x.y);
   return r;
 }
+
+// ---- 16-bit element types --------------------------------------------------------------------
+// A result that is going to be rounded to f16 (11 significant bits) or bf16 (8) does not need the
+// sub-ulp float evaluation above: the special function unit's exp2 and reciprocal (about 2^-22
+// relative) leave the 16-bit rounding right except within 2^-21 of a tie, i.e. at most one unit of
+// the 16-bit type off, at a fraction of the instructions.  Differences that would cancel (1 - e
+// and e - 1 near 0) are replaced by short series there.  Denormals are kept (no .ftz).
+__device__ __forceinline__ float dd_ex2_sfu(float x) {
+  float r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float dd_rcp_sfu(float x) {
+  float r;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+#define DD_LOG2E_F 1.4426950408889634f
+
+__device__ __forceinline__ float dd_sigmoid_light(float x) {
+  const float e = dd_ex2_sfu(-fabsf(x) * DD_LOG2E_F);  // exp(-|x|); NaN stays NaN
+  const float r = dd_rcp_sfu(1.0f + e);
+  return x >= 0.0f ? r : e * r;
+}
+// s * (1 - s) = e / (1 + e)^2, e = exp(-|x|)
+__device__ __forceinline__ float dd_dsigmoid_light(float x) {
+  const float e = dd_ex2_sfu(-fabsf(x) * DD_LOG2E_F);
+  const float r = dd_rcp_sfu(1.0f + e);
+  return e * r * r;
+}
+__device__ __forceinline__ float dd_tanh_light(float x) {
+  const float ax = fabsf(x);
+  const float e = dd_ex2_sfu(ax * (-2.0f * DD_LOG2E_F));  // exp(-2|x|)
+  float t = (1.0f - e) * dd_rcp_sfu(1.0f + e);
+  const float x2 = ax * ax;  // |x| < 0.25: x (1 - x^2/3 + 2 x^4/15 - 17 x^6/315), next term below 2^-19 relative
+  const float p = ax * fmaf(x2, fmaf(x2, fmaf(x2, -0.05396825397f, 0.13333333333f), -0.33333333333f), 1.0f);
+  t = ax < 0.25f ? p : t;
+  return copysignf(t, x);
+}
+// 1 - tanh^2 = 4 e / (1 + e)^2, e = exp(-2|x|)
+__device__ __forceinline__ float dd_dtanh_light(float x) {
+  const float e = dd_ex2_sfu(fabsf(x) * (-2.0f * DD_LOG2E_F));
+  const float r = dd_rcp_sfu(1.0f + e);
+  return 4.0f * e * r * r;
+}
+// exp(x) - 1 for x <= 0
+__device__ __forceinline__ float dd_expm1_neg_light(float x) {
+  const float e = dd_ex2_sfu(x * DD_LOG2E_F) - 1.0f;
+  // |x| < 0.25: x + x^2/2 + x^3/6 + x^4/24 + x^5/120, next term below 2^-19 relative
+  const float p = x * fmaf(x, fmaf(x, fmaf(x, fmaf(x, 0.00833333333f, 0.04166666667f), 0.16666666667f), 0.5f), 1.0f);
+  return x > -0.25f ? p : e;
+}
+__device__ __forceinline__ float dd_exp_neg_light(float x) { return dd_ex2_sfu(x * DD_LOG2E_F); }
+
+// bf16 results (8 significant bits) can take tanh from the special function unit directly: its
+// error of about 2^-11 relative keeps the rounded result within one bf16 unit of the true value.
+__device__ __forceinline__ float dd_tanh_sfu(float x) {
+  float r;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}

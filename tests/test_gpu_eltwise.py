@@ -221,6 +221,70 @@ def test_rows_views(fact, dev, oracle, mode):
         assert ok.all()
 
 
+def _round_to_bf16(x64):
+    """float64 -> bfloat16 bit patterns, rounded to nearest even ONCE (not through float32)."""
+    f32 = x64.astype(np.float32)
+    u = f32.view(np.uint32)
+    lo = u & np.uint32(0xFFFF0000)
+    hi = lo + np.uint32(0x10000)
+    with np.errstate(invalid="ignore", over="ignore"):
+        dlo = np.abs(x64 - lo.view(np.float32).astype(np.float64))
+        dhi = np.abs(hi.view(np.float32).astype(np.float64) - x64)
+    odd = ((lo >> np.uint32(16)) & np.uint32(1)).astype(bool)
+    up = (dhi < dlo) | ((dhi == dlo) & odd)
+    out = np.where(up, hi, lo)
+    out = np.where(np.isnan(x64), np.uint32(0x7FC00000), out)
+    out = np.where(np.isinf(x64), u, out)
+    return (out >> np.uint32(16)).astype(np.uint16)
+
+
+def _ordered16(bits):
+    i = bits.astype(np.int64)
+    return np.where(i >= 0x8000, 0x8000 - i, i)
+
+
+@pytest.mark.parametrize("dtype", ["half", "bf16"])
+@pytest.mark.parametrize("mode", ["tanh", "logistic", "elu"])
+def test_every_16_bit_input(fact, dev, mode, dtype):
+    """All 65536 bit patterns of f16 / bf16 through forward and backward (dy = 1): at most one unit
+    of the 16-bit type from the definition evaluated in double and rounded once."""
+    bits = np.arange(65536, dtype=np.uint16)
+    if dtype == "half":
+        x64 = bits.view(np.float16).astype(np.float64)
+        one = np.ones(65536, np.float16).view(np.uint16)
+    else:
+        x64 = (bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+        one = np.full(65536, 0x3F80, np.uint16)
+    with np.errstate(over="ignore", invalid="ignore"):
+        e = np.exp(-np.abs(x64))
+        if mode == "logistic":
+            f = np.where(x64 >= 0, 1 / (1 + e), e / (1 + e))
+            df = e / (1 + e) ** 2
+        elif mode == "tanh":
+            f, e2 = np.tanh(x64), np.exp(-2 * np.abs(x64))
+            df = 4 * e2 / (1 + e2) ** 2
+        else:
+            f = np.where(x64 > 0, x64, np.expm1(np.minimum(x64, 0)))
+            df = np.where(x64 > 0, 1.0, np.exp(np.minimum(x64, 0)))
+    d = core.tensor_descriptor([65536], dtype, [1])
+    ad = core.activation_descriptor(mode, True, 1.0 if mode == "elu" else 0.0)
+    tx, ty, tg, tdx = dev.put(bits), dev.put(np.zeros_like(bits)), dev.put(one), dev.put(np.zeros_like(bits))
+    core.activation_forward(fact.handle, ad, 1.0, d, tx, 0.0, d, ty)
+    core.activation_backward(fact.handle, ad, 1.0, d, None, d, tg, d, tx, 0.0, d, tdx)
+    for got, ref in ((dev.get(ty, np.uint16), f), (dev.get(tdx, np.uint16), df)):
+        if dtype == "half":
+            with np.errstate(over="ignore"):
+                want = ref.astype(np.float16).view(np.uint16)
+            nan_got = np.isnan(got.view(np.float16))
+        else:
+            want = _round_to_bf16(ref)
+            nan_got = np.isnan((got.astype(np.uint32) << 16).view(np.float32))
+        nan_want = np.isnan(ref)
+        assert np.array_equal(nan_got, nan_want)
+        diff = np.abs(_ordered16(got) - _ordered16(want))[~nan_want]
+        assert diff.max() <= 1, (mode, dtype, int(diff.max()), int((diff > 0).sum()))
+
+
 def _ordered(t):
     """float32 tensor -> int64 keys that are monotone in the float order (ulp distance = key diff)."""
     import torch
