@@ -690,6 +690,7 @@ class B200Factory:
             raise DiamondError(DOES_NOT_FIT_MSG, {"source": arr.size, "destination": n})
         src = torch.from_numpy(arr[:n].view(np.uint8))
         self._h2d.wait_stream(self.stream)
+        tz.alloc.record_stream(self._h2d)   # the allocator must not hand this memory out again before the copy ran
         with torch.cuda.stream(self._h2d):
             self._bytes(tz).copy_(src, non_blocking=True)
             ev = torch.cuda.Event()
@@ -705,6 +706,7 @@ class B200Factory:
         self._copy_streams()
         dst = torch.from_numpy(host_array.reshape(-1)[:tz.storage_elems].view(np.uint8))
         self._d2h.wait_stream(self.stream)
+        tz.alloc.record_stream(self._d2h)
         with torch.cuda.stream(self._d2h):
             dst.copy_(self._bytes(tz), non_blocking=True)
             ev = torch.cuda.Event()
