@@ -80,16 +80,41 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
     pl->kind = DD_RED_ROW;
     pl->vec = aligned && p.R2 % V == 0 && mult(p.K1, p.sxK1) && mult(p.R1, p.sxR1) && mult(p.K2, p.sxK2);
     const int v = pl->vec ? V : 1;
-    p.G = nred <= 2048 ? 32 : 256;
+    // threads per output: enough lanes to cover one run of R2 in a single pass (so that no lane
+    // idles on short runs), a whole CTA for long reductions, a warp for short ones
+    // threads per output: the group size whose passes over a run of R2 leave the fewest lanes idle
+    // (ties go to the larger group: fewer partials); a warp for short reductions
+    {
+      int best = 32;
+      double bestUse = -1.0;
+      for (int gsz = 32; gsz <= 256; gsz *= 2) {
+        const int64_t ch = (int64_t)gsz * v;
+        const double use = (double)p.R2 / (double)(((p.R2 + ch - 1) / ch) * ch);
+        if (use >= bestUse - 1e-9) { bestUse = use > bestUse ? use : bestUse; best = gsz; }
+      }
+      p.G = nred <= 2048 ? 32 : best;
+    }
     const int gpb = 256 / p.G;
     p.CH = (int64_t)p.G * v;
     p.cpr = (p.R2 + p.CH - 1) / p.CH;
     const int64_t want = desired * gpb;
     if (nout < want) {
       int64_t units = p.R1 * p.cpr;
-      // once splitting, aim at one full wave of the 4-CTA-per-SM residency (64 registers/thread)
-      int64_t S = ((int64_t)h->smCount * 4 * gpb) / nout;
-      if (S < 2) S = 2;
+      // once splitting, take the smallest split count whose CTAs fill whole waves of the
+      // 4-CTA-per-SM residency (64 registers/thread) to 95 % or better; failing that, the best seen
+      const int64_t slots = (int64_t)h->smCount * 4;
+      int64_t smax = units / 4;
+      if (smax > 64) smax = 64;
+      int64_t S = 2;
+      double bestEff = -1.0;
+      for (int64_t cand = 2; cand <= smax; cand++) {
+        const int64_t ctas = (nout * cand + gpb - 1) / gpb;
+        if (ctas < slots * 9 / 10) continue;  // less than a wave: keep adding splits
+        const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
+        if (eff > bestEff + 1e-9) { bestEff = eff; S = cand; }
+        if (eff >= 0.95) break;
+      }
+      if (bestEff < 0.0) S = smax < 2 ? 2 : smax;  // cannot reach a wave at all: as many splits as allowed
       if (S > units / 4) S = units / 4;
       if (S > 1024) S = 1024;
       if (S > 1) {

@@ -279,16 +279,26 @@ __device__ __forceinline__ C dd_group_reduce(C acc, int G, bool nanProp, C *smem
     acc = dd_red<C, OPC>::comb(acc, other, nanProp);
   }
   if (G == 32) return acc;
+  // G = 64, 128 or 256: the group's G/32 warps leave their values in shared memory and the first
+  // lane of the group folds them in warp order
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (lane == 0) smem[warp] = acc;
   __syncthreads();
-  if (warp == 0) {
-    acc = lane < (int)(blockDim.x >> 5) ? smem[lane] : dd_red<C, OPC>::identity();
+  if (G == 256) {  // the whole CTA is one group: warp 0 folds the eight values with shuffles
+    if (warp == 0) {
+      acc = lane < 8 ? smem[lane] : dd_red<C, OPC>::identity();
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
-      C other = __shfl_down_sync(0xffffffffu, acc, o);
-      acc = dd_red<C, OPC>::comb(acc, other, nanProp);
+      for (int o = 4; o > 0; o >>= 1) {
+        C other = __shfl_down_sync(0xffffffffu, acc, o);
+        acc = dd_red<C, OPC>::comb(acc, other, nanProp);
+      }
     }
+    return acc;
+  }
+  if ((threadIdx.x % G) == 0) {
+    const int gw = G >> 5;
+    acc = smem[warp];
+    for (int w = 1; w < gw; w++) acc = dd_red<C, OPC>::comb(acc, smem[warp + w], nanProp);
   }
   return acc;
 }
@@ -298,7 +308,7 @@ __device__ __forceinline__ C dd_group_reduce(C acc, int G, bool nanProp, C *smem
 template <typename T, typename C, int OPC, bool VEC, bool PEER>
 __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedParams p) {
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
-  constexpr int U = 4;  // independent loads in flight per thread
+  constexpr int U = 4;  // independent 16-byte loads in flight per thread
   __shared__ C smem[8];
   const bool nanProp = p.nanProp != 0;
   const int G = p.G;
@@ -334,7 +344,8 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
     const int64_t iters = (r1hi > r1lo && nj > 0) ? (r1hi - r1lo) * nj : 0;
     int64_t r1 = r1lo, j = jlo;
     for (int64_t it = 0; it < iters; it += U) {
-      C vals[U][V];
+      // U loads in flight, kept as loaded (16 bytes each) and converted only while accumulating
+      uint4 raw[U];
       bool ok[U];
 #pragma unroll
       for (int q = 0; q < U; q++) {
@@ -342,14 +353,8 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
         ok[q] = (it + q < iters) && (e < p.R2);
         if (ok[q]) {
           const T *ptr = xb + r1 * p.sxR1 + e;
-          if (VEC) {
-            uint4 w = *(const uint4 *)ptr;
-            const T *wv = (const T *)&w;
-#pragma unroll
-            for (int k = 0; k < V; k++) vals[q][k] = dd_load<C, T>(wv[k]);
-          } else {
-            vals[q][0] = dd_load<C, T>(*ptr);
-          }
+          if (VEC) raw[q] = *(const uint4 *)ptr;
+          else *(T *)&raw[q] = *ptr;
         }
         j += jstep;
         if (j >= p.cpr) { j = jlo; r1++; }
@@ -357,8 +362,9 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
 #pragma unroll
       for (int q = 0; q < U; q++) {
         if (ok[q]) {
+          const T *wv = (const T *)&raw[q];
 #pragma unroll
-          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, vals[q][k], nanProp);
+          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
         }
       }
     }
@@ -390,7 +396,7 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
 // col: CTA = TX lanes along k2 (V elements each, TX a power of two <= 256) x TY = 256/TX row
 // groups striding over r1.
 template <typename T, typename C, int OPC, bool VEC, bool PEER>
-__global__ void __launch_bounds__(256, PEER ? 4 : 8) dd_reduce_col_kernel(ddRedParams p) {
+__global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_reduce_col_kernel(ddRedParams p) {
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;
   __shared__ C smem[256 * V];
@@ -415,7 +421,7 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 8) dd_reduce_col_kernel(ddRedP
   if (k2 < p.K2) {
     const T *xb = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2;
     for (int64_t r0 = lo + ty; r0 < hi; r0 += (int64_t)TY * U) {
-      C vals[U][V];
+      uint4 raw[U];  // kept as loaded, converted while accumulating
       bool ok[U];
 #pragma unroll
       for (int q = 0; q < U; q++) {
@@ -423,21 +429,16 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 8) dd_reduce_col_kernel(ddRedP
         ok[q] = r1 < hi;
         if (ok[q]) {
           const T *ptr = xb + r1 * p.sxR1;
-          if (VEC) {
-            uint4 w = *(const uint4 *)ptr;
-            const T *wv = (const T *)&w;
-#pragma unroll
-            for (int k = 0; k < V; k++) vals[q][k] = dd_load<C, T>(wv[k]);
-          } else {
-            vals[q][0] = dd_load<C, T>(*ptr);
-          }
+          if (VEC) raw[q] = *(const uint4 *)ptr;
+          else *(T *)&raw[q] = *ptr;
         }
       }
 #pragma unroll
       for (int q = 0; q < U; q++) {
         if (ok[q]) {
+          const T *wv = (const T *)&raw[q];
 #pragma unroll
-          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], vals[q][k], nanProp);
+          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
         }
       }
     }
