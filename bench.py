@@ -153,10 +153,10 @@ def cpu_sample(oracle, n_batch, reps):
 
 
 def onednn_forward_sample(n_batch=32, reps=3):
-    """Real oneDNN (the build inside PyTorch, through mkldnn tensors) on the host cores for the three
-    forward activations it exposes: elements/s and GB/s on a [n_batch,256,28,28] slice.  It has no
-    elu, no backward and no nhwc reorder through this route, so it complements the oracle's number
-    rather than replacing it."""
+    """Real oneDNN (the build inside PyTorch, through mkldnn tensors) on the host cores for what that
+    route exposes: the three forward activations, same-shape add / mul and the f32 -> bf16 reorder;
+    elements/s and GB/s on a [n_batch,256,28,28] slice.  It has no elu, no backward, no broadcast,
+    no reduction and no nhwc reorder, so it complements the oracle's number rather than replacing it."""
     try:
         import torch
         torch.set_num_threads(os.cpu_count() or 1)
@@ -172,6 +172,19 @@ def onednn_forward_sample(n_batch=32, reps=3):
             dt = (time.perf_counter() - t0) / reps
             n = int(np.prod(shape))
             out[name] = {"Gelem/s": round(n / dt / 1e9, 3), "GB/s": round(n * 8 / dt / 1e9, 2)}
+        # the other ops this route exposes: same-shape add / mul (binary) and the f32 -> bf16 reorder
+        xd = torch.from_numpy(oracle.gen_normal(shape, 2.0, 1))
+        y = torch.from_numpy(oracle.gen_normal(shape, 1.0, 2)).to_mkldnn()
+        n = int(np.prod(shape))
+        for name, fn, nbytes in (("add (same shape)", lambda: torch.add(x, y), n * 12),
+                                 ("mul (same shape)", lambda: torch.mul(x, y), n * 12),
+                                 ("reorder f32 -> bf16", lambda: xd.to_mkldnn(torch.bfloat16), n * 6)):
+            fn()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn()
+            dt = (time.perf_counter() - t0) / reps
+            out[name] = {"Gelem/s": round(n / dt / 1e9, 3), "GB/s": round(nbytes / dt / 1e9, 2)}
         ver = [ln.strip(" -") for ln in torch.__config__.show().splitlines() if "MKL-DNN" in ln]
         out["library"] = ver[0] if ver else "oneDNN (version unknown)"
         out["threads"] = torch.get_num_threads()
