@@ -88,6 +88,29 @@ static inline void dd_launch_pdl(void (*kernel)(P), unsigned grid, unsigned bloc
   cudaLaunchKernelEx(&cfg, kernel, params);  // a failure is picked up by DD_LAUNCHED's cudaGetLastError
 }
 
+// The same for kernels with two parameter blocks.
+template <typename P, typename Q>
+static inline void dd_launch_pdl2(void (*kernel)(P, Q), unsigned grid, unsigned block, cudaStream_t stream,
+                                  const P &p, const Q &q) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, p, q);
+}
+
+// For kernels launched the ordinary way: lets a programmatically launched successor be scheduled
+// while this grid runs (the successor still waits for this grid's completion before it reads).
+__device__ __forceinline__ void dd_pdl_release_next() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 static inline int dd_type_size(ddDataType_t t) {
   switch (t) {
     case DD_DATA_FLOAT: return 4;

@@ -310,6 +310,7 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;  // independent 16-byte loads in flight per thread
   __shared__ C smem[8];
+  dd_pdl_release_next();
   const bool nanProp = p.nanProp != 0;
   const int G = p.G;
   const int gpb = 256 / G;  // groups per CTA
@@ -400,6 +401,7 @@ __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_redu
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;
   __shared__ C smem[256 * V];
+  dd_pdl_release_next();
   const bool nanProp = p.nanProp != 0;
   const int TX = p.TX, TY = 256 / TX;
   const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
@@ -534,6 +536,7 @@ __global__ void __launch_bounds__(256) dd_reduce_finish_kernel(ddRedParams p, co
 template <typename T, typename C, int OPC>
 __global__ void __launch_bounds__(256) dd_reduce_exchange_kernel(ddRedParams p, ddPeerParams q) {
   constexpr int NW = dd_words<C>::N;
+  dd_pdl_prologue();  // scheduled while the local pass drains; nothing is read before it has completed
   const int64_t nout = p.K1 * p.K2;
   unsigned char *mine = q.base[q.rank];
   unsigned *ctl = (unsigned *)mine;
@@ -704,7 +707,7 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
     p.partialOnly = 0;                                                                             \
     int64_t g = (pl.nout + 255) / 256;                                                             \
     unsigned grid = (unsigned)(g < 1 ? 1 : (g > DD_PEER_GRID_MAX ? DD_PEER_GRID_MAX : g));         \
-    dd_reduce_exchange_kernel<T, C, OPC><<<grid, 256, 0, h->stream>>>(p, q);                       \
+    dd_launch_pdl2(dd_reduce_exchange_kernel<T, C, OPC>, grid, 256u, h->stream, p, q);             \
     DD_LAUNCHED(h, "reduce/peer-exchange");                                                        \
     return DD_STATUS_SUCCESS;                                                                      \
   }                                                                                                \
