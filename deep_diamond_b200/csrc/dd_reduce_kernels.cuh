@@ -343,22 +343,26 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
     const T *xb = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2;
     const int64_t nj = jlo < p.cpr ? (p.cpr - jlo + jstep - 1) / jstep : 0;
     const int64_t iters = (r1hi > r1lo && nj > 0) ? (r1hi - r1lo) * nj : 0;
-    int64_t r1 = r1lo, j = jlo;
+    // the walk is kept in increments (no multiplication per load): `row` points at run r1, `e` is
+    // this lane's element offset inside it, `j` the chunk number
+    const T *row = xb + r1lo * p.sxR1;
+    const int64_t eFirst = jlo * p.CH + (int64_t)lane * V, eStep = jstep * p.CH;
+    int64_t e = eFirst, j = jlo, left = iters;
     for (int64_t it = 0; it < iters; it += U) {
       // U loads in flight, kept as loaded (16 bytes each) and converted only while accumulating
       uint4 raw[U];
       bool ok[U];
 #pragma unroll
       for (int q = 0; q < U; q++) {
-        const int64_t e = j * p.CH + (int64_t)lane * V;
-        ok[q] = (it + q < iters) && (e < p.R2);
+        ok[q] = (left > 0) && (e < p.R2);
         if (ok[q]) {
-          const T *ptr = xb + r1 * p.sxR1 + e;
-          if (VEC) raw[q] = *(const uint4 *)ptr;
-          else *(T *)&raw[q] = *ptr;
+          if (VEC) raw[q] = *(const uint4 *)(row + e);
+          else *(T *)&raw[q] = row[e];
         }
+        left--;
         j += jstep;
-        if (j >= p.cpr) { j = jlo; r1++; }
+        e += eStep;
+        if (j >= p.cpr) { j = jlo; e = eFirst; row += p.sxR1; }
       }
 #pragma unroll
       for (int q = 0; q < U; q++) {
