@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libdd_b200.so")
+# DD_B200_LIBRARY names another build of the same library (e.g. the `--tune` build of build.py)
+LIB_PATH = os.environ.get("DD_B200_LIBRARY") or os.path.join(_HERE, "libdd_b200.so")
 
 
 class DiamondError(RuntimeError):
@@ -88,7 +89,10 @@ _SIGS = {
     "ddShardedGetUniqueId": [_vp],
     "ddShardedCreate": [ctypes.POINTER(_vp), _vp, _int, _int, _vp],
     "ddShardedDestroy": [_vp],
-    "ddShardedReduceTensor": [_vp, _vp, _int, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ddShardedReduceTensor": [_vp, _vp, _int, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ddShardedPeerDetach": [_vp],
+    "ddShardedSetJoinLimit": [_dbl],
+    "ddResetCounters": [_vp],
     "ddShardedCheck": [_vp],
     "ddShardedPeerExport": [_vp, _vp],
     "ddShardedPeerAttach": [_vp, _vp],

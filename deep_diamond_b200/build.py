@@ -13,11 +13,16 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdd_b200.so")
 OBJ = os.path.join(HERE, "_obj")
+# `--tune` builds libdd_b200_tune.so with -DDD_TUNE (launch-plan overrides read from the environment,
+# for parameter sweeps); the package loads it when DD_B200_LIBRARY names it.
+if "--tune" in sys.argv:
+    OUT = os.path.join(HERE, "libdd_b200_tune.so")
+    OBJ = os.path.join(HERE, "_obj", "tune")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-]
+] + (["-DDD_TUNE"] if "--tune" in sys.argv else [])
 
 
 def _nvcc():

@@ -114,13 +114,27 @@ ddStatus_t ddCreate(ddHandle_t *handle) {
   }
   // the first 64 KB are arrival counters of split reductions: zero now, kept zero by the kernels
   h->counterSlots = (64 << 10) / sizeof(unsigned);
-  if (cudaMemset(h->scratch, 0, h->counterSlots * sizeof(unsigned)) != cudaSuccess) {
+  // (the memset runs on the legacy default stream; the handle may later be bound to a stream that
+  // is not ordered after it, so it is finished before the handle is handed out)
+  if (cudaMemset(h->scratch, 0, h->counterSlots * sizeof(unsigned)) != cudaSuccess ||
+      cudaDeviceSynchronize() != cudaSuccess) {
     cudaGetLastError();
     cudaFree(h->scratch);
     delete h;
     return DD_STATUS_ALLOC_FAILED;
   }
   *handle = h;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddResetCounters(ddHandle_t h) {
+  if (!h) return DD_STATUS_BAD_PARAM;
+  if (!h->scratch || h->counterSlots == 0) return DD_STATUS_SUCCESS;
+  cudaError_t e = cudaMemsetAsync(h->scratch, 0, h->counterSlots * sizeof(unsigned), h->stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    DD_FAIL(h, DD_STATUS_EXECUTION_FAILED, "ddResetCounters: %s", cudaGetErrorString(e));
+  }
   return DD_STATUS_SUCCESS;
 }
 
@@ -338,6 +352,7 @@ ddStatus_t ddGetReduceTensorDescriptor(ddReduceTensorDescriptor_t r, ddReduceTen
   } while (0)
 
 ddStatus_t ddSetTensor(ddHandle_t h, ddTensorDescriptor_t yd, void *y, const void *value) {
+  DD_RANGE("ddSetTensor");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, yd, "ddSetTensor y"));
   if (!y || !value) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddSetTensor: null pointer");
@@ -345,6 +360,7 @@ ddStatus_t ddSetTensor(ddHandle_t h, ddTensorDescriptor_t yd, void *y, const voi
 }
 
 ddStatus_t ddScaleTensor(ddHandle_t h, ddTensorDescriptor_t yd, void *y, const void *alpha) {
+  DD_RANGE("ddScaleTensor");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, yd, "ddScaleTensor y"));
   if (!y || !alpha) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddScaleTensor: null pointer");
@@ -353,6 +369,7 @@ ddStatus_t ddScaleTensor(ddHandle_t h, ddTensorDescriptor_t yd, void *y, const v
 
 ddStatus_t ddAddTensor(ddHandle_t h, const void *alpha, ddTensorDescriptor_t xd, const void *x,
                        const void *beta, ddTensorDescriptor_t yd, void *y) {
+  DD_RANGE("ddAddTensor");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, xd, "ddAddTensor x"));
   DD_CHECK(dd_check_desc(h, yd, "ddAddTensor y"));
@@ -366,6 +383,7 @@ ddStatus_t ddAddTensor(ddHandle_t h, const void *alpha, ddTensorDescriptor_t xd,
 ddStatus_t ddOpTensor(ddHandle_t h, ddOpTensorOp_t op, const void *alpha1, ddTensorDescriptor_t ad,
                       const void *A, const void *alpha2, ddTensorDescriptor_t bd, const void *B,
                       const void *beta, ddTensorDescriptor_t cd, void *C) {
+  DD_RANGE("ddOpTensor");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, ad, "ddOpTensor A"));
   DD_CHECK(dd_check_desc(h, bd, "ddOpTensor B"));
@@ -380,6 +398,7 @@ ddStatus_t ddOpTensor(ddHandle_t h, ddOpTensorOp_t op, const void *alpha1, ddTen
 
 ddStatus_t ddSumTensors(ddHandle_t h, int n, const float *scales, const ddTensorDescriptor_t *sd,
                         const void *const *srcs, ddTensorDescriptor_t dd, void *dst) {
+  DD_RANGE("ddSumTensors");
   DD_CHECK_HANDLE(h);
   if (n < 1 || n > 8) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddSumTensors: n must be in 1..8");
   if (!scales || !sd || !srcs || !dst) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddSumTensors: null pointer");
@@ -393,6 +412,7 @@ ddStatus_t ddSumTensors(ddHandle_t h, int n, const float *scales, const ddTensor
 
 ddStatus_t ddTransformTensor(ddHandle_t h, const void *alpha, ddTensorDescriptor_t xd,
                              const void *x, const void *beta, ddTensorDescriptor_t yd, void *y) {
+  DD_RANGE("ddTransformTensor");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, xd, "ddTransformTensor x"));
   DD_CHECK(dd_check_desc(h, yd, "ddTransformTensor y"));
@@ -406,6 +426,7 @@ ddStatus_t ddTransformTensor(ddHandle_t h, const void *alpha, ddTensorDescriptor
 ddStatus_t ddGatherTransform(ddHandle_t h, int count, const int64_t *srcOff, const int64_t *dstOff,
                              ddTensorDescriptor_t xd, const void *x, ddTensorDescriptor_t yd,
                              void *y) {
+  DD_RANGE("ddGatherTransform");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, xd, "ddGatherTransform x"));
   DD_CHECK(dd_check_desc(h, yd, "ddGatherTransform y"));
@@ -420,6 +441,7 @@ ddStatus_t ddGatherTransform(ddHandle_t h, int count, const int64_t *srcOff, con
 
 ddStatus_t ddTensorEquals(ddHandle_t h, ddTensorDescriptor_t xd, const void *x,
                           ddTensorDescriptor_t yd, const void *y, int *flag) {
+  DD_RANGE("ddTensorEquals");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, xd, "ddTensorEquals x"));
   DD_CHECK(dd_check_desc(h, yd, "ddTensorEquals y"));
@@ -432,6 +454,7 @@ ddStatus_t ddTensorEquals(ddHandle_t h, ddTensorDescriptor_t xd, const void *x,
 ddStatus_t ddActivationForward(ddHandle_t h, ddActivationDescriptor_t act, const void *alpha,
                                ddTensorDescriptor_t xd, const void *x, const void *beta,
                                ddTensorDescriptor_t yd, void *y) {
+  DD_RANGE("ddActivationForward");
   DD_CHECK_HANDLE(h);
   if (!act) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddActivationForward: null activation descriptor");
   DD_CHECK(dd_check_desc(h, xd, "ddActivationForward x"));
@@ -448,6 +471,7 @@ ddStatus_t ddActivationBackward(ddHandle_t h, ddActivationDescriptor_t act, cons
                                 ddTensorDescriptor_t yd, const void *y, ddTensorDescriptor_t dyd,
                                 const void *dy, ddTensorDescriptor_t xd, const void *x,
                                 const void *beta, ddTensorDescriptor_t dxd, void *dx) {
+  DD_RANGE("ddActivationBackward");
   (void)yd;
   (void)y;
   DD_CHECK_HANDLE(h);
@@ -496,6 +520,7 @@ ddStatus_t ddReduceTensor(ddHandle_t h, ddReduceTensorDescriptor_t red, void *in
                           size_t indicesBytes, void *ws, size_t wsBytes, const void *alpha,
                           ddTensorDescriptor_t xd, const void *x, const void *beta,
                           ddTensorDescriptor_t yd, void *y) {
+  DD_RANGE("ddReduceTensor");
   (void)indices;
   (void)indicesBytes;
   DD_CHECK_HANDLE(h);
@@ -515,6 +540,7 @@ ddStatus_t ddReduceTensor(ddHandle_t h, ddReduceTensorDescriptor_t red, void *in
 // + beta * db: the (N,H,W) sum of ddReduceTensor under the name the convolution layers call.
 ddStatus_t ddConvolutionBackwardBias(ddHandle_t h, const void *alpha, ddTensorDescriptor_t dyd,
                                      const void *dy, const void *beta, ddTensorDescriptor_t dbd, void *db) {
+  DD_RANGE("ddConvolutionBackwardBias");
   DD_CHECK_HANDLE(h);
   DD_CHECK(dd_check_desc(h, dyd, "ddConvolutionBackwardBias dy"));
   DD_CHECK(dd_check_desc(h, dbd, "ddConvolutionBackwardBias db"));

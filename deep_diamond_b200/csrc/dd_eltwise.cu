@@ -332,7 +332,7 @@ static ddStatus_t launch_elt(ddHandle_t h, const ddCanon &c, const void *x, cons
     uintptr_t bits = (uintptr_t)x | (uintptr_t)out | (BWD ? (uintptr_t)dy : 0);
     p.vec = (bits & 15) == 0;
     constexpr int V = 16 / sizeof(T);
-    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 16);
+    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, dd_tune("DD_ELTFLAT_CPS", 16));
     if (alpha == 1.0 && beta == 0.0) dd_launch_pdl(dd_elt_flat_kernel<T, C, MODE, BWD, true>, grid, 256, h->stream, p);
     else dd_launch_pdl(dd_elt_flat_kernel<T, C, MODE, BWD, false>, grid, 256, h->stream, p);
     DD_LAUNCHED(h, BWD ? "activation-bwd/flat" : "activation-fwd/flat");

@@ -8,7 +8,18 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/dd_b200.h"
+
+// An NVTX range around one library call, named after the entry point, so that a timeline shows the
+// calls of this library by name.  NVTX v3 is header-only: without a profiler attached (no injection
+// library named in the environment) a push or pop is one test of a function pointer.
+struct ddNvtxRange {
+  explicit ddNvtxRange(const char *name) { nvtxRangePushA(name); }
+  ~ddNvtxRange() { nvtxRangePop(); }
+};
+#define DD_RANGE(name) ddNvtxRange dd_nvtx_range_(name)
 
 // ------------------------------------------------------------------ host-side objects --------
 
@@ -88,6 +99,25 @@ static inline void dd_launch_pdl(void (*kernel)(P), unsigned grid, unsigned bloc
   cudaLaunchKernelEx(&cfg, kernel, params);  // a failure is picked up by DD_LAUNCHED's cudaGetLastError
 }
 
+// A launch whose CTAs form thread-block clusters of `cluster` along x (the grid is a multiple of it).
+template <typename P>
+static inline void dd_launch_cluster(void (*kernel)(P), unsigned grid, unsigned block, unsigned cluster,
+                                     cudaStream_t stream, const P &params) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, params);  // a failure is picked up by DD_LAUNCHED's cudaGetLastError
+}
+
 // The same for kernels with two parameter blocks.
 template <typename P, typename Q>
 static inline void dd_launch_pdl2(void (*kernel)(P, Q), unsigned grid, unsigned block, cudaStream_t stream,
@@ -110,6 +140,18 @@ static inline void dd_launch_pdl2(void (*kernel)(P, Q), unsigned grid, unsigned 
 __device__ __forceinline__ void dd_pdl_release_next() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+
+// Builds with -DDD_TUNE read launch-plan overrides (group sizes, split counts, grid sizes) from the
+// environment, for parameter sweeps on a GPU; ordinary builds compile the look-ups away.
+#ifdef DD_TUNE
+#include <stdlib.h>
+static inline int dd_tune(const char *name, int dflt) {
+  const char *v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+#else
+static inline int dd_tune(const char *, int dflt) { return dflt; }
+#endif
 
 static inline int dd_type_size(ddDataType_t t) {
   switch (t) {
@@ -402,7 +444,7 @@ struct ddPeerParams;
 ddStatus_t dd_reduce_fused_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,
                                          double count, double alpha, const ddTensorStruct *xd, const void *x,
                                          double beta, const ddTensorStruct *yd, void *y, void *partialOut,
-                                         bool *fused);
+                                         bool onlyDistributed, bool *fused);
 ddStatus_t dd_reduce_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,
                                    double count, double alpha, double beta, const ddTensorStruct *xd,
                                    const ddTensorStruct *yd, void *y);

@@ -74,6 +74,7 @@ static ddStatus_t multi_to(ddHandle_t h, ddDataType_t dt, const ddMultiParams &p
 extern "C" ddStatus_t ddMultiTransform(ddHandle_t h, int count, const ddTensorDescriptor_t *xDescs,
                                        const void *const *xs, const ddTensorDescriptor_t *yDescs,
                                        void *const *ys) {
+  DD_RANGE("ddMultiTransform");
   if (!h) return DD_STATUS_BAD_PARAM;
   if (count < 1 || count > DD_MULTI_MAX) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddMultiTransform: count must be in 1..%d", DD_MULTI_MAX);
   if (!xDescs || !xs || !yDescs || !ys) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddMultiTransform: null pointer");
@@ -249,6 +250,7 @@ __global__ void __launch_bounds__(256, 6) dd_cost_kernel(ddCostParams p) {
 
 extern "C" ddStatus_t ddCostDiff(ddHandle_t h, int kind, ddTensorDescriptor_t desc, const void *a,
                                  const void *y, void *d, void *cost) {
+  DD_RANGE("ddCostDiff");
   if (!h) return DD_STATUS_BAD_PARAM;
   ddStatus_t st = dd_check_desc(h, desc, "ddCostDiff");
   if (st != DD_STATUS_SUCCESS) return st;

@@ -257,7 +257,7 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
       p.fdInner = dd_fastdiv((uint32_t)inner);
       p.fdChannels = dd_fastdiv((uint32_t)channels);
     }
-    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 8);
+    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, dd_tune("DD_OPFLAT_CPS", 8));
     // add and mul (bias, per-channel scale, axpy, sum) get their own instantiations
     if (op == DD_OP_TENSOR_ADD && bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 0>, grid, 256, h->stream, p);
     else if (op == DD_OP_TENSOR_ADD) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 1>, grid, 256, h->stream, p);

@@ -9,9 +9,15 @@ static int next_pow2(int64_t v) {
   return p;
 }
 
+// flags: DD_PLAN_STRUCTURED: the caller needs the x[k1][r1][k2][r2] form (the sharded path addresses partial
+// results by (k1, k2)), so short reductions, which otherwise run one thread per output, take the
+// row kernel with warp-sized groups.  DD_PLAN_NO_CLUSTER: splits of the col kernel go through the
+// counter protocol (the fused cross-GPU form pushes from the CTA that folds the partials).
 ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd,
-                          const void *x, const ddTensorStruct *yd, ddRedPlan *pl) {
+                          const void *x, const ddTensorStruct *yd, ddRedPlan *pl, int flags) {
+  const bool structured = (flags & DD_PLAN_STRUCTURED) != 0;
   memset(pl, 0, sizeof(*pl));
+  pl->bs = 256;
   switch (red->op) {
     case DD_REDUCE_TENSOR_ADD: pl->opc = DD_OPC_SUM; pl->p.post = DD_POST_NONE; break;
     case DD_REDUCE_TENSOR_AVG: pl->opc = DD_OPC_SUM; pl->p.post = DD_POST_AVG; break;
@@ -76,47 +82,92 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
   const bool aligned = (((uintptr_t)x) & 15) == 0;
   auto mult = [&](int64_t extent, int64_t stride) { return extent == 1 || stride % V == 0; };
 
-  if (fits && p.R2 > 1 && p.sxR2 == 1 && nred > 32) {
+  if (fits && p.R2 > 1 && p.sxR2 == 1 && (nred > 32 || structured)) {
     pl->kind = DD_RED_ROW;
+    // one long contiguous run per output (norm over (C,H,W) of an nchw tensor): read it as rows of
+    // 256 16-byte vectors, so that splits take whole rows and the lean kernel applies
+    if (dd_tune("DD_ROW_FOLD", 1) && p.R1 == 1 && aligned && p.R2 % (256 * V) == 0 && p.R2 / (256 * V) >= 8) {
+      p.R1 = p.R2 / (256 * V);
+      p.R2 = 256 * V;
+      p.sxR1 = p.R2;
+    }
     pl->vec = aligned && p.R2 % V == 0 && mult(p.K1, p.sxK1) && mult(p.R1, p.sxR1) && mult(p.K2, p.sxK2);
     const int v = pl->vec ? V : 1;
-    // threads per output: enough lanes to cover one run of R2 in a single pass (so that no lane
-    // idles on short runs), a whole CTA for long reductions, a warp for short ones
-    // threads per output: the group size whose passes over a run of R2 leave the fewest lanes idle
-    // (ties go to the larger group: fewer partials); a warp for short reductions
+    // Threads per output (G) and per CTA (bs).  A group passes over a run of R2 in chunks of G
+    // 16-byte vectors; the lean kernel (8 loads in flight per thread) takes plans with at most 4
+    // chunks per run.  Score = the share of lanes that a pass keeps busy, times 1.25 when the lean
+    // kernel applies (it measured 8-25 % faster than the general walk at equal lane use); ties go to
+    // the larger group (fewer groups, fewer partials).  One exception to the tie rule: when every
+    // group of 128 fits one resident wave of 128-thread CTAs, groups of 256 would not, and a thread
+    // of the smaller group still has at most 32 loads to do, the smaller group wins (the whole
+    // reduction is then two to four round trips to memory with every CTA on the machine at once).
     {
+      auto cprOf = [&](int gsz) { return (p.R2 + (int64_t)gsz * v - 1) / ((int64_t)gsz * v); };
+      auto leanOk = [&](int gsz) { return pl->vec && cprOf(gsz) <= 4 && p.R1 < 0x7fffffffLL; };
       int best = 32;
-      double bestUse = -1.0;
-      for (int gsz = 32; gsz <= 256; gsz *= 2) {
+      double bestScore = -1.0;
+      for (int gsz = 256; gsz >= 32; gsz /= 2) {
         const int64_t ch = (int64_t)gsz * v;
-        const double use = (double)p.R2 / (double)(((p.R2 + ch - 1) / ch) * ch);
-        if (use >= bestUse - 1e-9) { bestUse = use > bestUse ? use : bestUse; best = gsz; }
+        const double use = (double)p.R2 / (double)(cprOf(gsz) * ch);
+        const double score = use * (leanOk(gsz) ? 1.25 : 1.0);
+        if (score > bestScore + 1e-9) { bestScore = score; best = gsz; }
+      }
+      if (best == 256 && leanOk(128) && cprOf(128) == 2 * cprOf(256) &&
+          nout <= (int64_t)h->smCount * 8 && nout > (int64_t)h->smCount * 4 && p.R1 * cprOf(128) <= 32)
+        best = 128;
+      // Too few outputs to fill the machine even with the best group size: splits are due anyway.
+      // With 128 outputs or more the smallest group that ties on the score measured fastest (f32
+      // 784-long runs, 256 outputs: 64 lanes 0.92 of the copy rate, 128 lanes 0.89, 256 lanes 0.75;
+      // bf16: 32 lanes 0.77, 64 lanes 0.64); with fewer outputs (one output takes tens of splits)
+      // the largest did (1024-long runs, 8 outputs: 256 lanes 10.5 us, 128 lanes 12.0, 64 lanes 13.8).
+      if (nout * best < (int64_t)h->smCount * 1024 * 4 / 5 && nout >= 128) {
+        const int lo = dd_tune("DD_ROW_GMIN", 32);
+        for (int gsz = lo; gsz < best; gsz *= 2)
+          if (leanOk(gsz) && cprOf(gsz) * gsz == cprOf(best) * best) { best = gsz; break; }
       }
       p.G = nred <= 2048 ? 32 : best;
     }
-    const int gpb = 256 / p.G;
+    p.G = dd_tune("DD_ROW_G", p.G);
+    // 128-thread CTAs for groups of 128 or fewer lanes (finer grain: 8 resident CTAs per SM)
+    pl->bs = dd_tune("DD_ROW_BS", (p.G <= 128 && nred > 2048) ? 128 : 256);
+    if (pl->bs < p.G) pl->bs = p.G;
+    const int gpb = pl->bs / p.G;
     p.CH = (int64_t)p.G * v;
     p.cpr = (p.R2 + p.CH - 1) / p.CH;
-    const int64_t want = desired * gpb;
-    if (nout < want) {
+    // groups wanted before an output's range is split: 6 CTAs of 256 threads per SM, or, with
+    // 128-thread CTAs, four fifths of one resident wave (1024 threads per SM at 64 registers): a split
+    // costs a partial store, a fence, an atomic and a fold by the last arrival, about 3 us
+    const int64_t want = pl->bs == 128 ? ((int64_t)h->smCount * 1024 * 4 / 5) / p.G : desired * gpb;
+    if (nout < want || dd_tune("DD_ROW_S", 0) > 1) {
       int64_t units = p.R1 * p.cpr;
-      // once splitting, take the smallest split count whose CTAs fill whole waves of the
-      // 4-CTA-per-SM residency (64 registers/thread) to 95 % or better; failing that, the best seen
-      const int64_t slots = (int64_t)h->smCount * 4;
+      const int64_t slots = (int64_t)h->smCount * (1024 / pl->bs);
       int64_t smax = units / 4;
-      if (smax > 64) smax = 64;
-      int64_t S = 2;
-      double bestEff = -1.0;
-      for (int64_t cand = 2; cand <= smax; cand++) {
-        const int64_t ctas = (nout * cand + gpb - 1) / gpb;
-        if (ctas < slots * 9 / 10) continue;  // less than a wave: keep adding splits
-        const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
-        if (eff > bestEff + 1e-9) { bestEff = eff; S = cand; }
-        if (eff >= 0.95) break;
+      if (smax > 1024) smax = 1024;
+      int64_t S = 0;
+      // first choice: ONE resident wave, as full as the split count allows and at least four fifths
+      // full (one wave of long-running threads measured faster than several waves of short ones, and
+      // 1152 CTAs in 1184 slots faster than 1024)
+      {
+        int64_t cand = slots * gpb / (nout > 0 ? nout : 1);
+        if (cand > smax) cand = smax;
+        if (cand >= 1 && (nout * cand + gpb - 1) / gpb >= slots * 4 / 5) S = cand;
       }
-      if (bestEff < 0.0) S = smax < 2 ? 2 : smax;  // cannot reach a wave at all: as many splits as allowed
+      if (S == 0) {
+        // none lands in one wave: the smallest split count whose CTAs fill whole waves to 95 % or
+        // better, failing that the best seen
+        double bestEff = -1.0;
+        for (int64_t cand = 2; cand <= smax; cand++) {
+          const int64_t ctas = (nout * cand + gpb - 1) / gpb;
+          if (ctas < slots * 9 / 10) continue;
+          const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
+          if (eff > bestEff + 1e-9) { bestEff = eff; S = cand; }
+          if (eff >= 0.95) break;
+        }
+      }
+      if (S == 0) S = smax < 2 ? 2 : smax;  // cannot reach a wave at all: as many splits as allowed
       if (S > units / 4) S = units / 4;
       if (S > 1024) S = 1024;
+      S = dd_tune("DD_ROW_S", (int)S);
       if (S > 1) {
         if (p.R1 >= S) {
           p.splitR1 = 1;
@@ -129,6 +180,9 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
       }
       p.S = S < 1 ? 1 : (int)S;
     }
+    // the lean kernel (8 loads in flight per thread) where the plan allows it
+    if (dd_tune("DD_ROW_LEAN", 1) && pl->vec && (p.S == 1 || p.splitR1) && p.cpr <= 4 && p.R1 < 0x7fffffffLL)
+      pl->lean = p.cpr == 3 ? 4 : (int)p.cpr;
     int64_t groups = nout * p.S;
     int64_t ctas = (groups + gpb - 1) / gpb;
     if (ctas > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: too many outputs");
@@ -139,23 +193,57 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
     const int v = pl->vec ? V : 1;
     int tx = next_pow2((p.K2 + v - 1) / v);
     p.TX = tx > 32 ? 32 : tx;
+    const int txMin = dd_tune("DD_COL_TXMIN", 8);
+    pl->pdl = dd_tune("DD_COL_PDL", 0);
     // narrower tiles (down to 8 lanes = 128 contiguous bytes) while that is what it takes to fill
     // the machine without splitting the reduced range
     auto tiles = [&](int t) { return (p.K2 + (int64_t)t * v - 1) / ((int64_t)t * v); };
-    while (p.TX > 8 && p.K1 * tiles(p.TX) < desired) p.TX /= 2;
+    while (p.TX > txMin && p.K1 * tiles(p.TX) < desired) p.TX /= 2;
+    // ... and narrower still while that cuts the padding of the last tile along k2 by a twentieth or
+    // more of the lanes (784 elements: 32 lanes of 16 bytes leave a quarter of the bf16 lanes idle)
+    if (dd_tune("DD_COL_PAD", esize >= 4 ? 1 : 0)) {  // (16-bit types measured slower with the narrower tiles)
+      auto laneUse = [&](int t) { return (double)p.K2 / (double)(tiles(t) * t * v); };
+      while (p.TX > txMin && laneUse(p.TX / 2) > laneUse(p.TX) + 0.05) p.TX /= 2;
+    }
+    p.TX = dd_tune("DD_COL_TX", p.TX);
     const int TY = 256 / p.TX;
     p.tilesK2 = tiles(p.TX);
     int64_t ctas0 = p.K1 * p.tilesK2;
+    // Too few tiles to fill the machine: split r1 (when the range is long enough to be worth it).
     if (ctas0 < desired) {
       int64_t S = (desired + ctas0 - 1) / ctas0;
       int64_t cap = p.R1 / ((int64_t)TY * 4);
       if (S > cap) S = cap;
       if (S > 1024) S = 1024;
+      S = dd_tune("DD_COL_S", (int)S);
       if (S > 1) {
         int64_t per = (p.R1 + S - 1) / S;
         S = (p.R1 + per - 1) / per;
       }
       p.S = S < 1 ? 1 : (int)S;
+    }
+    // Where a split is due and 2, 4 or 8 splits give at least half a resident wave of 128-thread
+    // CTAs, the splits of a tile form a thread-block cluster and combine through distributed shared
+    // memory (dd_reduce_colc_kernel): 256-byte runs along k2 (16 lanes), 8 row groups per CTA.  The
+    // fused cross-GPU form keeps the counter protocol.
+    if (p.S > 1 && pl->vec && !(flags & DD_PLAN_NO_CLUSTER) && dd_tune("DD_COL_CLUSTER", 1)) {
+      int txc = next_pow2((p.K2 + v - 1) / v);
+      if (txc > 16) txc = 16;
+      const int tyc = DD_COLC_THREADS / txc;
+      const int64_t tilesC = (p.K2 + (int64_t)txc * v - 1) / ((int64_t)txc * v);
+      const int64_t base = p.K1 * tilesC;
+      const int64_t wave = (int64_t)h->smCount * 8;
+      int sc = 2;
+      while (sc < 8 && base * sc < wave * 4 / 5) sc *= 2;
+      while (sc > 1 && p.R1 / ((int64_t)sc * tyc) < 1) sc /= 2;
+      sc = dd_tune("DD_COL_SC", sc);
+      if (sc >= 2 && sc <= 8 && base * sc >= wave / 2 && base * sc <= 0x7fffffffLL) {
+        pl->cluster = 1;
+        p.TX = txc;
+        p.tilesK2 = tilesC;
+        p.S = sc;
+        ctas0 = base;
+      }
     }
     int64_t ctas = ctas0 * p.S;
     if (ctas > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: too many outputs");
@@ -180,7 +268,11 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
     g.nanProp = p.nanProp;
     pl->grid = dd_flat_grid(h, nout, 256, 16);
   }
-  pl->wsBytes = p.S > 1 ? (size_t)nout * p.S * csize : 0;
+  pl->wsBytes = (p.S > 1 && !pl->cluster) ? (size_t)nout * p.S * csize : 0;
+  if (dd_tune("DD_PLAN_DEBUG", 0))
+    fprintf(stderr, "[dd plan] kind %d vec %d lean %d cluster %d bs %d G %d S %d splitR1 %d cpr %lld TX %d tiles %lld grid %u | K1 %lld R1 %lld K2 %lld R2 %lld\n",
+            pl->kind, pl->vec, pl->lean, pl->cluster, pl->bs, p.G, p.S, p.splitR1, (long long)p.cpr, p.TX,
+            (long long)p.tilesK2, pl->grid, (long long)p.K1, (long long)p.R1, (long long)p.K2, (long long)p.R2);
   return DD_STATUS_SUCCESS;
 }
 
@@ -214,7 +306,7 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
                           double alpha, const ddTensorStruct *xd, const void *x, double beta,
                           const ddTensorStruct *yd, void *y, bool partialOnly, void *partialOut) {
   ddRedPlan pl;
-  ddStatus_t st = dd_reduce_plan(h, red, xd, x, yd, &pl);
+  ddStatus_t st = dd_reduce_plan(h, red, xd, x, yd, &pl, partialOnly ? DD_PLAN_STRUCTURED : 0);
   if (st != DD_STATUS_SUCCESS) return st;
   if (partialOnly && pl.kind == DD_RED_GENERIC)
     DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
@@ -242,6 +334,7 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
   pl.p.partialOnly = partialOnly ? 1 : 0;
   for (int i = 0; i < DD_PEER_MAX; i++) pl.p.peerBase[i] = nullptr;
   pl.p.peerWorld = pl.p.peerRank = 0;
+  pl.p.peerDistributed = 0;
   pl.p.peerWaitNs = 0;
   pl.g.y = y;
   pl.g.partOut = partialOut;
@@ -255,7 +348,7 @@ ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, 
                                  double count, double alpha, double beta, const ddTensorStruct *xd,
                                  const ddTensorStruct *yd, void *y) {
   ddRedPlan pl;
-  ddStatus_t st = dd_reduce_plan(h, red, xd, (const void *)0, yd, &pl);
+  ddStatus_t st = dd_reduce_plan(h, red, xd, (const void *)0, yd, &pl, DD_PLAN_STRUCTURED);
   if (st != DD_STATUS_SUCCESS) return st;
   if (pl.kind == DD_RED_GENERIC)
     DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
@@ -273,19 +366,27 @@ ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, 
   DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
 }
 
-// Fused form: ONE kernel reduces the local shard, pushes each accumulator to the peers as soon as it
-// is final and lets its last CTA collect and finish.  *fused = false (nothing launched) when the plan
-// does not allow it: many outputs, or splits that a second kernel would have to combine.
+// Fused form: ONE kernel reduces the local shard and pushes each accumulator to the peers as soon as
+// it is final.  Who collects depends on the plan.  Row kernels whose whole grid is resident at once:
+// the thread that finished an output also waits for the other ranks' values of THAT output and
+// writes y ("distributed": the waits of all outputs run in parallel, and every rank's CTAs push
+// before they wait, so no wait depends on a CTA that is not running yet).  Otherwise the CTA that
+// finishes last collects every output (at most DD_PEER_FUSED_MAX_OUT of them).
+// *fused = false (nothing launched) when the plan does not allow the form asked for; `onlyDistributed`
+// restricts it to the first kind.
 #define DD_PEER_FUSED_MAX_OUT 4096
 ddStatus_t dd_reduce_fused_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddPeerParams *peer,
                                          double count, double alpha, const ddTensorStruct *xd, const void *x,
                                          double beta, const ddTensorStruct *yd, void *y, void *partialOut,
-                                         bool *fused) {
+                                         bool onlyDistributed, bool *fused) {
   *fused = false;
   ddRedPlan pl;
-  ddStatus_t st = dd_reduce_plan(h, red, xd, x, yd, &pl);
+  ddStatus_t st = dd_reduce_plan(h, red, xd, x, yd, &pl, DD_PLAN_STRUCTURED | DD_PLAN_NO_CLUSTER);
   if (st != DD_STATUS_SUCCESS) return st;
-  if (pl.kind == DD_RED_GENERIC || pl.nout > DD_PEER_FUSED_MAX_OUT) return DD_STATUS_SUCCESS;
+  if (pl.kind == DD_RED_GENERIC) return DD_STATUS_SUCCESS;
+  // resident CTAs per SM of the fused row kernels: 64 registers per thread (__launch_bounds__(256, 4))
+  const bool distributed = pl.kind == DD_RED_ROW && (int64_t)pl.grid <= (int64_t)h->smCount * (1024 / pl.bs);
+  if (!distributed && (onlyDistributed || pl.nout > DD_PEER_FUSED_MAX_OUT)) return DD_STATUS_SUCCESS;
   unsigned *counters = nullptr;
   void *ws = nullptr;
   if (pl.wsBytes > 0) {
@@ -307,6 +408,7 @@ ddStatus_t dd_reduce_fused_exchange_impl(ddHandle_t h, const ddReduceTensorStruc
   pl.p.peerWorld = peer->world;
   pl.p.peerRank = peer->rank;
   pl.p.peerWaitNs = peer->waitNs;
+  pl.p.peerDistributed = distributed ? 1 : 0;
   *fused = true;
   return launch_by_type(h, xd->dtype, pl);
 }
@@ -315,7 +417,7 @@ ddStatus_t dd_reduce_exchange_impl(ddHandle_t h, const ddReduceTensorStruct *red
                                    double count, double alpha, double beta, const ddTensorStruct *xd,
                                    const ddTensorStruct *yd, void *y) {
   ddRedPlan pl;
-  ddStatus_t st = dd_reduce_plan(h, red, xd, (const void *)0, yd, &pl);
+  ddStatus_t st = dd_reduce_plan(h, red, xd, (const void *)0, yd, &pl, DD_PLAN_STRUCTURED);
   if (st != DD_STATUS_SUCCESS) return st;
   if (pl.kind == DD_RED_GENERIC)
     DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
@@ -358,6 +460,7 @@ extern "C" ddStatus_t ddReduceTensorNoAlloc(void *stream, ddReduceTensorOp_t op,
                                             const void *alpha, ddTensorDescriptor_t xd, const void *x,
                                             const void *beta, ddTensorDescriptor_t yd, void *y,
                                             char *errbuf, size_t errbufLen) {
+  DD_RANGE("ddReduceTensorNoAlloc");
   noalloc_msg(errbuf, errbufLen, "");
   if (!alpha || !beta || !x || !y || !xd || !yd || !xd->set || !yd->set) {
     noalloc_msg(errbuf, errbufLen, "ddReduceTensorNoAlloc: null pointer or unset descriptor");

@@ -18,6 +18,7 @@
 // thread per output (generic).  All are HBM-bound: algorithmic bytes = input bytes + output bytes.
 #pragma once
 #include "dd_internal.cuh"
+#include <cooperative_groups.h>
 
 enum { DD_OPC_SUM = 0, DD_OPC_SUMABS, DD_OPC_SUMSQ, DD_OPC_PROD, DD_OPC_PRODNZ, DD_OPC_MIN, DD_OPC_MAX, DD_OPC_AMAX, DD_OPC_COUNT };
 enum { DD_POST_NONE = 0, DD_POST_AVG = 1, DD_POST_SQRT = 2 };
@@ -140,6 +141,9 @@ struct ddRedParams {
                      //    combines the world's accumulators and finishes into y (fused exchange)
   unsigned char *peerBase[DD_PEER_MAX];  // partialOnly == 2: every rank's exchange buffer
   int peerWorld, peerRank;
+  int peerDistributed;  // partialOnly == 2: the thread that finishes an output also collects the other
+                        // ranks' values for it and writes y (row kernels whose grid is resident at
+                        // once); 0: the CTA that finishes last collects every output
   unsigned long long peerWaitNs;
 };
 
@@ -156,10 +160,11 @@ __device__ __forceinline__ void dd_red_output(const ddRedParams &p, int64_t k1, 
 }
 
 // partialOnly == 2: this rank's accumulator of output o goes to the other ranks as tagged cells
+// `call`: this call's number when the caller has read it already, else 0 (read here).
 template <typename C>
-__device__ __forceinline__ void dd_peer_push(const ddRedParams &p, int64_t o, C acc) {
+__device__ __forceinline__ unsigned dd_peer_push(const ddRedParams &p, int64_t o, C acc, unsigned call = 0) {
   constexpr int NW = dd_words<C>::N;
-  const unsigned call = __ldcg((const unsigned *)p.peerBase[p.peerRank]) + 1u;
+  if (call == 0) call = __ldcg((const unsigned *)p.peerBase[p.peerRank]) + 1u;
   const size_t off = DD_PEER_SLOTS_OFF + ((size_t)(call & 1u) * DD_PEER_MAX + p.peerRank) * DD_PEER_SLOT_BYTES;
   unsigned w[NW];
   dd_words<C>::split(acc, w);
@@ -169,14 +174,31 @@ __device__ __forceinline__ void dd_peer_push(const ddRedParams &p, int64_t o, C 
 #pragma unroll
     for (int k = 0; k < NW; k++) dd_st_cell(cell + k, w[k], call);
   }
+  return call;
 }
 
-template <typename T, typename C, bool PEER = false>
-__device__ __forceinline__ void dd_red_finish(const ddRedParams &p, int64_t k1, int64_t k2, C acc) {
+template <typename T, typename C, int OPC>
+__device__ __forceinline__ bool dd_peer_collect(const ddRedParams &p, unsigned char *mine, unsigned call,
+                                                int W, int rank, unsigned long long t0,
+                                                unsigned long long waitNs, int64_t o, C mineVal);
+
+// OPC: only the distributed fused exchange needs it (the combine across ranks); -1 elsewhere.
+template <typename T, typename C, bool PEER = false, int OPC = -1>
+__device__ __forceinline__ void dd_red_finish(const ddRedParams &p, int64_t k1, int64_t k2, C acc,
+                                              unsigned peerCall = 0) {
   if (p.partialOnly) {
     const int64_t o = k1 * p.K2 + k2;
     ((C *)p.partOut)[o] = acc;
-    if constexpr (PEER) dd_peer_push<C>(p, o, acc);
+    if constexpr (PEER) {
+      const unsigned call = dd_peer_push<C>(p, o, acc, peerCall);
+      if constexpr (OPC >= 0) {
+        // this rank's value is on its way; now wait (bounded) for the other ranks' values of the
+        // same output, which their CTAs push at about the same time, and finish it here
+        if (p.peerDistributed)
+          dd_peer_collect<T, C, OPC>(p, p.peerBase[p.peerRank], call, p.peerWorld, p.peerRank, dd_globaltimer(),
+                                     p.peerWaitNs, o, acc);
+      }
+    }
     return;
   }
   dd_red_output<T, C>(p, k1, k2, acc);
@@ -257,11 +279,13 @@ __device__ __forceinline__ void dd_peer_tail(const ddRedParams &p) {
   if (!lastFlag) return;
   __threadfence();
   const unsigned call = __ldcg(ctl) + 1u;
-  const int64_t nout = p.K1 * p.K2;
-  const unsigned long long t0 = dd_globaltimer();
-  for (int64_t o = threadIdx.x; o < nout; o += blockDim.x)
-    dd_peer_collect<T, C, OPC>(p, mine, call, p.peerWorld, p.peerRank, t0, p.peerWaitNs, o,
-                               __ldcg((const C *)p.partOut + o));
+  if (!p.peerDistributed) {
+    const int64_t nout = p.K1 * p.K2;
+    const unsigned long long t0 = dd_globaltimer();
+    for (int64_t o = threadIdx.x; o < nout; o += blockDim.x)
+      dd_peer_collect<T, C, OPC>(p, mine, call, p.peerWorld, p.peerRank, t0, p.peerWaitNs, o,
+                                 __ldcg((const C *)p.partOut + o));
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     ctl[1] = 0;
@@ -303,29 +327,127 @@ __device__ __forceinline__ C dd_group_reduce(C acc, int G, bool nanProp, C *smem
   return acc;
 }
 
+// Distributed fused exchange, first thing in the kernel (every thread of the CTA calls it): reads
+// this call's number and counts the CTA's arrival.  The CTA that arrives last publishes the number
+// for the next launch right away: every CTA has read the old one by then, nothing else depends on
+// it during this launch, and the publication is off the critical path of the outputs.  Returns 0 in
+// the other fused form (dd_peer_tail publishes then).
+__device__ __forceinline__ unsigned dd_peer_begin(const ddRedParams &p) {
+  if (!p.peerDistributed) return 0;
+  __shared__ unsigned callShared;
+  unsigned *ctl = (unsigned *)p.peerBase[p.peerRank];
+  if (threadIdx.x == 0) {
+    // one thread reads the number and hands it to the CTA through shared memory, so that the value
+    // is in hand before this CTA's arrival counts
+    const unsigned call = __ldcg(ctl) + 1u;
+    callShared = call;
+    if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {
+      ctl[1] = 0;
+      __stcg(ctl, call);
+    }
+  }
+  __syncthreads();
+  return callShared;
+}
+
+// Folds the S partials of one output.  Called by all 32 lanes of a warp; the result is valid in
+// lane 0.  Up to 32 partials: lane 0 folds them in index order.  More: lane l folds partials l,
+// l + 32, ... in index order and the lanes combine in a shuffle tree.  The order is fixed either
+// way, and the in-kernel fold (last arrival) and dd_reduce_finish_kernel both come here, so the two
+// give the same bits.
+template <typename C, int OPC>
+__device__ __forceinline__ C dd_fold_partials(const C *part, int S, bool nanProp, int lane) {
+  if (S <= 32) {
+    C a = dd_red<C, OPC>::identity();
+    if (lane == 0) {
+      a = __ldcg(part);
+      for (int i = 1; i < S; i++) a = dd_red<C, OPC>::comb(a, __ldcg(part + i), nanProp);
+    }
+    return a;
+  }
+  C a = __ldcg(part + lane);
+  for (int i = lane + 32; i < S; i += 32) a = dd_red<C, OPC>::comb(a, __ldcg(part + i), nanProp);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    C other = __shfl_down_sync(0xffffffffu, a, o);
+    a = dd_red<C, OPC>::comb(a, other, nanProp);
+  }
+  return a;
+}
+
+// What follows a thread's own accumulation in the row kernels: the group's tree, then either the
+// finished output or this split's partial (the split that arrives last folds them all).
+template <typename T, typename C, int OPC, bool PEER>
+__device__ __forceinline__ void dd_row_epilogue(const ddRedParams &p, C acc, C *smem, unsigned peerCall) {
+  const bool nanProp = p.nanProp != 0;
+  acc = dd_group_reduce<C, OPC>(acc, p.G, nanProp, smem);
+  // which group this is and which output and split it works on: worked out again here rather than
+  // kept in registers across the kernel's main loop (which has none to spare)
+  const int lane = threadIdx.x % p.G;
+  const int64_t g = (int64_t)blockIdx.x * (blockDim.x / p.G) + threadIdx.x / p.G;
+  const bool live = g < p.K1 * p.K2 * p.S;
+  int64_t out = 0, k1 = 0, k2 = 0;
+  int s = 0;
+  if (live && lane < 32) {
+    out = g / p.S;
+    s = (int)(g - out * p.S);
+    k1 = out / p.K2;
+    k2 = out - k1 * p.K2;
+  }
+  if (p.S == 1) {
+    if (live && lane == 0) dd_red_finish<T, C, PEER, PEER ? OPC : -1>(p, k1, k2, acc, peerCall);
+  } else if (lane < 32) {
+    // the first warp of the group: lane 0 leaves this split's partial and counts its arrival; the
+    // split that arrives last folds all S partials with the whole warp (a fixed order, so the result
+    // does not depend on which split came last).  No waiting anywhere.
+    C *part = (C *)p.part + out * p.S;
+    int last = 0;
+    if (live && lane == 0) {
+      part[s] = acc;
+      if (p.counters) {
+        __threadfence();
+        last = atomicAdd(p.counters + out, 1u) == (unsigned)(p.S - 1);
+      }
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence();
+      const C a = dd_fold_partials<C, OPC>(part, p.S, nanProp, lane);
+      if (lane == 0) {
+        dd_red_finish<T, C, PEER, PEER ? OPC : -1>(p, k1, k2, a, peerCall);
+        p.counters[out] = 0;
+      }
+    }
+  }
+  if constexpr (PEER) {
+    if (!p.peerDistributed) dd_peer_tail<T, C, OPC>(p);
+  }
+}
+
 // PEER: the fused exchange (partialOnly == 2), its own instantiation so that the plain kernels keep
 // their register budget.
+// The CTA has 128 or 256 threads (blockDim.x), a whole number of groups.
 template <typename T, typename C, int OPC, bool VEC, bool PEER>
 __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedParams p) {
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;  // independent 16-byte loads in flight per thread
   __shared__ C smem[8];
   dd_pdl_prologue();
+  unsigned peerCall = 0;
+  if constexpr (PEER) peerCall = dd_peer_begin(p);
   const bool nanProp = p.nanProp != 0;
   const int G = p.G;
-  const int gpb = 256 / G;  // groups per CTA
+  const int gpb = blockDim.x / G;  // groups per CTA
   const int64_t g = (int64_t)blockIdx.x * gpb + threadIdx.x / G;
   const int lane = threadIdx.x % G;
   const int64_t nout = p.K1 * p.K2;
   C acc = dd_red<C, OPC>::identity();
   const bool live = g < nout * p.S;  // G == 32 only: trailing groups of the last CTA idle
-  int64_t out = 0, k1 = 0, k2 = 0;
-  int s = 0;
   if (live) {
-    out = g / p.S;
-    s = (int)(g - out * p.S);
-    k1 = out / p.K2;
-    k2 = out - k1 * p.K2;
+    const int64_t out = g / p.S;
+    const int s = (int)(g - out * p.S);
+    const int64_t k1 = out / p.K2;
+    const int64_t k2 = out - k1 * p.K2;
     // splits either partition r1 (each takes whole runs) or interleave the chunks of every run
     // (split s takes chunks s, s + S, ...): concurrently running splits of one output then read
     // neighbouring 16-byte-vector rows, like one flat stream
@@ -374,28 +496,82 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
       }
     }
   }
-  acc = dd_group_reduce<C, OPC>(acc, G, nanProp, smem);
-  if (live && lane == 0) {
-    if (p.S == 1) {
-      dd_red_finish<T, C, PEER>(p, k1, k2, acc);
-    } else {
-      C *part = (C *)p.part + out * p.S;
-      part[s] = acc;
-      if (p.counters) {
-        // last split to arrive folds all S partials in index order (same order as the finishing
-        // kernel, so the result does not depend on which split came last).  No waiting anywhere.
-        __threadfence();
-        if (atomicAdd(p.counters + out, 1u) == (unsigned)(p.S - 1)) {
-          __threadfence();
-          C a = __ldcg(part);
-          for (int i = 1; i < p.S; i++) a = dd_red<C, OPC>::comb(a, __ldcg(part + i), nanProp);
-          dd_red_finish<T, C, PEER>(p, k1, k2, a);
-          p.counters[out] = 0;
+  dd_row_epilogue<T, C, OPC, PEER>(p, acc, smem, peerCall);
+}
+
+// Lean form of the row kernel for small inputs, where the whole reduction is two or three round
+// trips to memory and what counts is how many bytes are in flight: EIGHT 16-byte loads per thread
+// and nothing else in the loop but one pointer.  Plans that qualify: 16-byte aligned runs, a
+// thread's share of a run at most CPR chunks (CPR = 1, 2 or 4; a row batch is 8 / CPR runs), and
+// splits, if any, that partition r1.  Same accumulation order as the general kernel.
+template <typename T, typename C, int OPC, int CPR, bool PEER>
+__global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int U = 8, RB = U / CPR;
+  __shared__ C smem[8];
+  dd_pdl_prologue();
+  unsigned peerCall = 0;
+  if constexpr (PEER) peerCall = dd_peer_begin(p);
+  const bool nanProp = p.nanProp != 0;
+  const int G = p.G;
+  const int gpb = blockDim.x / G;
+  const int64_t g = (int64_t)blockIdx.x * gpb + threadIdx.x / G;
+  const int lane = threadIdx.x % G;
+  const int64_t nout = p.K1 * p.K2;
+  C acc = dd_red<C, OPC>::identity();
+  const bool live = g < nout * p.S;
+  if (live) {
+    const int64_t out = g / p.S;
+    const int s = (int)(g - out * p.S);
+    const int64_t k1 = out / p.K2;
+    const int64_t k2 = out - k1 * p.K2;
+    int64_t r1lo = 0, r1hi = p.R1;
+    if (p.S > 1) {
+      int64_t per = (p.R1 + p.S - 1) / p.S;
+      r1lo = s * per;
+      r1hi = r1lo + per < p.R1 ? r1lo + per : p.R1;
+    }
+    const T *ptr = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2 + r1lo * p.sxR1 + (int64_t)lane * V;
+    const int nrows = r1hi > r1lo ? (int)(r1hi - r1lo) : 0;
+    const int ch = (int)p.CH;  // at most 256 vectors of V elements
+    bool okc[CPR];
+#pragma unroll
+    for (int c = 0; c < CPR; c++) okc[c] = (int64_t)lane * V + c * ch < p.R2;
+    int r = 0;
+    for (; r + RB <= nrows; r += RB) {
+      uint4 raw[U];
+#pragma unroll
+      for (int q = 0; q < RB; q++)
+#pragma unroll
+        for (int c = 0; c < CPR; c++)
+          if (okc[c]) raw[q * CPR + c] = *(const uint4 *)(ptr + q * p.sxR1 + c * ch);
+      ptr += RB * p.sxR1;
+#pragma unroll
+      for (int q = 0; q < RB; q++)
+#pragma unroll
+        for (int c = 0; c < CPR; c++)
+          if (okc[c]) {
+            const T *wv = (const T *)&raw[q * CPR + c];
+#pragma unroll
+            for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
+          }
+    }
+    for (; r < nrows; r++) {
+      uint4 raw[CPR];
+#pragma unroll
+      for (int c = 0; c < CPR; c++)
+        if (okc[c]) raw[c] = *(const uint4 *)(ptr + c * ch);
+      ptr += p.sxR1;
+#pragma unroll
+      for (int c = 0; c < CPR; c++)
+        if (okc[c]) {
+          const T *wv = (const T *)&raw[c];
+#pragma unroll
+          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
         }
-      }
     }
   }
-  if constexpr (PEER) dd_peer_tail<T, C, OPC>(p);
+  dd_row_epilogue<T, C, OPC, PEER>(p, acc, smem, peerCall);
 }
 
 // col: CTA = TX lanes along k2 (V elements each, TX a power of two <= 256) x TY = 256/TX row
@@ -405,7 +581,9 @@ __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_redu
   constexpr int V = VEC ? 16 / sizeof(T) : 1;
   constexpr int U = 4;
   __shared__ C smem[256 * V];
-  dd_pdl_release_next();  // launched the ordinary way: the programmatic launch measured 4 % slower here
+  // Large inputs launch this kernel the ordinary way (the programmatic launch measured 4 % slower on
+  // a 268 MB tensor), small ones programmatically; the wait returns at once in the first case.
+  dd_pdl_prologue();
   const bool nanProp = p.nanProp != 0;
   const int TX = p.TX, TY = 256 / TX;
   const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
@@ -488,6 +666,85 @@ __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_redu
   if constexpr (PEER) dd_peer_tail<T, C, OPC>(p);
 }
 
+// col, split over a thread-block cluster: the S = 2, 4 or 8 CTAs that share a tile of outputs are
+// one cluster, each reduces its share of r1 (eight 16-byte loads in flight per thread, nothing in
+// the loop but one pointer), folds its row groups in shared memory, and the cluster's first CTA
+// reads the other CTAs' folded values straight from THEIR shared memory (distributed shared
+// memory) and finishes, in rank order.  Two cluster barriers replace the partial store, fence,
+// atomic counter and re-read through global memory of the counter protocol (about 3 us on a 10 us
+// kernel).  CTA = 128 threads: TX lanes along k2 by TY = 128 / TX row groups.
+#define DD_COLC_THREADS 128
+template <typename T, typename C, int OPC>
+__global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRedParams p) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int U = 8;
+  constexpr int BS = DD_COLC_THREADS;
+  __shared__ C smem[BS * V];
+  __shared__ C folded[32 * V];
+  dd_pdl_prologue();
+  const bool nanProp = p.nanProp != 0;
+  const int TX = p.TX, TY = BS / TX;
+  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+  int64_t id = blockIdx.x;
+  const int s = (int)(id % p.S);  // = this CTA's rank in its cluster (1-D grid, cluster of S along x)
+  id /= p.S;
+  const int64_t tk = id % p.tilesK2;
+  const int64_t k1 = id / p.tilesK2;
+  const int64_t k2 = (tk * TX + tx) * V;
+  const int64_t per = (p.R1 + p.S - 1) / p.S;
+  const int64_t lo = s * per;
+  const int64_t hi = lo + per < p.R1 ? lo + per : p.R1;
+  C acc[V];
+#pragma unroll
+  for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::identity();
+  if (k2 < p.K2 && lo + ty < hi) {
+    const T *ptr = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2 + (lo + ty) * p.sxR1;
+    const int64_t step = (int64_t)TY * p.sxR1;
+    const int n = (int)((hi - lo - ty + TY - 1) / TY);  // rows of this thread
+    int r = 0;
+    for (; r + U <= n; r += U) {
+      uint4 raw[U];
+#pragma unroll
+      for (int q = 0; q < U; q++) raw[q] = *(const uint4 *)(ptr + q * step);
+      ptr += U * step;
+#pragma unroll
+      for (int q = 0; q < U; q++) {
+        const T *wv = (const T *)&raw[q];
+#pragma unroll
+        for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
+      }
+    }
+    for (; r < n; r++) {
+      const uint4 raw = *(const uint4 *)ptr;
+      ptr += step;
+      const T *wv = (const T *)&raw;
+#pragma unroll
+      for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < V; k++) smem[ty * (TX * V) + tx * V + k] = acc[k];
+  __syncthreads();
+  for (int col = threadIdx.x; col < TX * V; col += BS) {
+    C a = smem[col];
+    for (int r = 1; r < TY; r++) a = dd_red<C, OPC>::comb(a, smem[r * (TX * V) + col], nanProp);
+    folded[col] = a;
+  }
+  cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+  cluster.sync();  // every CTA's folded values are in its shared memory
+  if (s == 0) {
+    for (int col = threadIdx.x; col < TX * V; col += BS) {
+      const int64_t kk = tk * TX * V + col;
+      if (kk < p.K2) {
+        C a = folded[col];
+        for (int r = 1; r < p.S; r++) a = dd_red<C, OPC>::comb(a, *cluster.map_shared_rank(&folded[col], r), nanProp);
+        dd_red_finish<T, C>(p, k1, kk, a);
+      }
+    }
+  }
+  cluster.sync();  // nobody leaves while its shared memory may still be read
+}
+
 // Combines the S partials of each output in index order and finishes.  `part` may be an
 // all-reduced buffer (S == 1) on the multi-GPU path.
 template <typename T, typename C, int OPC>
@@ -495,6 +752,17 @@ __global__ void __launch_bounds__(256) dd_reduce_finish_kernel(ddRedParams p, co
   const bool nanProp = p.nanProp != 0;
   const int64_t nout = p.K1 * p.K2;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (p.S > 32) {  // a warp per output, the fold of dd_fold_partials
+    const int lane = threadIdx.x & 31;
+    for (int64_t o = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; o < nout; o += nthreads >> 5) {
+      const C acc = dd_fold_partials<C, OPC>((const C *)part + o * p.S, p.S, nanProp, lane);
+      if (lane == 0) {
+        const int64_t k1 = o / p.K2;
+        dd_red_finish<T, C>(p, k1, o - k1 * p.K2, acc);
+      }
+    }
+    return;
+  }
   for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < nout; o += nthreads) {
     const C *pp = (const C *)part + o * p.S;
     C acc = pp[0];
@@ -629,11 +897,16 @@ __global__ void __launch_bounds__(256) dd_reduce_generic_kernel(ddRedGenericPara
 // ------------------------------------------------------------------ host plan ----------------
 
 enum { DD_RED_ROW = 0, DD_RED_COL = 1, DD_RED_GENERIC = 2 };
+enum { DD_PLAN_STRUCTURED = 1, DD_PLAN_NO_CLUSTER = 2 };
 
 struct ddRedPlan {
   int kind;
   int vec;
   int opc;
+  int bs;   // row: threads per CTA (128 or 256)
+  int lean; // row: 0 = the general kernel, else the lean kernel with this many chunks per run (1, 2, 4)
+  int pdl;  // col: launched programmatically (small inputs) or the ordinary way
+  int cluster;  // col: the S splits of a tile form one thread-block cluster (dd_reduce_colc_kernel)
   ddRedParams p;
   ddRedGenericParams g;
   int64_t nout;
@@ -642,7 +915,7 @@ struct ddRedPlan {
 };
 
 ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd,
-                          const void *x, const ddTensorStruct *yd, ddRedPlan *pl);
+                          const void *x, const ddTensorStruct *yd, ddRedPlan *pl, int flags = 0);
 
 template <typename T, typename C>
 ddStatus_t dd_reduce_launch(ddHandle_t h, const ddRedPlan &pl);
@@ -663,9 +936,14 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
   template <int OPC>                                                                               \
   static ddStatus_t launch_opc_##T(ddHandle_t h, const ddRedPlan &pl) {                            \
     if (pl.p.partialOnly == 2) { /* fused exchange: row or col only, no second kernel */           \
-      if (pl.kind == DD_RED_ROW) {                                                                 \
-        if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, true>, pl.grid, 256u, h->stream, pl.p);  \
-        else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, true>, pl.grid, 256u, h->stream, pl.p);   \
+      if (pl.kind == DD_RED_ROW && pl.lean) {                                                      \
+        if (pl.lean == 1) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 1, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);  \
+        else if (pl.lean == 2) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 2, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);  \
+        else dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 4, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);  \
+        DD_LAUNCHED(h, "reduce/row+peer-exchange");                                                \
+      } else if (pl.kind == DD_RED_ROW) {                                                          \
+        if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);  \
+        else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
         DD_LAUNCHED(h, "reduce/row+peer-exchange");                                                \
       } else {                                                                                     \
         if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);  \
@@ -675,12 +953,24 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       return DD_STATUS_SUCCESS;                                                                    \
     }                                                                                              \
     if (pl.kind == DD_RED_ROW) {                                                                   \
-      if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, false>, pl.grid, 256u, h->stream, pl.p);   \
-      else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, false>, pl.grid, 256u, h->stream, pl.p);    \
+      if (pl.lean == 1) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 1, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
+      else if (pl.lean == 2) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 2, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
+      else if (pl.lean == 4) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 4, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
+      else if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
+      else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);    \
       DD_LAUNCHED(h, "reduce/row");                                                                \
+    } else if (pl.kind == DD_RED_COL && pl.cluster) {                                              \
+      dd_launch_cluster(dd_reduce_colc_kernel<T, C, OPC>, pl.grid, (unsigned)DD_COLC_THREADS, (unsigned)pl.p.S, h->stream, pl.p);  \
+      DD_LAUNCHED(h, "reduce/col-cluster");                                                        \
+      return DD_STATUS_SUCCESS;                                                                    \
     } else if (pl.kind == DD_RED_COL) {                                                            \
-      if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
-      else dd_reduce_col_kernel<T, C, OPC, false, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);    \
+      if (pl.pdl) {                                                                                \
+        if (pl.vec) dd_launch_pdl(dd_reduce_col_kernel<T, C, OPC, true, false>, pl.grid, 256u, h->stream, pl.p);   \
+        else dd_launch_pdl(dd_reduce_col_kernel<T, C, OPC, false, false>, pl.grid, 256u, h->stream, pl.p);    \
+      } else {                                                                                     \
+        if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
+        else dd_reduce_col_kernel<T, C, OPC, false, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);    \
+      }                                                                                            \
       DD_LAUNCHED(h, "reduce/col");                                                                \
     } else {                                                                                       \
       dd_reduce_generic_kernel<T, C, OPC><<<pl.grid, 256, 0, h->stream>>>(pl.g);                   \
@@ -688,7 +978,7 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       return DD_STATUS_SUCCESS;                                                                    \
     }                                                                                              \
     if (pl.p.S > 1 && pl.p.counters == nullptr) {                                                  \
-      unsigned fg = dd_flat_grid(h, pl.nout, 256, 8);                                              \
+      unsigned fg = dd_flat_grid(h, pl.p.S > 32 ? pl.nout * 32 : pl.nout, 256, 8);                 \
       dd_reduce_finish_kernel<T, C, OPC><<<fg, 256, 0, h->stream>>>(pl.p, pl.p.part);              \
       DD_LAUNCHED(h, pl.kind == DD_RED_ROW ? "reduce/row+finish" : "reduce/col+finish");           \
     }                                                                                              \

@@ -13,8 +13,12 @@
 #include "dd_reduce_kernels.cuh"
 
 #include <dlfcn.h>
+#include <chrono>
+#include <condition_variable>
+#include <memory>
 #include <mutex>
 #include <new>
+#include <thread>
 
 // The handful of NCCL declarations used, spelled out so the build needs no NCCL header.  They
 // follow NCCL's public C API (nccl.h): opaque communicator, 128-byte unique id, enum values of
@@ -62,6 +66,40 @@ static bool load_nccl() {
 
 #define DD_PARTIAL_BYTES (1u << 20)
 
+// ncclCommInitRank blocks until every rank has joined and has no limit of its own that a caller
+// could set per call.  It therefore runs on a helper thread; the calling thread waits for it with a
+// limit.  When the limit passes the helper is left behind (it still owns the state it writes to)
+// and the caller gets DD_STATUS_TIMEOUT.
+static double g_join_limit_s = 120.0;
+
+struct ddJoinState {
+  std::mutex mu;
+  std::condition_variable cv;
+  bool done = false;
+  ncclResult_t result = 0;
+  ncclComm_t comm = nullptr;
+};
+
+static int bounded_comm_init(int device, int nRanks, int rank, const ncclUniqueId &id, ncclComm_t *comm,
+                             ncclResult_t *result) {
+  auto st = std::make_shared<ddJoinState>();
+  std::thread([st, device, nRanks, rank, id]() {
+    ncclComm_t c = nullptr;
+    ncclResult_t r = cudaSetDevice(device) == cudaSuccess ? g_nccl.CommInitRank(&c, nRanks, id, rank) : 1;
+    std::lock_guard<std::mutex> lock(st->mu);
+    st->comm = c;
+    st->result = r;
+    st->done = true;
+    st->cv.notify_all();
+  }).detach();
+  std::unique_lock<std::mutex> lock(st->mu);
+  const bool joined = st->cv.wait_for(lock, std::chrono::duration<double>(g_join_limit_s), [&] { return st->done; });
+  if (!joined) return 0;
+  *comm = st->comm;
+  *result = st->result;
+  return 1;
+}
+
 struct ddShardedStruct {
   ddHandle_t h;
   ncclComm_t comm;  // NULL: created without an id, peer exchange only
@@ -72,9 +110,9 @@ struct ddShardedStruct {
   bool peerOpened[DD_PEER_MAX];          // mapped with cudaIpcOpenMemHandle (to be closed)
   bool attached;
   int usePeer;                           // 1: combine over the peer exchange when attached
-  int fuse;                              // 1: reduce + exchange in one kernel where the plan allows (measured
-                                         // slightly slower than the two-kernel form for a 4 KB result, so off
-                                         // by default)
+  int fuse;                              // reduce + exchange in one kernel: 0 never, 1 wherever the plan
+                                         // allows, 2 (default) only in the distributed form (each output is
+                                         // collected by the thread that finished it)
   unsigned long long waitNs;
 };
 
@@ -89,6 +127,12 @@ ddStatus_t ddShardedGetUniqueId(void *id128) {
   ncclUniqueId id;
   if (g_nccl.GetUniqueId(&id) != 0) return DD_STATUS_COMM_FAILED;
   memcpy(id128, &id, sizeof(id));
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddShardedSetJoinLimit(double seconds) {
+  if (!(seconds > 0.0)) return DD_STATUS_BAD_PARAM;
+  g_join_limit_s = seconds;
   return DD_STATUS_SUCCESS;
 }
 
@@ -112,7 +156,7 @@ ddStatus_t ddShardedCreate(ddShardedHandle_t *out, ddHandle_t h, int nRanks, int
   }
   s->attached = false;
   s->usePeer = 1;
-  s->fuse = 0;
+  s->fuse = 2;
   s->waitNs = 2000000000ull;  // 2 s
   if (cudaMalloc(&s->partial, DD_PARTIAL_BYTES) != cudaSuccess) {
     cudaGetLastError();
@@ -122,7 +166,12 @@ ddStatus_t ddShardedCreate(ddShardedHandle_t *out, ddHandle_t h, int nRanks, int
   if (id128) {
     ncclUniqueId id;
     memcpy(&id, id128, sizeof(id));
-    ncclResult_t r = g_nccl.CommInitRank(&s->comm, nRanks, id, rank);
+    ncclResult_t r = 0;
+    if (!bounded_comm_init(h->device, nRanks, rank, id, &s->comm, &r)) {
+      cudaFree(s->partial);
+      delete s;
+      DD_FAIL(h, DD_STATUS_TIMEOUT, "ddShardedCreate: not every one of the %d ranks joined within %.0f s", nRanks, g_join_limit_s);
+    }
     if (r != 0) {
       cudaFree(s->partial);
       delete s;
@@ -142,12 +191,27 @@ static void peer_detach(ddShardedStruct *s) {
   s->attached = false;
 }
 
-ddStatus_t ddShardedDestroy(ddShardedHandle_t s) {
+ddStatus_t ddShardedPeerDetach(ddShardedHandle_t s) {
   if (!s) return DD_STATUS_BAD_PARAM;
   if (s->h) cudaStreamSynchronize(s->h->stream);  // no exchange of this rank may still be in flight
   peer_detach(s);
+  cudaGetLastError();
+  return DD_STATUS_SUCCESS;
+}
+
+// Collective when the exchange is attached: every rank detaches, the ranks meet at a host barrier,
+// then every rank destroys (see the header).  An exchange buffer whose status word says that a wait
+// ran out is not freed: a late peer may still store into it.
+ddStatus_t ddShardedDestroy(ddShardedHandle_t s) {
+  if (!s) return DD_STATUS_BAD_PARAM;
+  if (s->h) cudaStreamSynchronize(s->h->stream);
+  peer_detach(s);
   if (s->comm) g_nccl.CommDestroy(s->comm);
-  if (s->xbuf) cudaFree(s->xbuf);
+  if (s->xbuf) {
+    int status = 0;
+    if (cudaMemcpy(&status, s->xbuf + 2 * sizeof(unsigned), sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) status = -1;
+    if (status == 0) cudaFree(s->xbuf);
+  }
   if (s->partial) cudaFree(s->partial);
   cudaGetLastError();
   delete s;
@@ -220,7 +284,9 @@ ddStatus_t ddShardedPeerConfigure(ddShardedHandle_t s, int usePeer, double waitS
   if (!s) return DD_STATUS_BAD_PARAM;
   if (usePeer >= 0) {
     s->usePeer = usePeer ? 1 : 0;
-    s->fuse = usePeer == 2 ? 1 : 0;  // 2: push from inside the reduce kernel where the plan allows
+    // 1: fused only in its distributed form, else the exchange kernel; 2: fused wherever the plan
+    // allows; 3: never fused
+    s->fuse = usePeer == 2 ? 1 : (usePeer == 3 ? 0 : 2);
   }
   if (waitSeconds > 0) s->waitNs = (unsigned long long)(waitSeconds * 1e9);
   return DD_STATUS_SUCCESS;
@@ -253,8 +319,9 @@ ddStatus_t ddShardedCheck(ddShardedHandle_t s) {
 }
 
 ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t red, int spans,
-                                 const void *alpha, ddTensorDescriptor_t xd, const void *x,
+                                 int64_t globalCount, const void *alpha, ddTensorDescriptor_t xd, const void *x,
                                  const void *beta, ddTensorDescriptor_t yd, void *y) {
+  DD_RANGE("ddShardedReduceTensor");
   if (!s) return DD_STATUS_BAD_PARAM;
   ddHandle_t h = s->h;
   if (!spans || s->nRanks == 1)
@@ -280,6 +347,12 @@ ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t
     default: ncclOp = DD_NCCL_MAX; break;  // MAX, AMAX
   }
   double a = dd_read_scalar(alpha, xd->dtype), b = dd_read_scalar(beta, yd->dtype);
+  if (globalCount < 0 || (globalCount > 0 && globalCount < nredLocal))
+    DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddShardedReduceTensor: global count %lld is smaller than this rank's %lld",
+            (long long)globalCount, (long long)nredLocal);
+  // elements folded into one output over all ranks: given by the caller (uneven shards), or nRanks
+  // times the local count (equal shards)
+  const double count = globalCount > 0 ? (double)globalCount : (double)nredLocal * s->nRanks;
   const bool peer = s->attached && s->usePeer;
   if (!peer && !s->comm)
     DD_FAIL(h, DD_STATUS_NOT_INITIALIZED, "ddShardedReduceTensor: no NCCL communicator and no peer exchange attached");
@@ -291,11 +364,11 @@ ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t
     q.world = s->nRanks;
     q.rank = s->rank;
     q.waitNs = s->waitNs;
-    // equal shards: the global count is nRanks times the local one
-    const double count = (double)nredLocal * s->nRanks;
     if (s->fuse) {
+      // fuse == 2 (the default): only the distributed form, which measured faster than the
+      // two-kernel form; fuse == 1 (asked for): also the form whose last CTA collects
       bool fused = false;
-      st = dd_reduce_fused_exchange_impl(h, red, &q, count, a, xd, x, b, yd, y, s->partial, &fused);
+      st = dd_reduce_fused_exchange_impl(h, red, &q, count, a, xd, x, b, yd, y, s->partial, s->fuse == 2, &fused);
       if (st != DD_STATUS_SUCCESS || fused) return st;
     }
     st = dd_reduce_impl(h, red, nullptr, 0, 1.0, xd, x, 0.0, yd, y, true, s->partial);
@@ -307,8 +380,7 @@ ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t
   ncclResult_t r = g_nccl.AllReduce(s->partial, s->partial, (size_t)nout, dbl ? DD_NCCL_FLOAT64 : DD_NCCL_FLOAT32,
                                     ncclOp, s->comm, h->stream);
   if (r != 0) DD_FAIL(h, DD_STATUS_COMM_FAILED, "ncclAllReduce: %s", g_nccl.GetErrorString(r));
-  // equal shards: the global count is nRanks times the local one
-  return dd_reduce_finish_impl(h, red, s->partial, (double)nredLocal * s->nRanks, a, b, xd, yd, y);
+  return dd_reduce_finish_impl(h, red, s->partial, count, a, b, xd, yd, y);
 }
 
 }  // extern "C"

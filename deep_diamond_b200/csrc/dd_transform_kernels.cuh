@@ -125,6 +125,9 @@ struct ddTileParams {
   int64_t bdims[DD_TILE_BATCH_DIMS], bsx[DD_TILE_BATCH_DIMS], bsy[DD_TILE_BATCH_DIMS];
   int64_t tilesA, tilesB;
   ddFastDiv fdA, fdB, fdBatch[DD_TILE_BATCH_DIMS];  // divisors tilesA, tilesB, bdims[] (tile count < 2^31)
+  uint32_t ntiles;   // all tiles; a CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+  int na, nbLog2;    // vector tile kernel: CTA of na x (1 << nbLog2) threads
+  ddFastDiv fdNA;
   double alpha;
 };
 
@@ -132,108 +135,121 @@ template <typename S, typename D>
 struct dd_tile_geom {
   static constexpr int VS = 16 / sizeof(S);  // elements per 16-byte load along A
   static constexpr int VD = 16 / sizeof(D);  // elements per 16-byte store along B
-  static constexpr int NA = 16;              // threads along A
-  static constexpr int NB = (VS >= 16) ? 8 : 16;  // threads along B (keeps the tile <= 32 KB)
-  static constexpr int TA = NA * VS;
-  static constexpr int TB = NB * VD;
-  static constexpr int NT = NA * NB;
-  static constexpr int SMEM = TA * NB * 16;
+  static constexpr int NA = 16;              // threads along A, at most
+  static constexpr int NB = (VS >= 16) ? 8 : 16;  // threads along B when NA > 8 (keeps the tile <= 32 KB)
+  static constexpr int NT = NA * NB;         // threads per CTA, at most
+  static constexpr int SMEM = NA * VS * NB * 16;
+  // resident CTAs per SM the bit-copy kernels are held to: 8 CTAs of 256 threads (32 registers per
+  // thread) for 4- and 8-byte elements; narrower elements keep more 16-byte loads in flight per
+  // thread (8 or 16) and take the registers that needs
+  static constexpr int MINB_RAW = VS <= 4 ? 8 : 0;
 };
 
+// The CTA is na x nb threads (ddTileParams): na <= 16 lanes along A, chosen on the host by the
+// padding the edge tiles would carry (784 bytes of int8 are 49 vectors: 4 tiles of 13 lanes, where
+// 16 lanes would leave the fourth tile 6 % full), and nb = NB lanes along B, 2 NB when na <= 8.
+// The tile is TA = na * VS elements along A by TB = nb * VD along B.  A CTA walks the tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ...: the grid is either one CTA per tile or, for the
+// converting kernels, one resident wave.
 template <typename S, typename D, typename C, bool RAW>
-__global__ void __launch_bounds__((dd_tile_geom<S, D>::NT)) dd_tile_kernel(ddTileParams p) {
+__global__ void __launch_bounds__((dd_tile_geom<S, D>::NT), (RAW ? dd_tile_geom<S, D>::MINB_RAW : 0)) dd_tile_kernel(ddTileParams p) {
   typedef dd_tile_geom<S, D> G;
-  constexpr int VS = G::VS, VD = G::VD, NA = G::NA, NB = G::NB, TA = G::TA, TB = G::TB;
-  __shared__ uint4 tile[TA * NB];
+  constexpr int VS = G::VS, VD = G::VD;
+  __shared__ uint4 tile[G::SMEM / 16];
   dd_pdl_prologue();
-
-  // tile id -> (batch index, tile along B, tile along A); A varies fastest
-  uint32_t id = blockIdx.x, ta, tb;
-  dd_divmod(id, p.fdA, id, ta);
-  dd_divmod(id, p.fdB, id, tb);
-  int64_t offx = 0, offy = 0;
-  for (int d = p.nb - 1; d >= 0; d--) {
-    uint32_t r;
-    dd_divmod(id, p.fdBatch[d], id, r);
-    offx += (int64_t)r * p.bsx[d];
-    offy += (int64_t)r * p.bsy[d];
-  }
-  const S *xb = (const S *)p.x + offx;
-  D *yb = (D *)p.y + offy;
-  const int64_t a0 = (int64_t)ta * TA, b0 = (int64_t)tb * TB;
+  const int NA = p.na, NB = 1 << p.nbLog2;
+  const int TA = NA * VS, TB = NB * VD;
+  const int t = threadIdx.x;
   const C alpha = (C)p.alpha;
 
-  const int t = threadIdx.x;
-  {  // load 16-byte vectors along A for VD consecutive rows of B, convert, transpose in registers
-    const int ma = t % NA, mb = t / NA;
-    const int64_t a = a0 + ma * VS;
-    // one 64-bit multiplication per thread: the rows follow at a fixed step, and what is left of
-    // the tensor below this thread's first row fits an int
-    const int64_t bFirst = b0 + mb * VD;
-    const int64_t left = p.LB - bFirst;
-    const int rows = a < p.LA ? (left < VD ? (left > 0 ? (int)left : 0) : VD) : 0;
-    const S *src = xb + bFirst * p.sxB + a;
-    uint4 in[VD];
-#pragma unroll
-    for (int j = 0; j < VD; j++) {
-      in[j] = j < rows ? *(const uint4 *)src : make_uint4(0, 0, 0, 0);
-      src += p.sxB;
+  for (uint32_t tileId = blockIdx.x; tileId < p.ntiles; tileId += gridDim.x) {
+    // tile id -> (batch index, tile along B, tile along A); A varies fastest
+    uint32_t id = tileId, ta, tb;
+    dd_divmod(id, p.fdA, id, ta);
+    dd_divmod(id, p.fdB, id, tb);
+    int64_t offx = 0, offy = 0;
+    for (int d = p.nb - 1; d >= 0; d--) {
+      uint32_t r;
+      dd_divmod(id, p.fdBatch[d], id, r);
+      offx += (int64_t)r * p.bsx[d];
+      offy += (int64_t)r * p.bsy[d];
     }
-    __align__(16) D reg[VS][VD];
-    if constexpr (RAW && sizeof(S) == 1 && sizeof(D) == 1) {
-      // 16 x 16 bytes as sixteen 4 x 4 byte blocks, each transposed with 8 byte permutes: word w of
-      // rows 4jj..4jj+3 becomes word jj of columns 4w..4w+3
-      uint4 *outv = (uint4 *)&reg[0][0];
-#pragma unroll
-      for (int w = 0; w < 4; w++) {
-        uint32_t c[4][4];
-#pragma unroll
-        for (int jj = 0; jj < 4; jj++) {
-          const uint32_t r0 = (&in[4 * jj + 0].x)[w], r1 = (&in[4 * jj + 1].x)[w];
-          const uint32_t r2 = (&in[4 * jj + 2].x)[w], r3 = (&in[4 * jj + 3].x)[w];
-          const uint32_t t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r0, r1, 0x7362);
-          const uint32_t t2 = __byte_perm(r2, r3, 0x5140), t3 = __byte_perm(r2, r3, 0x7362);
-          c[0][jj] = __byte_perm(t0, t2, 0x5410);
-          c[1][jj] = __byte_perm(t0, t2, 0x7632);
-          c[2][jj] = __byte_perm(t1, t3, 0x5410);
-          c[3][jj] = __byte_perm(t1, t3, 0x7632);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; k++) outv[4 * w + k] = make_uint4(c[k][0], c[k][1], c[k][2], c[k][3]);
-      }
-    } else {
+    const S *xb = (const S *)p.x + offx;
+    D *yb = (D *)p.y + offy;
+    const int64_t a0 = (int64_t)ta * TA, b0 = (int64_t)tb * TB;
+
+    {  // load 16-byte vectors along A for VD consecutive rows of B, convert, transpose in registers
+      uint32_t mbU, maU;
+      dd_divmod((uint32_t)t, p.fdNA, mbU, maU);
+      const int ma = (int)maU, mb = (int)mbU;  // lanes run along A first
+      const int64_t a = a0 + ma * VS;
+      // one 64-bit multiplication per thread: the rows follow at a fixed step, and what is left of
+      // the tensor below this thread's first row fits an int
+      const int64_t bFirst = b0 + mb * VD;
+      const int64_t left = p.LB - bFirst;
+      const int rows = a < p.LA ? (left < VD ? (left > 0 ? (int)left : 0) : VD) : 0;
+      const S *src = xb + bFirst * p.sxB + a;
+      uint4 in[VD];
 #pragma unroll
       for (int j = 0; j < VD; j++) {
-        const S *sv = (const S *)&in[j];
+        in[j] = j < rows ? *(const uint4 *)src : make_uint4(0, 0, 0, 0);
+        src += p.sxB;
+      }
+      __align__(16) D reg[VS][VD];
+      if constexpr (RAW && sizeof(S) == 1 && sizeof(D) == 1) {
+        // 16 x 16 bytes as sixteen 4 x 4 byte blocks, each transposed with 8 byte permutes: word w of
+        // rows 4jj..4jj+3 becomes word jj of columns 4w..4w+3
+        uint4 *outv = (uint4 *)&reg[0][0];
 #pragma unroll
-        for (int i = 0; i < VS; i++) reg[i][j] = dd_cvt<S, D, C, RAW>::f(sv[i], alpha);
+        for (int w = 0; w < 4; w++) {
+          uint32_t c[4][4];
+#pragma unroll
+          for (int jj = 0; jj < 4; jj++) {
+            const uint32_t r0 = (&in[4 * jj + 0].x)[w], r1 = (&in[4 * jj + 1].x)[w];
+            const uint32_t r2 = (&in[4 * jj + 2].x)[w], r3 = (&in[4 * jj + 3].x)[w];
+            const uint32_t t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r0, r1, 0x7362);
+            const uint32_t t2 = __byte_perm(r2, r3, 0x5140), t3 = __byte_perm(r2, r3, 0x7362);
+            c[0][jj] = __byte_perm(t0, t2, 0x5410);
+            c[1][jj] = __byte_perm(t0, t2, 0x7632);
+            c[2][jj] = __byte_perm(t1, t3, 0x5410);
+            c[3][jj] = __byte_perm(t1, t3, 0x7632);
+          }
+#pragma unroll
+          for (int k = 0; k < 4; k++) outv[4 * w + k] = make_uint4(c[k][0], c[k][1], c[k][2], c[k][3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VD; j++) {
+          const S *sv = (const S *)&in[j];
+#pragma unroll
+          for (int i = 0; i < VS; i++) reg[i][j] = dd_cvt<S, D, C, RAW>::f(sv[i], alpha);
+        }
+      }
+      // row = index along A inside the tile; 16-byte chunk index along B swizzled by the row's
+      // micro-block number so that the 8 lanes of a quarter warp hit 8 different bank groups
+      uint4 *dstRow = tile + (((ma * VS) << p.nbLog2) + (mb ^ (ma & 7)));
+#pragma unroll
+      for (int i = 0; i < VS; i++) dstRow[i << p.nbLog2] = *(const uint4 *)reg[i];
+    }
+    __syncthreads();
+    {  // write rows of the tile: NB consecutive lanes cover one contiguous run along B
+      const int rb = t & (NB - 1), ra = t >> p.nbLog2;  // lanes run along B first
+      const int64_t b = b0 + rb * VD;
+      const int64_t leftA = p.LA - a0;
+      const int rowsA = b < p.LB ? (leftA < TA ? (int)leftA : TA) : 0;  // rows of this tile inside the tensor
+      D *dst = yb + (a0 + ra) * p.syA + b;
+      const int64_t step = (int64_t)NA * p.syA;
+#pragma unroll
+      for (int k = 0; k < VS; k++) {
+        const int row = ra + k * NA;
+        if (row < rowsA) {
+          uint4 v = tile[(row << p.nbLog2) + (rb ^ ((row / VS) & 7))];
+          *(uint4 *)dst = v;
+        }
+        dst += step;
       }
     }
-    // row = index along A inside the tile; 16-byte chunk index along B swizzled by the row's
-    // micro-block number so that the 8 lanes of a quarter warp hit 8 different bank groups
-#pragma unroll
-    for (int i = 0; i < VS; i++) {
-      const int row = ma * VS + i;
-      tile[row * NB + (mb ^ (ma & 7))] = *(const uint4 *)reg[i];
-    }
-  }
-  __syncthreads();
-  {  // write rows of the tile: NB consecutive lanes cover one contiguous run along B
-    const int rb = t % NB, ra = t / NB;
-    const int64_t b = b0 + rb * VD;
-    const int64_t leftA = p.LA - a0;
-    const int rowsA = b < p.LB ? (leftA < TA ? (int)leftA : TA) : 0;  // rows of this tile inside the tensor
-    D *dst = yb + (a0 + ra) * p.syA + b;
-    const int64_t step = (int64_t)NA * p.syA;
-#pragma unroll
-    for (int k = 0; k < VS; k++) {
-      const int row = ra + k * NA;
-      if (row < rowsA) {
-        uint4 v = tile[row * NB + (rb ^ ((row / VS) & 7))];
-        *(uint4 *)dst = v;
-      }
-      dst += step;
-    }
+    if (tileId + gridDim.x < p.ntiles) __syncthreads();  // the next tile reuses the shared-memory stage
   }
 }
 
@@ -450,8 +466,36 @@ static int dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
   }
   // a tile that is mostly padding wastes the machine: leave short dims to the other kernels
   if (c.dims[A] < G::VS * 2 || c.dims[B] < G::VD * 2) vec = false;
-  const int TAe = vec ? G::TA : 32, TBe = vec ? G::TB : 32;
   if (!vec && (c.dims[A] < 8 || c.dims[B] < 8)) return 0;  // too thin to be worth a tile
+  // CTA shape of the vector kernel: na lanes along A (5..16) by nb lanes along B (NB, or 2 NB when
+  // na <= 8), chosen by the padding the edge tiles would carry
+  int na = G::NA, nbLog2 = 0;
+  while ((1 << nbLog2) < G::NB) nbLog2++;
+  if (vec) {
+    const int64_t vecsA = c.dims[A] / G::VS, vecsB = c.dims[B] / G::VD;
+    const int naLo = dd_tune("DD_TILE_NA_LO", vecsA < 5 ? (int)vecsA : 5), naHi = dd_tune("DD_TILE_NA_HI", G::NA);
+    auto eff = [&](int cand) {
+      const int nbc = cand <= 8 ? 2 * G::NB : G::NB;
+      const double effA = (double)vecsA / (double)(((vecsA + cand - 1) / cand) * cand);
+      const double effB = (double)vecsB / (double)(((vecsB + nbc - 1) / nbc) * nbc);
+      return effA * effB;
+    };
+    double best = -1.0;
+    for (int cand = naHi; cand >= naLo; cand--) best = eff(cand) > best ? eff(cand) : best;
+    // the widest CTA within a tenth of the best: longer contiguous runs along A measured faster
+    // than the last few per cent of padding (49 vectors: 13 lanes beat 7 and 10; 196: 16 beat 14)
+    for (int cand = naHi; cand >= naLo; cand--)
+      if (eff(cand) >= best - 0.1) {
+        na = cand;
+        break;
+      }
+    nbLog2 = 0;
+    while ((1 << nbLog2) < (na <= 8 ? 2 * G::NB : G::NB)) nbLog2++;
+  }
+  const int TAe = vec ? na * G::VS : 32, TBe = vec ? (1 << nbLog2) * G::VD : 32;
+  tp->na = na;
+  tp->nbLog2 = nbLog2;
+  tp->fdNA = dd_fastdiv((uint32_t)na);
   tp->x = pl.x;
   tp->y = pl.y;
   tp->LA = c.dims[A];
@@ -485,7 +529,15 @@ static ddStatus_t dd_launch_tile(ddHandle_t h, const ddTileParams &tp, int kind)
   for (int i = 0; i < tp.nb; i++) tiles *= tp.bdims[i];
   if (tiles > 0x7fffffffLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "transform/tile: too many tiles");
   if (kind == 1) {
-    dd_launch_pdl(dd_tile_kernel<S, D, C, RAW>, (unsigned)tiles, (unsigned)G::NT, h->stream, tp);
+    ddTileParams tq = tp;
+    tq.ntiles = (uint32_t)tiles;
+    // Converting kernels (48 registers, 5 resident CTAs of 256 threads per SM) run as one resident
+    // wave whose CTAs walk the tiles: measured 6 % faster on f32 -> bf16 than a CTA per tile.  The
+    // bit-copy kernels measured the same or slower that way and keep a CTA per tile.
+    const int cps = dd_tune("DD_TILE_CPS", RAW ? 0 : 5);
+    int64_t grid = tiles;
+    if (cps > 0 && grid > (int64_t)h->smCount * cps) grid = (int64_t)h->smCount * cps;
+    dd_launch_pdl(dd_tile_kernel<S, D, C, RAW>, (unsigned)grid, (unsigned)(tq.na << tq.nbLog2), h->stream, tq);
     DD_LAUNCHED(h, "transform/tile");
   } else {
     dd_tile_scalar_kernel<S, D, C, RAW><<<(unsigned)tiles, 256, 0, h->stream>>>(tp);

@@ -141,6 +141,15 @@ DD_API ddStatus_t ddGetLaunchCount(ddHandle_t handle, uint64_t *count);
 /* Name of the kernel family chosen by the most recent compute call ("flat", "tile", "strided",
  * "rowreduce", ...): lets tests assert that the intended fast path ran. */
 DD_API const char *ddGetLastKernelName(ddHandle_t handle);
+/* No counterpart in the reference.  Split reductions and ddCostDiff count CTA arrivals in the first
+ * 64 KB of the handle's scratch; every launch leaves those counters at zero when it completes.  A
+ * launch that did NOT complete (a call that returned DD_STATUS_EXECUTION_FAILED, or a later CUDA
+ * error that names one of this library's kernels) may leave some of them non-zero, and the next
+ * split reduction through the same handle would then never see its last arrival and write no
+ * result.  After such a failure either destroy the handle and create a new one, or call
+ * ddResetCounters: it zeroes the counters on the handle's stream (ordered after everything already
+ * enqueued there).  Nothing else in a handle depends on an earlier launch. */
+DD_API ddStatus_t ddResetCounters(ddHandle_t handle);
 
 /* --------------------------------------------------------------- descriptors ---------------- */
 
@@ -345,18 +354,43 @@ DD_API ddStatus_t ddReduceTensorNoAlloc(void *stream, ddReduceTensorOp_t op, ddN
  * (libnccl.so.2); nothing else in this header needs it.
  *
  * ddShardedGetUniqueId fills a 128-byte id on one rank; the caller ships it to the other ranks by
- * any means; every rank then calls ddShardedCreate (collective, blocks until all ranks join or the
- * library's own init timeout fires). */
+ * any means; every rank then calls ddShardedCreate.  The call is collective and returns when all
+ * ranks have joined.  The join is bounded: if it has not completed after the join limit (120 s
+ * unless ddShardedSetJoinLimit changed it) the call returns DD_STATUS_TIMEOUT; the communicator is
+ * then unusable and the process should exit (the library cannot cancel NCCL's own rendezvous, the
+ * thread that runs it is left behind).  Host code that has a transport of its own should first check
+ * over it that every rank has arrived (deep_diamond_b200/sharded.py does, with its own limit), so
+ * that this limit is the second line only. */
 #define DD_UNIQUE_ID_BYTES 128
 DD_API ddStatus_t ddShardedGetUniqueId(void *id128);
+DD_API ddStatus_t ddShardedSetJoinLimit(double seconds);
 DD_API ddStatus_t ddShardedCreate(ddShardedHandle_t *sharded, ddHandle_t handle, int nRanks, int rank,
                            const void *id128);
+/* Tear-down is COLLECTIVE when the peer exchange is attached, in three steps:
+ *   1. every rank calls ddShardedPeerDetach: it waits for this rank's own work (stream
+ *      synchronise) and closes this rank's mappings of the other ranks' buffers, so that this rank
+ *      can no longer store into them;
+ *   2. all ranks meet at a barrier of the caller's (any host transport);
+ *   3. every rank calls ddShardedDestroy, which frees the buffer this rank exported.
+ * Freeing an exported buffer while another process still has it mapped is undefined, and a late
+ * store into it can fault that process's GPU: do not skip the barrier.  If a bounded wait ran out
+ * (ddShardedPeerStatus reported DD_STATUS_TIMEOUT) a peer may still be running a kernel that
+ * stores into this rank's buffer; ddShardedDestroy then does NOT free the exchange buffer (it stays
+ * allocated until the process exits).  Without an attached exchange ddShardedDestroy alone is
+ * enough. */
+DD_API ddStatus_t ddShardedPeerDetach(ddShardedHandle_t sharded);
 DD_API ddStatus_t ddShardedDestroy(ddShardedHandle_t sharded);
 /* xDesc describes the LOCAL shard; yDesc the (replicated) result.  `spansShardedDim` != 0 says the
  * sharded dim is among the reduced ones, so partial results are combined across ranks; with 0 the
- * call is ddReduceTensor on the local shard.  AVG divides by the GLOBAL element count. */
+ * call is ddReduceTensor on the local shard.  AVG divides by `globalCount`, the number of elements
+ * folded into one output over ALL ranks (for a batch of N images sharded unevenly: N * H * W for a
+ * reduction over (N,H,W), whatever this rank's share of N is).  globalCount == 0 means equal
+ * shards: nRanks times this rank's own count.  A globalCount smaller than the local count is
+ * refused with DD_STATUS_BAD_PARAM.  The other ops do not use it.  A rank whose shard is empty
+ * cannot describe it (extents are positive): it must sit the call out, which the peer exchange and
+ * NCCL do not allow, so every rank needs at least one batch entry. */
 DD_API ddStatus_t ddShardedReduceTensor(ddShardedHandle_t sharded, ddReduceTensorDescriptor_t red,
-                                 int spansShardedDim, const void *alpha,
+                                 int spansShardedDim, int64_t globalCount, const void *alpha,
                                  ddTensorDescriptor_t xDesc, const void *x, const void *beta,
                                  ddTensorDescriptor_t yDesc, void *y);
 /* Peer exchange: the combine step as ONE kernel per rank over NVLink instead of the NCCL call
@@ -366,12 +400,15 @@ DD_API ddStatus_t ddShardedReduceTensor(ddShardedHandle_t sharded, ddReduceTenso
  * ddShardedPeerAttach with the nRanks * DD_PEER_HANDLE_BYTES bytes; from then on
  * ddShardedReduceTensor uses the exchange.  Up to 8 ranks.  ddShardedCreate accepts a NULL id for
  * a handle that only ever uses the peer exchange (no NCCL needed).
- * The exchange is a small kernel of its own after the local pass.  A fused form exists as well
- * (few outputs, <= 4096: the reduce kernel pushes each result the moment it is final and its last
- * CTA collects and finishes, ONE kernel for reduce + exchange); it measured about 2 us slower per
- * call than the two-kernel form on a 4 KB result, so it is opt-in.
- * ddShardedPeerConfigure: usePeer 0 = NCCL, 1 = the exchange kernel, 2 = the fused form where the
- * plan allows, -1 = leave as is; and
+ * Two forms.  FUSED: the reduce kernel itself pushes each result to the other ranks the moment it is
+ * final, ONE kernel for reduce + exchange.  Where the whole grid of a row reduction is resident at
+ * once, the thread that finished an output then also waits (bounded) for the other ranks' values of
+ * that output and writes y, so all outputs are collected in parallel; otherwise (<= 4096 outputs)
+ * the CTA that finishes last collects them one after the other.  SEPARATE: a small exchange kernel
+ * after the local pass.
+ * ddShardedPeerConfigure: usePeer 0 = NCCL; 1 = the peer exchange in the form the library prefers
+ * (fused when each output is collected where it was finished, else separate; the default);
+ * 2 = fused wherever the plan allows; 3 = always separate; -1 = leave as is; and
  * waitSeconds > 0 sets the limit of the kernel's bounded waits (default 2 s).
  * ddShardedPeerStatus synchronises the handle's stream and reports whether a wait ran out
  * (*status = 1 + the rank waited for, return DD_STATUS_TIMEOUT); the kernel that gave up wrote no

@@ -149,12 +149,60 @@ def main():
     if not np.array_equal(y.cpu().numpy().reshape(yshape), want):
         failures.append(("max over C (local)",))
 
+    # uneven shards: 4 * world + 1 images, rank 0 owns one more; the mean divides by the global count
+    # that the caller passes.  Both combine paths.
+    ushape = [4 * world + 1, 64, 16, 16]
+    ufull = oracle.gen_signed_lognormal(ushape, 11)
+    ulo, uhi = sharded.shard_range(ushape[0], world, rank, even=False)
+    ux = torch.from_numpy(np.ascontiguousarray(ufull[ulo:uhi])).to(fact.device)
+    uxd = core.tensor_descriptor([uhi - ulo] + ushape[1:], "float", "nchw")
+    for path in ("peer", "nccl"):
+        sh.peer_configure(use_peer=(path == "peer"))
+        for op in ("avg", "add", "norm2"):
+            want = np.zeros([1, 64, 1, 1], np.float32)
+            oracle.reduce(op, ufull, want)
+            y = torch.zeros(64, device=fact.device)
+            sh.reduce_tensor(core.reduce_tensor_descriptor(op, "float"), 1.0, uxd, ux, 0.0,
+                             core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y, global_batch=ushape[0])
+            fact.synchronize()
+            if not within(y.cpu().numpy().reshape(want.shape), want, ufull, 1.0, (0, 2, 3)):
+                failures.append(("uneven shards", path, op))
+    sh.peer_configure(use_peer=True)
+    # a global count below the local one is refused
+    import ctypes
+    from deep_diamond_b200._lib import DiamondError, check, lib
+    one, zero = core._scalar(1.0, 0), core._scalar(0.0, 0)
+    try:
+        check(lib.ddShardedReduceTensor(sh.ptr, core.reduce_tensor_descriptor("avg", "float").ptr, 1, 3,
+                                        ctypes.byref(one), uxd.ptr, core._ptr(ux), ctypes.byref(zero),
+                                        core.tensor_descriptor([1, 64, 1, 1], "float", "nchw").ptr, core._ptr(y)),
+              fact.handle.ptr, "ddShardedReduceTensor")
+        failures.append(("global count below the local one was accepted",))
+    except DiamondError as e:
+        if e.data.get("type") != "bad-param":
+            failures.append(("unexpected error for a bad global count", str(e)))
+
+    # a small shard: 32 or fewer reduced elements per rank still takes the structured (row) form
+    sshape = [2 * world, 64, 2, 2]
+    sfull = oracle.gen_signed_lognormal(sshape, 13)
+    slo, shi = sharded.shard_range(sshape[0], world, rank)
+    sx = torch.from_numpy(np.ascontiguousarray(sfull[slo:shi])).to(fact.device)
+    want = np.zeros([1, 64, 1, 1], np.float32)
+    oracle.reduce("add", sfull, want)
+    y = torch.zeros(64, device=fact.device)
+    sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0,
+                     core.tensor_descriptor([shi - slo] + sshape[1:], "float", "nchw"), sx, 0.0,
+                     core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y)
+    fact.synchronize()
+    if not within(y.cpu().numpy().reshape(want.shape), want, sfull, 1.0, (0, 2, 3)):
+        failures.append(("small shard",))
+
     if sh.peer_status() != 0:
         failures.append(("peer status",))
     flag = torch.tensor([len(failures)], device=fact.device)
     dist.all_reduce(flag)
-    dist.barrier()
-    sh.release()
+    # collective tear-down: detach, host barrier, destroy
+    sh.release(barrier=dist.barrier)
     fact.release()
     dist.destroy_process_group()
     if failures:

@@ -148,3 +148,112 @@ def test_sharded_reduce_logic_world_size_2_gloo(tmp_path):
     procs = [subprocess.Popen([sys.executable, str(script), ROOT, str(port), str(r)]) for r in range(2)]
     codes = [p.wait(timeout=180) for p in procs]
     assert codes == [0, 0]
+
+
+def test_uneven_shards_and_global_count():
+    from deep_diamond_b200 import sharded
+    from deep_diamond_b200._lib import DiamondError
+    # 10 images over 4 ranks: the first two ranks own one more
+    assert [sharded.shard_range(10, 4, r, even=False) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    with pytest.raises(DiamondError):
+        sharded.shard_range(3, 4, 0, even=False)          # a rank would be left without a batch entry
+    # elements folded into one output over all ranks, whatever this rank's share of the batch is
+    assert sharded.global_reduced_count([3, 64, 16, 16], [1, 64, 1, 1], 10) == 10 * 16 * 16
+    assert sharded.global_reduced_count([2, 64, 16, 16], [1, 64, 1, 1], 10) == 10 * 16 * 16
+    assert sharded.global_reduced_count([3, 64, 16, 16], [1, 1, 1, 1], 10) == 10 * 64 * 16 * 16
+    # the mean over unevenly sharded data: combine the partial sums, divide by the GLOBAL count
+    rng = np.random.default_rng(3)
+    full = rng.standard_normal((10, 6, 5, 4))
+    parts = []
+    for r in range(4):
+        lo, hi = sharded.shard_range(10, 4, r, even=False)
+        parts.append(full[lo:hi].sum(axis=(0, 2, 3)))
+    got = np.stack(parts).sum(axis=0) / sharded.global_reduced_count([3, 6, 5, 4], [1, 6, 1, 1], 10)
+    assert np.allclose(got, full.mean(axis=(0, 2, 3)))
+
+
+_TEARDOWN_WORKER = r'''
+import datetime, os, sys, time
+import torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from deep_diamond_b200 import sharded
+from deep_diamond_b200._lib import DiamondError
+
+rank, world, mode = int(sys.argv[3]), 2, sys.argv[4]
+store = dist.TCPStore("127.0.0.1", int(sys.argv[2]), world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=60))
+if mode == "teardown":
+    # The order of the collective tear-down, with stand-ins for the library calls (no GPU here): a rank
+    # may free the buffer it exported only after EVERY rank has closed its mappings.  Rank 1 is slow
+    # to detach; rank 0 must still find both detached when it frees.
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=world)
+    log = []
+
+    def detach():
+        if rank == 1:
+            time.sleep(1.0)
+        store.add("detached", 1)
+        log.append("detach")
+
+    def destroy():
+        log.append("destroy with %d detached" % store.add("detached", 0))
+    sharded.collective_release(detach, dist.barrier, destroy)
+    ok = log == ["detach", "destroy with 2 detached"]
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+else:
+    # The bounded join: rank 1 never announces itself; rank 0 gives up after its limit and says who
+    # is missing.  No communicator is created, nothing touches a GPU.
+    if rank == 1:
+        time.sleep(3.0)          # arrives after rank 0 has given up, and never joins
+        sys.exit(0)
+    t0 = time.time()
+    try:
+        sharded.join_with_limit(store, rank, world, 1.0)
+        sys.exit(1)
+    except DiamondError as e:
+        took = time.time() - t0
+        ok = e.data.get("type") == "timeout" and e.data.get("missing-ranks") == [1] and took < 2.5
+        sys.exit(0 if ok else 1)
+'''
+
+
+@pytest.mark.parametrize("mode", ["teardown", "join"])
+def test_collective_teardown_order_and_bounded_join_gloo(tmp_path, mode):
+    """World size 2 on CPU.  `teardown`: detach -> host barrier -> destroy, so that no rank frees the
+    buffer it exported while another still has it mapped.  `join`: a rank that never joins makes the
+    others fail with a timeout after the limit instead of blocking in the communicator set-up."""
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    script = tmp_path / "worker.py"
+    script.write_text(_TEARDOWN_WORKER)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, str(port), str(r), mode]) for r in range(2)]
+    codes = [p.wait(timeout=180) for p in procs]
+    assert codes == [0, 0]
+
+
+def test_release_of_an_attached_handle_needs_the_barrier():
+    """`ShardedHandle.release` refuses to free an attached exchange without the ranks' barrier."""
+    from deep_diamond_b200 import sharded
+    from deep_diamond_b200._lib import DiamondError
+
+    class Fake(sharded.ShardedHandle):
+        def __init__(self):                       # no library call: only the release logic is under test
+            self.ptr, self.peer_attached, self.world_size, self.calls = object(), True, 2, []
+
+        def detach(self):
+            self.calls.append("detach")
+            self.peer_attached = False
+
+        def destroy(self):
+            self.calls.append("destroy")
+            self.ptr = None
+    h = Fake()
+    with pytest.raises(DiamondError):
+        h.release()
+    assert h.calls == []
+    h.release(barrier=lambda: h.calls.append("barrier"))
+    assert h.calls == ["detach", "barrier", "destroy"]

@@ -61,14 +61,19 @@ def test_matches_the_handle_entry_point_on_consecutive_calls(fact, dev):
 
 
 def test_refuses_what_does_not_fit(fact, dev):
-    shape, yshape = [256, 20000], [1, 20000]
-    xd = core.tensor_descriptor(shape, "float", [20000, 1])
-    yd = core.tensor_descriptor(yshape, "float", [20000, 1])
+    # a reduction whose plan needs more scratch than the built-in array holds (few tiles of outputs,
+    # a long reduced range: many splits per output)
     rtd = core.reduce_tensor_descriptor("add", "float")
-    need = core.reduction_workspace_size(fact.handle, rtd, xd, yd)
+    need = 0
+    for rows, cols in ((8192, 2048), (256, 20000), (65536, 1024), (32768, 4096)):
+        xd = core.tensor_descriptor([rows, cols], "float", [cols, 1])
+        yd = core.tensor_descriptor([1, cols], "float", [cols, 1])
+        need = core.reduction_workspace_size(fact.handle, rtd, xd, yd)
+        if need > (64 << 10):
+            break
     assert need > (64 << 10)
-    tx = dev.empty(256 * 20000 * 4, fill=0)
-    ty = dev.empty(20000 * 4, fill=0)
+    tx = dev.empty(rows * cols * 4, fill=0)
+    ty = dev.empty(cols * 4, fill=0)
     st, msg = no_alloc_reduce(fact, "add", xd, tx, yd, ty)
     assert st == 9 and "scratch" in msg and str(need) in msg     # DD_STATUS_NOT_SUPPORTED
     st, msg = no_alloc_reduce(fact, "add", xd, None, yd, ty)
@@ -84,3 +89,28 @@ def test_unsplit_reductions_and_other_types(fact, dev, oracle):
     st, msg = no_alloc_reduce(fact, "max", xd, dev.put(x), yd, ty)
     assert st == 0, msg
     assert dev.get(ty, np.float32).tolist() == [79.0, 99.0, 119.0]
+
+
+def test_device_memory_does_not_move(fact, dev):
+    """Free device memory is the same before and after the calls: nothing is allocated or freed on
+    the way.  (One warm-up call per plan first: the CUDA runtime loads a kernel's code, and with it
+    the library's built-in array, the first time that kernel is used.)"""
+    import torch
+    rng = np.random.default_rng(41)
+    prepared = []
+    for op, shape, yshape in CASES:
+        x = rng.standard_normal(int(np.prod(shape))).astype(np.float32)
+        xd = core.tensor_descriptor(shape, "float", "nchw")
+        yd = core.tensor_descriptor(yshape, "float", "nchw")
+        tx, ty = dev.put(x), dev.put(np.zeros(int(np.prod(yshape)), np.float32))
+        st, msg = no_alloc_reduce(fact, op, xd, tx, yd, ty)
+        assert st == 0, msg
+        prepared.append((op, xd, tx, yd, ty))
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(2):
+        for op, xd, tx, yd, ty in prepared:
+            st, msg = no_alloc_reduce(fact, op, xd, tx, yd, ty)
+            assert st == 0, msg
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
