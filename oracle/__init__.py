@@ -28,7 +28,9 @@ CODES = {"f32": F32, "float": F32, "f64": F64, "double": F64, "f16": F16, "half"
 NP_OF = {F32: np.float32, F64: np.float64, F16: np.float16, S8: np.int8, S32: np.int32,
          U8: np.uint8, BF16: np.uint16, S64: np.int64}
 ACT = {"sigmoid": 0, "logistic": 0, "relu": 1, "tanh": 2, "clipped-relu": 3, "elu": 4,
-       "linear": 5, "identity": 5, "abs": 6}
+       "linear": 5, "identity": 5, "abs": 6,
+       # elu as oneDNN's fp32 kernels form it, alpha * (float(exp(x)) - 1): forward only, oracle only
+       "elu-fp32-exp-minus-1": 7}
 BINOP = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5}
 REDOP = {"add": 0, "sum": 0, "mul": 1, "min": 2, "max": 3, "amax": 4, "avg": 5, "mean": 5,
          "norm1": 6, "norm2": 7, "mul-no-zeros": 8}
@@ -270,3 +272,16 @@ def gen_signed_lognormal(shape, seed):
 def quantize_s8(x):
     """The int8 copy of the reorder configuration: scale 1/127, round-to-nearest-even, saturate."""
     return np.clip(np.rint(x * np.float32(127.0)), -128, 127).astype(np.int8)
+
+
+def ulp_diff_f32(a, b):
+    """Distance in units of float32 last place between two float32 arrays (NaN == NaN -> 0)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    ia = a.view(np.int32).astype(np.int64)
+    ib = b.view(np.int32).astype(np.int64)
+    ia = np.where(ia < 0, np.int64(-(2 ** 31)) - ia, ia)  # monotone mapping of the float order
+    ib = np.where(ib < 0, np.int64(-(2 ** 31)) - ib, ib)
+    d = np.abs(ia - ib)
+    both_nan = np.isnan(a) & np.isnan(b)
+    return np.where(both_nan, 0, d)

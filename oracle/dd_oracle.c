@@ -284,7 +284,11 @@ int oracle_reorder(int nd, const int64_t *dims, int st, const int64_t *sst, cons
 
 /* ------------------------------------------------------------ eltwise ------------------------ */
 
-enum { A_SIGMOID = 0, A_RELU = 1, A_TANH = 2, A_CLIP = 3, A_ELU = 4, A_LINEAR = 5, A_ABS = 6 };
+/* A_ELU_FP32: elu as oneDNN's fp32 kernels form it, alpha * (exp(x) - 1) with exp(x) rounded to
+ * float BEFORE the subtraction (what dnnl/constants.clj:277-308 `:elu` binds).  Near zero the
+ * subtraction cancels: the result keeps only the bits of exp(x) above 1.  Oracle-only: it exists so
+ * that the tests can state how far the library's elu (alpha * expm1(x), no cancellation) sits from it. */
+enum { A_SIGMOID = 0, A_RELU = 1, A_TANH = 2, A_CLIP = 3, A_ELU = 4, A_LINEAR = 5, A_ABS = 6, A_ELU_FP32 = 7 };
 
 static float act_fwd_f(int alg, float x, float a, float b, int nanprop) {
   switch (alg) {
@@ -298,6 +302,7 @@ static float act_fwd_f(int alg, float x, float a, float b, int nanprop) {
     case A_SIGMOID: { double e = exp(-fabs((double)x)); double r = 1.0 / (1.0 + e); return (float)(x >= 0.f ? r : e * r); }
     case A_TANH: return (float)tanh((double)x);
     case A_ELU: return x > 0.f ? x : a * (float)expm1((double)x);
+    case A_ELU_FP32: return x > 0.f ? x : a * ((float)exp((double)x) - 1.f);
     case A_LINEAR: return fmaf(a, x, b);
     case A_CLIP:
       if (nanprop && x != x) return x;
@@ -318,6 +323,7 @@ static double act_fwd_d(int alg, double x, double a, double b, int nanprop) {
     case A_SIGMOID: return 1.0 / (1.0 + exp(-x));
     case A_TANH: return tanh(x);
     case A_ELU: return x > 0.0 ? x : a * expm1(x);
+    case A_ELU_FP32: return x > 0.0 ? x : a * (exp(x) - 1.0);
     case A_LINEAR: return fma(a, x, b);
     case A_CLIP:
       if (nanprop && x != x) return x;
@@ -381,6 +387,24 @@ int oracle_eltwise_fwd(int alg, double coef, double shift, int nanprop, int t, i
                        void *y, double alpha, double beta) {
   const int64_t n = total_of(nd, dims);
   const int dense = is_default(nd, dims, xst) && is_default(nd, dims, yst);
+  if (dense && t == T_F32 && alpha == 1.0 && beta == 0.0) {
+    /* the common case (dense fp32, no blend) without the per-element type and layout dispatch; the
+     * arithmetic is act_fwd_f's, so the results are the same bits */
+    const float *xf = (const float *)x;
+    float *yf = (float *)y;
+    const float a = (float)coef, b = (float)shift;
+    if (alg == A_RELU && a == 0.f) {
+#pragma omp parallel for simd schedule(static)
+      for (int64_t i = 0; i < n; i++) {
+        const float v = xf[i];
+        yf[i] = (nanprop && v != v) ? v : fmaxf(v, 0.f);
+      }
+      return 0;
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) yf[i] = act_fwd_f(alg, xf[i], a, b, nanprop);
+    return 0;
+  }
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; i++) {
     int64_t xo = dense ? i : offset_of(nd, dims, xst, i), yo = dense ? i : offset_of(nd, dims, yst, i);
@@ -400,6 +424,19 @@ int oracle_eltwise_bwd(int alg, double coef, int t, int nd, const int64_t *dims,
                        void *dx, double alpha, double beta) {
   const int64_t n = total_of(nd, dims);
   const int dense = is_default(nd, dims, xst) && is_default(nd, dims, dyst) && is_default(nd, dims, dxst);
+  if (dense && t == T_F32 && alpha == 1.0 && beta == 0.0) {
+    const float *xf = (const float *)x, *gf = (const float *)dy;
+    float *of = (float *)dx;
+    const float a = (float)coef;
+    if (alg == A_RELU) {
+#pragma omp parallel for simd schedule(static)
+      for (int64_t i = 0; i < n; i++) of[i] = xf[i] > 0.f ? gf[i] : a * gf[i];
+      return 0;
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) of[i] = act_bwd_f(alg, xf[i], gf[i], a);
+    return 0;
+  }
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; i++) {
     int64_t xo = dense ? i : offset_of(nd, dims, xst, i), go = dense ? i : offset_of(nd, dims, dyst, i),

@@ -68,13 +68,6 @@ def dev(fact):
 
 
 def ulp_diff_f32(a, b):
-    """Distance in units of float32 last place between two float32 arrays (NaN == NaN -> 0)."""
-    a = np.ascontiguousarray(a, dtype=np.float32)
-    b = np.ascontiguousarray(b, dtype=np.float32)
-    ia = a.view(np.int32).astype(np.int64)
-    ib = b.view(np.int32).astype(np.int64)
-    ia = np.where(ia < 0, np.int64(-(2 ** 31)) - ia, ia)  # monotone mapping of the float order
-    ib = np.where(ib < 0, np.int64(-(2 ** 31)) - ib, ib)
-    d = np.abs(ia - ib)
-    both_nan = np.isnan(a) & np.isnan(b)
-    return np.where(both_nan, 0, d)
+    """Distance in units of float32 last place (the oracle package's helper, re-exported for the tests)."""
+    import oracle as _oracle
+    return _oracle.ulp_diff_f32(a, b)
