@@ -48,9 +48,9 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE activation-backward launch on the bench's
 # [256,256,28,28] tensors, from the ncu capture named here (refresh it when dd_elt_flat_kernel changes)
-TRAFFIC_BWD = {"bytes": 584.8e6, "profile": "profiles/eltwise_flat_kernel_ncu_full.md",
-               "captured_at_commit": "aa0ee71", "captured_on": "2026-11-25",
-               "note": "reads 411.1 MB = the algorithmic input; writes 173.8 MB (the tail of dx is still in L2 when the "
+TRAFFIC_BWD = {"bytes": 581.1e6, "profile": "profiles/eltwise_backward_dram_traffic.md",
+               "captured_at_commit": "a6bdb21", "captured_on": "2026-11-25",
+               "note": "reads 411.1 MB = the algorithmic input; writes 170.0 MB (the tail of dx is still in L2 when the "
                        "kernel ends) against 616.6 MB algorithmic"}
 PASSES_PER_STEP = 36          # 36 passes x 0.71 ms: 20 steps last about half a second
 STEP_BYTES_PER_PASS = 4 * (2 + 3) * len(ACTS) * 256 * 256 * 28 * 28
@@ -548,14 +548,21 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_on
         xf = torch.randn(n, dtype=torch.float32, device=dev, generator=g)
         for tag, tdt, es in (("float", torch.float32, 4), ("bf16", torch.bfloat16, 2), ("half", torch.float16, 2)):
             xt = xf if tdt == torch.float32 else xf.to(tdt)
+            sets = rotation(n * es)        # the 16-bit tensors (103 MB) would otherwise sit in L2
+            xts = [xt] + [xt.clone() for _ in range(sets - 1)]
             xd = core.tensor_descriptor(shp, tag, "nchw")
             for op, yshape, label in (("add", [1, 256, 1, 1], "sum over (N,H,W)"), ("max", [256, 1, 28, 28], "max over C")):
                 yd = core.tensor_descriptor(yshape, tag, "nchw")
                 yb = dbuf(int(np.prod(yshape)) * es)
                 rtd = core.reduce_tensor_descriptor(op, "float")
-                measure("reduce " + label + ", " + tag, "[256,256,28,28] %s" % tag, n * es + int(np.prod(yshape)) * es, n,
-                        lambda rtd=rtd, xd=xd, xt=xt, yd=yd, yb=yb: core.reduce_tensor(h, rtd, 1.0, xd, xt, 0.0, yd, yb), 5, 10)
-            del xt
+
+                def fn(rtd=rtd, xd=xd, xts=xts, yd=yd, yb=yb, sets=sets):
+                    i = it[0] % sets
+                    it[0] += 1
+                    core.reduce_tensor(h, rtd, 1.0, xd, xts[i], 0.0, yd, yb)
+                measure("reduce " + label + ", " + tag, "[256,256,28,28] %s%s" % (tag, "" if sets == 1 else ", cold L2 (rotating %d copies)" % sets),
+                        n * es + int(np.prod(yshape)) * es, n, fn, 2 * max(sets, 3), 10)
+            del xt, xts
         one = dbuf(4)
         measure("reduce sum of all elements (what asum / nrm2 / sum of a tensor run)", "[256,256,28,28] float -> 1 value",
                 n * 4, n, lambda: core.reduce_tensor(h, core.reduce_tensor_descriptor("add", "float"), 1.0,

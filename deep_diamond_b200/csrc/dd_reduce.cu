@@ -222,7 +222,7 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
       }
       p.S = S < 1 ? 1 : (int)S;
     }
-    // Where a split is due and 2, 4 or 8 splits give at least half a resident wave of 128-thread
+    // Where a split is due and 2, 4 or 8 splits give at least a quarter of a resident wave of 128-thread
     // CTAs, the splits of a tile form a thread-block cluster and combine through distributed shared
     // memory (dd_reduce_colc_kernel): 256-byte runs along k2 (16 lanes), 8 row groups per CTA.  The
     // fused cross-GPU form keeps the counter protocol.
@@ -237,12 +237,35 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
       while (sc < 8 && base * sc < wave * 4 / 5) sc *= 2;
       while (sc > 1 && p.R1 / ((int64_t)sc * tyc) < 1) sc /= 2;
       sc = dd_tune("DD_COL_SC", sc);
-      if (sc >= 2 && sc <= 8 && base * sc >= wave / 2 && base * sc <= 0x7fffffffLL) {
+      if (sc >= 2 && sc <= 8 && base * sc >= wave / 4 && base * sc <= 0x7fffffffLL) {
         pl->cluster = 1;
         p.TX = txc;
         p.tilesK2 = tilesC;
         p.S = sc;
         ctas0 = base;
+      }
+    }
+    // 16-bit element types without a split: the same lean kernel, no cluster.  The general kernel
+    // keeps 8 accumulators and 4 loads of 8 elements per thread in 64 registers at 4 CTAs per SM;
+    // the lean one runs 8 CTAs of 128 threads with 8 loads each.  Lanes along k2: 8 to 16, the count
+    // that pads the last tile least (784 elements = 98 vectors: 14 lanes, 7 tiles).
+    if (p.S == 1 && !pl->cluster && pl->vec && esize == 2 && !(flags & DD_PLAN_NO_CLUSTER) &&
+        dd_tune("DD_COL_LEAN16", 1)) {
+      const int64_t vecs = p.K2 / v;
+      int txc = 16;
+      double bestUse = -1.0;
+      for (int cand = 16; cand >= 8; cand--) {
+        const double use = (double)vecs / (double)(((vecs + cand - 1) / cand) * cand);
+        if (use > bestUse + 1e-9) { bestUse = use; txc = cand; }
+      }
+      if (vecs < 8) txc = (int)vecs;
+      const int tyc = DD_COLC_THREADS / txc;
+      const int64_t tilesC = (vecs + txc - 1) / txc;
+      if (p.R1 / tyc >= 8 && p.K1 * tilesC >= (int64_t)h->smCount * 4 && p.K1 * tilesC <= 0x7fffffffLL) {
+        pl->cluster = 1;
+        p.TX = txc;
+        p.tilesK2 = tilesC;
+        ctas0 = p.K1 * tilesC;
       }
     }
     int64_t ctas = ctas0 * p.S;

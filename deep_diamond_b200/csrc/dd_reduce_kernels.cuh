@@ -672,7 +672,10 @@ __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_redu
 // reads the other CTAs' folded values straight from THEIR shared memory (distributed shared
 // memory) and finishes, in rank order.  Two cluster barriers replace the partial store, fence,
 // atomic counter and re-read through global memory of the counter protocol (about 3 us on a 10 us
-// kernel).  CTA = 128 threads: TX lanes along k2 by TY = 128 / TX row groups.
+// kernel).  CTA = 128 threads: TX lanes along k2 (any number up to 32) by TY = 128 / TX row groups;
+// threads beyond TX * TY idle.  With S = 1 (launched without a cluster) it is the column reduce for
+// 16-bit element types: eight loads in flight where the general kernel, at twice the registers per
+// accumulator set, keeps four.
 #define DD_COLC_THREADS 128
 template <typename T, typename C, int OPC>
 __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRedParams p) {
@@ -684,7 +687,7 @@ __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRe
   dd_pdl_prologue();
   const bool nanProp = p.nanProp != 0;
   const int TX = p.TX, TY = BS / TX;
-  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;  // ty == TY: a thread left over, idle
   int64_t id = blockIdx.x;
   const int s = (int)(id % p.S);  // = this CTA's rank in its cluster (1-D grid, cluster of S along x)
   id /= p.S;
@@ -697,7 +700,7 @@ __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRe
   C acc[V];
 #pragma unroll
   for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::identity();
-  if (k2 < p.K2 && lo + ty < hi) {
+  if (k2 < p.K2 && ty < TY && lo + ty < hi) {
     const T *ptr = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2 + (lo + ty) * p.sxR1;
     const int64_t step = (int64_t)TY * p.sxR1;
     const int n = (int)((hi - lo - ty + TY - 1) / TY);  // rows of this thread
@@ -722,14 +725,22 @@ __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRe
       for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
     }
   }
+  if (ty < TY) {
 #pragma unroll
-  for (int k = 0; k < V; k++) smem[ty * (TX * V) + tx * V + k] = acc[k];
+    for (int k = 0; k < V; k++) smem[ty * (TX * V) + tx * V + k] = acc[k];
+  }
   __syncthreads();
   for (int col = threadIdx.x; col < TX * V; col += BS) {
     C a = smem[col];
     for (int r = 1; r < TY; r++) a = dd_red<C, OPC>::comb(a, smem[r * (TX * V) + col], nanProp);
-    folded[col] = a;
+    if (p.S == 1) {
+      const int64_t kk = tk * TX * V + col;
+      if (kk < p.K2) dd_red_finish<T, C>(p, k1, kk, a);
+    } else {
+      folded[col] = a;
+    }
   }
+  if (p.S == 1) return;  // no cluster: every thread of the grid takes this branch
   cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
   cluster.sync();  // every CTA's folded values are in its shared memory
   if (s == 0) {
@@ -906,7 +917,8 @@ struct ddRedPlan {
   int bs;   // row: threads per CTA (128 or 256)
   int lean; // row: 0 = the general kernel, else the lean kernel with this many chunks per run (1, 2, 4)
   int pdl;  // col: launched programmatically (small inputs) or the ordinary way
-  int cluster;  // col: the S splits of a tile form one thread-block cluster (dd_reduce_colc_kernel)
+  int cluster;  // col: dd_reduce_colc_kernel (S > 1: the S splits of a tile form one thread-block cluster;
+                // S == 1: the same kernel without a cluster, for 16-bit element types)
   ddRedParams p;
   ddRedGenericParams g;
   int64_t nout;
@@ -959,6 +971,10 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       else if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
       else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);    \
       DD_LAUNCHED(h, "reduce/row");                                                                \
+    } else if (pl.kind == DD_RED_COL && pl.cluster && pl.p.S == 1) {                               \
+      dd_reduce_colc_kernel<T, C, OPC><<<pl.grid, DD_COLC_THREADS, 0, h->stream>>>(pl.p);          \
+      DD_LAUNCHED(h, "reduce/col-lean");                                                           \
+      return DD_STATUS_SUCCESS;                                                                    \
     } else if (pl.kind == DD_RED_COL && pl.cluster) {                                              \
       dd_launch_cluster(dd_reduce_colc_kernel<T, C, OPC>, pl.grid, (unsigned)DD_COLC_THREADS, (unsigned)pl.p.S, h->stream, pl.p);  \
       DD_LAUNCHED(h, "reduce/col-cluster");                                                        \
