@@ -970,7 +970,7 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       else if (pl.lean == 4) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 4, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
       else if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
       else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);    \
-      DD_LAUNCHED(h, "reduce/row");                                                                \
+      DD_LAUNCHED(h, pl.lean ? "reduce/row-lean" : "reduce/row");                                  \
     } else if (pl.kind == DD_RED_COL && pl.cluster && pl.p.S == 1) {                               \
       dd_reduce_colc_kernel<T, C, OPC><<<pl.grid, DD_COLC_THREADS, 0, h->stream>>>(pl.p);          \
       DD_LAUNCHED(h, "reduce/col-lean");                                                           \
