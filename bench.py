@@ -863,6 +863,11 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     host_binding = bind_near_gpu(local_rank) if world > 1 else {"bound": False, "note": "one rank: left unbound"}
     dist = None
+    # stdout carries ONE JSON line: whatever libraries print there meanwhile (NCCL announces its
+    # version on stdout at the first communicator) goes to stderr instead
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -1032,6 +1037,7 @@ def run_ours(args):
                "steps": e2e_steps, "work_per_step": "one pass (the 8 ops) over the batch",
                "h2d_GB/s_in_step": round(h2d / e2e_s / 1e9, 1), "d2h_GB/s_in_step": round(d2h / e2e_s / 1e9, 1),
                "h2d_GB/s_alone": round(n * 4 / up_s / 1e9, 1), "d2h_GB/s_alone": round(n * 4 / down_s / 1e9, 1),
+               "host_memory_traffic_GB/s_all_ranks": round(world * (h2d + d2h) / e2e_s / 1e9, 1),
                "host": host_binding,
                "api": "tensor.transfer_async (pinned numpy <-> device, uploads and downloads on separate copy "
                       "streams), tensor.transfer (device -> device), dnn.activation layers forward/backward"}
@@ -1112,10 +1118,15 @@ def run_ours(args):
             "sharded_parity": shard_par,
             "scaling_summary": summary,
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     fact.release()
     if dist:
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
 
 
 def main():

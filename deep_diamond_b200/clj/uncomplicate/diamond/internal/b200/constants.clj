@@ -140,15 +140,21 @@
                     {:mode mode :available (keys dd-activation-mode)})))
 
 (def ^{:const true
-       :doc "Binary ops of ddOpTensor: cudnnOpTensor's four and the arithmetic ones of oneDNN's
-  binary primitive (dnnl/constants.clj:359-371)."}
+       :doc "Binary ops of ddOpTensor: cudnnOpTensor's four and the kinds of oneDNN's binary
+  primitive (dnnl/constants.clj:359-371), comparisons included (1 / 0 in the tensors' type)."}
   dd-op-tensor-op
   {:add 0
    :mul 1
    :min 2
    :max 3
    :sub 4
-   :div 5})
+   :div 5
+   :ge 6
+   :gt 7
+   :le 8
+   :lt 9
+   :eq 10
+   :ne 11})
 
 (def ^{:const true
        :doc "Reduce ops (cudnn/constants.clj:171-180) with oneDNN's names accepted too

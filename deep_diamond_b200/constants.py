@@ -31,7 +31,8 @@ ACTIVATION_MODE = {"logistic": 0, "sigmoid": 0, "relu": 1, "tanh": 2, "clipped-r
 ACTIVATION_NAME = {0: "logistic", 1: "relu", 2: "tanh", 3: "clipped-relu", 4: "elu", 5: "linear",
                    6: "abs"}
 
-OP_TENSOR = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5}
+OP_TENSOR = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5,
+             "ge": 6, "gt": 7, "le": 8, "lt": 9, "eq": 10, "ne": 11}
 
 REDUCE_OP = {"add": 0, "sum": 0, "mul": 1, "min": 2, "max": 3, "amax": 4, "avg": 5, "mean": 5,
              "norm1": 6, "norm2": 7, "mul-no-zeros": 8}

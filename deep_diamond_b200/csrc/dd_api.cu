@@ -390,7 +390,7 @@ ddStatus_t ddOpTensor(ddHandle_t h, ddOpTensorOp_t op, const void *alpha1, ddTen
   DD_CHECK(dd_check_desc(h, cd, "ddOpTensor C"));
   if (!A || !B || !C || !alpha1 || !alpha2 || !beta)
     DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddOpTensor: null pointer");
-  if ((int)op < 0 || (int)op > DD_OP_TENSOR_DIV) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddOpTensor: bad op");
+  if ((int)op < 0 || (int)op > DD_OP_TENSOR_NE) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddOpTensor: bad op");
   return dd_optensor_impl(h, op, dd_read_scalar(alpha1, ad->dtype), ad, A,
                           dd_read_scalar(alpha2, bd->dtype), bd, B, dd_read_scalar(beta, cd->dtype),
                           cd, C);

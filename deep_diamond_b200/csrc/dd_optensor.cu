@@ -19,6 +19,12 @@ __device__ __forceinline__ C dd_binop(int op, C a, C b) {
     case DD_OP_TENSOR_MIN: return a < b ? a : b;
     case DD_OP_TENSOR_MAX: return a > b ? a : b;
     case DD_OP_TENSOR_SUB: return dd_add_rn(a, -b);
+    case DD_OP_TENSOR_GE: return a >= b ? (C)1 : (C)0;
+    case DD_OP_TENSOR_GT: return a > b ? (C)1 : (C)0;
+    case DD_OP_TENSOR_LE: return a <= b ? (C)1 : (C)0;
+    case DD_OP_TENSOR_LT: return a < b ? (C)1 : (C)0;
+    case DD_OP_TENSOR_EQ: return a == b ? (C)1 : (C)0;
+    case DD_OP_TENSOR_NE: return a != b ? (C)1 : (C)0;
     default: return a / b;  // DIV (IEEE round-to-nearest division)
   }
 }

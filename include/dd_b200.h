@@ -89,14 +89,22 @@ typedef enum {
 typedef enum { DD_NOT_PROPAGATE_NAN = 0, DD_PROPAGATE_NAN = 1 } ddNanPropagation_t;
 
 /* Binary ops: cudnnOpTensor's set, plus the oneDNN binary kinds the reference names in
- * dnnl/constants.clj:359-371 that are arithmetic. */
+ * dnnl/constants.clj:359-371: the arithmetic ones and the comparisons (1 where the relation holds
+ * between alpha1*A and alpha2*B, else 0, stored in the tensors' data type; a NaN compares false,
+ * except under NE). */
 typedef enum {
   DD_OP_TENSOR_ADD = 0,
   DD_OP_TENSOR_MUL = 1,
   DD_OP_TENSOR_MIN = 2,
   DD_OP_TENSOR_MAX = 3,
   DD_OP_TENSOR_SUB = 4,
-  DD_OP_TENSOR_DIV = 5
+  DD_OP_TENSOR_DIV = 5,
+  DD_OP_TENSOR_GE = 6,
+  DD_OP_TENSOR_GT = 7,
+  DD_OP_TENSOR_LE = 8,
+  DD_OP_TENSOR_LT = 9,
+  DD_OP_TENSOR_EQ = 10,
+  DD_OP_TENSOR_NE = 11
 } ddOpTensorOp_t;
 
 /* Reduce ops, cudnn/constants.clj:171-180; oneDNN's kinds (dnnl/constants.clj:393-402) map as

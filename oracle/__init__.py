@@ -31,7 +31,8 @@ ACT = {"sigmoid": 0, "logistic": 0, "relu": 1, "tanh": 2, "clipped-relu": 3, "el
        "linear": 5, "identity": 5, "abs": 6,
        # elu as oneDNN's fp32 kernels form it, alpha * (float(exp(x)) - 1): forward only, oracle only
        "elu-fp32-exp-minus-1": 7}
-BINOP = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5}
+BINOP = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5,
+         "ge": 6, "gt": 7, "le": 8, "lt": 9, "eq": 10, "ne": 11}
 REDOP = {"add": 0, "sum": 0, "mul": 1, "min": 2, "max": 3, "amax": 4, "avg": 5, "mean": 5,
          "norm1": 6, "norm2": 7, "mul-no-zeros": 8}
 

@@ -466,7 +466,10 @@ int oracle_eltwise_bwd_truth(int alg, double coef, int64_t n, const float *x, co
 
 /* ------------------------------------------------------------ binary / sum ------------------- */
 
-enum { B_ADD = 0, B_MUL = 1, B_MIN = 2, B_MAX = 3, B_SUB = 4, B_DIV = 5 };
+/* 6..11: oneDNN's comparison kinds (dnnl/constants.clj:359-371 :ge :gt :le :lt :eq :ne): 1 where the
+ * relation holds, else 0, in the destination's type. */
+enum { B_ADD = 0, B_MUL = 1, B_MIN = 2, B_MAX = 3, B_SUB = 4, B_DIV = 5, B_GE = 6, B_GT = 7, B_LE = 8, B_LT = 9,
+       B_EQ = 10, B_NE = 11 };
 
 /* C = op(alpha1*A, alpha2*bcast(B)) + beta*C; bdims[i] is dims[i] or 1. */
 int oracle_binary(int op, int t, int nd, const int64_t *dims, double alpha1, const int64_t *ast,
@@ -491,6 +494,12 @@ int oracle_binary(int op, int t, int nd, const int64_t *dims, double alpha1, con
         case B_MIN: r = a < b ? a : b; break;
         case B_MAX: r = a > b ? a : b; break;
         case B_SUB: r = a - b; break;
+        case B_GE: r = a >= b ? 1.0 : 0.0; break;
+        case B_GT: r = a > b ? 1.0 : 0.0; break;
+        case B_LE: r = a <= b ? 1.0 : 0.0; break;
+        case B_LT: r = a < b ? 1.0 : 0.0; break;
+        case B_EQ: r = a == b ? 1.0 : 0.0; break;
+        case B_NE: r = a != b ? 1.0 : 0.0; break;
         default: r = a / b; break;
       }
       if (beta != 0.0) r = r + beta * load_as_double(C, t, co);
@@ -505,6 +514,12 @@ int oracle_binary(int op, int t, int nd, const int64_t *dims, double alpha1, con
         case B_MIN: r = a < b ? a : b; break;
         case B_MAX: r = a > b ? a : b; break;
         case B_SUB: r = a - b; break;
+        case B_GE: r = a >= b ? 1.f : 0.f; break;
+        case B_GT: r = a > b ? 1.f : 0.f; break;
+        case B_LE: r = a <= b ? 1.f : 0.f; break;
+        case B_LT: r = a < b ? 1.f : 0.f; break;
+        case B_EQ: r = a == b ? 1.f : 0.f; break;
+        case B_NE: r = a != b ? 1.f : 0.f; break;
         default: r = a / b; break;
       }
       if (beta != 0.0) r = r + (float)beta * load_as_float(C, t, co);

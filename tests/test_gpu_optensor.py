@@ -24,7 +24,7 @@ def rnd(shape, seed, lo=-1.0, hi=1.0):
     ([3, 5, 2, 6], [1, 5, 1, 6]),        # two broadcast dims apart: strided kernel
     ([3, 5, 2, 6], [3, 1, 1, 1]),        # per-sample
 ])
-@pytest.mark.parametrize("op", ["add", "mul", "min", "max", "sub", "div"])
+@pytest.mark.parametrize("op", ["add", "mul", "min", "max", "sub", "div", "ge", "gt", "le", "lt", "eq", "ne"])
 def test_op_tensor_broadcast(fact, dev, oracle, shape, bshape, op):
     a = rnd(shape, 1)
     b = rnd(bshape, 2, 0.5, 1.5)
@@ -175,3 +175,38 @@ def test_tensor_equals(fact, dev, oracle):
     core.tensor_equals(fact.handle, dx, tx, dx, tx, flag)
     fact.synchronize()
     assert int(flag.item()) == 0 and fact.handle.last_kernel() == "equals/flat"
+
+
+def test_comparison_kinds_on_known_values(fact, dev):
+    """oneDNN's comparison kinds (dnnl/constants.clj:359-371): 1 where the relation holds, else 0; a
+    NaN compares false except under :ne; -0 equals +0."""
+    a = np.array([1.0, 2.0, 3.0, np.nan, -0.0, 5.0, 7.0, 7.0], np.float32)
+    b = np.array([2.0, 2.0, 1.0, 1.0, 0.0, np.nan, 7.0, 8.0], np.float32)
+    d = core.tensor_descriptor([8], "float", [1])
+    want = {"ge": a >= b, "gt": a > b, "le": a <= b, "lt": a < b, "eq": a == b, "ne": a != b}
+    for op, w in want.items():
+        tc = dev.put(np.full(8, -9.0, np.float32))
+        core.op_tensor(fact.handle, op, 1.0, d, dev.put(a), 1.0, d, dev.put(b), 0.0, d, tc)
+        assert dev.get(tc, np.float32).tolist() == w.astype(np.float32).tolist(), op
+
+
+def test_equality_stops_early_and_stays_exact(fact, dev):
+    """A mismatch anywhere (first element, last element, the scalar tail) raises the flag; equal
+    tensors leave it alone; a flag already raised stays raised."""
+    import torch
+    n = (1 << 22) + 3
+    x = np.random.default_rng(5).standard_normal(n).astype(np.float32)
+    d = core.tensor_descriptor([n], "float", [1])
+    tx = dev.put(x)
+    for where in (None, 0, n // 2, n - 4, n - 1):
+        y = x.copy()
+        if where is not None:
+            y[where] += 1.0
+        flag = torch.zeros(1, dtype=torch.int32, device=fact.device)
+        core.tensor_equals(fact.handle, d, tx, d, dev.put(y), flag)
+        fact.synchronize()
+        assert (int(flag.item()) != 0) == (where is not None), where
+    flag = torch.ones(1, dtype=torch.int32, device=fact.device)
+    core.tensor_equals(fact.handle, d, tx, d, tx, flag)
+    fact.synchronize()
+    assert int(flag.item()) != 0
