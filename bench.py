@@ -491,6 +491,11 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_on
                 measure("reduce " + label, "C4 shard [%d,1024,32,32]%s + 4 KB exchanged over NVLink by the library's own "
                         "kernels (the form the library picks)" % (shp[0], cold), nb, n, fn, 2 * max(sets, 5), 20, rid=rid)
                 if op == "add":
+                    def fn_warm(rtd=rtd, yd=yd, y=y):
+                        sharded.reduce_tensor(rtd, 1.0, xd, xs[0], 0.0, yd, y, spans=True)
+                    if sets > 1:
+                        measure("reduce " + label + " (warm L2: the same shard every call)",
+                                "C4 shard [%d,1024,32,32] resident in L2" % shp[0], nb, n, fn_warm, 10, 20)
                     for form, kw in (("reduce + exchange in ONE kernel", dict(fused=True)),
                                      ("exchange kernel after the local pass", dict(fused=False))):
                         sharded.peer_configure(use_peer=True, **kw)

@@ -3,7 +3,7 @@
 ;; counterpart of uncomplicate.diamond.internal.cudnn.core (deep-diamond-cuda,
 ;; src/clojure/uncomplicate/diamond/internal/cudnn/core.clj:48-231 and :344-350), with the same
 ;; function names and argument orders, so that tensor.clj / factory.clj / directed.clj of a B200
-;; backend are the cuDNN ones with the namespace swapped (INTEGRATION.md lists what else changes).
+;; backend are the cuDNN ones with the namespace swapped.
 ;; NOT EXECUTED where it was written (no JVM there).
 
 (ns uncomplicate.diamond.internal.b200.core
