@@ -5,17 +5,24 @@
 // which covers nchw/nhwc reductions over any subset of (N, C, spatial).  Two kernel families:
 //
 //   row   r2 > 1 and contiguous in x (reduce over the innermost run; e.g. nchw sum over (N,H,W)
-//         or norm over (C,H,W)).  A group of 32 or 256 threads owns one (output, split): 16-byte
+//         or norm over (C,H,W)).  A group of 32 to 256 threads owns one (output, split): 16-byte
 //         loads along r2, register accumulation, warp shuffle tree, shared-memory tree across warps.
+//         dd_reduce_rowl_kernel (lean: 8 loads in flight, aligned runs of at most 4 chunks per
+//         thread) takes the plans it can, dd_reduce_row_kernel (general walk, 4 loads) the rest.
 //   col   r2 == 1 and k2 contiguous in x (reduce across a strided dim; e.g. nchw max over C).
-//         Lanes run along k2 with 16-byte loads, warps stride over r1, shared-memory combine.
+//         Lanes run along k2 with 16-byte loads, warps stride over r1, shared-memory combine:
+//         dd_reduce_col_kernel; dd_reduce_colc_kernel (lean, 128 threads) when the reduced range
+//         is split over a thread-block cluster, and for 16-bit element types.
 //
-// When an output's reduce range is split over several CTAs (few outputs, long ranges) each split
-// writes one partial to the workspace and bumps an arrival counter; the split that arrives last
-// combines all partials in index order and finishes (one launch, nobody waits, and the order of
-// the combine is fixed, so results are run-to-run identical).  Without counters (caller-owned
-// set-up that cannot guarantee zeroed memory) dd_reduce_finish_kernel does the combine instead.  Anything that does not fit the 4-level form runs one
-// thread per output (generic).  All are HBM-bound: algorithmic bytes = input bytes + output bytes.
+// When an output's reduce range is split over several CTAs (few outputs, long ranges) the splits
+// are combined one of two ways.  Column reductions with 2, 4 or 8 splits: the splits form a cluster
+// and the first CTA reads the others' results from their shared memory.  Everything else: each
+// split writes one partial to the workspace and bumps an arrival counter; the split that arrives
+// last folds all partials in a fixed order and finishes (one launch, nobody waits, results are
+// run-to-run identical).  Without counters (the entry point that has no handle, whose memory
+// nobody has zeroed) dd_reduce_finish_kernel does the fold instead.  Anything that does not fit the
+// 4-level form runs one thread per output (generic).  All are HBM-bound: algorithmic bytes = input
+// bytes + output bytes.
 #pragma once
 #include "dd_internal.cuh"
 #include <cooperative_groups.h>
