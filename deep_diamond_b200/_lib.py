@@ -93,6 +93,7 @@ _SIGS = {
     "ddShardedPeerDetach": [_vp],
     "ddShardedSetJoinLimit": [_dbl],
     "ddResetCounters": [_vp],
+    "ddGetDeviceFault": [_vp, ctypes.POINTER(ctypes.c_int)],
     "ddShardedCheck": [_vp],
     "ddShardedPeerExport": [_vp, _vp],
     "ddShardedPeerAttach": [_vp, _vp],

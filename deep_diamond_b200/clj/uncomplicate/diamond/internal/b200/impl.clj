@@ -64,6 +64,7 @@
 (defdowncall dd-get-launch-count                  "ddGetLaunchCount" I [P P])
 (defdowncall dd-get-last-kernel-name              "ddGetLastKernelName" P [P])
 (defdowncall dd-reset-counters                    "ddResetCounters" I [P])
+(defdowncall dd-get-device-fault                  "ddGetDeviceFault" I [P P])
 (defdowncall dd-create-tensor-descriptor          "ddCreateTensorDescriptor" I [P])
 (defdowncall dd-destroy-tensor-descriptor         "ddDestroyTensorDescriptor" I [P])
 (defdowncall dd-set-tensor4d-descriptor           "ddSetTensor4dDescriptor" I [P I I L L L L])
@@ -218,6 +219,13 @@
 
 (defn reset-counters* [hdl]
   (with-check hdl (invoke dd-reset-counters (seg hdl)) hdl))
+
+(defn device-fault*
+  "0 unless a kernel of this handle gave up a bounded wait for a tile copy (read after a synchronize)."
+  ^long [hdl]
+  (with-out [cell]
+    (with-check hdl (invoke dd-get-device-fault (seg hdl) cell)
+      (long (.get ^MemorySegment cell ValueLayout/JAVA_INT 0)))))
 
 ;; =========================== Tensor descriptor =========================================
 

@@ -56,6 +56,12 @@ class Handle:
     def last_kernel(self):
         return lib.ddGetLastKernelName(self.ptr).decode()
 
+    def device_fault(self):
+        """0 unless a kernel of this handle gave up a bounded wait (read after a synchronize)."""
+        w = ctypes.c_int(0)
+        check(lib.ddGetDeviceFault(self.ptr, ctypes.byref(w)), self.ptr)
+        return int(w.value)
+
     def release(self):
         if self.ptr is not None and self.ptr.value:
             lib.ddDestroy(self.ptr)

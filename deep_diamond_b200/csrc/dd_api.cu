@@ -123,7 +123,24 @@ ddStatus_t ddCreate(ddHandle_t *handle) {
     delete h;
     return DD_STATUS_ALLOC_FAILED;
   }
+  if (cudaHostAlloc((void **)&h->faultWord, 64, cudaHostAllocMapped) == cudaSuccess)
+    *h->faultWord = 0;
+  else {
+    cudaGetLastError();
+    h->faultWord = nullptr;
+  }
+  // The TMA-loading form of the 1-byte transposing reorder measured within 2 % of the
+  // register-staged kernel on tensors of 50 MB and 3 % behind it on larger ones, so it is not the
+  // default; DD_B200_TILE_TMA=1 in the environment of ddCreate selects it for this handle.
+  const char *tma = getenv("DD_B200_TILE_TMA");
+  h->tileTma = (tma && tma[0] == '1') ? 1 : 0;
   *handle = h;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddGetDeviceFault(ddHandle_t h, int *word) {
+  if (!h || !word) return DD_STATUS_BAD_PARAM;
+  *word = h->faultWord ? *(volatile int *)h->faultWord : 0;
   return DD_STATUS_SUCCESS;
 }
 
@@ -141,6 +158,7 @@ ddStatus_t ddResetCounters(ddHandle_t h) {
 ddStatus_t ddDestroy(ddHandle_t h) {
   if (!h) return DD_STATUS_BAD_PARAM;
   if (h->scratch) cudaFree(h->scratch);
+  if (h->faultWord) cudaFreeHost(h->faultWord);
   delete h;
   return DD_STATUS_SUCCESS;
 }

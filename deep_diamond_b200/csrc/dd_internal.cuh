@@ -53,6 +53,12 @@ struct ddContext {
   int64_t counterSlots;  // leading unsigned counters of `scratch` kept zero between launches (0: none)
   uint64_t launches;
   const char *lastKernel;
+  // One int in mapped host memory that a kernel raises when one of its bounded waits ran out (the
+  // copy engine never signalled a tile): the host reads it without a device round trip.  Null if
+  // the allocation failed, and then no kernel that needs it is launched.
+  int *faultWord;
+  bool tmaAttr;  // the tile-tma kernel's shared-memory limit has been raised on this device
+  int tileTma;   // 1: the 1-byte transposing reorder uses the TMA-loading kernel where it qualifies
   char msg[256];
 };
 

@@ -33,6 +33,9 @@ static void plan_canon(ddCanon *c, const ddTensorStruct *xd, const ddTensorStruc
 
 ddStatus_t dd_transform_impl(ddHandle_t h, double alpha, const ddTensorStruct *xd, const void *x,
                              double beta, const ddTensorStruct *yd, void *y) {
+  if (h->faultWord && *(volatile int *)h->faultWord)
+    DD_FAIL(h, DD_STATUS_EXECUTION_FAILED,
+            "ddTransformTensor: an earlier transform/tile-tma kernel gave up waiting for a tile copy; its output is incomplete");
   ddXformPlan pl;
   plan_canon(&pl.canon, xd, yd);
   pl.alpha = alpha;

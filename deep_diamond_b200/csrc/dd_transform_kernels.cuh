@@ -522,6 +522,10 @@ static int dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
   return vec ? 1 : 2;
 }
 
+// The 1-byte bit copy with tile loads by the tensor memory accelerator (dd_tile_tma.cu); false when
+// the reorder does not qualify, and then nothing was launched.
+bool dd_launch_tile_tma(ddHandle_t h, const ddTileParams &tp);
+
 template <typename S, typename D, typename C, bool RAW>
 static ddStatus_t dd_launch_tile(ddHandle_t h, const ddTileParams &tp, int kind) {
   typedef dd_tile_geom<S, D> G;
@@ -597,7 +601,11 @@ static ddStatus_t dd_xform_typed(ddHandle_t h, const ddXformPlan &pl) {
   const ddCanon &c = pl.canon;
   if (c.nd == 1 && c.st[0][0] == 1 && c.st[1][0] == 1) return dd_launch_flat<S, D, C, RAW>(h, pl);
   ddTileParams tp;
-  if (int kind = dd_tile_plan<S, D>(pl, &tp)) return dd_launch_tile<S, D, C, RAW>(h, tp, kind);
+  if (int kind = dd_tile_plan<S, D>(pl, &tp)) {
+    if constexpr (RAW && sizeof(S) == 1)
+      if (kind == 1 && dd_launch_tile_tma(h, tp)) return DD_STATUS_SUCCESS;
+    return dd_launch_tile<S, D, C, RAW>(h, tp, kind);
+  }
   if (dd_launch_rows<S, D, C, RAW>(h, pl)) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) DD_FAIL(h, DD_STATUS_EXECUTION_FAILED, "transform/rows: %s", cudaGetErrorString(e));

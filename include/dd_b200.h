@@ -158,6 +158,14 @@ DD_API const char *ddGetLastKernelName(ddHandle_t handle);
  * ddResetCounters: it zeroes the counters on the handle's stream (ordered after everything already
  * enqueued there).  Nothing else in a handle depends on an earlier launch. */
 DD_API ddStatus_t ddResetCounters(ddHandle_t handle);
+/* No counterpart in the reference.  The transposing reorder of 1-byte elements has the GPU's copy
+ * engine (TMA) bring its tiles into shared memory, and the kernel's waits for those copies are
+ * bounded: a CTA whose tile never arrives raises a word in host-mapped memory, leaves its part of
+ * the output unwritten and returns, so that the context stays usable.  *word is that word as of
+ * now: 0 = no kernel of this handle ever gave up; read it after synchronising the handle's stream
+ * to learn whether the launches so far completed.  Once it is non-zero every later
+ * ddTransformTensor on the handle returns DD_STATUS_EXECUTION_FAILED; destroy the handle. */
+DD_API ddStatus_t ddGetDeviceFault(ddHandle_t handle, int *word);
 
 /* --------------------------------------------------------------- descriptors ---------------- */
 
