@@ -63,13 +63,15 @@ def build(force=False, verbose=True):
         objs = list(ex.map(lambda s: _compile(s, force, hdr_mtime), srcs))
     newest = max(os.path.getmtime(o) for o in objs)
     if force or not os.path.exists(OUT) or os.path.getmtime(OUT) < newest:
-        cmd = [_nvcc(), "-shared", "-o", OUT] + objs + [
+        tmp = OUT + ".partial"  # linked beside the target and renamed over it: a reader never sees half a file
+        cmd = [_nvcc(), "-shared", "-o", tmp] + objs + [
             "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-ldl",
             "-Xlinker", "--no-undefined",
         ]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+        os.replace(tmp, OUT)
     if verbose:
         print("built", OUT)
     return OUT

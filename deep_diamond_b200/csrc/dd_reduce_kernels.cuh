@@ -127,6 +127,7 @@ struct ddRedParams {
   void *y;
   void *part;     // workspace: [out][split] accumulators of the compute type (used when S > 1)
   void *partOut;  // partialOnly: [out] raw accumulators (no post/alpha/beta) instead of y
+  int rowCluster;      // row, lean: the splits of an output are the groups of this many consecutive CTAs, one cluster (0: none)
   unsigned *counters;  // S > 1: per-output (row) / per-tile (col) arrival counters, zero between launches;
                        // the last split to arrive combines all partials and finishes.  NULL: a separate
                        // finishing kernel does it.
@@ -388,6 +389,34 @@ template <typename T, typename C, int OPC, bool PEER>
 __device__ __forceinline__ void dd_row_epilogue(const ddRedParams &p, C acc, C *smem, unsigned peerCall) {
   const bool nanProp = p.nanProp != 0;
   acc = dd_group_reduce<C, OPC>(acc, p.G, nanProp, smem);
+  if constexpr (!PEER) {
+    if (p.rowCluster) {
+      // The S splits of an output are the groups of rowCluster consecutive CTAs, launched as one
+      // thread-block cluster: each group leaves its value in its CTA's shared memory and the
+      // cluster's first CTA folds them in split order, reading the other CTAs' values through
+      // distributed shared memory.  Two cluster barriers instead of the partial store, fence, atomic
+      // and re-read through global memory.
+      namespace cg = cooperative_groups;
+      cg::cluster_group cluster = cg::this_cluster();
+      __shared__ C cpart[8];
+      if (threadIdx.x % p.G == 0) cpart[threadIdx.x / p.G] = acc;
+      cluster.sync();
+      if (cluster.block_rank() == 0 && threadIdx.x == 0) {
+        const int gpb = blockDim.x / p.G;
+        C a = cpart[0];
+        for (int w = 1; w < gpb; w++) a = dd_red<C, OPC>::comb(a, cpart[w], nanProp);
+        for (int r = 1; r < p.rowCluster; r++) {
+          const C *rp = cluster.map_shared_rank(cpart, r);
+          for (int w = 0; w < gpb; w++) a = dd_red<C, OPC>::comb(a, rp[w], nanProp);
+        }
+        const int64_t out = blockIdx.x / p.rowCluster;
+        const int64_t k1 = out / p.K2;
+        dd_red_finish<T, C, false, -1>(p, k1, out - k1 * p.K2, a, 0u);
+      }
+      cluster.sync();  // nobody leaves while its shared memory may still be read
+      return;
+    }
+  }
   // which group this is and which output and split it works on: worked out again here rather than
   // kept in registers across the kernel's main loop (which has none to spare)
   const int lane = threadIdx.x % p.G;
@@ -434,10 +463,11 @@ __device__ __forceinline__ void dd_row_epilogue(const ddRedParams &p, C acc, C *
 // PEER: the fused exchange (partialOnly == 2), its own instantiation so that the plain kernels keep
 // their register budget.
 // The CTA has 128 or 256 threads (blockDim.x), a whole number of groups.
-template <typename T, typename C, int OPC, bool VEC, bool PEER>
+template <typename T, typename C, int OPC, int VEC, bool PEER>
 __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedParams p) {
-  constexpr int V = VEC ? 16 / sizeof(T) : 1;
-  constexpr int U = 4;  // independent 16-byte loads in flight per thread
+  // VEC: 1 = 16-byte loads, 2 = 8-byte loads (16-bit types whose runs are only 8-byte aligned), 0 = one element
+  constexpr int V = VEC == 1 ? 16 / sizeof(T) : (VEC == 2 ? 8 / sizeof(T) : 1);
+  constexpr int U = VEC == 2 ? 8 : 4;  // independent loads in flight per thread (the 8-byte ones: twice as many)
   __shared__ C smem[8];
   dd_pdl_prologue();
   unsigned peerCall = 0;
@@ -485,7 +515,8 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
       for (int q = 0; q < U; q++) {
         ok[q] = (left > 0) && (e < p.R2);
         if (ok[q]) {
-          if (VEC) raw[q] = *(const uint4 *)(row + e);
+          if (VEC == 1) raw[q] = *(const uint4 *)(row + e);
+          else if (VEC == 2) *(uint2 *)&raw[q] = *(const uint2 *)(row + e);
           else *(T *)&raw[q] = row[e];
         }
         left--;
@@ -544,38 +575,63 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
     bool okc[CPR];
 #pragma unroll
     for (int c = 0; c < CPR; c++) okc[c] = (int64_t)lane * V + c * ch < p.R2;
-    int r = 0;
-    for (; r + RB <= nrows; r += RB) {
-      uint4 raw[U];
+    if constexpr (!PEER) {
+      // batches of RB runs; the loads of a batch go out together, those of the last, partial batch
+      // too (a run at a time they would be up to RB - 1 more round trips to memory)
+      for (int left = nrows; left > 0; left -= RB) {
+        uint4 raw[U];
 #pragma unroll
-      for (int q = 0; q < RB; q++)
+        for (int q = 0; q < RB; q++)
+#pragma unroll
+          for (int c = 0; c < CPR; c++)
+            if (q < left && okc[c]) raw[q * CPR + c] = *(const uint4 *)(ptr + q * p.sxR1 + c * ch);
+        ptr += RB * p.sxR1;
+#pragma unroll
+        for (int q = 0; q < RB; q++)
+#pragma unroll
+          for (int c = 0; c < CPR; c++)
+            if (q < left && okc[c]) {
+              const T *wv = (const T *)&raw[q * CPR + c];
+#pragma unroll
+              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
+            }
+      }
+    } else {
+      // the fused exchange keeps more values live across the loop (the call number, the exchange
+      // buffers): whole batches without the predicate, then the remaining runs one at a time
+      int r = 0;
+      for (; r + RB <= nrows; r += RB) {
+        uint4 raw[U];
+#pragma unroll
+        for (int q = 0; q < RB; q++)
+#pragma unroll
+          for (int c = 0; c < CPR; c++)
+            if (okc[c]) raw[q * CPR + c] = *(const uint4 *)(ptr + q * p.sxR1 + c * ch);
+        ptr += RB * p.sxR1;
+#pragma unroll
+        for (int q = 0; q < RB; q++)
+#pragma unroll
+          for (int c = 0; c < CPR; c++)
+            if (okc[c]) {
+              const T *wv = (const T *)&raw[q * CPR + c];
+#pragma unroll
+              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
+            }
+      }
+      for (; r < nrows; r++) {
+        uint4 raw[CPR];
 #pragma unroll
         for (int c = 0; c < CPR; c++)
-          if (okc[c]) raw[q * CPR + c] = *(const uint4 *)(ptr + q * p.sxR1 + c * ch);
-      ptr += RB * p.sxR1;
-#pragma unroll
-      for (int q = 0; q < RB; q++)
+          if (okc[c]) raw[c] = *(const uint4 *)(ptr + c * ch);
+        ptr += p.sxR1;
 #pragma unroll
         for (int c = 0; c < CPR; c++)
           if (okc[c]) {
-            const T *wv = (const T *)&raw[q * CPR + c];
+            const T *wv = (const T *)&raw[c];
 #pragma unroll
             for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
           }
-    }
-    for (; r < nrows; r++) {
-      uint4 raw[CPR];
-#pragma unroll
-      for (int c = 0; c < CPR; c++)
-        if (okc[c]) raw[c] = *(const uint4 *)(ptr + c * ch);
-      ptr += p.sxR1;
-#pragma unroll
-      for (int c = 0; c < CPR; c++)
-        if (okc[c]) {
-          const T *wv = (const T *)&raw[c];
-#pragma unroll
-          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
-        }
+      }
     }
   }
   dd_row_epilogue<T, C, OPC, PEER>(p, acc, smem, peerCall);
@@ -583,10 +639,10 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
 
 // col: CTA = TX lanes along k2 (V elements each, TX a power of two <= 256) x TY = 256/TX row
 // groups striding over r1.
-template <typename T, typename C, int OPC, bool VEC, bool PEER>
+template <typename T, typename C, int OPC, int VEC, bool PEER>
 __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_reduce_col_kernel(ddRedParams p) {
-  constexpr int V = VEC ? 16 / sizeof(T) : 1;
-  constexpr int U = 4;
+  constexpr int V = VEC == 1 ? 16 / sizeof(T) : (VEC == 2 ? 8 / sizeof(T) : 1);  // as in the row kernel
+  constexpr int U = VEC == 2 ? 8 : 4;
   __shared__ C smem[256 * V];
   // Large inputs launch this kernel the ordinary way (the programmatic launch measured 4 % slower on
   // a 268 MB tensor), small ones programmatically; the wait returns at once in the first case.
@@ -620,7 +676,8 @@ __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_redu
         ok[q] = r1 < hi;
         if (ok[q]) {
           const T *ptr = xb + r1 * p.sxR1;
-          if (VEC) raw[q] = *(const uint4 *)ptr;
+          if (VEC == 1) raw[q] = *(const uint4 *)ptr;
+          else if (VEC == 2) *(uint2 *)&raw[q] = *(const uint2 *)ptr;
           else *(T *)&raw[q] = *ptr;
         }
       }
@@ -711,25 +768,21 @@ __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRe
     const T *ptr = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2 + (lo + ty) * p.sxR1;
     const int64_t step = (int64_t)TY * p.sxR1;
     const int n = (int)((hi - lo - ty + TY - 1) / TY);  // rows of this thread
-    int r = 0;
-    for (; r + U <= n; r += U) {
+    // batches of U rows; the loads of a batch go out together, those of the last, partial batch too
+    // (one at a time they would be up to seven more round trips to memory)
+    for (int left = n; left > 0; left -= U) {
       uint4 raw[U];
 #pragma unroll
-      for (int q = 0; q < U; q++) raw[q] = *(const uint4 *)(ptr + q * step);
+      for (int q = 0; q < U; q++)
+        if (q < left) raw[q] = *(const uint4 *)(ptr + q * step);
       ptr += U * step;
 #pragma unroll
-      for (int q = 0; q < U; q++) {
-        const T *wv = (const T *)&raw[q];
+      for (int q = 0; q < U; q++)
+        if (q < left) {
+          const T *wv = (const T *)&raw[q];
 #pragma unroll
-        for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
-      }
-    }
-    for (; r < n; r++) {
-      const uint4 raw = *(const uint4 *)ptr;
-      ptr += step;
-      const T *wv = (const T *)&raw;
-#pragma unroll
-      for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
+          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
+        }
     }
   }
   if (ty < TY) {
@@ -919,13 +972,14 @@ enum { DD_PLAN_STRUCTURED = 1, DD_PLAN_NO_CLUSTER = 2 };
 
 struct ddRedPlan {
   int kind;
-  int vec;
+  int vec;  // 0: element loads; 1: 16-byte loads; 2: 8-byte loads (16-bit types, rows only 8-byte aligned)
   int opc;
   int bs;   // row: threads per CTA (128 or 256)
   int lean; // row: 0 = the general kernel, else the lean kernel with this many chunks per run (1, 2, 4)
   int pdl;  // col: launched programmatically (small inputs) or the ordinary way
   int cluster;  // col: dd_reduce_colc_kernel (S > 1: the S splits of a tile form one thread-block cluster;
-                // S == 1: the same kernel without a cluster, for 16-bit element types)
+                // S == 1: the same kernel without a cluster, for 16-bit element types);
+                // row: the lean kernel launched in clusters of p.rowCluster CTAs
   ddRedParams p;
   ddRedGenericParams g;
   int64_t nout;
@@ -961,23 +1015,32 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
         else dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 4, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);  \
         DD_LAUNCHED(h, "reduce/row+peer-exchange");                                                \
       } else if (pl.kind == DD_RED_ROW) {                                                          \
-        if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);  \
-        else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
+        if (pl.vec == 1) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, 1, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);  \
+        else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, 0, true>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
         DD_LAUNCHED(h, "reduce/row+peer-exchange");                                                \
       } else {                                                                                     \
-        if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);  \
-        else dd_reduce_col_kernel<T, C, OPC, false, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
+        if (pl.vec == 1) dd_reduce_col_kernel<T, C, OPC, 1, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);  \
+        else dd_reduce_col_kernel<T, C, OPC, 0, true><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
         DD_LAUNCHED(h, "reduce/col+peer-exchange");                                                \
       }                                                                                            \
+      return DD_STATUS_SUCCESS;                                                                    \
+    }                                                                                              \
+    if (pl.kind == DD_RED_ROW && pl.lean && pl.cluster) {                                          \
+      const unsigned cs = (unsigned)pl.p.rowCluster;                                               \
+      if (pl.lean == 1) dd_launch_cluster(dd_reduce_rowl_kernel<T, C, OPC, 1, false>, pl.grid, (unsigned)pl.bs, cs, h->stream, pl.p);   \
+      else if (pl.lean == 2) dd_launch_cluster(dd_reduce_rowl_kernel<T, C, OPC, 2, false>, pl.grid, (unsigned)pl.bs, cs, h->stream, pl.p);   \
+      else dd_launch_cluster(dd_reduce_rowl_kernel<T, C, OPC, 4, false>, pl.grid, (unsigned)pl.bs, cs, h->stream, pl.p);   \
+      DD_LAUNCHED(h, "reduce/row-cluster");                                                        \
       return DD_STATUS_SUCCESS;                                                                    \
     }                                                                                              \
     if (pl.kind == DD_RED_ROW) {                                                                   \
       if (pl.lean == 1) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 1, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
       else if (pl.lean == 2) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 2, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
       else if (pl.lean == 4) dd_launch_pdl(dd_reduce_rowl_kernel<T, C, OPC, 4, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
-      else if (pl.vec) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, true, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
-      else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, false, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);    \
-      DD_LAUNCHED(h, pl.lean ? "reduce/row-lean" : "reduce/row");                                  \
+      else if (pl.vec == 1) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, 1, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);   \
+      else if (pl.vec == 2) { if constexpr (sizeof(T) == 2 && OPC >= 0) dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, 2, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p); }  \
+      else dd_launch_pdl(dd_reduce_row_kernel<T, C, OPC, 0, false>, pl.grid, (unsigned)pl.bs, h->stream, pl.p);    \
+      DD_LAUNCHED(h, pl.lean ? "reduce/row-lean" : (pl.vec == 2 ? "reduce/row-v8" : "reduce/row"));  \
     } else if (pl.kind == DD_RED_COL && pl.cluster && pl.p.S == 1) {                               \
       dd_reduce_colc_kernel<T, C, OPC><<<pl.grid, DD_COLC_THREADS, 0, h->stream>>>(pl.p);          \
       DD_LAUNCHED(h, "reduce/col-lean");                                                           \
@@ -988,13 +1051,15 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       return DD_STATUS_SUCCESS;                                                                    \
     } else if (pl.kind == DD_RED_COL) {                                                            \
       if (pl.pdl) {                                                                                \
-        if (pl.vec) dd_launch_pdl(dd_reduce_col_kernel<T, C, OPC, true, false>, pl.grid, 256u, h->stream, pl.p);   \
-        else dd_launch_pdl(dd_reduce_col_kernel<T, C, OPC, false, false>, pl.grid, 256u, h->stream, pl.p);    \
+        if (pl.vec == 1) dd_launch_pdl(dd_reduce_col_kernel<T, C, OPC, 1, false>, pl.grid, 256u, h->stream, pl.p);   \
+        else if (pl.vec == 2) { if constexpr (sizeof(T) == 2 && OPC >= 0) dd_launch_pdl(dd_reduce_col_kernel<T, C, OPC, 2, false>, pl.grid, 256u, h->stream, pl.p); }  \
+        else dd_launch_pdl(dd_reduce_col_kernel<T, C, OPC, 0, false>, pl.grid, 256u, h->stream, pl.p);    \
       } else {                                                                                     \
-        if (pl.vec) dd_reduce_col_kernel<T, C, OPC, true, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
-        else dd_reduce_col_kernel<T, C, OPC, false, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);    \
+        if (pl.vec == 1) dd_reduce_col_kernel<T, C, OPC, 1, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);   \
+        else if (pl.vec == 2) { if constexpr (sizeof(T) == 2 && OPC >= 0) dd_reduce_col_kernel<T, C, OPC, 2, false><<<pl.grid, 256, 0, h->stream>>>(pl.p); }  \
+        else dd_reduce_col_kernel<T, C, OPC, 0, false><<<pl.grid, 256, 0, h->stream>>>(pl.p);    \
       }                                                                                            \
-      DD_LAUNCHED(h, "reduce/col");                                                                \
+      DD_LAUNCHED(h, pl.vec == 2 ? "reduce/col-v8" : "reduce/col");                                \
     } else {                                                                                       \
       dd_reduce_generic_kernel<T, C, OPC><<<pl.grid, 256, 0, h->stream>>>(pl.g);                   \
       DD_LAUNCHED(h, "reduce/generic");                                                            \

@@ -17,7 +17,9 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("shape,yshape,kernel", [
     ([8, 1024, 32, 32], [1, 1024, 1, 1], "reduce/row-lean"),    # 2 chunks per run, 128-thread CTAs, no split
     ([8, 1024, 32, 32], [8, 1, 1, 1], "reduce/row-lean"),       # one long run per output, folded into rows; ~70 splits
-    ([32, 256, 28, 28], [1, 256, 1, 1], "reduce/row-lean"),     # 784-long runs: 4 chunks of 64 lanes, split over r1
+    ([32, 64, 28, 28], [1, 64, 1, 1], "reduce/row-lean"),       # 784-long runs: 4 chunks of 64 lanes, split over r1 (arrival counters)
+    ([32, 256, 28, 28], [1, 256, 1, 1], "reduce/row-lean"),     # the same with 256 outputs: 8 splits of 4 runs
+    ([37, 200, 28, 28], [1, 200, 1, 1], "reduce/row-lean"),     # uneven: 9 splits of 4 runs and one of 1
     ([2, 3, 28, 28], [1, 3, 1, 1], "reduce/row"),               # short reductions: warp groups, general walk
     ([3, 5, 7, 1030], [3, 5, 7, 1], "reduce/row"),              # runs that are not 16-byte aligned
     ([8, 1024, 32, 32], [8, 1, 32, 32], "reduce/col-cluster"),  # 8 splits of a tile as one cluster
@@ -58,7 +60,16 @@ def test_hundreds_of_splits_folded_by_a_warp(fact, dev, oracle):
     ("max", [96, 96, 28, 28], [96, 1, 28, 28], "reduce/col-lean"),    # 98 vectors: 14 lanes along the kept dim
     ("add", [96, 96, 28, 28], [96, 1, 28, 28], "reduce/col-lean"),
     ("add", [16, 128, 28, 28], [1, 128, 1, 1], "reduce/row-lean"),
+    ("add", [70, 256, 28, 28], [1, 256, 1, 1], "reduce/row-cluster"),   # 16 splits of 5 runs: 14 used, 2 empty
+    ("max", [70, 256, 28, 28], [1, 256, 1, 1], "reduce/row-cluster"),
+    ("add", [64, 200, 28, 28], [1, 200, 1, 1], "reduce/row-cluster"),   # 16 splits of 4 runs, all used
     ("max", [8, 256, 32, 32], [8, 1, 32, 32], "reduce/col-cluster"),
+    # 14 x 14 maps: runs of 196 elements start on 8-byte boundaries only, so 8-byte loads
+    ("max", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),
+    ("add", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),
+    ("add", [32, 512, 14, 14], [1, 512, 1, 1], "reduce/row-v8"),
+    ("max", [2, 6, 14, 14], [1, 6, 1, 1], "reduce/row-v8"),
+    ("add", [3, 5, 7, 10], [3, 1, 7, 10], "reduce/col"),          # 70 elements per row: not a multiple of 4
 ])
 def test_sixteen_bit_types(fact, dev, oracle, tag, np_t, to16, op, shape, yshape, kernel):
     """16-bit storage, fp32 accumulation; the result is rounded once to the 16-bit type, so it must be
