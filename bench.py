@@ -1106,7 +1106,7 @@ def run_ours(args):
                                                "launch; the event records between its launches cost it a few per cent, "
                                                "which is why it can read below the sustained figure" % len(pass_ms)},
             "frac_of_measured_peak": round(value / world / peak, 4),
-            "roofline": {"bound": "hbm", "kernel": "dd_elt_flat_kernel<float,float,MODE,BWD=true> (activation backward)",
+            "roofline": {"bound": "hbm", "kernel": "activation backward: dd_elt_flat_kernel<float,float,relu,BWD> and dd_elt_flat_multi_kernel<tanh|logistic|elu,BWD,2>",
                          "achieved": round(achieved, 1), "peak": peak, "peak_kind": "of " + peak_kind, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                          "traffic": TRAFFIC_BWD["bytes"], "traffic_source": TRAFFIC_BWD,
