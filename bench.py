@@ -47,10 +47,10 @@ METRIC = "HBM GB/s (algorithmic bytes / device time) on the tensor hot path: elt
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE activation-backward launch on the bench's
-# [256,256,28,28] tensors, from the ncu capture named here (refresh it when dd_elt_flat_kernel changes)
-TRAFFIC_BWD = {"bytes": 581.1e6, "profile": "profiles/eltwise_backward_dram_traffic.md",
-               "captured_at_commit": "a6bdb21", "captured_on": "2026-11-25",
-               "note": "reads 411.1 MB = the algorithmic input; writes 170.0 MB (the tail of dx is still in L2 when the "
+# [256,256,28,28] tensors, from the ncu capture named here (refresh it when the activation kernels change)
+TRAFFIC_BWD = {"bytes": 578.6e6, "profile": "profiles/eltwise_backward_dram_traffic.md",
+               "captured_at_commit": "7b2758d", "captured_on": "2026-11-25",
+               "note": "reads 411.1 MB = the algorithmic input; writes 167.5 MB (the tail of dx is still in L2 when the "
                        "kernel ends) against 616.6 MB algorithmic"}
 PASSES_PER_STEP = 36          # 36 passes x 0.71 ms: 20 steps last about half a second
 STEP_BYTES_PER_PASS = 4 * (2 + 3) * len(ACTS) * 256 * 256 * 28 * 28
