@@ -467,7 +467,9 @@ template <typename T, typename C, int OPC, int VEC, bool PEER>
 __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedParams p) {
   // VEC: 1 = 16-byte loads, 2 = 8-byte loads (16-bit types whose runs are only 8-byte aligned), 0 = one element
   constexpr int V = VEC == 1 ? 16 / sizeof(T) : (VEC == 2 ? 8 / sizeof(T) : 1);
-  constexpr int U = VEC == 2 ? 8 : 4;  // independent loads in flight per thread (the 8-byte ones: twice as many)
+  // independent loads in flight per thread: four of 16 bytes, eight of 8 bytes; element loads (runs
+  // that are not vector-aligned: 7 x 7 and 13 x 13 maps) 16 of a 16-bit type, 8 of a 32-bit one
+  constexpr int U = VEC == 2 ? 8 : (VEC == 0 ? (sizeof(T) == 2 ? 16 : (sizeof(T) == 4 ? 8 : 4)) : 4);
   __shared__ C smem[8];
   dd_pdl_prologue();
   unsigned peerCall = 0;
@@ -642,7 +644,7 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
 template <typename T, typename C, int OPC, int VEC, bool PEER>
 __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_reduce_col_kernel(ddRedParams p) {
   constexpr int V = VEC == 1 ? 16 / sizeof(T) : (VEC == 2 ? 8 / sizeof(T) : 1);  // as in the row kernel
-  constexpr int U = VEC == 2 ? 8 : 4;
+  constexpr int U = VEC == 2 ? 8 : (VEC == 0 ? (sizeof(T) == 2 ? 16 : (sizeof(T) == 4 ? 8 : 4)) : 4);
   __shared__ C smem[256 * V];
   // Large inputs launch this kernel the ordinary way (the programmatic launch measured 4 % slower on
   // a 268 MB tensor), small ones programmatically; the wait returns at once in the first case.
