@@ -360,6 +360,63 @@ static ddStatus_t launch_by_type(ddHandle_t h, ddDataType_t t, const ddRedPlan &
   DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
 }
 
+// Reductions over (outer dim, innermost runs) whose runs are NOT vector-aligned -- the per-channel
+// sum of an nchw tensor with 7 x 7 or 13 x 13 maps, which is also the bias gradient of such a layer:
+// x[r1][k2][r2] dense, r2 odd.  The row kernel would walk the runs with element loads (0.13-0.24 of
+// the copy rate measured on [512,1024,7,7]).  The whole block of one r1 is contiguous and a whole
+// number of 16-byte vectors though, so the work is done in two launches instead: a column reduce
+// over r1 that treats (k2, r2) as one kept dim of k2 * r2 elements (16-byte loads, raw accumulators
+// into the handle's scratch), then the finishing kernel folding the r2 accumulators of each k2 in
+// index order and applying the post-operation, alpha and beta.  *done = false: not this case, nothing
+// launched.
+static ddStatus_t dd_reduce_two_stage(ddHandle_t h, const ddReduceTensorStruct *red, const ddRedPlan &pl,
+                                      double alpha, const ddTensorStruct *xd, const void *x, double beta,
+                                      void *y, bool *done) {
+  *done = false;
+  const ddRedParams &p = pl.p;
+  // (a real handle only: the entry point without one has 64 KiB of scratch and keeps to one launch plan)
+  if (!dd_tune("DD_RED_TWO_STAGE", 1) || pl.kind != DD_RED_ROW || pl.vec == 1 || !h->scratch || h->counterSlots == 0)
+    return DD_STATUS_SUCCESS;
+  const int esize = dd_type_size(xd->dtype);
+  const int V = 16 / esize;
+  const int csize = xd->dtype == DD_DATA_DOUBLE ? 8 : 4;
+  const int64_t inner = p.K2 * p.R2;
+  if (p.K1 != 1 || p.R1 < 8 || p.R2 < 2 || p.R2 > 4096 || p.sxR2 != 1 || (p.K2 > 1 && p.sxK2 != p.R2) ||
+      p.sxR1 != inner || inner % V != 0 || (((uintptr_t)x) & 15) || inner >= (1LL << 31))
+    return DD_STATUS_SUCCESS;
+  // stage 1 as a reduction of the [R1, inner] matrix over its first dim
+  ddTensorStruct x1 = *xd, y1 = *xd;
+  x1.nd = y1.nd = 2;
+  x1.dims[0] = p.R1; x1.dims[1] = inner; x1.strides[0] = inner; x1.strides[1] = 1;
+  y1.dims[0] = 1; y1.dims[1] = inner; y1.strides[0] = inner; y1.strides[1] = 1;
+  ddRedPlan p1;
+  ddStatus_t st = dd_reduce_plan(h, red, &x1, x, &y1, &p1, DD_PLAN_STRUCTURED);
+  if (st != DD_STATUS_SUCCESS || p1.kind != DD_RED_COL || p1.vec != 1) return DD_STATUS_SUCCESS;
+  const size_t tempBytes = (((size_t)inner * csize) + 255) & ~(size_t)255;
+  const size_t ctrBytes = h->counterSlots * sizeof(unsigned);
+  if (h->scratchBytes < ctrBytes + p1.wsBytes + tempBytes + 256) return DD_STATUS_SUCCESS;
+  void *temp = (char *)h->scratch + h->scratchBytes - tempBytes;  // stage 1's own partials sit at the front
+  st = dd_reduce_impl(h, red, nullptr, 0, 1.0, &x1, x, 0.0, &y1, nullptr, /*partialOnly=*/true, temp);
+  if (st != DD_STATUS_SUCCESS) return st;
+  ddRedPlan p2 = pl;  // the outputs, post-operation and count of the whole reduction
+  p2.foldS = (int)p.R2;
+  p2.p.y = y;
+  p2.p.alpha = alpha;
+  p2.p.beta = beta;
+  p2.p.partOut = nullptr;
+  p2.p.counters = nullptr;
+  p2.p.peerDistributed = 0;
+  switch (xd->dtype) {
+    case DD_DATA_FLOAT: st = dd_reduce_finish_launch<float, float>(h, p2, temp); break;
+    case DD_DATA_DOUBLE: st = dd_reduce_finish_launch<double, double>(h, p2, temp); break;
+    case DD_DATA_HALF: st = dd_reduce_finish_launch<__half, float>(h, p2, temp); break;
+    case DD_DATA_BFLOAT16: st = dd_reduce_finish_launch<__nv_bfloat16, float>(h, p2, temp); break;
+    default: DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
+  }
+  *done = st == DD_STATUS_SUCCESS;
+  return st;
+}
+
 ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *ws, size_t wsBytes,
                           double alpha, const ddTensorStruct *xd, const void *x, double beta,
                           const ddTensorStruct *yd, void *y, bool partialOnly, void *partialOut) {
@@ -368,6 +425,11 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
   if (st != DD_STATUS_SUCCESS) return st;
   if (partialOnly && pl.kind == DD_RED_GENERIC)
     DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "sharded reduce: this dim pattern is not supported");
+  if (!partialOnly) {
+    bool done = false;
+    st = dd_reduce_two_stage(h, red, pl, alpha, xd, x, beta, y, &done);
+    if (st != DD_STATUS_SUCCESS || done) return st;
+  }
   unsigned *counters = nullptr;
   if (pl.wsBytes > 0) {
     // arrival counters live in the first DD_COUNTER_BYTES of the handle's own scratch (zeroed at

@@ -987,6 +987,7 @@ struct ddRedPlan {
   int64_t nout;
   size_t wsBytes;  // workspace needed (0 when every output has a single split)
   unsigned grid;
+  int foldS;       // finishing launch only: values of `part` folded per output (0: one, the all-reduced form)
 };
 
 ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd,
@@ -1077,11 +1078,11 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
   template <int OPC>                                                                               \
   static ddStatus_t finish_opc_##T(ddHandle_t h, const ddRedPlan &pl, const void *part) {          \
     ddRedParams p = pl.p;                                                                          \
-    p.S = 1;                                                                                       \
+    p.S = pl.foldS > 0 ? pl.foldS : 1;                                                             \
     p.partialOnly = 0;                                                                             \
-    unsigned fg = dd_flat_grid(h, pl.nout, 256, 8);                                                \
+    unsigned fg = dd_flat_grid(h, p.S > 32 ? pl.nout * 32 : pl.nout, 256, 8);                      \
     dd_reduce_finish_kernel<T, C, OPC><<<fg, 256, 0, h->stream>>>(p, part);                        \
-    DD_LAUNCHED(h, "reduce/finish");                                                               \
+    DD_LAUNCHED(h, pl.foldS > 0 ? "reduce/col+fold-runs" : "reduce/finish");                       \
     return DD_STATUS_SUCCESS;                                                                      \
   }                                                                                                \
   template <int OPC>                                                                               \

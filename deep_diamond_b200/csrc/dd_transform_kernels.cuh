@@ -288,6 +288,142 @@ __global__ void __launch_bounds__(256) dd_tile_scalar_kernel(ddTileParams p) {
   }
 }
 
+// ------------------------------------------------------------------ tile, short odd rows ------
+// The same A/B transposition when the rows on ONE side are short and not 16-byte aligned (7 x 7,
+// 13 x 13, 14 x 14 maps of an nchw tensor: rows of 49, 169, 196 elements) while the block those rows
+// form is contiguous and starts on a 16-byte boundary.  That side is then moved as a FLAT stream of
+// aligned 16-byte vectors that pays no attention to where rows begin, the other side with 16-byte
+// vectors along its own rows, and shared memory (element accesses, which are cheap there) does the
+// re-indexing between the two.  Against dd_tile_scalar_kernel, whose global accesses are single
+// elements: 16-byte global accesses on both sides for every element width.
+//
+//   flat-in   x[batch][b][a] with rows of LA elements back to back (sxB == LA): a CTA copies `rows`
+//             rows of B (a contiguous chunk of x) into shared memory as it lies, then writes, for
+//             every a, 16-byte vectors along b gathered from the chunk.
+//   flat-out  y[batch][a][b] with rows of LB elements back to back (syA == LB): a CTA reads `rows`
+//             elements of A for every b (16-byte vectors along a) into a pitched shared-memory
+//             matrix, then writes its chunk of y as flat 16-byte vectors gathered from it.
+struct ddTileFlatParams {
+  const void *x;
+  void *y;
+  int64_t LA, LB;
+  int64_t sxB, syA;          // flat-in: sxB == LA; flat-out: syA == LB
+  int nb;
+  int64_t bdims[DD_TILE_BATCH_DIMS], bsx[DD_TILE_BATCH_DIMS], bsy[DD_TILE_BATCH_DIMS];
+  ddFastDiv fdBatch[DD_TILE_BATCH_DIMS];
+  int rows;                  // rows of B (flat-in) or of A (flat-out) per CTA, a multiple of 16
+  uint32_t chunks;           // CTAs per batch entry
+  ddFastDiv fdChunks;
+  ddFastDiv fdInner;         // flat-in: 2 * LA (output items run a-fastest in pairs along b); flat-out: LB
+  ddFastDiv fdVPR;           // flat-out: 16-byte vectors per full row of the chunk (rows / VS, at most 256)
+  int pitch;                 // flat-out: elements of S between rows of the shared-memory matrix
+  unsigned smemBytes;
+  double alpha;
+};
+
+template <typename S>
+__device__ __forceinline__ void dd_tile_flat_batch(const ddTileFlatParams &p, uint32_t id, int64_t &offx, int64_t &offy) {
+  offx = 0;
+  offy = 0;
+  for (int d = p.nb - 1; d >= 0; d--) {
+    uint32_t r;
+    dd_divmod(id, p.fdBatch[d], id, r);
+    offx += (int64_t)r * p.bsx[d];
+    offy += (int64_t)r * p.bsy[d];
+  }
+}
+
+template <typename S, typename D, typename C, bool RAW>
+__global__ void __launch_bounds__(256) dd_tile_flatin_kernel(ddTileFlatParams p) {
+  constexpr int VS = 16 / sizeof(S), VD = 16 / sizeof(D);
+  extern __shared__ __align__(16) unsigned char dd_flat_smem[];
+  S *chunk = (S *)dd_flat_smem;
+  dd_pdl_prologue();
+  uint32_t batch, ck;
+  dd_divmod(blockIdx.x, p.fdChunks, batch, ck);
+  int64_t offx, offy;
+  dd_tile_flat_batch<S>(p, batch, offx, offy);
+  const int64_t b0 = (int64_t)ck * p.rows;
+  const int rb = (int)(p.LB - b0 < p.rows ? p.LB - b0 : p.rows);  // rows of B in this chunk (a multiple of VD)
+  const int LA = (int)p.LA;
+  const S *xc = (const S *)p.x + offx + b0 * LA;                  // 16-byte aligned: b0 is a multiple of 16
+  const int n = rb * LA;
+  const C alpha = (C)p.alpha;
+  {  // the chunk as it lies: 16-byte vectors, then the few elements that do not fill one
+    const int nv = n / VS;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) ((uint4 *)chunk)[i] = ((const uint4 *)xc)[i];
+    for (int i = nv * VS + threadIdx.x; i < n; i += blockDim.x) chunk[i] = xc[i];
+  }
+  __syncthreads();
+  // output items: (pair of 16-byte vectors along b) x (a), lanes running over the two vectors of a
+  // pair first (one 32-byte sector) and over a next
+  D *yc = (D *)p.y + offy + b0;
+  const int nvb = rb / VD;
+  const uint32_t items = (uint32_t)(((nvb + 1) / 2) * 2 * LA);
+  for (uint32_t i = threadIdx.x; i < items; i += blockDim.x) {
+    uint32_t pr, rem;
+    dd_divmod(i, p.fdInner, pr, rem);
+    const int a = (int)(rem >> 1), bv = (int)(pr * 2 + (rem & 1u));
+    if (bv >= nvb) continue;
+    const S *src = chunk + (size_t)(bv * VD) * LA + a;
+    __align__(16) D out[VD];
+#pragma unroll
+    for (int j = 0; j < VD; j++) out[j] = dd_cvt<S, D, C, RAW>::f(src[(size_t)j * LA], alpha);
+    *(uint4 *)(yc + (int64_t)a * p.syA + bv * VD) = *(const uint4 *)out;
+  }
+}
+
+template <typename S, typename D, typename C, bool RAW>
+__global__ void __launch_bounds__(256) dd_tile_flatout_kernel(ddTileFlatParams p) {
+  constexpr int VS = 16 / sizeof(S), VD = 16 / sizeof(D);
+  extern __shared__ __align__(16) unsigned char dd_flat_smem[];
+  S *mat = (S *)dd_flat_smem;  // [LB][pitch]; the pitch is an odd number of 32-bit words (of 64-bit ones for 8-byte S)
+  dd_pdl_prologue();
+  uint32_t batch, ck;
+  dd_divmod(blockIdx.x, p.fdChunks, batch, ck);
+  int64_t offx, offy;
+  dd_tile_flat_batch<S>(p, batch, offx, offy);
+  const int64_t a0 = (int64_t)ck * p.rows;
+  const int ra = (int)(p.LA - a0 < p.rows ? p.LA - a0 : p.rows);  // elements of A in this chunk (a multiple of VS)
+  const int LB = (int)p.LB;
+  const S *xc = (const S *)p.x + offx + a0;
+  const C alpha = (C)p.alpha;
+  {  // rows of x (16-byte vectors along a) into the matrix, 32 bits at a time (the pitch is not a
+     // multiple of 16 bytes); threads run over the vectors of a row first
+    const int nva = ra / VS;
+    uint32_t tb, tv;
+    dd_divmod(threadIdx.x, p.fdVPR, tb, tv);
+    const int step = (int)(blockDim.x / p.fdVPR.d);
+    if ((int)tv < nva)
+      for (int b = (int)tb; b < LB; b += step) {
+        const uint4 in = *(const uint4 *)(xc + (int64_t)b * p.sxB + tv * VS);
+        uint32_t *dst = (uint32_t *)(mat + (size_t)b * p.pitch + tv * VS);
+        dst[0] = in.x; dst[1] = in.y; dst[2] = in.z; dst[3] = in.w;
+      }
+  }
+  __syncthreads();
+  // the chunk of y, a0 * LB elements into the batch entry's block, as flat 16-byte vectors
+  D *yc = (D *)p.y + offy + a0 * LB;
+  const int n = ra * LB;
+  const int nv = n / VD;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint32_t ar, b;
+    dd_divmod((uint32_t)(i * VD), p.fdInner, ar, b);
+    __align__(16) D out[VD];
+#pragma unroll
+    for (int j = 0; j < VD; j++) {
+      out[j] = dd_cvt<S, D, C, RAW>::f(mat[(size_t)b * p.pitch + ar], alpha);
+      if (++b == (uint32_t)LB) { b = 0; ar++; }
+    }
+    *(uint4 *)(yc + (int64_t)i * VD) = *(const uint4 *)out;
+  }
+  for (int f = nv * VD + threadIdx.x; f < n; f += blockDim.x) {
+    uint32_t ar, b;
+    dd_divmod((uint32_t)f, p.fdInner, ar, b);
+    yc[f] = dd_cvt<S, D, C, RAW>::f(mat[(size_t)b * p.pitch + ar], alpha);
+  }
+}
+
 // ------------------------------------------------------------------ strided ------------------
 
 struct ddStridedXformParams {
@@ -550,6 +686,100 @@ static ddStatus_t dd_launch_tile(ddHandle_t h, const ddTileParams &tp, int kind)
   return DD_STATUS_SUCCESS;
 }
 
+// The short-odd-rows forms for a transposition that dd_tile_plan left to the scalar tile: returns 0
+// (neither applies), 3 (flat-in) or 4 (flat-out) and fills `fp`.
+template <typename S, typename D>
+static int dd_tile_flat_plan(const ddTileParams &tp, ddTileFlatParams *fp) {
+  constexpr int VS = 16 / (int)sizeof(S), VD = 16 / (int)sizeof(D);
+  if (!dd_tune("DD_TILE_FLAT", 1)) return 0;
+  // shared memory per CTA: 16 KB measured best over 8, 16, 24 and 32 on 7 x 7 and 14 x 14 maps of f32 and
+  // int8 tensors, both directions (more resident CTAs against longer contiguous chunks)
+  const int64_t SMEM = (int64_t)dd_tune("DD_TILE_FLAT_KB", 16) << 10;
+  if ((((uintptr_t)tp.x) | ((uintptr_t)tp.y)) & 15) return 0;
+  if (tp.LA >= (1 << 20) || tp.LB >= (1 << 20)) return 0;
+  int64_t batches = 1;
+  for (int i = 0; i < tp.nb; i++) batches *= tp.bdims[i];
+  auto all = [&](const int64_t *st, int64_t m) {
+    for (int i = 0; i < tp.nb; i++)
+      if (tp.bdims[i] > 1 && st[i] % m) return false;
+    return true;
+  };
+  int kind = 0, rows = 0;
+  // (rows too long for sixteen of them in that much get twice as much)
+  for (int64_t budget = SMEM; !kind && budget <= 2 * SMEM; budget *= 2) {
+    if (tp.sxB == tp.LA && tp.LB % VD == 0 && tp.syA % VD == 0 && all(tp.bsx, VS) && all(tp.bsy, VD)) {
+      rows = (int)((budget / (tp.LA * (int64_t)sizeof(S))) / 16 * 16);
+      if (rows >= 16) kind = 3;
+    }
+    if (!kind && tp.syA == tp.LB && tp.LA % VS == 0 && tp.sxB % VS == 0 && all(tp.bsx, VS) && all(tp.bsy, VD)) {
+      // rows of A per CTA: LB * (rows + pad) elements of S in shared memory, at most 256 vectors per row
+      const int pad = sizeof(S) >= 4 ? 1 : 4 / (int)sizeof(S);
+      rows = (int)((budget / (tp.LB * (int64_t)sizeof(S)) - pad) / 16 * 16);
+      if (rows > 256 * VS) rows = 256 * VS;
+      if (rows >= 16) kind = 4;
+    }
+  }
+  if (!kind) return 0;
+  const int64_t extent = kind == 3 ? tp.LB : tp.LA;
+  if (rows > (extent + 15) / 16 * 16) rows = (int)((extent + 15) / 16 * 16);
+  const int64_t chunks = (extent + rows - 1) / rows;
+  if (batches * chunks >= 0x7fffffffLL) return 0;
+  fp->x = tp.x;
+  fp->y = tp.y;
+  fp->LA = tp.LA;
+  fp->LB = tp.LB;
+  fp->sxB = tp.sxB;
+  fp->syA = tp.syA;
+  fp->nb = tp.nb;
+  for (int i = 0; i < tp.nb; i++) {
+    fp->bdims[i] = tp.bdims[i];
+    fp->bsx[i] = tp.bsx[i];
+    fp->bsy[i] = tp.bsy[i];
+    fp->fdBatch[i] = tp.fdBatch[i];
+  }
+  fp->rows = rows;
+  fp->chunks = (uint32_t)chunks;
+  fp->fdChunks = dd_fastdiv((uint32_t)chunks);
+  fp->alpha = tp.alpha;
+  if (kind == 3) {
+    fp->fdInner = dd_fastdiv((uint32_t)(2 * tp.LA));
+    fp->fdVPR = dd_fastdiv(1);
+    fp->pitch = 0;
+    fp->smemBytes = (unsigned)(rows * tp.LA * (int64_t)sizeof(S) + 16);
+  } else {
+    const int pad = sizeof(S) >= 4 ? 1 : 4 / (int)sizeof(S);
+    fp->fdInner = dd_fastdiv((uint32_t)tp.LB);
+    fp->fdVPR = dd_fastdiv((uint32_t)(rows / VS));
+    fp->pitch = rows + pad;
+    fp->smemBytes = (unsigned)(tp.LB * (int64_t)fp->pitch * (int64_t)sizeof(S) + 16);
+  }
+  return kind;
+}
+
+template <typename S, typename D, typename C, bool RAW>
+static ddStatus_t dd_launch_tile_flat(ddHandle_t h, const ddTileFlatParams &fp, int kind) {
+  int64_t batches = 1;
+  for (int i = 0; i < fp.nb; i++) batches *= fp.bdims[i];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(batches * fp.chunks), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = fp.smemBytes;
+  cfg.stream = h->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (kind == 3) {
+    cudaLaunchKernelEx(&cfg, dd_tile_flatin_kernel<S, D, C, RAW>, fp);
+    DD_LAUNCHED(h, "transform/tile-flat-in");
+  } else {
+    cudaLaunchKernelEx(&cfg, dd_tile_flatout_kernel<S, D, C, RAW>, fp);
+    DD_LAUNCHED(h, "transform/tile-flat-out");
+  }
+  return DD_STATUS_SUCCESS;
+}
+
 template <typename S, typename D, typename C, bool RAW>
 static ddStatus_t dd_launch_strided(ddHandle_t h, const ddXformPlan &pl) {
   ddStridedXformParams p;
@@ -604,6 +834,10 @@ static ddStatus_t dd_xform_typed(ddHandle_t h, const ddXformPlan &pl) {
   if (int kind = dd_tile_plan<S, D>(pl, &tp)) {
     if constexpr (RAW && sizeof(S) == 1)
       if (kind == 1 && dd_launch_tile_tma(h, tp)) return DD_STATUS_SUCCESS;
+    if (kind == 2) {
+      ddTileFlatParams fp;
+      if (int fk = dd_tile_flat_plan<S, D>(tp, &fp)) return dd_launch_tile_flat<S, D, C, RAW>(h, fp, fk);
+    }
     return dd_launch_tile<S, D, C, RAW>(h, tp, kind);
   }
   if (dd_launch_rows<S, D, C, RAW>(h, pl)) {

@@ -32,6 +32,30 @@ def test_each_plan_against_the_oracle(fact, dev, oracle, op, shape, yshape, kern
     assert fact.handle.last_kernel() == kernel
 
 
+@pytest.mark.parametrize("op", ["add", "avg", "norm1", "norm2", "max", "min", "amax", "mul"])
+@pytest.mark.parametrize("shape", [[64, 256, 7, 7], [16, 96, 13, 13], [9, 8, 3, 5], [40, 4, 1, 50]])
+def test_dense_odd_runs_reduce_in_two_stages(fact, dev, oracle, op, shape):
+    """Per-channel reductions of nchw tensors whose maps are not whole 16-byte vectors (49, 169, 15
+    elements; and rows of 50 that are not 16-byte aligned from one channel to the next): a column reduce over
+    n with (c, h, w) as one kept dim, then a fold of each channel's run."""
+    n, c, h, w = shape
+    run_reduce(fact, dev, oracle, op, shape, [1, c, 1, 1], seed=71, expect="reduce/col+fold-runs")
+
+
+def test_bias_gradient_on_seven_by_seven_maps(fact, dev, oracle):
+    """ddConvolutionBackwardBias (sum of dy over n, h, w) on [32, 512, 7, 7]: the same two-stage plan."""
+    shape = [32, 512, 7, 7]
+    dyv = oracle.gen_signed_lognormal(shape, 72)
+    want = dyv.astype(np.float64).sum(axis=(0, 2, 3))
+    mag = np.abs(dyv.astype(np.float64)).sum(axis=(0, 2, 3))
+    tdy, tdb = dev.put(dyv), dev.put(np.zeros(512, np.float32))
+    core.convolution_bwd_bias(fact.handle, 1.0, core.tensor_descriptor(shape, "float", "nchw"), tdy, 0.0,
+                              core.tensor_descriptor([1, 512, 1, 1], "float", "nchw"), tdb)
+    assert fact.handle.last_kernel() == "reduce/col+fold-runs"
+    got = dev.get(tdb, np.float32).astype(np.float64)
+    assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 64 * 6e-8 * mag).all()
+
+
 def test_hundreds_of_splits_folded_by_a_warp(fact, dev, oracle):
     """One output over 6.4 M elements: more than 32 splits, so the last arrival folds the partials
     with a whole warp; and the same through the entry point that has no arrival counters (its
@@ -67,7 +91,8 @@ def test_hundreds_of_splits_folded_by_a_warp(fact, dev, oracle):
     # 14 x 14 maps: runs of 196 elements start on 8-byte boundaries only, so 8-byte loads
     ("max", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),
     ("add", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),
-    ("add", [32, 512, 14, 14], [1, 512, 1, 1], "reduce/row-v8"),
+    ("add", [32, 512, 14, 14], [1, 512, 1, 1], "reduce/col+fold-runs"),  # dense odd runs: column reduce over n, then a fold of each run
+    ("add", [6, 512, 14, 14], [1, 512, 1, 1], "reduce/row-v8"),           # too few rows for that: 8-byte loads along the runs
     ("max", [2, 6, 14, 14], [1, 6, 1, 1], "reduce/row-v8"),
     ("add", [3, 5, 7, 10], [3, 1, 7, 10], "reduce/col"),          # 70 elements per row: not a multiple of 4
 ])

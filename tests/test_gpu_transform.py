@@ -56,7 +56,7 @@ def run_case(fact, dev, oracle, shape, sx, sy, sdt, ddt, alpha=1.0, beta=0.0, se
     core.transform_tensor(fact.handle, alpha, xd, dx, beta, yd, dy)
     got = dev.get(dy, NP[ddt])
     if expect:
-        assert fact.handle.last_kernel() == expect
+        assert fact.handle.last_kernel() in ((expect,) if isinstance(expect, str) else expect), fact.handle.last_kernel()
     same = got.view(np.uint8) == want.view(np.uint8)
     if not same.all() and ddt in ("half", "bf16", "float", "double"):
         # NaN payloads may differ between the CPU and GPU converters; everything else is exact
@@ -130,12 +130,19 @@ def test_nchw_nhwc_both_ways(fact, dev, oracle, shape, pair):
     run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=5)
 
 
+ODD_TILE = ("transform/tile-scalar", "transform/tile-flat-in", "transform/tile-flat-out")
+
+
 def test_unaligned_transposes_use_the_scalar_tile(fact, dev, oracle):
-    # rows not 16-byte aligned: odd spatial sizes (7x7, 13x13), odd channel counts, every type width
+    # rows not 16-byte aligned: odd spatial sizes (7x7, 13x13), odd channel counts, every type width.
+    # Where the short side's block is contiguous and the long side is vector-aligned the flat forms
+    # run (asserted exactly in test_short_odd_rows_go_through_the_flat_tile), else the scalar tile.
     for shape in ([3, 24, 7, 7], [2, 33, 13, 13], [5, 9, 3, 11], [1, 100, 1, 37]):
         for sdt, ddt in (("float", "float"), ("float", "bf16"), ("byte", "byte"), ("half", "float"), ("double", "float")):
-            run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), sdt, ddt, seed=31, expect="transform/tile-scalar")
-            run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=32, expect="transform/tile-scalar")
+            run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), sdt, ddt, seed=31, expect=ODD_TILE)
+            run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=32, expect=ODD_TILE)
+    for shape in ([2, 33, 13, 13], [5, 9, 3, 11]):  # odd channel counts: neither side is vector-aligned
+        run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), "float", "float", seed=31, expect="transform/tile-scalar")
     # an unaligned base pointer demotes an otherwise aligned reorder to the scalar tile
     shape = [2, 32, 8, 16]
     xs = make_values(np.random.default_rng(33), 1 + int(np.prod(shape)), "float")
@@ -157,6 +164,44 @@ def test_tile_ragged_edges(fact, dev, oracle):
              seed=7, expect="transform/tile")
     run_case(fact, dev, oracle, [2, 144, 4, 40], nchw([2, 144, 4, 40]), nhwc([2, 144, 4, 40]), "float", "bf16",
              seed=8, expect="transform/tile")
+
+
+@pytest.mark.parametrize("pair", [("float", "float"), ("byte", "byte"), ("float", "bf16"), ("bf16", "float"),
+                                  ("half", "half"), ("double", "double"), ("float", "byte"), ("byte", "float"),
+                                  ("uint8", "uint8"), ("int", "float"), ("long", "long")])
+@pytest.mark.parametrize("shape", [[3, 64, 7, 7], [2, 48, 13, 13], [5, 32, 14, 14], [2, 256, 7, 7], [1, 16, 3, 5],
+                                   [2, 400, 5, 5], [7, 16, 9, 9]])
+def test_short_odd_rows_go_through_the_flat_tile(fact, dev, oracle, shape, pair):
+    """nchw <-> nhwc with maps of 49, 169, 196, 15, 25, 81 elements and channel counts that are whole
+    vectors: the nchw side moves as a flat stream of aligned 16-byte vectors (flat-in when it is the
+    source, flat-out when it is the destination).  Bit for bit against the oracle; the canary in
+    run_case checks that nothing is written outside the tensor."""
+    sdt, ddt = pair
+    n, c, hgt, w = shape
+    vs, vd = 16 // np.dtype(NP[sdt]).itemsize, 16 // np.dtype(NP[ddt]).itemsize
+    hw = hgt * w
+    aligned_in = (c * hw) % vs == 0 or n == 1     # every batch entry's nchw block starts on a 16-byte boundary
+    aligned_out = (c * hw) % vd == 0 or n == 1
+    ok_in = aligned_in and c % vd == 0 and hw % vs != 0 and 16 * hw * np.dtype(NP[sdt]).itemsize <= 32768
+    ok_out = aligned_out and c % vs == 0 and hw % vd != 0
+    run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), sdt, ddt, seed=61,
+             expect="transform/tile-flat-in" if ok_in else ODD_TILE + ("transform/tile", "transform/strided"))
+    run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=62,
+             expect="transform/tile-flat-out" if ok_out else ODD_TILE + ("transform/tile", "transform/strided"))
+
+
+def test_flat_tile_many_chunks_and_batches(fact, dev, oracle):
+    # more rows than one CTA's chunk holds (2048 channels of 49 bytes: 7 chunks; 2000 of 169 floats: 125 chunks),
+    # a partial last chunk, and two batch dims that do not merge
+    run_case(fact, dev, oracle, [3, 2048, 7, 7], nchw([3, 2048, 7, 7]), nhwc([3, 2048, 7, 7]), "byte", "byte", seed=63,
+             expect="transform/tile-flat-in")
+    run_case(fact, dev, oracle, [3, 2048, 7, 7], nhwc([3, 2048, 7, 7]), nchw([3, 2048, 7, 7]), "byte", "byte", seed=64,
+             expect="transform/tile-flat-out")
+    shape = [2, 2000, 13, 13]
+    run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), "float", "bf16", seed=65, expect="transform/tile-flat-in")
+    run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), "bf16", "float", seed=66, expect="transform/tile-flat-out")
+    run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), "byte", "byte", seed=67, expect="transform/tile-flat-in")
+    run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), "byte", "byte", seed=68, expect="transform/tile-flat-out")
 
 
 def test_padded_strides_round_trip(fact, dev, oracle):
