@@ -417,6 +417,67 @@ static ddStatus_t dd_reduce_two_stage(ddHandle_t h, const ddReduceTensorStruct *
   return st;
 }
 
+static ddStatus_t finish_by_type(ddHandle_t h, ddDataType_t t, const ddRedPlan &pl, const void *part) {
+  switch (t) {
+    case DD_DATA_FLOAT: return dd_reduce_finish_launch<float, float>(h, pl, part);
+    case DD_DATA_DOUBLE: return dd_reduce_finish_launch<double, double>(h, pl, part);
+    case DD_DATA_HALF: return dd_reduce_finish_launch<__half, float>(h, pl, part);
+    case DD_DATA_BFLOAT16: return dd_reduce_finish_launch<__nv_bfloat16, float>(h, pl, part);
+    default: break;
+  }
+  DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data type must be floating point");
+}
+
+// Column reductions (reduce across a strided dim, innermost kept: max over C of an nchw tensor) whose
+// kept rows are NOT whole vectors (7 x 7 maps: 49 elements) but follow one another densely:
+// x[k1][r1][k2], sxR1 == K2.  P = V / gcd(K2, V) consecutive rows together are a whole number of
+// vectors, so the reduction runs over r1 / P with P * K2 kept elements (16-byte loads; element
+// j * K2 + k2 of a kept row belongs to output k2 and to the rows r1 = j mod P), raw accumulators into
+// the handle's scratch, and a second launch folds the P sets.  *done = false: not this case.
+static ddStatus_t dd_reduce_col_periodic(ddHandle_t h, const ddReduceTensorStruct *red, const ddRedPlan &pl,
+                                         double alpha, const ddTensorStruct *xd, const void *x, double beta,
+                                         void *y, bool *done) {
+  *done = false;
+  const ddRedParams &p = pl.p;
+  if (!dd_tune("DD_RED_PERIODIC", 1) || pl.kind != DD_RED_COL || pl.vec == 1 || !h->scratch || h->counterSlots == 0)
+    return DD_STATUS_SUCCESS;
+  const int esize = dd_type_size(xd->dtype);
+  const int V = 16 / esize;
+  const int csize = xd->dtype == DD_DATA_DOUBLE ? 8 : 4;
+  int g = V;
+  for (int64_t a = p.K2 % V; a;) { int64_t t = g % a; g = (int)a; a = t; }  // gcd(K2, V)
+  const int P = V / g;
+  if (P < 2 || p.K2 < 2 || p.sxK2 != 1 || p.sxR1 != p.K2 || p.R1 % P != 0 || p.R1 / P < 8 ||
+      (p.K1 > 1 && p.sxK1 % V != 0) || (((uintptr_t)x) & 15) || p.K1 * P * p.K2 >= (1LL << 31))
+    return DD_STATUS_SUCCESS;
+  ddTensorStruct x1 = *xd, y1 = *xd;
+  x1.nd = y1.nd = 3;
+  x1.dims[0] = p.K1; x1.dims[1] = p.R1 / P; x1.dims[2] = P * p.K2;
+  x1.strides[0] = p.K1 > 1 ? p.sxK1 : p.R1 * p.K2; x1.strides[1] = P * p.K2; x1.strides[2] = 1;
+  y1.dims[0] = p.K1; y1.dims[1] = 1; y1.dims[2] = P * p.K2;
+  y1.strides[0] = P * p.K2; y1.strides[1] = P * p.K2; y1.strides[2] = 1;
+  ddRedPlan p1;
+  ddStatus_t st = dd_reduce_plan(h, red, &x1, x, &y1, &p1, DD_PLAN_STRUCTURED);
+  if (st != DD_STATUS_SUCCESS || p1.kind != DD_RED_COL || p1.vec != 1) return DD_STATUS_SUCCESS;
+  const size_t tempBytes = (((size_t)(p.K1 * P * p.K2) * csize) + 255) & ~(size_t)255;
+  const size_t ctrBytes = h->counterSlots * sizeof(unsigned);
+  if (h->scratchBytes < ctrBytes + p1.wsBytes + tempBytes + 256) return DD_STATUS_SUCCESS;
+  void *temp = (char *)h->scratch + h->scratchBytes - tempBytes;
+  st = dd_reduce_impl(h, red, nullptr, 0, 1.0, &x1, x, 0.0, &y1, nullptr, /*partialOnly=*/true, temp);
+  if (st != DD_STATUS_SUCCESS) return st;
+  ddRedPlan p2 = pl;
+  p2.foldS = -P;
+  p2.p.y = y;
+  p2.p.alpha = alpha;
+  p2.p.beta = beta;
+  p2.p.partOut = nullptr;
+  p2.p.counters = nullptr;
+  p2.p.peerDistributed = 0;
+  st = finish_by_type(h, xd->dtype, p2, temp);
+  *done = st == DD_STATUS_SUCCESS;
+  return st;
+}
+
 ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *ws, size_t wsBytes,
                           double alpha, const ddTensorStruct *xd, const void *x, double beta,
                           const ddTensorStruct *yd, void *y, bool partialOnly, void *partialOut) {
@@ -428,6 +489,8 @@ ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *w
   if (!partialOnly) {
     bool done = false;
     st = dd_reduce_two_stage(h, red, pl, alpha, xd, x, beta, y, &done);
+    if (st != DD_STATUS_SUCCESS || done) return st;
+    st = dd_reduce_col_periodic(h, red, pl, alpha, xd, x, beta, y, &done);
     if (st != DD_STATUS_SUCCESS || done) return st;
   }
   unsigned *counters = nullptr;

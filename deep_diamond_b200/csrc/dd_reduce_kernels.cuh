@@ -845,6 +845,23 @@ __global__ void __launch_bounds__(256) dd_reduce_finish_kernel(ddRedParams p, co
   }
 }
 
+// Second launch of the column reduce over rows that are not whole vectors (dd_reduce_col_periodic in
+// dd_reduce.cu): `part` holds, per k1, P interleaved sets of K2 raw accumulators (set j covers the
+// rows r1 = j mod P); output (k1, k2) is their fold in set order.
+template <typename T, typename C, int OPC>
+__global__ void __launch_bounds__(256) dd_reduce_fold_sets_kernel(ddRedParams p, const void *part, int P) {
+  const bool nanProp = p.nanProp != 0;
+  const int64_t nout = p.K1 * p.K2;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < nout; o += nthreads) {
+    const int64_t k1 = o / p.K2, k2 = o - k1 * p.K2;
+    const C *pp = (const C *)part + k1 * (P * p.K2) + k2;
+    C acc = pp[0];
+    for (int j = 1; j < P; j++) acc = dd_red<C, OPC>::comb(acc, pp[(int64_t)j * p.K2], nanProp);
+    dd_red_finish<T, C>(p, k1, k2, acc);
+  }
+}
+
 // ------------------------------------------------------------------ cross-GPU exchange --------
 //
 // One process per GPU, every rank holding the raw accumulators of its own shard (nout values of C).
@@ -987,7 +1004,8 @@ struct ddRedPlan {
   int64_t nout;
   size_t wsBytes;  // workspace needed (0 when every output has a single split)
   unsigned grid;
-  int foldS;       // finishing launch only: values of `part` folded per output (0: one, the all-reduced form)
+  int foldS;       // finishing launch only: values of `part` folded per output (0: one, the all-reduced form;
+                   // negative: -foldS interleaved sets, dd_reduce_fold_sets_kernel)
 };
 
 ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd,
@@ -1080,6 +1098,12 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
     ddRedParams p = pl.p;                                                                          \
     p.S = pl.foldS > 0 ? pl.foldS : 1;                                                             \
     p.partialOnly = 0;                                                                             \
+    if (pl.foldS < 0) {                                                                            \
+      unsigned fs = dd_flat_grid(h, pl.nout, 256, 8);                                              \
+      dd_reduce_fold_sets_kernel<T, C, OPC><<<fs, 256, 0, h->stream>>>(p, part, -pl.foldS);        \
+      DD_LAUNCHED(h, "reduce/col+fold-sets");                                                      \
+      return DD_STATUS_SUCCESS;                                                                    \
+    }                                                                                              \
     unsigned fg = dd_flat_grid(h, p.S > 32 ? pl.nout * 32 : pl.nout, 256, 8);                      \
     dd_reduce_finish_kernel<T, C, OPC><<<fg, 256, 0, h->stream>>>(p, part);                        \
     DD_LAUNCHED(h, pl.foldS > 0 ? "reduce/col+fold-runs" : "reduce/finish");                       \

@@ -42,6 +42,16 @@ def test_dense_odd_runs_reduce_in_two_stages(fact, dev, oracle, op, shape):
     run_reduce(fact, dev, oracle, op, shape, [1, c, 1, 1], seed=71, expect="reduce/col+fold-runs")
 
 
+@pytest.mark.parametrize("op", ["add", "avg", "norm2", "max", "min", "amax"])
+@pytest.mark.parametrize("shape", [[16, 64, 7, 7], [3, 256, 13, 13], [1, 96, 3, 5], [5, 40, 1, 6]])
+def test_odd_kept_rows_reduce_in_periodic_sets(fact, dev, oracle, op, shape):
+    """Reductions over C of nchw tensors whose maps are not whole vectors (49, 169, 15, 6 elements):
+    four (or two) consecutive channel rows are, so the column reduce runs over groups of them and a
+    second launch folds the interleaved sets."""
+    n, c, h, w = shape
+    run_reduce(fact, dev, oracle, op, shape, [n, 1, h, w], seed=73, expect="reduce/col+fold-sets")
+
+
 def test_bias_gradient_on_seven_by_seven_maps(fact, dev, oracle):
     """ddConvolutionBackwardBias (sum of dy over n, h, w) on [32, 512, 7, 7]: the same two-stage plan."""
     shape = [32, 512, 7, 7]
@@ -89,8 +99,10 @@ def test_hundreds_of_splits_folded_by_a_warp(fact, dev, oracle):
     ("add", [64, 200, 28, 28], [1, 200, 1, 1], "reduce/row-cluster"),   # 16 splits of 4 runs, all used
     ("max", [8, 256, 32, 32], [8, 1, 32, 32], "reduce/col-cluster"),
     # 14 x 14 maps: runs of 196 elements start on 8-byte boundaries only, so 8-byte loads
-    ("max", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),
-    ("add", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),
+    ("max", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col+fold-sets"),  # pairs of rows are whole vectors
+    ("add", [32, 512, 14, 14], [32, 1, 14, 14], "reduce/col+fold-sets"),
+    ("max", [32, 14, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),          # too few rows for that: 8-byte loads
+    ("add", [32, 15, 14, 14], [32, 1, 14, 14], "reduce/col-v8"),          # an odd number of rows
     ("add", [32, 512, 14, 14], [1, 512, 1, 1], "reduce/col+fold-runs"),  # dense odd runs: column reduce over n, then a fold of each run
     ("add", [6, 512, 14, 14], [1, 512, 1, 1], "reduce/row-v8"),           # too few rows for that: 8-byte loads along the runs
     ("max", [2, 6, 14, 14], [1, 6, 1, 1], "reduce/row-v8"),
