@@ -85,9 +85,27 @@ __global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
       C bs = (C)0;
       if (BMODE == 0) {
         bin = *(const uint4 *)(B + e0);
-      } else {  // inner % V == 0: the whole vector shares one channel
+      } else if (BMODE == 1) {  // inner % V == 0: the whole vector shares one channel
         const int64_t ch = dd_channel_of(p, e0);
         bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch * p.sB)));
+      }
+      // BMODE 2: runs of B's value (7 x 7 maps: 49 elements) that are not whole vectors; a vector may
+      // straddle channels, so each element takes its own (the walk below), the accesses to A and C
+      // staying 16 bytes wide
+      int64_t ch2 = 0, pos2 = 0;
+      if (BMODE == 2) {
+        if (p.fast) {
+          uint32_t q, r, c;
+          dd_divmod((uint32_t)e0, p.fdInner, q, r);
+          dd_divmod(q, p.fdChannels, c, q);
+          ch2 = q;
+          pos2 = r;
+        } else {
+          const int64_t q = e0 / p.inner;
+          pos2 = e0 - q * p.inner;
+          ch2 = q % p.channels;
+        }
+        bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch2 * p.sB)));
       }
       uint4 res;
       const T *av = (const T *)&ain, *bv = (const T *)&bin, *ov = (const T *)&oin;
@@ -99,6 +117,11 @@ __global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
         C r = dd_binop<C>(op, a, b);
         if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
         rv[k] = dd_store<T, C>(r);
+        if (BMODE == 2 && ++pos2 == p.inner) {  // the next element starts the next channel's run
+          pos2 = 0;
+          if (++ch2 == p.channels) ch2 = 0;
+          bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch2 * p.sB)));
+        }
       }
       *(uint4 *)(Cp + e0) = res;
     }
@@ -257,7 +280,9 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
     p.alpha2 = alpha2;
     p.beta = beta;
     uintptr_t bits = (uintptr_t)A | (uintptr_t)Cp | (bmode == 0 ? (uintptr_t)B : 0);
-    p.vec = (bits & 15) == 0 && (bmode == 0 || inner % V == 0);
+    p.vec = (bits & 15) == 0;
+    if (bmode == 1 && inner % V != 0) bmode = dd_tune("DD_OP_MIXED", 1) ? 2 : (p.vec = 0, 1);
+    p.bmode = bmode;
     p.fast = c.total < 0x7fffffffLL;
     if (p.fast) {
       p.fdInner = dd_fastdiv((uint32_t)inner);
@@ -265,6 +290,13 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
     }
     unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, dd_tune("DD_OPFLAT_CPS", 8));
     // add and mul (bias, per-channel scale, axpy, sum) get their own instantiations
+    if (bmode == 2) {
+      if (op == DD_OP_TENSOR_ADD) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 2>, grid, 256, h->stream, p);
+      else if (op == DD_OP_TENSOR_MUL) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 2>, grid, 256, h->stream, p);
+      else dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 2>, grid, 256, h->stream, p);
+      DD_LAUNCHED(h, "optensor/flat-bcast-mixed");
+      return DD_STATUS_SUCCESS;
+    }
     if (op == DD_OP_TENSOR_ADD && bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 0>, grid, 256, h->stream, p);
     else if (op == DD_OP_TENSOR_ADD) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 1>, grid, 256, h->stream, p);
     else if (op == DD_OP_TENSOR_MUL && bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 0>, grid, 256, h->stream, p);

@@ -43,6 +43,30 @@ def test_op_tensor_broadcast(fact, dev, oracle, shape, bshape, op):
 
 
 @pytest.mark.parametrize("op", ["add", "mul", "max"])
+@pytest.mark.parametrize("shape,layout", [([6, 40, 7, 7], "nchw"), ([3, 24, 13, 13], "nchw"), ([5, 3, 1, 5], "nchw"),
+                                          ([4, 36, 6, 6], "nhwc"), ([2, 1000, 3, 3], "nchw")])
+def test_channel_runs_that_are_not_whole_vectors(fact, dev, oracle, op, shape, layout):
+    """Bias / per-channel scale where a channel's run (49, 169, 5, 9 elements; 1 for nhwc) is not a
+    multiple of four floats: A and C still move as 16-byte vectors and each element takes its own
+    channel's value."""
+    bshape = [1, shape[1], 1, 1]
+    st = oracle.default_strides(shape) if layout == "nchw" else oracle.nhwc_strides(shape)
+    bst = oracle.default_strides(bshape)
+    a, b, c0 = rnd(shape, 21), rnd(bshape, 22, 0.5, 1.5), rnd(shape, 23)
+    for (a1, a2, beta) in ((1.0, 1.0, 0.0), (0.75, -2.0, 0.5)):
+        want = c0.copy()
+        oracle.binary(op, oracle.as_layout(a, shape, st), oracle.as_layout(b, bshape, bst),
+                      oracle.as_layout(want, shape, st), alpha1=a1, alpha2=a2, beta=beta)
+        ta, tb, tc = dev.put(a), dev.put(b), dev.put(c0)
+        core.op_tensor(fact.handle, op, a1, core.tensor_descriptor(shape, "float", st), ta, a2,
+                       core.tensor_descriptor(bshape, "float", bst), tb, beta,
+                       core.tensor_descriptor(shape, "float", st), tc)
+        assert fact.handle.last_kernel() == "optensor/flat-bcast-mixed"
+        got = dev.get(tc, np.float32)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (op, a1, a2, beta)
+
+
+@pytest.mark.parametrize("op", ["add", "mul", "max"])
 @pytest.mark.parametrize("bshape", [[1, 6, 1, 1], [4, 6, 8, 16], [1, 1, 1, 16], [4, 1, 8, 1]])
 def test_op_tensor_rows_views(fact, dev, oracle, op, bshape):
     """A and C are channel windows of wider tensors (rows contiguous and 16-byte aligned), B a bias,
