@@ -722,6 +722,35 @@ def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
     # fill and scale
     measure("set-tensor (fill)", "[256,256,28,28] f32", n * 4, n, lambda: core.set_tensor(h, d4, y, 0.5))
     measure("scale-tensor", "[256,256,28,28] f32", n * 8, n, lambda: core.scale_tensor(h, 1.0009765625, d4, y))
+    del z
+
+    # the late stages of a CNN: 7 x 7 maps, whose rows of 49 elements are not whole 16-byte vectors
+    s7 = [1024, 1024, 7, 7]
+    n7 = int(np.prod(s7))                       # as many elements as [256,256,28,28]
+    d7 = core.tensor_descriptor(s7, "float", "nchw")
+    d7h = core.tensor_descriptor(s7, "float", "nhwc")
+    bias7 = torch.randn(1024, dtype=torch.float32, device=dev, generator=g)
+    db7 = core.tensor_descriptor([1, 1024, 1, 1], "float", "nchw")
+    measure("bias add on 7x7 maps", "[1024,1024,7,7] f32 nchw", n7 * 8, n7,
+            lambda: core.op_tensor(h, "add", 1.0, d7, x, 1.0, db7, bias7, 0.0, d7, y))
+    gb7 = torch.zeros(1024, dtype=torch.float32, device=dev)
+    measure("bias gradient (sum over N,H,W) on 7x7 maps", "[1024,1024,7,7] f32 nchw", n7 * 4, n7,
+            lambda: core.convolution_bwd_bias(h, 1.0, d7, x, 0.0, db7, gb7))
+    mx7 = torch.zeros(1024 * 49, dtype=torch.float32, device=dev)
+    rmax = core.reduce_tensor_descriptor("max", "float")
+    dm7 = core.tensor_descriptor([1024, 1, 7, 7], "float", "nchw")
+    measure("max over C on 7x7 maps", "[1024,1024,7,7] f32 nchw", n7 * 4, n7,
+            lambda: core.reduce_tensor(h, rmax, 1.0, d7, x, 0.0, dm7, mx7))
+    measure("reorder nchw -> nhwc on 7x7 maps", "[1024,1024,7,7] f32", n7 * 8, n7,
+            lambda: core.transform_tensor(h, 1.0, d7, x, 0.0, d7h, y))
+    measure("reorder nhwc -> nchw on 7x7 maps", "[1024,1024,7,7] f32", n7 * 8, n7,
+            lambda: core.transform_tensor(h, 1.0, d7h, x, 0.0, d7, y))
+    s7b = [2048, 2048, 7, 7]
+    n7b = int(np.prod(s7b))                     # 205 MB of int8, the bytes of x
+    d7b = core.tensor_descriptor(s7b, "byte", "nchw")
+    d7bh = core.tensor_descriptor(s7b, "byte", "nhwc")
+    measure("reorder int8 nchw -> nhwc on 7x7 maps", "[2048,2048,7,7] s8", n7b * 2, n7b,
+            lambda: core.transform_tensor(h, 1.0, d7b, x, 0.0, d7bh, y))
     return rows
 
 
