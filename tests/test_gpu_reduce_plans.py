@@ -52,6 +52,23 @@ def test_odd_kept_rows_reduce_in_periodic_sets(fact, dev, oracle, op, shape):
     run_reduce(fact, dev, oracle, op, shape, [n, 1, h, w], seed=73, expect="reduce/col+fold-sets")
 
 
+def test_two_launch_forms_blend_with_alpha_and_beta(fact, dev, oracle):
+    """y = alpha * reduce(x) + beta * y through both two-launch forms (the blend happens in the
+    second launch), and double precision through the first."""
+    run_reduce(fact, dev, oracle, "add", [32, 48, 7, 7], [1, 48, 1, 1], alpha=0.5, beta=2.0, seed=74,
+               expect="reduce/col+fold-runs")
+    run_reduce(fact, dev, oracle, "norm2", [32, 48, 7, 7], [1, 48, 1, 1], alpha=-1.5, beta=0.25, seed=75,
+               expect="reduce/col+fold-runs")
+    run_reduce(fact, dev, oracle, "max", [8, 64, 7, 7], [8, 1, 7, 7], alpha=0.5, beta=2.0, seed=76,
+               expect="reduce/col+fold-sets")
+    run_reduce(fact, dev, oracle, "avg", [8, 64, 5, 5], [8, 1, 5, 5], alpha=3.0, beta=-1.0, seed=77,
+               expect="reduce/col+fold-sets")
+    run_reduce(fact, dev, oracle, "add", [16, 24, 3, 3], [1, 24, 1, 1], seed=78, dtype="double",
+               expect="reduce/col+fold-runs")
+    run_reduce(fact, dev, oracle, "amax", [4, 64, 3, 3], [4, 1, 3, 3], seed=79, dtype="double",
+               expect="reduce/col+fold-sets")
+
+
 def test_bias_gradient_on_seven_by_seven_maps(fact, dev, oracle):
     """ddConvolutionBackwardBias (sum of dy over n, h, w) on [32, 512, 7, 7]: the same two-stage plan."""
     shape = [32, 512, 7, 7]
