@@ -706,15 +706,15 @@ static int dd_tile_flat_plan(const ddTileParams &tp, ddTileFlatParams *fp) {
   };
   int kind = 0, rows = 0;
   // (rows too long for sixteen of them in that much get twice as much)
-  for (int64_t budget = SMEM; !kind && budget <= 2 * SMEM; budget *= 2) {
+  for (int64_t room = SMEM; !kind && room <= 2 * SMEM; room *= 2) {
     if (tp.sxB == tp.LA && tp.LB % VD == 0 && tp.syA % VD == 0 && all(tp.bsx, VS) && all(tp.bsy, VD)) {
-      rows = (int)((budget / (tp.LA * (int64_t)sizeof(S))) / 16 * 16);
+      rows = (int)((room / (tp.LA * (int64_t)sizeof(S))) / 16 * 16);
       if (rows >= 16) kind = 3;
     }
     if (!kind && tp.syA == tp.LB && tp.LA % VS == 0 && tp.sxB % VS == 0 && all(tp.bsx, VS) && all(tp.bsy, VD)) {
       // rows of A per CTA: LB * (rows + pad) elements of S in shared memory, at most 256 vectors per row
       const int pad = sizeof(S) >= 4 ? 1 : 4 / (int)sizeof(S);
-      rows = (int)((budget / (tp.LB * (int64_t)sizeof(S)) - pad) / 16 * 16);
+      rows = (int)((room / (tp.LB * (int64_t)sizeof(S)) - pad) / 16 * 16);
       if (rows > 256 * VS) rows = 256 * VS;
       if (rows >= 16) kind = 4;
     }

@@ -250,8 +250,8 @@ def set_num_threads(n):
 
 
 # ---------------------------------------------------------------- synthetic inputs ------------
-# Seeded generators for the benchmark configurations (shapes, value distributions and seeds as
-# BASELINE.json states them).  Shared by the GPU and CPU legs so both see identical inputs.
+# Seeded generators for the benchmark configurations (their shapes, value distributions and seeds).
+# Shared by the GPU and CPU legs so both see identical inputs.
 
 def gen_uniform(shape, lo, hi, seed):
     rng = np.random.default_rng(seed)
