@@ -751,6 +751,16 @@ def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
     d7bh = core.tensor_descriptor(s7b, "byte", "nhwc")
     measure("reorder int8 nchw -> nhwc on 7x7 maps", "[2048,2048,7,7] s8", n7b * 2, n7b,
             lambda: core.transform_tensor(h, 1.0, d7b, x, 0.0, d7bh, y))
+    # a batch of images as a loader hands them over (uint8, channels last) into the f32 nchw tensor a
+    # network reads: 3 channels, too thin for a tile
+    simg = [336, 3, 224, 224]
+    nimg = int(np.prod(simg))                   # 50.6 M elements: 50.6 MB in, 202 MB out
+    measure("uint8 nhwc images -> f32 nchw", "[336,3,224,224]", nimg * 5, nimg,
+            lambda: core.transform_tensor(h, 1.0, core.tensor_descriptor(simg, "uint8", "nhwc"), x, 0.0,
+                                          core.tensor_descriptor(simg, "float", "nchw"), y))
+    measure("f32 nchw -> nhwc, 3 channels", "[336,3,224,224]", nimg * 8, nimg,
+            lambda: core.transform_tensor(h, 1.0, core.tensor_descriptor(simg, "float", "nchw"), x, 0.0,
+                                          core.tensor_descriptor(simg, "float", "nhwc"), y))
     return rows
 
 

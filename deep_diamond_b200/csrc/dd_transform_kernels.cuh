@@ -581,7 +581,9 @@ static ddStatus_t dd_launch_flat(ddHandle_t h, const ddXformPlan &pl) {
 }
 
 // Fills tile parameters if the canonical space fits a tile kernel; returns 0 if not, 1 for the
-// 16-byte vector tile kernel, 2 for the scalar tile kernel (rows not 16-byte aligned).
+// 16-byte vector tile kernel, 2 for the scalar tile kernel (rows not 16-byte aligned), -1 for a
+// transposition whose A or B is too thin for either (3 or 4 channels of an image: the parameters are
+// filled for the short-rows forms, which take it if they can).
 template <typename S, typename D>
 static int dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
   typedef dd_tile_geom<S, D> G;
@@ -602,7 +604,7 @@ static int dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
   }
   // a tile that is mostly padding wastes the machine: leave short dims to the other kernels
   if (c.dims[A] < G::VS * 2 || c.dims[B] < G::VD * 2) vec = false;
-  if (!vec && (c.dims[A] < 8 || c.dims[B] < 8)) return 0;  // too thin to be worth a tile
+  const bool thin = !vec && (c.dims[A] < 8 || c.dims[B] < 8);  // too thin to be worth a tile
   // CTA shape of the vector kernel: na lanes along A (5..16) by nb lanes along B (NB, or 2 NB when
   // na <= 8), chosen by the padding the edge tiles would carry
   int na = G::NA, nbLog2 = 0;
@@ -655,7 +657,7 @@ static int dd_tile_plan(const ddXformPlan &pl, ddTileParams *tp) {
   tp->fdB = dd_fastdiv((uint32_t)tp->tilesB);
   for (int i = 0; i < tp->nb; i++) tp->fdBatch[i] = dd_fastdiv((uint32_t)tp->bdims[i]);
   tp->alpha = pl.alpha;
-  return vec ? 1 : 2;
+  return thin ? -1 : (vec ? 1 : 2);
 }
 
 // The 1-byte bit copy with tile loads by the tensor memory accelerator (dd_tile_tma.cu); false when
@@ -834,11 +836,11 @@ static ddStatus_t dd_xform_typed(ddHandle_t h, const ddXformPlan &pl) {
   if (int kind = dd_tile_plan<S, D>(pl, &tp)) {
     if constexpr (RAW && sizeof(S) == 1)
       if (kind == 1 && dd_launch_tile_tma(h, tp)) return DD_STATUS_SUCCESS;
-    if (kind == 2) {
+    if (kind == 2 || kind == -1) {
       ddTileFlatParams fp;
       if (int fk = dd_tile_flat_plan<S, D>(tp, &fp)) return dd_launch_tile_flat<S, D, C, RAW>(h, fp, fk);
     }
-    return dd_launch_tile<S, D, C, RAW>(h, tp, kind);
+    if (kind > 0) return dd_launch_tile<S, D, C, RAW>(h, tp, kind);
   }
   if (dd_launch_rows<S, D, C, RAW>(h, pl)) {
     cudaError_t e = cudaGetLastError();

@@ -204,6 +204,21 @@ def test_flat_tile_many_chunks_and_batches(fact, dev, oracle):
     run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), "byte", "byte", seed=68, expect="transform/tile-flat-out")
 
 
+@pytest.mark.parametrize("pair", [("float", "float"), ("uint8", "uint8"), ("uint8", "float"), ("float", "uint8"),
+                                  ("byte", "byte"), ("half", "float"), ("float", "bf16")])
+@pytest.mark.parametrize("shape", [[4, 3, 32, 48], [2, 4, 64, 64], [3, 1, 16, 80], [5, 2, 8, 24], [1, 3, 224, 224]])
+def test_images_with_a_few_channels(fact, dev, oracle, shape, pair):
+    """nchw <-> nhwc with 1 to 4 channels (a batch of images): the channel dim is too thin for a tile,
+    so the interleaved side moves as a flat vector stream (the short-rows forms with rows of 3 or 4
+    elements).  One channel is the same layout both ways: a flat copy."""
+    sdt, ddt = pair
+    n, c, hgt, w = shape
+    to_nhwc = "transform/flat" if c == 1 else "transform/tile-flat-out"
+    to_nchw = "transform/flat" if c == 1 else "transform/tile-flat-in"
+    run_case(fact, dev, oracle, shape, nchw(shape), nhwc(shape), sdt, ddt, seed=81, expect=to_nhwc)
+    run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=82, expect=to_nchw)
+
+
 def test_padded_strides_round_trip(fact, dev, oracle):
     # core_test.clj:301-340: [2 2 3 2] through strides [48 100 8 3]; tensor_test.clj:171-194
     run_case(fact, dev, oracle, [2, 2, 3, 2], nchw([2, 2, 3, 2]), [48, 100, 8, 3], "float", "float", seed=9)
