@@ -215,7 +215,8 @@ static ddEncodeTiledFn dd_encode_tiled() {
 // extents that fit the 32-bit coordinates of a tensor map.
 bool dd_launch_tile_tma(ddHandle_t h, const ddTileParams &tp) {
   if (!dd_tune("DD_TILE_TMA", h->tileTma) || !h->faultWord) return false;
-  if (tp.nb > 1 || tp.na < 1 || tp.na > 16) return false;
+  if (tp.nb > 1 || tp.na < 1) return false;
+  const int na = tp.na > 16 ? 16 : tp.na;  // (the register-staged kernel may have chosen a wider CTA for a short B)
   if ((((uintptr_t)tp.x) & 15) || (tp.sxB & 15) || (tp.LA & 15) || (tp.LB & 15)) return false;
   if (tp.nb == 1 && (tp.bsx[0] & 15)) return false;
   const int64_t batch = tp.nb == 1 ? tp.bdims[0] : 1;
@@ -228,7 +229,9 @@ bool dd_launch_tile_tma(ddHandle_t h, const ddTileParams &tp) {
   ddTileTmaParams q;
   q.t = tp;
   q.t.nbLog2 = 3;
-  const int TA = tp.na * 16;
+  const int TA = na * 16;
+  q.t.na = na;
+  q.t.fdNA = dd_fastdiv((uint32_t)na);
   q.t.tilesA = (tp.LA + TA - 1) / TA;
   q.t.tilesB = (tp.LB + DD_TMA_TB - 1) / DD_TMA_TB;
   const int64_t tiles = q.t.tilesA * q.t.tilesB * batch;
@@ -272,7 +275,7 @@ bool dd_launch_tile_tma(ddHandle_t h, const ddTileParams &tp) {
   int64_t grid = tiles < (int64_t)h->smCount * cps ? tiles : (int64_t)h->smCount * cps;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3((unsigned)(tp.na * 8), 1, 1);
+  cfg.blockDim = dim3((unsigned)(na * 8), 1, 1);
   cfg.dynamicSmemBytes = smemBytes;
   cfg.stream = h->stream;
   cudaLaunchAttribute attr[1];

@@ -219,6 +219,25 @@ def test_images_with_a_few_channels(fact, dev, oracle, shape, pair):
     run_case(fact, dev, oracle, shape, nhwc(shape), nchw(shape), sdt, ddt, seed=82, expect=to_nchw)
 
 
+@pytest.mark.parametrize("pair", [("float", "float"), ("float", "bf16"), ("byte", "byte"), ("half", "half"), ("double", "double")])
+@pytest.mark.parametrize("n,c,hgt,w,blk", [(3, 64, 12, 20, 16), (2, 48, 28, 28, 8), (5, 64, 8, 16, 32), (1, 32, 6, 40, 4)])
+def test_blocked_channel_layouts(fact, dev, oracle, n, c, hgt, w, blk, pair):
+    """nchw <-> nChw{blk}c (oneDNN's blocked formats, written as rank-5 strides: the channel dim split
+    into c / blk blocks and blk channels innermost).  A transposition whose B is only blk elements:
+    the tile kernel runs it with as few lanes along B as cover blk (or the flat / strided forms where
+    blk is less than two vectors).  Bit for bit against the oracle, both ways."""
+    sdt, ddt = pair
+    shape5 = [n, c // blk, blk, hgt, w]
+    plain = [c * hgt * w, blk * hgt * w, hgt * w, w, 1]
+    blocked = [c * hgt * w, blk * hgt * w, 1, blk * w, blk]
+    run_case(fact, dev, oracle, shape5, plain, blocked, sdt, ddt, seed=91)
+    run_case(fact, dev, oracle, shape5, blocked, plain, sdt, ddt, seed=92)
+    vd = 16 // np.dtype(NP[ddt]).itemsize
+    vs = 16 // np.dtype(NP[sdt]).itemsize
+    if blk >= 2 * vd and (hgt * w) % vs == 0 and hgt * w >= 2 * vs:
+        run_case(fact, dev, oracle, shape5, plain, blocked, sdt, ddt, seed=93, expect="transform/tile")
+
+
 def test_padded_strides_round_trip(fact, dev, oracle):
     # core_test.clj:301-340: [2 2 3 2] through strides [48 100 8 3]; tensor_test.clj:171-194
     run_case(fact, dev, oracle, [2, 2, 3, 2], nchw([2, 2, 3, 2]), [48, 100, 8, 3], "float", "float", seed=9)
