@@ -170,7 +170,11 @@
    :mean 5
    :norm1 6
    :norm2 7
-   :mul-no-zeros 8})
+   :mul-no-zeros 8
+   :norm-lp-max 9
+   :norm-lp-sum 10
+   :norm-lp-power-p-max 11
+   :norm-lp-power-p-sum 12})
 
 (defn dec-reduce-tensor-op [^long op]
   (case op
@@ -183,6 +187,10 @@
     6 :norm1
     7 :norm2
     8 :mul-no-zeros
+    9 :norm-lp-max
+    10 :norm-lp-sum
+    11 :norm-lp-power-p-max
+    12 :norm-lp-power-p-sum
     (dragan-says-ex "This reduce op is not supported by libdd_b200."
                     {:op op :available (keys dd-reduce-tensor-op)})))
 

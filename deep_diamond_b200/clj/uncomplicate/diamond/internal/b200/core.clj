@@ -207,7 +207,19 @@
 ;; =========================== Reduce ====================================================
 
 (defn reduce-tensor-descriptor
-  "After reduce-tensor-descriptor, cudnn/core.clj:188-205; indices are never produced."
+  "After reduce-tensor-descriptor, cudnn/core.clj:188-205; indices are never produced.  The
+  5-argument arity carries the p and epsilon of the DNNL backend's `reduction`
+  (dnnl/core.clj:796-803) for the :norm-lp-* kinds."
+  ([op comp-type nan-opt p eps]
+   (let [rtd (reduce-tensor-descriptor*)]
+     (try
+       (reduce-tensor-descriptor* rtd (enc-keyword dd-reduce-tensor-op op)
+                                  (enc-keyword dd-data-type comp-type)
+                                  (enc-nan-propagation nan-opt)
+                                  (double p) (double eps))
+       (catch Exception e
+         (destroy-reduce-tensor-descriptor* rtd)
+         (throw e)))))
   ([op comp-type nan-opt]
    (let [rtd (reduce-tensor-descriptor*)]
      (try

@@ -94,6 +94,8 @@
 (defdowncall dd-destroy-reduce-tensor-descriptor  "ddDestroyReduceTensorDescriptor" I [P])
 (defdowncall dd-set-reduce-tensor-descriptor      "ddSetReduceTensorDescriptor" I [P I I I])
 (defdowncall dd-get-reduce-tensor-descriptor      "ddGetReduceTensorDescriptor" I [P P P P])
+(defdowncall dd-set-reduce-tensor-descriptor-lp   "ddSetReduceTensorDescriptorLp" I [P I I I D D])
+(defdowncall dd-get-reduce-tensor-descriptor-lp   "ddGetReduceTensorDescriptorLp" I [P P P])
 (defdowncall dd-get-reduction-indices-size        "ddGetReductionIndicesSize" I [P P P P P])
 (defdowncall dd-get-reduction-workspace-size      "ddGetReductionWorkspaceSize" I [P P P P P])
 (defdowncall dd-reduce-tensor                     "ddReduceTensor" I [P P P L P L P P P P P P])
@@ -449,6 +451,11 @@
   ([rtd ^long op ^long comp-type ^long nan-opt]
    (with-check nil
      (invoke dd-set-reduce-tensor-descriptor (seg rtd) (int op) (int comp-type) (int nan-opt))
+     rtd))
+  ([rtd ^long op ^long comp-type ^long nan-opt ^double p ^double eps]
+   (with-check nil
+     (invoke dd-set-reduce-tensor-descriptor-lp (seg rtd) (int op) (int comp-type) (int nan-opt)
+             (double p) (double eps))
      rtd)))
 
 (defn destroy-reduce-tensor-descriptor* [rtd]
@@ -463,6 +470,14 @@
         {:op (.get op ValueLayout/JAVA_INT 0)
          :comp-type (.get comp-type ValueLayout/JAVA_INT 0)
          :nan-opt (.get nan-opt ValueLayout/JAVA_INT 0)}))))
+
+(defn get-reduce-tensor-descriptor-lp* [rtd]
+  (with-open [arena (Arena/ofConfined)]
+    (let [p (.allocate arena 8 8)
+          eps (.allocate arena 8 8)]
+      (with-check nil (invoke dd-get-reduce-tensor-descriptor-lp (seg rtd) p eps)
+        {:p (.get p ValueLayout/JAVA_DOUBLE 0)
+         :eps (.get eps ValueLayout/JAVA_DOUBLE 0)}))))
 
 (defn reduction-indices-size* ^long [hdl rtd desc-x desc-y]
   (with-out [cell]

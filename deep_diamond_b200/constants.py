@@ -35,9 +35,12 @@ OP_TENSOR = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5,
              "ge": 6, "gt": 7, "le": 8, "lt": 9, "eq": 10, "ne": 11}
 
 REDUCE_OP = {"add": 0, "sum": 0, "mul": 1, "min": 2, "max": 3, "amax": 4, "avg": 5, "mean": 5,
-             "norm1": 6, "norm2": 7, "mul-no-zeros": 8}
+             "norm1": 6, "norm2": 7, "mul-no-zeros": 8,
+             # oneDNN's norm kinds, which take p and epsilon (dnnl/constants.clj:393-402)
+             "norm-lp-max": 9, "norm-lp-sum": 10, "norm-lp-power-p-max": 11, "norm-lp-power-p-sum": 12}
 REDUCE_NAME = {0: "add", 1: "mul", 2: "min", 3: "max", 4: "amax", 5: "avg", 6: "norm1", 7: "norm2",
-               8: "mul-no-zeros"}
+               8: "mul-no-zeros", 9: "norm-lp-max", 10: "norm-lp-sum", 11: "norm-lp-power-p-max",
+               12: "norm-lp-power-p-sum"}
 
 
 def enc_keyword(table, kw, what="keyword"):

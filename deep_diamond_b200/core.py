@@ -326,16 +326,26 @@ def activation_backward(handle, ad, alpha, desc_y, buf_y, desc_dy, buf_dy, desc_
 # ============================ Reduce ==============================================
 
 class ReduceTensorDescriptor:
-    def __init__(self, op, comp_type="float", nan_opt=True):
+    def __init__(self, op, comp_type="float", nan_opt=True, p=None, eps=None):
         d = ctypes.c_void_p()
         check(lib.ddCreateReduceTensorDescriptor(ctypes.byref(d)), None)
         self.ptr = d
         self.op = enc_keyword(REDUCE_OP, op, "reduce op")
-        st = lib.ddSetReduceTensorDescriptor(d, self.op, enc_keyword(DATA_TYPE, comp_type, "data type"),
-                                             1 if nan_opt else 0)
+        comp = enc_keyword(DATA_TYPE, comp_type, "data type")
+        if p is None and eps is None:
+            st = lib.ddSetReduceTensorDescriptor(d, self.op, comp, 1 if nan_opt else 0)
+        else:
+            st = lib.ddSetReduceTensorDescriptorLp(d, self.op, comp, 1 if nan_opt else 0,
+                                                   2.0 if p is None else float(p), 0.0 if eps is None else float(eps))
         if st != 0:
             lib.ddDestroyReduceTensorDescriptor(d)
             check(st, None, "ddSetReduceTensorDescriptor")
+
+    def lp(self):
+        """(p, eps) of the norm kinds."""
+        p, eps = ctypes.c_double(), ctypes.c_double()
+        check(lib.ddGetReduceTensorDescriptorLp(self.ptr, ctypes.byref(p), ctypes.byref(eps)), None)
+        return p.value, eps.value
 
     def release(self):
         if self.ptr is not None:
@@ -344,9 +354,10 @@ class ReduceTensorDescriptor:
         return True
 
 
-def reduce_tensor_descriptor(op, comp_type="float", nan_opt=True):
-    """``reduce-tensor-descriptor`` (:188-203)."""
-    return ReduceTensorDescriptor(op, comp_type, nan_opt)
+def reduce_tensor_descriptor(op, comp_type="float", nan_opt=True, p=None, eps=None):
+    """``reduce-tensor-descriptor`` (:188-203).  ``p`` and ``eps`` are the two extra arguments of the
+    DNNL backend's ``reduction`` (dnnl/core.clj:796-803), read by the ``norm-lp-*`` kinds."""
+    return ReduceTensorDescriptor(op, comp_type, nan_opt, p, eps)
 
 
 def reduction_indices_size(handle, rtd, desc_x, desc_y):

@@ -342,11 +342,30 @@ ddStatus_t ddDestroyReduceTensorDescriptor(ddReduceTensorDescriptor_t desc) {
 ddStatus_t ddSetReduceTensorDescriptor(ddReduceTensorDescriptor_t r, ddReduceTensorOp_t op,
                                        ddDataType_t comp, ddNanPropagation_t nanOpt) {
   if (!r) return DD_STATUS_BAD_PARAM;
-  if ((int)op < 0 || (int)op > DD_REDUCE_TENSOR_MUL_NO_ZEROS) return DD_STATUS_BAD_PARAM;
+  if ((int)op < 0 || (int)op > DD_REDUCE_TENSOR_NORM_LP_POWER_P_SUM) return DD_STATUS_BAD_PARAM;
   if (comp != DD_DATA_FLOAT && comp != DD_DATA_DOUBLE) return DD_STATUS_NOT_SUPPORTED;
   r->op = op;
   r->comp = comp;
   r->nan = nanOpt;
+  r->p = 2.0;
+  r->eps = 0.0;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddSetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t r, ddReduceTensorOp_t op, ddDataType_t comp,
+                                         ddNanPropagation_t nanOpt, double p, double eps) {
+  if (!(p >= 1.0) || !(eps == eps)) return DD_STATUS_BAD_PARAM;  // oneDNN: p >= 1; NaN refused
+  ddStatus_t st = ddSetReduceTensorDescriptor(r, op, comp, nanOpt);
+  if (st != DD_STATUS_SUCCESS) return st;
+  r->p = p;
+  r->eps = eps;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddGetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t r, double *p, double *eps) {
+  if (!r) return DD_STATUS_BAD_PARAM;
+  if (p) *p = r->p;
+  if (eps) *eps = r->eps;
   return DD_STATUS_SUCCESS;
 }
 

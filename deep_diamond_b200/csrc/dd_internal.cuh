@@ -42,6 +42,8 @@ struct ddReduceTensorStruct {
   ddReduceTensorOp_t op;
   ddDataType_t comp;
   ddNanPropagation_t nan;
+  double p = 2.0;    // the NORM_LP kinds: exponent and epsilon
+  double eps = 0.0;
 };
 
 struct ddContext {

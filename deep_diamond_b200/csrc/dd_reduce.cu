@@ -28,6 +28,17 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
     case DD_REDUCE_TENSOR_MIN: pl->opc = DD_OPC_MIN; pl->p.post = DD_POST_NONE; break;
     case DD_REDUCE_TENSOR_MAX: pl->opc = DD_OPC_MAX; pl->p.post = DD_POST_NONE; break;
     case DD_REDUCE_TENSOR_AMAX: pl->opc = DD_OPC_AMAX; pl->p.post = DD_POST_NONE; break;
+    case DD_REDUCE_TENSOR_NORM_LP_MAX: case DD_REDUCE_TENSOR_NORM_LP_SUM:
+    case DD_REDUCE_TENSOR_NORM_LP_POWER_P_MAX: case DD_REDUCE_TENSOR_NORM_LP_POWER_P_SUM:
+      // sum of |x|^p: p = 1 and p = 2 are the NORM1 / NORM2 accumulations, any other p goes through pow
+      if (!(red->p >= 1.0)) DD_FAIL(h, DD_STATUS_BAD_PARAM, "reduce: the norm's p must be at least 1");
+      pl->opc = red->p == 1.0 ? DD_OPC_SUMABS : (red->p == 2.0 ? DD_OPC_SUMSQ : DD_OPC_SUMPOW);
+      pl->p.post = DD_POST_LP;
+      pl->p.lpP = red->p;
+      pl->p.lpEps = red->eps;
+      pl->p.lpMax = red->op == DD_REDUCE_TENSOR_NORM_LP_MAX || red->op == DD_REDUCE_TENSOR_NORM_LP_POWER_P_MAX;
+      pl->p.lpRoot = red->op == DD_REDUCE_TENSOR_NORM_LP_MAX || red->op == DD_REDUCE_TENSOR_NORM_LP_SUM;
+      break;
     default: DD_FAIL(h, DD_STATUS_BAD_PARAM, "reduce: unknown op");
   }
   if (xd->dtype != yd->dtype) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: x and y must share one data type");
@@ -318,6 +329,7 @@ ddStatus_t dd_reduce_plan(ddHandle_t h, const ddReduceTensorStruct *red, const d
     g.nred = nred;
     g.count = (double)nred;
     g.post = p.post;
+    g.lpP = p.lpP; g.lpEps = p.lpEps; g.lpMax = p.lpMax; g.lpRoot = p.lpRoot;
     g.nanProp = p.nanProp;
     pl->grid = dd_flat_grid(h, nout, 256, 16);
   }

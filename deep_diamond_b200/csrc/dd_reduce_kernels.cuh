@@ -27,8 +27,8 @@
 #include "dd_internal.cuh"
 #include <cooperative_groups.h>
 
-enum { DD_OPC_SUM = 0, DD_OPC_SUMABS, DD_OPC_SUMSQ, DD_OPC_PROD, DD_OPC_PRODNZ, DD_OPC_MIN, DD_OPC_MAX, DD_OPC_AMAX, DD_OPC_COUNT };
-enum { DD_POST_NONE = 0, DD_POST_AVG = 1, DD_POST_SQRT = 2 };
+enum { DD_OPC_SUM = 0, DD_OPC_SUMABS, DD_OPC_SUMSQ, DD_OPC_PROD, DD_OPC_PRODNZ, DD_OPC_MIN, DD_OPC_MAX, DD_OPC_AMAX, DD_OPC_SUMPOW, DD_OPC_COUNT };
+enum { DD_POST_NONE = 0, DD_POST_AVG = 1, DD_POST_SQRT = 2, DD_POST_LP = 3 };
 
 template <typename C> __device__ __forceinline__ C dd_inf();
 template <> __device__ __forceinline__ float dd_inf<float>() { return __int_as_float(0x7f800000); }
@@ -45,6 +45,8 @@ __device__ __forceinline__ float dd_sqrt(float v) { return __fsqrt_rn(v); }
 __device__ __forceinline__ double dd_sqrt(double v) { return __dsqrt_rn(v); }
 __device__ __forceinline__ float dd_div(float a, float b) { return __fdiv_rn(a, b); }
 __device__ __forceinline__ double dd_div(double a, double b) { return __ddiv_rn(a, b); }
+__device__ __forceinline__ float dd_pow(float a, float b) { return powf(a, b); }
+__device__ __forceinline__ double dd_pow(double a, double b) { return pow(a, b); }
 
 template <typename C, int OPC>
 struct dd_red {
@@ -54,8 +56,9 @@ struct dd_red {
     if (OPC == DD_OPC_MAX) return -dd_inf<C>();
     return (C)0;
   }
-  // acc (+)= pre(v)
-  static __device__ __forceinline__ C accum(C acc, C v, bool nanProp) {
+  // acc (+)= pre(v); pw: the exponent of the general Lp sum, unused by every other kind
+  static __device__ __forceinline__ C accum(C acc, C v, bool nanProp, C pw) {
+    if (OPC == DD_OPC_SUMPOW) return dd_add_rn(acc, dd_pow(dd_abs(v), pw));
     if (OPC == DD_OPC_SUM) return dd_add_rn(acc, v);
     if (OPC == DD_OPC_SUMABS) return dd_add_rn(acc, dd_abs(v));
     if (OPC == DD_OPC_SUMSQ) return dd_fma(v, v, acc);
@@ -66,7 +69,7 @@ struct dd_red {
   }
   // combines two accumulators
   static __device__ __forceinline__ C comb(C a, C b, bool nanProp) {
-    if (OPC == DD_OPC_SUM || OPC == DD_OPC_SUMABS || OPC == DD_OPC_SUMSQ) return dd_add_rn(a, b);
+    if (OPC == DD_OPC_SUM || OPC == DD_OPC_SUMABS || OPC == DD_OPC_SUMSQ || OPC == DD_OPC_SUMPOW) return dd_add_rn(a, b);
     if (OPC == DD_OPC_PROD || OPC == DD_OPC_PRODNZ) return dd_mul_rn(a, b);
     // propagate: a NaN on either side wins (b beats a only when it compares so or is NaN; a NaN in a
     // survives because every comparison with it is false).  Otherwise IEEE maxNum/minNum: the number wins.
@@ -143,6 +146,8 @@ struct ddRedParams {
   int64_t tilesK2;   // col: tiles along k2
   double alpha, beta, count;
   int post;
+  double lpP, lpEps;   // DD_POST_LP (oneDNN's norm_lp kinds): exponent and epsilon,
+  int lpMax, lpRoot;   //   max(S, eps) instead of S + eps; the 1/p power taken or not
   int nanProp;
   int partialOnly;   // 1: store the raw accumulator into partOut[out] and leave y alone
                      // 2: the same, and push it to the other ranks; the last CTA of the grid then
@@ -155,12 +160,22 @@ struct ddRedParams {
   unsigned long long peerWaitNs;
 };
 
+// what follows the fold of an output: mean's division, the norms' root, epsilon
+template <typename C, typename P>
+__device__ __forceinline__ C dd_red_post(const P &p, C v) {
+  if (p.post == DD_POST_AVG) v = dd_div(v, (C)p.count);
+  if (p.post == DD_POST_SQRT) v = dd_sqrt(v);
+  if (p.post == DD_POST_LP) {
+    v = p.lpMax ? dd_fmax(v, (C)p.lpEps) : dd_add_rn(v, (C)p.lpEps);
+    if (p.lpRoot) v = p.lpP == 2.0 ? dd_sqrt(v) : (p.lpP == 1.0 ? v : dd_pow(v, (C)(1.0 / p.lpP)));
+  }
+  return v;
+}
+
 // post-processing + alpha/beta + store of one finished output
 template <typename T, typename C>
 __device__ __forceinline__ void dd_red_output(const ddRedParams &p, int64_t k1, int64_t k2, C acc) {
-  C v = acc;
-  if (p.post == DD_POST_AVG) v = dd_div(v, (C)p.count);
-  if (p.post == DD_POST_SQRT) v = dd_sqrt(v);
+  C v = dd_red_post(p, acc);
   v = dd_scale((C)p.alpha, v);
   T *yp = (T *)p.y + k1 * p.syK1 + k2 * p.syK2;
   if (p.beta != 0.0) v = dd_add_rn(v, dd_mul_rn((C)p.beta, dd_load<C, T>(*yp)));
@@ -531,7 +546,7 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
         if (ok[q]) {
           const T *wv = (const T *)&raw[q];
 #pragma unroll
-          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
+          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
         }
       }
     }
@@ -595,7 +610,7 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
             if (q < left && okc[c]) {
               const T *wv = (const T *)&raw[q * CPR + c];
 #pragma unroll
-              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
+              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
             }
       }
     } else {
@@ -617,7 +632,7 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
             if (okc[c]) {
               const T *wv = (const T *)&raw[q * CPR + c];
 #pragma unroll
-              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
+              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
             }
       }
       for (; r < nrows; r++) {
@@ -631,7 +646,7 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
           if (okc[c]) {
             const T *wv = (const T *)&raw[c];
 #pragma unroll
-            for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp);
+            for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
           }
       }
     }
@@ -688,7 +703,7 @@ __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_redu
         if (ok[q]) {
           const T *wv = (const T *)&raw[q];
 #pragma unroll
-          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
+          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
         }
       }
     }
@@ -783,7 +798,7 @@ __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRe
         if (q < left) {
           const T *wv = (const T *)&raw[q];
 #pragma unroll
-          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp);
+          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
         }
     }
   }
@@ -945,6 +960,8 @@ struct ddRedGenericParams {
   int64_t rd[DD_DIM_MAX], rx[DD_DIM_MAX];                  // reduced dims: extent, x stride
   int64_t nout, nred;
   double alpha, beta, count;
+  double lpP, lpEps;
+  int lpMax, lpRoot;
   int post, nanProp, partialOnly;
 };
 
@@ -968,14 +985,12 @@ __global__ void __launch_bounds__(256) dd_reduce_generic_kernel(ddRedGenericPara
         off += (rr - q * p.rd[d]) * p.rx[d];
         rr = q;
       }
-      acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(((const T *)p.x)[off]), nanProp);
+      acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(((const T *)p.x)[off]), nanProp, (C)p.lpP);
     }
     if (p.partialOnly) {
       ((C *)p.partOut)[o] = acc;
     } else {
-      C v = acc;
-      if (p.post == DD_POST_AVG) v = dd_div(v, (C)p.count);
-      if (p.post == DD_POST_SQRT) v = dd_sqrt(v);
+      C v = dd_red_post(p, acc);
       v = dd_scale((C)p.alpha, v);
       T *yp = (T *)p.y + oy;
       if (p.beta != 0.0) v = dd_add_rn(v, dd_mul_rn((C)p.beta, dd_load<C, T>(*yp)));
@@ -1131,6 +1146,7 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       case DD_OPC_MIN: return exchange_opc_##T<DD_OPC_MIN>(h, pl, q);                              \
       case DD_OPC_MAX: return exchange_opc_##T<DD_OPC_MAX>(h, pl, q);                              \
       case DD_OPC_AMAX: return exchange_opc_##T<DD_OPC_AMAX>(h, pl, q);                            \
+      case DD_OPC_SUMPOW: return exchange_opc_##T<DD_OPC_SUM>(h, pl, q);  /* accumulators add */   \
     }                                                                                              \
     return DD_STATUS_INTERNAL_ERROR;                                                               \
   }                                                                                                \
@@ -1145,6 +1161,7 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       case DD_OPC_MIN: return launch_opc_##T<DD_OPC_MIN>(h, pl);                                   \
       case DD_OPC_MAX: return launch_opc_##T<DD_OPC_MAX>(h, pl);                                   \
       case DD_OPC_AMAX: return launch_opc_##T<DD_OPC_AMAX>(h, pl);                                 \
+      case DD_OPC_SUMPOW: return launch_opc_##T<DD_OPC_SUMPOW>(h, pl);                             \
     }                                                                                              \
     return DD_STATUS_INTERNAL_ERROR;                                                               \
   }                                                                                                \
@@ -1159,6 +1176,7 @@ DD_REDUCE_DECLARE(__nv_bfloat16, float)
       case DD_OPC_MIN: return finish_opc_##T<DD_OPC_MIN>(h, pl, part);                             \
       case DD_OPC_MAX: return finish_opc_##T<DD_OPC_MAX>(h, pl, part);                             \
       case DD_OPC_AMAX: return finish_opc_##T<DD_OPC_AMAX>(h, pl, part);                           \
+      case DD_OPC_SUMPOW: return finish_opc_##T<DD_OPC_SUM>(h, pl, part);  /* accumulators add */  \
     }                                                                                              \
     return DD_STATUS_INTERNAL_ERROR;                                                               \
   }

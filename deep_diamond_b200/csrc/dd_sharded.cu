@@ -341,6 +341,8 @@ ddStatus_t ddShardedReduceTensor(ddShardedHandle_t s, ddReduceTensorDescriptor_t
   int ncclOp;
   switch (red->op) {
     case DD_REDUCE_TENSOR_ADD: case DD_REDUCE_TENSOR_AVG: case DD_REDUCE_TENSOR_NORM1: case DD_REDUCE_TENSOR_NORM2:
+    case DD_REDUCE_TENSOR_NORM_LP_MAX: case DD_REDUCE_TENSOR_NORM_LP_SUM:
+    case DD_REDUCE_TENSOR_NORM_LP_POWER_P_MAX: case DD_REDUCE_TENSOR_NORM_LP_POWER_P_SUM:
       ncclOp = DD_NCCL_SUM; break;
     case DD_REDUCE_TENSOR_MUL: case DD_REDUCE_TENSOR_MUL_NO_ZEROS: ncclOp = DD_NCCL_PROD; break;
     case DD_REDUCE_TENSOR_MIN: ncclOp = DD_NCCL_MIN; break;

@@ -108,7 +108,12 @@ typedef enum {
 } ddOpTensorOp_t;
 
 /* Reduce ops, cudnn/constants.clj:171-180; oneDNN's kinds (dnnl/constants.clj:393-402) map as
- * sum->ADD, mean->AVG, max, min, mul, norm-lp-sum p=1 -> NORM1, norm-lp-sum p=2 -> NORM2. */
+ * sum->ADD, mean->AVG, max, min, mul, norm-lp-sum p=1 -> NORM1, norm-lp-sum p=2 -> NORM2.
+ * The four NORM_LP kinds are oneDNN's own, with the p and epsilon that the reference's `reduction`
+ * passes (dnnl/core.clj:796-803); S = sum of |x|^p over the reduced dims:
+ *   NORM_LP_MAX          max(S, eps)^(1/p)        NORM_LP_SUM          (S + eps)^(1/p)
+ *   NORM_LP_POWER_P_MAX  max(S, eps)              NORM_LP_POWER_P_SUM  S + eps
+ * p and eps are set with ddSetReduceTensorDescriptorLp (p = 2, eps = 0 otherwise). */
 typedef enum {
   DD_REDUCE_TENSOR_ADD = 0,
   DD_REDUCE_TENSOR_MUL = 1,
@@ -118,7 +123,11 @@ typedef enum {
   DD_REDUCE_TENSOR_AVG = 5,
   DD_REDUCE_TENSOR_NORM1 = 6,
   DD_REDUCE_TENSOR_NORM2 = 7,
-  DD_REDUCE_TENSOR_MUL_NO_ZEROS = 8
+  DD_REDUCE_TENSOR_MUL_NO_ZEROS = 8,
+  DD_REDUCE_TENSOR_NORM_LP_MAX = 9,
+  DD_REDUCE_TENSOR_NORM_LP_SUM = 10,
+  DD_REDUCE_TENSOR_NORM_LP_POWER_P_MAX = 11,
+  DD_REDUCE_TENSOR_NORM_LP_POWER_P_SUM = 12
 } ddReduceTensorOp_t;
 
 typedef struct ddContext *ddHandle_t;
@@ -314,6 +323,14 @@ DD_API ddStatus_t ddSetReduceTensorDescriptor(ddReduceTensorDescriptor_t desc, d
                                        ddDataType_t compType, ddNanPropagation_t nanOpt);
 DD_API ddStatus_t ddGetReduceTensorDescriptor(ddReduceTensorDescriptor_t desc, ddReduceTensorOp_t *op,
                                        ddDataType_t *compType, ddNanPropagation_t *nanOpt);
+/* The descriptor of oneDNN's reduction with its two extra arguments (dnnl/impl.clj:557-562
+ * `reduction*` alg p epsilon; dnnl/core.clj:796-803).  p >= 1 (1 and 2 run the NORM1 / NORM2
+ * accumulation, any other p raises |x| to it element by element); p and eps are read by the four
+ * NORM_LP kinds only.  ddGetReduceTensorDescriptorLp returns them. */
+DD_API ddStatus_t ddSetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t desc, ddReduceTensorOp_t op,
+                                         ddDataType_t compType, ddNanPropagation_t nanOpt, double p,
+                                         double eps);
+DD_API ddStatus_t ddGetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t desc, double *p, double *eps);
 DD_API ddStatus_t ddGetReductionIndicesSize(ddHandle_t handle, ddReduceTensorDescriptor_t red,
                                      ddTensorDescriptor_t xDesc, ddTensorDescriptor_t yDesc,
                                      size_t *bytes);

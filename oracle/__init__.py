@@ -214,6 +214,25 @@ def reduce(op, x, y, alpha=1.0, beta=0.0, nanprop=True, tag=None, want_truth=Fal
     return (y, truth.reshape(y.shape)) if want_truth else y
 
 
+LP_REDOP = {"norm-lp-max": 9, "norm-lp-sum": 10, "norm-lp-power-p-max": 11, "norm-lp-power-p-sum": 12}
+
+
+def reduce_lp(op, p, eps, x, y, alpha=1.0, beta=0.0, tag=None, want_truth=False):
+    """oneDNN's norm reductions with exponent ``p`` and ``eps`` (dnnl/constants.clj:393-402):
+    S = sum |x|^p over the dims where y's extent is 1, then max(S,eps)^(1/p), (S+eps)^(1/p),
+    max(S,eps) or S+eps."""
+    assert len(x.shape) == len(y.shape)
+    xd, xs, xp = _desc(x)
+    yd, ys, yp = _desc(y)
+    truth = np.empty(y.size, dtype=np.float64) if want_truth else None
+    tp = ctypes.c_void_p(truth.ctypes.data) if want_truth else ctypes.c_void_p(0)
+    rc = lib().oracle_reduce_lp(LP_REDOP[op], ctypes.c_double(p), ctypes.c_double(eps), code_of(x, tag),
+                                len(x.shape), xd, xs, xp, yd, ys, yp, ctypes.c_double(alpha),
+                                ctypes.c_double(beta), tp)
+    assert rc == 0
+    return (y, truth.reshape(y.shape)) if want_truth else y
+
+
 def equals(x, y, tag=None):
     dims, xs, xp = _desc(x)
     _, ys, yp = _desc(y)

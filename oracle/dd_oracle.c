@@ -556,7 +556,11 @@ int oracle_sum(int n, const float *scales, int t, int64_t total, const void *con
 
 /* ------------------------------------------------------------ reduction ---------------------- */
 
-enum { R_ADD = 0, R_MUL = 1, R_MIN = 2, R_MAX = 3, R_AMAX = 4, R_AVG = 5, R_NORM1 = 6, R_NORM2 = 7, R_MULNZ = 8 };
+enum { R_ADD = 0, R_MUL = 1, R_MIN = 2, R_MAX = 3, R_AMAX = 4, R_AVG = 5, R_NORM1 = 6, R_NORM2 = 7, R_MULNZ = 8,
+       /* oneDNN's norm kinds with their p and epsilon (dnnl/constants.clj:393-402, `reduction` in
+        * dnnl/core.clj:796-803), S = sum of |x|^p:  max(S,eps)^(1/p), (S+eps)^(1/p), max(S,eps), S+eps */
+       R_LP_MAX = 9, R_LP_SUM = 10, R_LP_POWER_P_MAX = 11, R_LP_POWER_P_SUM = 12 };
+#define R_IS_LP(op) ((op) >= R_LP_MAX && (op) <= R_LP_POWER_P_SUM)
 
 static double minmax_d(int op, double a, double b, int nanprop) {
   double r = (op == R_MIN) ? (a < b ? a : b) : (a > b ? a : b);
@@ -575,7 +579,12 @@ typedef struct {
   const int64_t *rd, *rx;
   const void *x;
   int64_t xo;
+  double p;
 } red_ctx;
+
+/* |v|^p of one element, in the arithmetic of the accumulator */
+static float lp_term_f(float v, double p) { return p == 1.0 ? fabsf(v) : (p == 2.0 ? v * v : powf(fabsf(v), (float)p)); }
+static double lp_term_d(double v, double p) { return p == 1.0 ? fabs(v) : (p == 2.0 ? v * v : pow(fabs(v), p)); }
 
 static double red_value(const red_ctx *c, int64_t r) {
   return load_as_double(c->x, c->t, c->xo + offset_of(c->nr, c->rd, c->rx, r));
@@ -586,7 +595,7 @@ static float pair_f(const red_ctx *c, int64_t lo, int64_t hi) {
     float acc = 0.f;
     for (int64_t r = lo; r < hi; r++) {
       float v = (float)red_value(c, r);
-      acc += c->op == R_NORM1 ? fabsf(v) : (c->op == R_NORM2 ? v * v : v);
+      acc += R_IS_LP(c->op) ? lp_term_f(v, c->p) : (c->op == R_NORM1 ? fabsf(v) : (c->op == R_NORM2 ? v * v : v));
     }
     return acc;
   }
@@ -599,7 +608,7 @@ static double pair_d(const red_ctx *c, int64_t lo, int64_t hi) {
     double acc = 0.0;
     for (int64_t r = lo; r < hi; r++) {
       double v = red_value(c, r);
-      acc += c->op == R_NORM1 ? fabs(v) : (c->op == R_NORM2 ? v * v : v);
+      acc += R_IS_LP(c->op) ? lp_term_d(v, c->p) : (c->op == R_NORM1 ? fabs(v) : (c->op == R_NORM2 ? v * v : v));
     }
     return acc;
   }
@@ -610,9 +619,9 @@ static double pair_d(const red_ctx *c, int64_t lo, int64_t hi) {
 /* y = alpha*reduce(x) + beta*y; reduced dims are those with ydims == 1 and xdims != 1.
  * `truth`, if not NULL, receives the reduction (before alpha/beta) accumulated in long double, one
  * value per output in logical order of y. */
-int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, const int64_t *xst,
-                  const void *x, const int64_t *ydims, const int64_t *yst, void *y, double alpha,
-                  double beta, double *truth) {
+static int reduce_core(int op, int t, int nanprop, int nd, const int64_t *xdims, const int64_t *xst,
+                       const void *x, const int64_t *ydims, const int64_t *yst, void *y, double alpha,
+                       double beta, double *truth, double p, double eps) {
   int64_t kd[MAXD], rd[MAXD], kx[MAXD], rx[MAXD], ky[MAXD];
   int nk = 0, nr = 0;
   for (int i = 0; i < nd; i++) {
@@ -621,7 +630,7 @@ int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, cons
   }
   const int64_t nout = total_of(nk, kd), nred = total_of(nr, rd);
   const int dbl = (t == T_F64);
-  const int sumlike = (op == R_ADD || op == R_AVG || op == R_NORM1 || op == R_NORM2);
+  const int sumlike = (op == R_ADD || op == R_AVG || op == R_NORM1 || op == R_NORM2 || R_IS_LP(op));
 #pragma omp parallel for schedule(static)
   for (int64_t o = 0; o < nout; o++) {
     const int64_t xo = offset_of(nk, kd, kx, o), yo = offset_of(nk, kd, ky, o);
@@ -635,7 +644,7 @@ int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, cons
       default: accd = 0; accf = 0; acct = 0; break;
     }
     if (sumlike) {
-      red_ctx c = {op, t, nr, rd, rx, x, xo};
+      red_ctx c = {op, t, nr, rd, rx, x, xo, p};
       if (dbl) accd = pair_d(&c, 0, nred);
       else accf = pair_f(&c, 0, nred);
     }
@@ -647,6 +656,8 @@ int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, cons
         case R_ADD: case R_AVG: acct += vd; break;
         case R_NORM1: acct += fabs(vd); break;
         case R_NORM2: acct += (long double)vd * vd; break;
+        case R_LP_MAX: case R_LP_SUM: case R_LP_POWER_P_MAX: case R_LP_POWER_P_SUM:
+          acct += powl(fabsl((long double)vd), (long double)p); break;
         case R_MUL: accd *= vd; accf *= vf; acct *= vd; break;
         case R_MULNZ: if (vd != 0) { accd *= vd; accf *= vf; acct *= vd; } break;
         case R_MIN: case R_MAX:
@@ -659,6 +670,20 @@ int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, cons
     }
     if (op == R_AVG) { accd = accd / (double)nred; accf = accf / (float)nred; acct = acct / (long double)nred; }
     if (op == R_NORM2) { accd = sqrt(accd); accf = sqrtf(accf); acct = sqrtl(acct); }
+    if (R_IS_LP(op)) {
+      if (op == R_LP_MAX || op == R_LP_POWER_P_MAX) {
+        accd = accd > eps ? accd : eps; accf = accf > (float)eps ? accf : (float)eps;
+        acct = acct > (long double)eps ? acct : (long double)eps;
+      } else {
+        accd += eps; accf += (float)eps; acct += (long double)eps;
+      }
+      if (op == R_LP_MAX || op == R_LP_SUM) {
+        if (p == 2.0) { accd = sqrt(accd); accf = sqrtf(accf); acct = sqrtl(acct); }
+        else if (p != 1.0) {
+          accd = pow(accd, 1.0 / p); accf = powf(accf, (float)(1.0 / p)); acct = powl(acct, 1.0L / (long double)p);
+        }
+      }
+    }
     if (truth) truth[o] = (double)acct;
     if (dbl) {
       store_from_double(y, t, yo, blend_d(alpha, accd, beta, y, t, yo));
@@ -667,6 +692,23 @@ int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, cons
     }
   }
   return 0;
+}
+
+int oracle_reduce(int op, int t, int nanprop, int nd, const int64_t *xdims, const int64_t *xst,
+                  const void *x, const int64_t *ydims, const int64_t *yst, void *y, double alpha,
+                  double beta, double *truth) {
+  if (R_IS_LP(op)) return -1;
+  return reduce_core(op, t, nanprop, nd, xdims, xst, x, ydims, yst, y, alpha, beta, truth, 2.0, 0.0);
+}
+
+/* The norm kinds of oneDNN's reduction with p >= 1 and epsilon, as the reference's `reduction`
+ * passes them (dnnl/core.clj:796-803; the known answer at dnnl-t/core_test.clj:926-943 is
+ * norm-lp-sum with p = 2, eps = 0). */
+int oracle_reduce_lp(int op, double p, double eps, int t, int nd, const int64_t *xdims, const int64_t *xst,
+                     const void *x, const int64_t *ydims, const int64_t *yst, void *y, double alpha,
+                     double beta, double *truth) {
+  if (!R_IS_LP(op) || !(p >= 1.0)) return -1;
+  return reduce_core(op, t, 1, nd, xdims, xst, x, ydims, yst, y, alpha, beta, truth, p, eps);
 }
 
 /* any-mismatch over two strided views (typed compare) -- restates blas-plus.cu:9-101 of the

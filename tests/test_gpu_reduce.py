@@ -195,3 +195,57 @@ def test_convolution_bwd_bias(fact, dev, oracle):
                               core.tensor_descriptor(bshape, "float", "nchw"), tdb)
     got = dev.get(tdb, np.float32).reshape(bshape)
     assert np.allclose(got, want, rtol=1e-5, atol=1e-4)
+
+
+LP_KINDS = ["norm-lp-max", "norm-lp-sum", "norm-lp-power-p-max", "norm-lp-power-p-sum"]
+
+
+@pytest.mark.parametrize("kind", LP_KINDS)
+@pytest.mark.parametrize("p,eps", [(1.0, 0.0), (2.0, 0.0), (2.0, 0.25), (3.0, 1e-3), (2.5, 0.0), (1.5, 1e12)])
+def test_norm_lp_kinds(fact, dev, oracle, kind, p, eps):
+    """oneDNN's norm reductions with p and epsilon (dnnl/constants.clj:393-402, `reduction` of
+    dnnl/core.clj:796-803) against the oracle: row, column, split and generic plans; fp32 and fp64.
+    Bar: 1e-5 relative (all terms are non-negative, nothing cancels); CUDA's powf is within a few ulp
+    of the oracle's."""
+    rng = np.random.default_rng(17)
+    cases = [([6, 20, 12, 16], [1, 20, 1, 1]), ([6, 20, 12, 16], [6, 1, 12, 16]), ([2, 3, 4, 5], [2, 3, 4, 1]),
+             ([4, 8, 64, 64], [4, 1, 1, 1]), ([3, 5, 7, 11], [1, 5, 1, 11])]
+    for dtype, np_t, rel in (("float", np.float32, 1e-5), ("double", np.float64, 1e-12)):
+        for shape, yshape in cases:
+            n = int(np.prod(shape))
+            data = (np.exp(0.5 * rng.standard_normal(n)) * np.where(rng.random(n) < 0.5, -1, 1)).astype(np_t)
+            y0 = rng.standard_normal(int(np.prod(yshape))).astype(np_t)
+            want = y0.copy().reshape(yshape)
+            _, truth = oracle.reduce_lp(kind, p, eps, data.reshape(shape), want, alpha=1.5, beta=0.5, want_truth=True)
+            tx, ty = dev.put(data), dev.put(y0)
+            xd, yd = core.tensor_descriptor(shape, dtype, "nchw"), core.tensor_descriptor(yshape, dtype, "nchw")
+            rtd = core.reduce_tensor_descriptor(kind, dtype, True, p, eps)
+            assert rtd.lp() == (p, eps)
+            core.reduce_tensor(fact.handle, rtd, 1.5, xd, tx, 0.5, yd, ty)
+            got = dev.get(ty, np_t).reshape(yshape).astype(np.float64)
+            tv = 1.5 * truth + 0.5 * y0.reshape(yshape).astype(np.float64)
+            assert (np.abs(got - tv) <= rel * np.abs(tv) + rel * np.abs(0.5 * y0.reshape(yshape))).all(), (dtype, shape, yshape)
+            assert (np.abs(got - want.astype(np.float64)) <= 2 * rel * np.abs(tv) + rel).all(), (dtype, shape, yshape)
+            rtd.release()
+
+
+def test_norm_lp_matches_the_named_norms_bit_for_bit(fact, dev, oracle):
+    """norm-lp-sum with p = 2, eps = 0 IS norm2 (same accumulation, same root), p = 1 IS norm1."""
+    shape, yshape = [8, 32, 16, 16], [1, 32, 1, 1]
+    data = oracle.gen_normal(shape, 1.0, 9).reshape(-1)
+    xd, yd = core.tensor_descriptor(shape, "float", "nchw"), core.tensor_descriptor(yshape, "float", "nchw")
+    tx = dev.put(data)
+    outs = {}
+    for name, args in (("norm2", ("norm2",)), ("lp2", ("norm-lp-sum", "float", True, 2.0, 0.0)),
+                       ("norm1", ("norm1",)), ("lp1", ("norm-lp-sum", "float", True, 1.0, 0.0))):
+        ty = dev.put(np.zeros(32, np.float32))
+        core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor(*args), 1.0, xd, tx, 0.0, yd, ty)
+        outs[name] = dev.get(ty, np.float32)
+    assert np.array_equal(outs["norm2"], outs["lp2"])
+    assert np.array_equal(outs["norm1"], outs["lp1"])
+
+
+def test_norm_lp_bad_p(fact):
+    from deep_diamond_b200.constants import DiamondError
+    with pytest.raises(DiamondError):
+        core.reduce_tensor_descriptor("norm-lp-sum", "float", True, 0.5, 0.0)

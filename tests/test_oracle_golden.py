@@ -302,6 +302,32 @@ def test_reductions(oracle):
     assert float(s.reshape(-1)[0]) == 3.5
 
 
+def test_reduction_norm_lp_kinds(oracle):
+    """The four norm kinds of dnnl/constants.clj:393-402 with the p and epsilon that `reduction`
+    passes (dnnl/core.clj:796-803).  norm-lp-sum, p = 2, eps = 0 over W of `range 120` is the known
+    answer of dnnl-t/core_test.clj:926-943; the other kinds follow from the same sums by oneDNN's
+    definitions and are checked against double-precision numpy."""
+    x = np.arange(120, dtype=np.float32).reshape(2, 3, 4, 5)
+    y = np.zeros((2, 3, 4, 1), np.float32)
+    oracle.reduce_lp("norm-lp-sum", 2.0, 0.0, x, y)
+    want = [np.float32(np.sqrt(sum(i * i for i in range(a, a + 5)))) for a in range(0, 120, 5)]
+    assert y.reshape(-1).tolist() == [float(v) for v in want]
+    xs = (x - 60.0).astype(np.float32)
+    for p in (1.0, 2.0, 3.0, 2.5):
+        s = (np.abs(xs.astype(np.float64)) ** p).sum(axis=3, keepdims=True)
+        for eps in (0.0, 1e-3, 1e9):
+            table = {"norm-lp-max": np.maximum(s, eps) ** (1 / p), "norm-lp-sum": (s + eps) ** (1 / p),
+                     "norm-lp-power-p-max": np.maximum(s, eps), "norm-lp-power-p-sum": s + eps}
+            for kind, ref in table.items():
+                _, truth = oracle.reduce_lp(kind, p, eps, xs, y, want_truth=True)
+                assert np.allclose(truth, ref, rtol=1e-12, atol=0), (kind, p, eps)
+                assert np.allclose(y, ref, rtol=2e-6, atol=0), (kind, p, eps)
+    # alpha / beta blend like every other reduction
+    y[:] = 1.0
+    oracle.reduce_lp("norm-lp-power-p-sum", 1.0, 0.5, xs, y, alpha=2.0, beta=3.0)
+    assert np.array_equal(y, (2.0 * (np.abs(xs).sum(axis=3, keepdims=True) + 0.5) + 3.0).astype(np.float32))
+
+
 # ----------------------------------------------------------------------------- real oneDNN -----
 
 def fixtures():
