@@ -114,8 +114,9 @@
     :long 8))
 
 (def ^{:const true
-       :doc "Activation modes: cuDNN's (cudnn/constants.clj:150-158) plus :abs, which the DNNL
-  backend has (dnnl/constants.clj:277-308).  :linear / :identity is a real mode here."}
+       :doc "Activation modes: cuDNN's (cudnn/constants.clj:150-158) plus the kinds of the DNNL
+  backend's table (dnnl/constants.clj:277-308; like that table, :square-dst-bwd maps onto oneDNN's
+  sqrt_use_dst_for_bwd).  :linear / :identity is a real mode here."}
   dd-activation-mode
   {:logistic 0
    :sigmoid 0
@@ -125,7 +126,31 @@
    :elu 4
    :linear 5
    :identity 5
-   :abs 6})
+   :abs 6
+   :square 7
+   :sqrt 8
+   :exp 9
+   :log 10
+   :soft-relu 11
+   :swish 12
+   :gelu 13
+   :gelu-tanh 13
+   :gelu-erf 14
+   :hardswish 15
+   :clip 16
+   :clip-v2 17
+   :pow 18
+   :mish 19
+   :round 20
+   :relu-dst-bwd 21
+   :tanh-dst-bwd 22
+   :elu-dst-bwd 23
+   :square-dst-bwd 24
+   :sqrt-dst-bwd 24
+   :logistic-dst-bwd 25
+   :sigmoid-dst-bwd 25
+   :exp-dst-bwd 26
+   :clip-v2-dst-bwd 27})
 
 (defn dec-activation-mode [^long mode]
   (case mode
@@ -136,6 +161,27 @@
     4 :elu
     5 :linear
     6 :abs
+    7 :square
+    8 :sqrt
+    9 :exp
+    10 :log
+    11 :soft-relu
+    12 :swish
+    13 :gelu-tanh
+    14 :gelu-erf
+    15 :hardswish
+    16 :clip
+    17 :clip-v2
+    18 :pow
+    19 :mish
+    20 :round
+    21 :relu-dst-bwd
+    22 :tanh-dst-bwd
+    23 :elu-dst-bwd
+    24 :sqrt-dst-bwd
+    25 :logistic-dst-bwd
+    26 :exp-dst-bwd
+    27 :clip-v2-dst-bwd
     (dragan-says-ex "This mode is not supported by libdd_b200."
                     {:mode mode :available (keys dd-activation-mode)})))
 

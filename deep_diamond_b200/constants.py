@@ -27,9 +27,19 @@ NUMPY_TYPE = {0: np.float32, 1: np.float64, 2: np.float16, 3: np.int8, 4: np.int
 FORMAT = {"nchw": 0, "nhwc": 1, "abcd": 0, "acdb": 1, "oihw": 0, "ohwi": 1}
 
 ACTIVATION_MODE = {"logistic": 0, "sigmoid": 0, "relu": 1, "tanh": 2, "clipped-relu": 3, "elu": 4,
-                   "linear": 5, "identity": 5, "abs": 6}
+                   "linear": 5, "identity": 5, "abs": 6,
+                   # the rest of the DNNL backend's table (dnnl/constants.clj:277-308); the reference maps
+                   # :square-dst-bwd onto oneDNN's sqrt_use_dst_for_bwd, and so does this table
+                   "square": 7, "sqrt": 8, "exp": 9, "log": 10, "soft-relu": 11, "swish": 12, "gelu": 13,
+                   "gelu-tanh": 13, "gelu-erf": 14, "hardswish": 15, "clip": 16, "clip-v2": 17, "pow": 18,
+                   "mish": 19, "round": 20, "relu-dst-bwd": 21, "tanh-dst-bwd": 22, "elu-dst-bwd": 23,
+                   "square-dst-bwd": 24, "sqrt-dst-bwd": 24, "logistic-dst-bwd": 25, "sigmoid-dst-bwd": 25,
+                   "exp-dst-bwd": 26, "clip-v2-dst-bwd": 27}
 ACTIVATION_NAME = {0: "logistic", 1: "relu", 2: "tanh", 3: "clipped-relu", 4: "elu", 5: "linear",
-                   6: "abs"}
+                   6: "abs", 7: "square", 8: "sqrt", 9: "exp", 10: "log", 11: "soft-relu", 12: "swish",
+                   13: "gelu-tanh", 14: "gelu-erf", 15: "hardswish", 16: "clip", 17: "clip-v2", 18: "pow",
+                   19: "mish", 20: "round", 21: "relu-dst-bwd", 22: "tanh-dst-bwd", 23: "elu-dst-bwd",
+                   24: "sqrt-dst-bwd", 25: "logistic-dst-bwd", 26: "exp-dst-bwd", 27: "clip-v2-dst-bwd"}
 
 OP_TENSOR = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5,
              "ge": 6, "gt": 7, "le": 8, "lt": 9, "eq": 10, "ne": 11}

@@ -314,11 +314,14 @@ def activation_forward(handle, ad, alpha, desc_x, buf_x, beta, desc_y, buf_y):
 
 def activation_backward(handle, ad, alpha, desc_y, buf_y, desc_dy, buf_dy, desc_x, buf_x, beta,
                         desc_dx, buf_dx):
-    """``activation-backward`` (:174-184): dx = alpha*act'(x)*dy + beta*dx (y is not read)."""
-    dyy, ddy, dx, ddx = desc(desc_y), desc(desc_dy), desc(desc_x), desc(desc_dx)
-    a, b = _scalar(alpha, dx.dtype_code), _scalar(beta, ddx.dtype_code)
+    """``activation-backward`` (:174-184): dx = alpha*act'(x)*dy + beta*dx.  y is read by the
+    ``*-dst-bwd`` kinds only (they take the derivative from the forward result)."""
+    dyy, ddy, ddx = desc(desc_y), desc(desc_dy), desc(desc_dx)
+    dx = desc(desc_x) if desc_x is not None else None  # may be absent for a *-dst-bwd kind
+    a, b = _scalar(alpha, ddy.dtype_code), _scalar(beta, ddx.dtype_code)
     check(lib.ddActivationBackward(handle.ptr, ad.ptr, ctypes.byref(a), dyy.ptr, _ptr(buf_y),
-                                   ddy.ptr, _ptr(buf_dy), dx.ptr, _ptr(buf_x), ctypes.byref(b),
+                                   ddy.ptr, _ptr(buf_dy), dx.ptr if dx is not None else None,
+                                   _ptr(buf_x) if buf_x is not None else None, ctypes.byref(b),
                                    ddx.ptr, _ptr(buf_dx)), handle.ptr, "ddActivationBackward")
     return handle
 

@@ -298,7 +298,7 @@ ddStatus_t ddDestroyActivationDescriptor(ddActivationDescriptor_t desc) {
 ddStatus_t ddSetActivationDescriptorEx(ddActivationDescriptor_t a, ddActivationMode_t mode,
                                        ddNanPropagation_t nanOpt, double coef, double shift) {
   if (!a) return DD_STATUS_BAD_PARAM;
-  if ((int)mode < 0 || (int)mode > DD_ACTIVATION_ABS) return DD_STATUS_BAD_PARAM;
+  if ((int)mode < 0 || (int)mode > DD_ACTIVATION_CLIP_V2_DST_BWD) return DD_STATUS_BAD_PARAM;
   a->mode = mode;
   a->nan = nanOpt;
   a->coef = coef;
@@ -509,10 +509,13 @@ ddStatus_t ddActivationBackward(ddHandle_t h, ddActivationDescriptor_t act, cons
                                 const void *dy, ddTensorDescriptor_t xd, const void *x,
                                 const void *beta, ddTensorDescriptor_t dxd, void *dx) {
   DD_RANGE("ddActivationBackward");
-  (void)yd;
-  (void)y;
   DD_CHECK_HANDLE(h);
   if (!act) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddActivationBackward: null activation descriptor");
+  // the *-dst-bwd kinds differentiate from the forward result: y takes the place of x
+  if (act->mode >= DD_ACTIVATION_RELU_DST_BWD && act->mode <= DD_ACTIVATION_CLIP_V2_DST_BWD) {
+    xd = yd;
+    x = y;
+  }
   DD_CHECK(dd_check_desc(h, dyd, "ddActivationBackward dy"));
   DD_CHECK(dd_check_desc(h, xd, "ddActivationBackward x"));
   DD_CHECK(dd_check_desc(h, dxd, "ddActivationBackward dx"));

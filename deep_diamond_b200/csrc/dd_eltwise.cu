@@ -16,6 +16,16 @@
 //   linear    f = a*x+b                    f' = a
 //   clip-relu f = min(max(x,0),a)          f' = 0<x<=a ? 1 : 0
 //   abs       f = |x|                      f' = sign(x)
+// and the rest of the reference's oneDNN table (dnnl/constants.clj:277-308; a = coef, b = shift):
+//   square x^2 | sqrt | exp | log | soft-relu log(1+exp(a x))/a | swish x*sigma(a x) |
+//   gelu-tanh x*sigma(2 g), g = sqrt(2/pi) x (1 + 0.044715 x^2)  (= 0.5 x (1 + tanh g)) |
+//   gelu-erf 0.5 x erfc(-x/sqrt 2)  (= 0.5 x (1 + erf(x/sqrt 2))) | hardswish x*max(0,min(1,a x+b)) |
+//   clip, clip-v2 min(max(x,a),b) | pow a*x^b | mish x*tanh(log(1+exp x)) | round (to nearest even)
+// each with oneDNN's documented derivative, written so that nothing cancels (sigma(2g) for
+// 1 + tanh g, erfc for 1 + erf, e(e+2)/(e(e+2)+2) for tanh(softplus)).  The *-dst-bwd kinds run the
+// same forward and take the derivative from the forward RESULT: relu, tanh 1-y^2, elu y+a,
+// sqrt 1/(2y), logistic y(1-y), exp y, clip-v2.  These kinds run as two kernel families whose
+// arithmetic is selected by a grid-uniform switch (one instantiation per family, not per kind).
 // f*(1-f) and 1-f^2 are evaluated as e/(1+e)^2 forms (no cancellation near saturation); the fp32
 // exp/logistic/tanh come from dd_math_f32.cuh (under 1 ulp), not from the CUDA math library.
 #include "dd_internal.cuh"
@@ -43,6 +53,12 @@ template <> struct dd_math<float> {
     return dd_e_over_one_plus_e_sq<float, 2>(dd_lane<float>::neg_abs_clamped<2>(x, -104.0f));
   }
   static __device__ __forceinline__ float exp_neg(float x) { return dd_exp_neg_rounded<float>(x); }
+  static __device__ __forceinline__ float log(float x) { return logf(x); }
+  static __device__ __forceinline__ float log1p(float x) { return log1pf(x); }
+  static __device__ __forceinline__ float erfc(float x) { return erfcf(x); }
+  static __device__ __forceinline__ float pow(float a, float b) { return powf(a, b); }
+  static __device__ __forceinline__ float sqrt(float x) { return __fsqrt_rn(x); }
+  static __device__ __forceinline__ float rint(float x) { return rintf(x); }
 };
 template <> struct dd_math<double> {
   static __device__ __forceinline__ double exp(double x) { return ::exp(x); }
@@ -71,12 +87,123 @@ template <> struct dd_math<double> {
     return x != x ? x : 4.0 * e * r * r;
   }
   static __device__ __forceinline__ double exp_neg(double x) { return ::exp(x); }
+  static __device__ __forceinline__ double log(double x) { return ::log(x); }
+  static __device__ __forceinline__ double log1p(double x) { return ::log1p(x); }
+  static __device__ __forceinline__ double erfc(double x) { return ::erfc(x); }
+  static __device__ __forceinline__ double pow(double a, double b) { return ::pow(a, b); }
+  static __device__ __forceinline__ double sqrt(double x) { return __dsqrt_rn(x); }
+  static __device__ __forceinline__ double rint(double x) { return ::rint(x); }
 };
 
 struct ddActArgs {
   double coef, shift;
   int nanProp;
+  int kind;  // the families below: which of their kinds (a ddActivationMode_t), the same for the whole grid
 };
+
+// Kernel families of the oneDNN-only kinds: one template instantiation each, the kind chosen at run
+// time.  CHEAP: a few arithmetic instructions.  TRANS: exp / log / erfc / pow inside.
+enum { DD_ACT_FAM_CHEAP = 100, DD_ACT_FAM_TRANS = 101 };
+
+template <typename C>
+__device__ __forceinline__ C dd_ext_cheap_fwd(int kind, C x, C a, C b) {
+  typedef dd_math<C> M;
+  switch (kind) {
+    case DD_ACTIVATION_SQUARE: return dd_mul_rn(x, x);
+    case DD_ACTIVATION_SQRT: return M::sqrt(x);
+    case DD_ACTIVATION_CLIP: case DD_ACTIVATION_CLIP_V2: return x <= a ? a : (x > b ? b : x);
+    case DD_ACTIVATION_HARDSWISH: {
+      const C t = M::fma(a, x, b);
+      return dd_mul_rn(x, t <= (C)0 ? (C)0 : (t >= (C)1 ? (C)1 : t));
+    }
+    default: return M::rint(x);  // ROUND
+  }
+}
+
+// x is the forward source, or the forward result for the *_DST kinds
+template <typename C>
+__device__ __forceinline__ C dd_ext_cheap_bwd(int kind, C x, C dy, C a, C b) {
+  typedef dd_math<C> M;
+  switch (kind) {
+    case DD_ACTIVATION_SQUARE: return dd_mul_rn(dy, dd_add_rn(x, x));
+    case DD_ACTIVATION_SQRT: case DD_ACTIVATION_SQRT_DST_BWD: {
+      const C r = kind == DD_ACTIVATION_SQRT ? M::sqrt(x) : x;
+      return M::div(dy, dd_add_rn(r, r));
+    }
+    case DD_ACTIVATION_CLIP: return (x > a && x <= b) ? dy : (C)0;
+    case DD_ACTIVATION_CLIP_V2: return (x > a && x < b) ? dy : (C)0;
+    case DD_ACTIVATION_HARDSWISH: {
+      const C t = M::fma(a, x, b);
+      return t <= (C)0 ? (C)0 : (t >= (C)1 ? dy : dd_mul_rn(dy, M::fma(dd_add_rn(a, a), x, b)));
+    }
+    case DD_ACTIVATION_TANH_DST_BWD: return dd_mul_rn(dy, M::fma(-x, x, (C)1));
+    case DD_ACTIVATION_ELU_DST_BWD: return x > (C)0 ? dy : dd_mul_rn(dy, dd_add_rn(x, a));
+    case DD_ACTIVATION_LOGISTIC_DST_BWD: return dd_mul_rn(dy, dd_mul_rn(x, dd_add_rn((C)1, -x)));
+    default: return dd_mul_rn(dy, x);  // EXP_DST_BWD
+  }
+}
+
+template <typename C>
+__device__ __forceinline__ C dd_ext_trans_fwd(int kind, C x, C a, C b) {
+  typedef dd_math<C> M;
+  switch (kind) {
+    case DD_ACTIVATION_EXP: return M::exp(x);
+    case DD_ACTIVATION_LOG: return M::log(x);
+    case DD_ACTIVATION_SOFT_RELU: {
+      const C t = dd_mul_rn(a, x);
+      const C sp = t > (C)0 ? dd_add_rn(t, M::log1p(M::exp(-t))) : M::log1p(M::exp(t));
+      return M::div(sp, a);
+    }
+    case DD_ACTIVATION_SWISH: return dd_mul_rn(x, M::sigmoid(dd_mul_rn(a, x)));
+    case DD_ACTIVATION_GELU_TANH: {
+      const C g = dd_mul_rn(dd_mul_rn((C)0.7978845608028654, x), M::fma((C)0.044715, dd_mul_rn(x, x), (C)1));
+      return dd_mul_rn(x, M::sigmoid(dd_add_rn(g, g)));
+    }
+    case DD_ACTIVATION_GELU_ERF:
+      return dd_mul_rn(dd_mul_rn((C)0.5, x), M::erfc(dd_mul_rn((C)-0.7071067811865476, x)));
+    case DD_ACTIVATION_POW: return dd_mul_rn(a, M::pow(x, b));
+    default: {  // MISH: tanh(log(1 + e)) = e(e+2) / (e(e+2) + 2)
+      if (x > (C)20) return x;
+      const C e = M::exp(x);
+      const C n = dd_mul_rn(e, dd_add_rn(e, (C)2));
+      return dd_mul_rn(x, M::div(n, dd_add_rn(n, (C)2)));
+    }
+  }
+}
+
+template <typename C>
+__device__ __forceinline__ C dd_ext_trans_bwd(int kind, C x, C dy, C a, C b) {
+  typedef dd_math<C> M;
+  switch (kind) {
+    case DD_ACTIVATION_EXP: return dd_mul_rn(dy, M::exp(x));
+    case DD_ACTIVATION_LOG: return M::div(dy, x);
+    case DD_ACTIVATION_SOFT_RELU: return dd_mul_rn(dy, M::sigmoid(dd_mul_rn(a, x)));
+    case DD_ACTIVATION_SWISH: {  // s + a x s (1 - s)
+      const C t = dd_mul_rn(a, x);
+      return dd_mul_rn(dy, M::fma(t, M::dsigmoid(t), M::sigmoid(t)));
+    }
+    case DD_ACTIVATION_GELU_TANH: {  // s + 2 x s (1 - s) g',  s = sigma(2g)
+      const C x2 = dd_mul_rn(x, x);
+      const C g = dd_mul_rn(dd_mul_rn((C)0.7978845608028654, x), M::fma((C)0.044715, x2, (C)1));
+      const C gp = dd_mul_rn((C)0.7978845608028654, M::fma((C)0.134145, x2, (C)1));
+      const C g2 = dd_add_rn(g, g);
+      return dd_mul_rn(dy, M::fma(dd_mul_rn(dd_add_rn(x, x), gp), M::dsigmoid(g2), M::sigmoid(g2)));
+    }
+    case DD_ACTIVATION_GELU_ERF: {  // 0.5 erfc(-x/sqrt 2) + x exp(-x^2/2)/sqrt(2 pi)
+      const C h = dd_mul_rn((C)0.5, M::erfc(dd_mul_rn((C)-0.7071067811865476, x)));
+      const C q = dd_mul_rn(dd_mul_rn((C)0.3989422804014327, x), M::exp(dd_mul_rn((C)-0.5, dd_mul_rn(x, x))));
+      return dd_mul_rn(dy, dd_add_rn(h, q));
+    }
+    case DD_ACTIVATION_POW: return dd_mul_rn(dy, dd_mul_rn(dd_mul_rn(a, b), M::pow(x, dd_add_rn(b, (C)-1))));
+    default: {  // MISH: e w / d^2,  w = 4(x+1) + 4e^2 + e^3 + e(4x+6),  d = e^2 + 2e + 2
+      if (x > (C)20) return dy;
+      const C e = M::exp(x);
+      const C d = M::fma(e, dd_add_rn(e, (C)2), (C)2);
+      const C w = M::fma(e, M::fma(e, dd_add_rn(e, (C)4), M::fma((C)4, x, (C)6)), dd_mul_rn((C)4, dd_add_rn(x, (C)1)));
+      return dd_mul_rn(dy, M::div(dd_mul_rn(e, w), dd_mul_rn(d, d)));
+    }
+  }
+}
 
 // The result of a 16-bit element type takes the special-function-unit forms of dd_math_f32.cuh for
 // the transcendental modes (at most one unit of the 16-bit type off).
@@ -86,8 +213,10 @@ template <> struct dd_light<__half> { static constexpr int value = 1; };
 template <> struct dd_light<__nv_bfloat16> { static constexpr int value = 2; };
 
 template <typename C, int MODE, int LIGHT = 0>
-__device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp) {
+__device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp, int kind = 0) {
   typedef dd_math<C> M;
+  if (MODE == DD_ACT_FAM_CHEAP) return dd_ext_cheap_fwd<C>(kind, x, coef, shift);
+  if (MODE == DD_ACT_FAM_TRANS) return dd_ext_trans_fwd<C>(kind, x, coef, shift);
   if constexpr (LIGHT != 0 && sizeof(C) == 4) {
     if (MODE == DD_ACTIVATION_SIGMOID) return dd_sigmoid_light(x);
     if (MODE == DD_ACTIVATION_TANH) return LIGHT == 2 ? dd_tanh_sfu(x) : dd_tanh_light(x);
@@ -117,8 +246,10 @@ __device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp) {
 
 // returns act'(x) * dy
 template <typename C, int MODE, int LIGHT = 0>
-__device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef) {
+__device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef, C shift = (C)0, int kind = 0) {
   typedef dd_math<C> M;
+  if (MODE == DD_ACT_FAM_CHEAP) return dd_ext_cheap_bwd<C>(kind, x, dy, coef, shift);
+  if (MODE == DD_ACT_FAM_TRANS) return dd_ext_trans_bwd<C>(kind, x, dy, coef, shift);
   if constexpr (LIGHT != 0 && sizeof(C) == 4) {
     if (MODE == DD_ACTIVATION_SIGMOID) return dd_mul_rn(dy, dd_dsigmoid_light(x));
     if (MODE == DD_ACTIVATION_TANH) return dd_mul_rn(dy, dd_dtanh_light(x));
@@ -184,8 +315,9 @@ struct ddEltFlatParams {
 };
 
 // PLAIN: alpha == 1 and beta == 0 (what every layer passes): no blend arithmetic at all.
+// (the two run-time-switched families get 64 registers: the math library's slow paths spill at 32)
 template <typename T, typename C, int MODE, bool BWD, bool PLAIN>
-__global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) {
+__global__ void __launch_bounds__(256, MODE >= DD_ACT_FAM_CHEAP ? 4 : 8) dd_elt_flat_kernel(ddEltFlatParams p) {
   dd_pdl_prologue();
   constexpr int V = 16 / sizeof(T);
   const T *x = (const T *)p.x;
@@ -220,8 +352,8 @@ __global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) 
 #pragma unroll
         for (int k = 0; k < V; k++) {
           C xc = dd_load<C, T>(xv[k]);
-          C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef)
-                    : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
+          C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef, shift, p.act.kind)
+                    : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp, p.act.kind);
           rv[k] = PLAIN ? dd_store<T, C>(v) : dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
         }
       }
@@ -231,8 +363,8 @@ __global__ void __launch_bounds__(256, 8) dd_elt_flat_kernel(ddEltFlatParams p) 
   }
   for (int64_t i = done + tid; i < p.n; i += nthreads) {
     C xc = dd_load<C, T>(x[i]);
-    C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dy[i]), coef)
-              : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
+    C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dy[i]), coef, shift, p.act.kind)
+              : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp, p.act.kind);
     C old = useOld ? dd_load<C, T>(out[i]) : (C)0;
     out[i] = dd_store<T, C>(dd_blend(alpha, v, beta, old, useOld));
   }
@@ -281,7 +413,7 @@ __global__ void __launch_bounds__(256, 4) dd_elt_flat_multi_kernel(ddEltFlatPara
   }
   for (int64_t i = nv * 4 + tid; i < p.n; i += nthreads) {
     const float xc = x[i];
-    out[i] = BWD ? dd_act_bwd<float, MODE, false>(xc, dy[i], coef) : dd_act_fwd<float, MODE, false>(xc, coef, shift, nanProp);
+    out[i] = BWD ? dd_act_bwd<float, MODE, false>(xc, dy[i], coef) : dd_act_fwd<float, MODE, false>(xc, coef, shift, nanProp, p.act.kind);
   }
 }
 
@@ -306,8 +438,8 @@ __global__ void __launch_bounds__(256) dd_elt_strided_kernel(ddEltStridedParams 
     int64_t off[3];
     dd_offsets<3, int64_t>(p.sp, i, off);
     C xc = dd_load<C, T>(x[off[0]]);
-    C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dy[off[1]]), coef)
-              : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
+    C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dy[off[1]]), coef, shift, p.act.kind)
+              : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp, p.act.kind);
     C old = useOld ? dd_load<C, T>(out[off[2]]) : (C)0;
     out[off[2]] = dd_store<T, C>(dd_blend(alpha, v, beta, old, useOld));
   }
@@ -338,8 +470,8 @@ __global__ void __launch_bounds__(256) dd_elt_rows_kernel(ddEltStridedParams p) 
 #pragma unroll
     for (int k = 0; k < V; k++) {
       C xc = dd_load<C, T>(xv[k]);
-      C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef)
-                : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp);
+      C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef, shift, p.act.kind)
+                : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp, p.act.kind);
       rv[k] = dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
     }
     *(uint4 *)(out + off[2]) = res;
@@ -444,6 +576,15 @@ static ddStatus_t dispatch_mode(ddHandle_t h, int mode, const ddCanon &c, const 
     case DD_ACTIVATION_ELU: return launch_elt<T, C, DD_ACTIVATION_ELU, BWD>(h, c, x, dy, out, alpha, beta, act);
     case DD_ACTIVATION_LINEAR: return launch_elt<T, C, DD_ACTIVATION_LINEAR, BWD>(h, c, x, dy, out, alpha, beta, act);
     case DD_ACTIVATION_ABS: return launch_elt<T, C, DD_ACTIVATION_ABS, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_ROUND:
+      if (BWD) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "activation: round has no backward (oneDNN defines it forward only)");
+    case DD_ACTIVATION_SQUARE: case DD_ACTIVATION_SQRT: case DD_ACTIVATION_HARDSWISH: case DD_ACTIVATION_CLIP:
+    case DD_ACTIVATION_CLIP_V2: case DD_ACTIVATION_TANH_DST_BWD: case DD_ACTIVATION_ELU_DST_BWD:
+    case DD_ACTIVATION_SQRT_DST_BWD: case DD_ACTIVATION_LOGISTIC_DST_BWD: case DD_ACTIVATION_EXP_DST_BWD:
+      return launch_elt<T, C, DD_ACT_FAM_CHEAP, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_EXP: case DD_ACTIVATION_LOG: case DD_ACTIVATION_SOFT_RELU: case DD_ACTIVATION_SWISH:
+    case DD_ACTIVATION_GELU_TANH: case DD_ACTIVATION_GELU_ERF: case DD_ACTIVATION_POW: case DD_ACTIVATION_MISH:
+      return launch_elt<T, C, DD_ACT_FAM_TRANS, BWD>(h, c, x, dy, out, alpha, beta, act);
   }
   DD_FAIL(h, DD_STATUS_BAD_PARAM, "activation: unknown mode %d", mode);
 }
@@ -473,8 +614,20 @@ ddStatus_t dd_activation_fwd_impl(ddHandle_t h, const ddActivationStruct *a, dou
   }
   ddCanon c;
   dd_canonicalize(&c, xd->nd, xd->dims, 3, st, 2);
-  ddActArgs act = {a->coef, a->shift, a->nan == DD_PROPAGATE_NAN};
-  return dispatch_type<false>(h, xd->dtype, a->mode, c, x, nullptr, y, alpha, beta, act);
+  // a *-dst-bwd kind runs the forward of the kind it is named after
+  int mode = a->mode;
+  switch (mode) {
+    case DD_ACTIVATION_RELU_DST_BWD: mode = DD_ACTIVATION_RELU; break;
+    case DD_ACTIVATION_TANH_DST_BWD: mode = DD_ACTIVATION_TANH; break;
+    case DD_ACTIVATION_ELU_DST_BWD: mode = DD_ACTIVATION_ELU; break;
+    case DD_ACTIVATION_SQRT_DST_BWD: mode = DD_ACTIVATION_SQRT; break;
+    case DD_ACTIVATION_LOGISTIC_DST_BWD: mode = DD_ACTIVATION_SIGMOID; break;
+    case DD_ACTIVATION_EXP_DST_BWD: mode = DD_ACTIVATION_EXP; break;
+    case DD_ACTIVATION_CLIP_V2_DST_BWD: mode = DD_ACTIVATION_CLIP_V2; break;
+    default: break;
+  }
+  ddActArgs act = {a->coef, a->shift, a->nan == DD_PROPAGATE_NAN, mode};
+  return dispatch_type<false>(h, xd->dtype, mode, c, x, nullptr, y, alpha, beta, act);
 }
 
 ddStatus_t dd_activation_bwd_impl(ddHandle_t h, const ddActivationStruct *a, double alpha,
@@ -489,6 +642,11 @@ ddStatus_t dd_activation_bwd_impl(ddHandle_t h, const ddActivationStruct *a, dou
   }
   ddCanon c;
   dd_canonicalize(&c, xd->nd, xd->dims, 3, st, 2);
-  ddActArgs act = {a->coef, a->shift, a->nan == DD_PROPAGATE_NAN};
-  return dispatch_type<true>(h, xd->dtype, a->mode, c, x, dy, dx, alpha, beta, act);
+  // `x` is the forward result for the *-dst-bwd kinds (the caller has put y in its place); relu and
+  // clip-v2 have the same derivative written in terms of either
+  int mode = a->mode;
+  if (mode == DD_ACTIVATION_RELU_DST_BWD) mode = DD_ACTIVATION_RELU;
+  if (mode == DD_ACTIVATION_CLIP_V2_DST_BWD) mode = DD_ACTIVATION_CLIP_V2;
+  ddActArgs act = {a->coef, a->shift, a->nan == DD_PROPAGATE_NAN, mode};
+  return dispatch_type<true>(h, xd->dtype, mode, c, x, dy, dx, alpha, beta, act);
 }

@@ -140,7 +140,9 @@ class B200ActivationBlueprint:
         dst_tz = self.fact.create_tensor(self.diff_desc.view(), diff_src_tz.batch_index(), False)
         if linear:
             return B200LinearActivationTraining(self.fact.handle, self, src_tz, dst_tz, diff_src_tz)
-        if self.activ in ("sigmoid", "logistic"):
+        # a kind whose derivative reads the forward result needs that result kept apart from the
+        # incoming gradient (the *-dst-bwd kinds of the DNNL table), like sigmoid in the reference
+        if self.activ in ("sigmoid", "logistic") or self.activ.endswith("-dst-bwd"):
             diff_dst_tz = self.fact.create_tensor(self.diff_desc.view(), dst_tz.batch_index(), False)
             return B200ActivationTraining(self.fact.handle, self, self.ad, src_tz, dst_tz, diff_dst_tz, diff_src_tz)
         return B200ActivationTraining(self.fact.handle, self, self.ad, src_tz, dst_tz, dst_tz, diff_src_tz)

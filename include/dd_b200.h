@@ -83,7 +83,33 @@ typedef enum {
   DD_ACTIVATION_CLIPPED_RELU = 3, /* :clipped-relu          y = min(max(x,0),coef)               */
   DD_ACTIVATION_ELU = 4,          /* :elu                   y = x>0 ? x : coef*(exp(x)-1)        */
   DD_ACTIVATION_LINEAR = 5,       /* :linear / :identity    y = coef*x + shift                   */
-  DD_ACTIVATION_ABS = 6           /* :abs (dnnl only; dnnl-t/core_test.clj:183-200)             */
+  DD_ACTIVATION_ABS = 6,          /* :abs (dnnl only; dnnl-t/core_test.clj:183-200)             */
+  /* The other kinds of the reference's oneDNN table (dnnl/constants.clj:277-308), which its DNNL
+   * backend accepts in `activation`; a = coef, b = shift of ddSetActivationDescriptorEx, defined as
+   * oneDNN documents them. */
+  DD_ACTIVATION_SQUARE = 7,       /* :square      y = x^2                                        */
+  DD_ACTIVATION_SQRT = 8,         /* :sqrt                                                       */
+  DD_ACTIVATION_EXP = 9,          /* :exp                                                        */
+  DD_ACTIVATION_LOG = 10,         /* :log                                                        */
+  DD_ACTIVATION_SOFT_RELU = 11,   /* :soft-relu   y = log(1+exp(a*x))/a                          */
+  DD_ACTIVATION_SWISH = 12,       /* :swish       y = x/(1+exp(-a*x))                            */
+  DD_ACTIVATION_GELU_TANH = 13,   /* :gelu :gelu-tanh  y = 0.5x(1+tanh(sqrt(2/pi)(x+0.044715x^3))) */
+  DD_ACTIVATION_GELU_ERF = 14,    /* :gelu-erf    y = 0.5x(1+erf(x/sqrt 2))                      */
+  DD_ACTIVATION_HARDSWISH = 15,   /* :hardswish   y = x*max(0,min(1,a*x+b))                      */
+  DD_ACTIVATION_CLIP = 16,        /* :clip        y = min(max(x,a),b); dx = dy where a < x <= b  */
+  DD_ACTIVATION_CLIP_V2 = 17,     /* :clip-v2     the same;            dx = dy where a < x <  b  */
+  DD_ACTIVATION_POW = 18,         /* :pow         y = a*x^b                                      */
+  DD_ACTIVATION_MISH = 19,        /* :mish        y = x*tanh(log(1+exp(x)))                      */
+  DD_ACTIVATION_ROUND = 20,       /* :round       to nearest, ties to even; forward only         */
+  /* Same forward as the kind named; backward takes the derivative from the forward RESULT, which
+   * ddActivationBackward then reads from its y argument (x may be NULL). */
+  DD_ACTIVATION_RELU_DST_BWD = 21,
+  DD_ACTIVATION_TANH_DST_BWD = 22,
+  DD_ACTIVATION_ELU_DST_BWD = 23,
+  DD_ACTIVATION_SQRT_DST_BWD = 24,
+  DD_ACTIVATION_LOGISTIC_DST_BWD = 25,
+  DD_ACTIVATION_EXP_DST_BWD = 26,
+  DD_ACTIVATION_CLIP_V2_DST_BWD = 27
 } ddActivationMode_t;
 
 typedef enum { DD_NOT_PROPAGATE_NAN = 0, DD_PROPAGATE_NAN = 1 } ddNanPropagation_t;

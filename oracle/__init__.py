@@ -30,7 +30,12 @@ NP_OF = {F32: np.float32, F64: np.float64, F16: np.float16, S8: np.int8, S32: np
 ACT = {"sigmoid": 0, "logistic": 0, "relu": 1, "tanh": 2, "clipped-relu": 3, "elu": 4,
        "linear": 5, "identity": 5, "abs": 6,
        # elu as oneDNN's fp32 kernels form it, alpha * (float(exp(x)) - 1): forward only, oracle only
-       "elu-fp32-exp-minus-1": 7}
+       "elu-fp32-exp-minus-1": 7,
+       # the rest of the reference's oneDNN table (dnnl/constants.clj:277-308)
+       "square": 20, "sqrt": 21, "exp": 22, "log": 23, "soft-relu": 24, "swish": 25, "gelu": 26, "gelu-tanh": 26,
+       "gelu-erf": 27, "hardswish": 28, "clip": 29, "clip-v2": 30, "pow": 31, "mish": 32, "round": 33,
+       "relu-dst-bwd": 34, "tanh-dst-bwd": 35, "elu-dst-bwd": 36, "sqrt-dst-bwd": 37, "logistic-dst-bwd": 38,
+       "sigmoid-dst-bwd": 38, "exp-dst-bwd": 39, "clip-v2-dst-bwd": 40}
 BINOP = {"add": 0, "mul": 1, "min": 2, "max": 3, "sub": 4, "div": 5,
          "ge": 6, "gt": 7, "le": 8, "lt": 9, "eq": 10, "ne": 11}
 REDOP = {"add": 0, "sum": 0, "mul": 1, "min": 2, "max": 3, "amax": 4, "avg": 5, "mean": 5,
@@ -141,14 +146,15 @@ def eltwise_fwd(alg, x, y, coef=0.0, shift=0.0, alpha=1.0, beta=0.0, nanprop=Tru
     return y
 
 
-def eltwise_bwd(alg, x, dy, dx, coef=0.0, alpha=1.0, beta=0.0, tag=None):
+def eltwise_bwd(alg, x, dy, dx, coef=0.0, alpha=1.0, beta=0.0, tag=None, shift=0.0):
+    """``x`` is the forward source; for the ``*-dst-bwd`` kinds pass the forward result there."""
     assert x.shape == dy.shape == dx.shape
     dims, xs, xp = _desc(x)
     _, gs, gp = _desc(dy)
     _, os_, op = _desc(dx)
-    rc = lib().oracle_eltwise_bwd(ACT[alg], ctypes.c_double(coef), code_of(x, tag), len(x.shape),
-                                  dims, xs, xp, gs, gp, os_, op, ctypes.c_double(alpha),
-                                  ctypes.c_double(beta))
+    rc = lib().oracle_eltwise_bwd_ex(ACT[alg], ctypes.c_double(coef), ctypes.c_double(shift), code_of(x, tag),
+                                     len(x.shape), dims, xs, xp, gs, gp, os_, op, ctypes.c_double(alpha),
+                                     ctypes.c_double(beta))
     assert rc == 0
     return dx
 
@@ -162,13 +168,13 @@ def eltwise_fwd_truth(alg, x, coef=0.0, shift=0.0):
     return out
 
 
-def eltwise_bwd_truth(alg, x, dy, coef=0.0):
+def eltwise_bwd_truth(alg, x, dy, coef=0.0, shift=0.0):
     x = np.ascontiguousarray(x, dtype=np.float32).ravel()
     dy = np.ascontiguousarray(dy, dtype=np.float32).ravel()
     out = np.empty(x.size, dtype=np.float64)
-    lib().oracle_eltwise_bwd_truth(ACT[alg], ctypes.c_double(coef), ctypes.c_int64(x.size),
-                                   ctypes.c_void_p(x.ctypes.data), ctypes.c_void_p(dy.ctypes.data),
-                                   ctypes.c_void_p(out.ctypes.data))
+    lib().oracle_eltwise_bwd_truth_ex(ACT[alg], ctypes.c_double(coef), ctypes.c_double(shift),
+                                      ctypes.c_int64(x.size), ctypes.c_void_p(x.ctypes.data),
+                                      ctypes.c_void_p(dy.ctypes.data), ctypes.c_void_p(out.ctypes.data))
     return out
 
 

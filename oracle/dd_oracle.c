@@ -288,7 +288,83 @@ int oracle_reorder(int nd, const int64_t *dims, int st, const int64_t *sst, cons
  * float BEFORE the subtraction (what dnnl/constants.clj:277-308 `:elu` binds).  Near zero the
  * subtraction cancels: the result keeps only the bits of exp(x) above 1.  Oracle-only: it exists so
  * that the tests can state how far the library's elu (alpha * expm1(x), no cancellation) sits from it. */
-enum { A_SIGMOID = 0, A_RELU = 1, A_TANH = 2, A_CLIP = 3, A_ELU = 4, A_LINEAR = 5, A_ABS = 6, A_ELU_FP32 = 7 };
+enum { A_SIGMOID = 0, A_RELU = 1, A_TANH = 2, A_CLIP = 3, A_ELU = 4, A_LINEAR = 5, A_ABS = 6, A_ELU_FP32 = 7,
+       /* the rest of the reference's oneDNN table, dnnl/constants.clj:277-308, by oneDNN's documented
+        * definitions (a = alpha, b = beta of the primitive); X_DST = derivative from the forward result */
+       X_SQUARE = 20, X_SQRT, X_EXP, X_LOG, X_SOFT_RELU, X_SWISH, X_GELU_TANH, X_GELU_ERF, X_HARDSWISH,
+       X_CLIP, X_CLIP_V2, X_POW, X_MISH, X_ROUND,
+       X_RELU_DST, X_TANH_DST, X_ELU_DST, X_SQRT_DST, X_LOGISTIC_DST, X_EXP_DST, X_CLIP_V2_DST };
+
+/* forward kind behind a *-dst-bwd kind */
+static int fwd_alg_of(int alg) {
+  switch (alg) {
+    case X_RELU_DST: return A_RELU;
+    case X_TANH_DST: return A_TANH;
+    case X_ELU_DST: return A_ELU;
+    case X_SQRT_DST: return X_SQRT;
+    case X_LOGISTIC_DST: return A_SIGMOID;
+    case X_EXP_DST: return X_EXP;
+    case X_CLIP_V2_DST: return X_CLIP_V2;
+  }
+  return alg;
+}
+
+#define SQRT_2_OVER_PI 0.7978845608028654
+#define GELU_C 0.044715
+
+/* the transcendental kinds of the table in double (x, a, b already double) */
+static double ext_fwd_d(int alg, double x, double a, double b) {
+  switch (alg) {
+    case X_SQUARE: return x * x;
+    case X_SQRT: return sqrt(x);
+    case X_EXP: return exp(x);
+    case X_LOG: return log(x);
+    case X_SOFT_RELU: { double t = a * x; return (t > 0 ? t + log1p(exp(-t)) : log1p(exp(t))) / a; }
+    case X_SWISH: return x / (1.0 + exp(-a * x));
+    case X_GELU_TANH: { double g = SQRT_2_OVER_PI * x * (1.0 + GELU_C * x * x); return x / (1.0 + exp(-2.0 * g)); }
+    case X_GELU_ERF: return 0.5 * x * erfc(-x * M_SQRT1_2);
+    case X_HARDSWISH: { double t = fma(a, x, b); return x * (t <= 0 ? 0.0 : (t >= 1 ? 1.0 : t)); }
+    case X_CLIP: case X_CLIP_V2: return x <= a ? a : (x > b ? b : x);
+    case X_POW: return a * pow(x, b);
+    case X_MISH: { if (x > 20) return x; double e = exp(x), n = e * (e + 2.0); return x * (n / (n + 2.0)); }
+    case X_ROUND: return rint(x);
+  }
+  return NAN;
+}
+
+/* derivative (not yet times dy); x is the forward source, or the forward result for X_*_DST */
+static double ext_der_d(int alg, double x, double a, double b) {
+  switch (alg) {
+    case X_SQUARE: return x + x;
+    case X_SQRT: return 1.0 / (2.0 * sqrt(x));
+    case X_EXP: return exp(x);
+    case X_LOG: return 1.0 / x;
+    case X_SOFT_RELU: return 1.0 / (1.0 + exp(-a * x));
+    case X_SWISH: { double s = 1.0 / (1.0 + exp(-a * x)); return s * (1.0 + a * x * (1.0 - s)); }
+    case X_GELU_TANH: {
+      double g = SQRT_2_OVER_PI * x * (1.0 + GELU_C * x * x), gp = SQRT_2_OVER_PI * (1.0 + 3.0 * GELU_C * x * x);
+      double e = exp(-2.0 * fabs(g)), r = 1.0 / (1.0 + e), s = g >= 0 ? r : e * r;
+      return s + 2.0 * x * gp * (e * r * r);
+    }
+    case X_GELU_ERF: return 0.5 * erfc(-x * M_SQRT1_2) + x * exp(-0.5 * x * x) * 0.3989422804014327;
+    case X_HARDSWISH: { double t = fma(a, x, b); return t <= 0 ? 0.0 : (t >= 1 ? 1.0 : fma(a + a, x, b)); }
+    case X_CLIP: return (x > a && x <= b) ? 1.0 : 0.0;
+    case X_CLIP_V2: case X_CLIP_V2_DST: return (x > a && x < b) ? 1.0 : 0.0;
+    case X_POW: return a * b * pow(x, b - 1.0);
+    case X_MISH: {
+      if (x > 20) return 1.0;
+      double e = exp(x), d = e * e + 2.0 * e + 2.0;
+      double w = 4.0 * (x + 1.0) + 4.0 * e * e + e * e * e + e * (4.0 * x + 6.0);
+      return e * w / (d * d);
+    }
+    case X_TANH_DST: return 1.0 - x * x;
+    case X_ELU_DST: return x > 0 ? 1.0 : x + a;
+    case X_SQRT_DST: return 1.0 / (2.0 * x);
+    case X_LOGISTIC_DST: return x * (1.0 - x);
+    case X_EXP_DST: return x;
+  }
+  return NAN;
+}
 
 static float act_fwd_f(int alg, float x, float a, float b, int nanprop) {
   switch (alg) {
@@ -308,7 +384,15 @@ static float act_fwd_f(int alg, float x, float a, float b, int nanprop) {
       if (nanprop && x != x) return x;
       return fminf(fmaxf(x, 0.f), a);
     case A_ABS: return fabsf(x);
+    /* the few-instruction kinds in the float arithmetic the definition spells out (so bit-exact) */
+    case X_SQUARE: return x * x;
+    case X_SQRT: return sqrtf(x);
+    case X_CLIP: case X_CLIP_V2: return x <= a ? a : (x > b ? b : x);
+    case X_HARDSWISH: { float t = fmaf(a, x, b); return x * (t <= 0.f ? 0.f : (t >= 1.f ? 1.f : t)); }
+    case X_ROUND: return rintf(x);
   }
+  /* the transcendental kinds: the definition in double on the float arguments, rounded once */
+  if (alg >= X_SQUARE) return (float)ext_fwd_d(alg, (double)x, (double)a, (double)b);
   return NAN;
 }
 
@@ -330,12 +414,25 @@ static double act_fwd_d(int alg, double x, double a, double b, int nanprop) {
       return fmin(fmax(x, 0.0), a);
     case A_ABS: return fabs(x);
   }
+  if (alg >= X_SQUARE) return ext_fwd_d(alg, x, a, b);
   return NAN;
 }
 
 /* derivative times dy, from the forward source */
-static float act_bwd_f(int alg, float x, float dy, float a) {
+static float act_bwd_f(int alg, float x, float dy, float a, float b) {
   switch (alg) {
+    case X_RELU_DST: return x > 0.f ? dy : a * dy;
+    case X_SQUARE: return dy * (x + x);
+    case X_SQRT: { float r = sqrtf(x); return dy / (r + r); }
+    case X_SQRT_DST: return dy / (x + x);
+    case X_CLIP: return (x > a && x <= b) ? dy : 0.f;
+    case X_CLIP_V2: case X_CLIP_V2_DST: return (x > a && x < b) ? dy : 0.f;
+    case X_HARDSWISH: { float t = fmaf(a, x, b); return t <= 0.f ? 0.f : (t >= 1.f ? dy : dy * fmaf(a + a, x, b)); }
+    case X_TANH_DST: return dy * fmaf(-x, x, 1.f);
+    case X_ELU_DST: return x > 0.f ? dy : dy * (x + a);
+    case X_LOGISTIC_DST: return dy * (x * (1.f - x));
+    case X_EXP_DST: return dy * x;
+    case X_LOG: return dy / x;
     case A_RELU: return x > 0.f ? dy : a * dy;
     /* derivative evaluated in double and rounded once, then one fp32 product with dy */
     case A_SIGMOID: { double e = exp(-fabs((double)x)); double r = 1.0 / (1.0 + e); return dy * (float)(e * r * r); }
@@ -345,11 +442,17 @@ static float act_bwd_f(int alg, float x, float dy, float a) {
     case A_CLIP: return (x > 0.f && x <= a) ? dy : 0.f;
     case A_ABS: return x > 0.f ? dy : (x < 0.f ? -dy : 0.f);
   }
+  /* transcendental kinds: the derivative in double, rounded once, then one fp32 product with dy */
+  if (alg >= X_SQUARE) return dy * (float)ext_der_d(alg, (double)x, (double)a, (double)b);
   return NAN;
 }
 
-static double act_bwd_d(int alg, double x, double dy, double a) {
+static double act_bwd_d(int alg, double x, double dy, double a, double b) {
   switch (alg) {
+    case X_RELU_DST: return x > 0.0 ? dy : a * dy;
+    case X_LOG: return dy / x;
+    case X_SQRT: { double r = sqrt(x); return dy / (r + r); }
+    case X_SQRT_DST: return dy / (x + x);
     case A_RELU: return x > 0.0 ? dy : a * dy;
     case A_SIGMOID: { double e = exp(-fabs(x)); double r = 1.0 / (1.0 + e); return dy * (e * r * r); }
     case A_TANH: { double e = exp(-2.0 * fabs(x)); double r = 1.0 / (1.0 + e); return dy * (4.0 * e * r * r); }
@@ -358,6 +461,7 @@ static double act_bwd_d(int alg, double x, double dy, double a) {
     case A_CLIP: return (x > 0.0 && x <= a) ? dy : 0.0;
     case A_ABS: return x > 0.0 ? dy : (x < 0.0 ? -dy : 0.0);
   }
+  if (alg >= X_SQUARE) return dy * ext_der_d(alg, x, a, b);
   return NAN;
 }
 
@@ -387,6 +491,7 @@ int oracle_eltwise_fwd(int alg, double coef, double shift, int nanprop, int t, i
                        void *y, double alpha, double beta) {
   const int64_t n = total_of(nd, dims);
   const int dense = is_default(nd, dims, xst) && is_default(nd, dims, yst);
+  alg = fwd_alg_of(alg);
   if (dense && t == T_F32 && alpha == 1.0 && beta == 0.0) {
     /* the common case (dense fp32, no blend) without the per-element type and layout dispatch; the
      * arithmetic is act_fwd_f's, so the results are the same bits */
@@ -419,9 +524,10 @@ int oracle_eltwise_fwd(int alg, double coef, double shift, int nanprop, int t, i
   return 0;
 }
 
-int oracle_eltwise_bwd(int alg, double coef, int t, int nd, const int64_t *dims, const int64_t *xst,
-                       const void *x, const int64_t *dyst, const void *dy, const int64_t *dxst,
-                       void *dx, double alpha, double beta) {
+/* `x` is the forward source; for the X_*_DST kinds the caller passes the forward result there */
+int oracle_eltwise_bwd_ex(int alg, double coef, double shift, int t, int nd, const int64_t *dims,
+                          const int64_t *xst, const void *x, const int64_t *dyst, const void *dy,
+                          const int64_t *dxst, void *dx, double alpha, double beta) {
   const int64_t n = total_of(nd, dims);
   const int dense = is_default(nd, dims, xst) && is_default(nd, dims, dyst) && is_default(nd, dims, dxst);
   if (dense && t == T_F32 && alpha == 1.0 && beta == 0.0) {
@@ -434,7 +540,7 @@ int oracle_eltwise_bwd(int alg, double coef, int t, int nd, const int64_t *dims,
       return 0;
     }
 #pragma omp parallel for schedule(static)
-    for (int64_t i = 0; i < n; i++) of[i] = act_bwd_f(alg, xf[i], gf[i], a);
+    for (int64_t i = 0; i < n; i++) of[i] = act_bwd_f(alg, xf[i], gf[i], a, (float)shift);
     return 0;
   }
 #pragma omp parallel for schedule(static)
@@ -442,25 +548,36 @@ int oracle_eltwise_bwd(int alg, double coef, int t, int nd, const int64_t *dims,
     int64_t xo = dense ? i : offset_of(nd, dims, xst, i), go = dense ? i : offset_of(nd, dims, dyst, i),
             oo = dense ? i : offset_of(nd, dims, dxst, i);
     if (t == T_F64) {
-      double v = act_bwd_d(alg, ((const double *)x)[xo], ((const double *)dy)[go], coef);
+      double v = act_bwd_d(alg, ((const double *)x)[xo], ((const double *)dy)[go], coef, shift);
       ((double *)dx)[oo] = blend_d(alpha, v, beta, dx, t, oo);
     } else {
-      float v = act_bwd_f(alg, load_as_float(x, t, xo), load_as_float(dy, t, go), (float)coef);
+      float v = act_bwd_f(alg, load_as_float(x, t, xo), load_as_float(dy, t, go), (float)coef, (float)shift);
       store_from_float(dx, t, oo, blend_f((float)alpha, v, (float)beta, dx, t, oo));
     }
   }
   return 0;
 }
 
+int oracle_eltwise_bwd(int alg, double coef, int t, int nd, const int64_t *dims, const int64_t *xst,
+                       const void *x, const int64_t *dyst, const void *dy, const int64_t *dxst,
+                       void *dx, double alpha, double beta) {
+  return oracle_eltwise_bwd_ex(alg, coef, 0.0, t, nd, dims, xst, x, dyst, dy, dxst, dx, alpha, beta);
+}
+
 /* The same definitions evaluated in double on float inputs (error attribution). */
 int oracle_eltwise_fwd_truth(int alg, double coef, double shift, int64_t n, const float *x, double *out) {
 #pragma omp parallel for schedule(static)
-  for (int64_t i = 0; i < n; i++) out[i] = act_fwd_d(alg, (double)x[i], coef, shift, 1);
+  for (int64_t i = 0; i < n; i++) out[i] = act_fwd_d(fwd_alg_of(alg), (double)x[i], coef, shift, 1);
   return 0;
 }
 int oracle_eltwise_bwd_truth(int alg, double coef, int64_t n, const float *x, const float *dy, double *out) {
 #pragma omp parallel for schedule(static)
-  for (int64_t i = 0; i < n; i++) out[i] = act_bwd_d(alg, (double)x[i], (double)dy[i], coef);
+  for (int64_t i = 0; i < n; i++) out[i] = act_bwd_d(alg, (double)x[i], (double)dy[i], coef, 0.0);
+  return 0;
+}
+int oracle_eltwise_bwd_truth_ex(int alg, double coef, double shift, int64_t n, const float *x, const float *dy, double *out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) out[i] = act_bwd_d(alg, (double)x[i], (double)dy[i], coef, shift);
   return 0;
 }
 

@@ -247,6 +247,19 @@ def test_constants_match_the_header(table, prefix, names):
         assert clj[kw] == enums[prefix + c_suffix], (table, kw)
 
 
+@pytest.mark.parametrize("table,prefix", [("dd-activation-mode", "DD_ACTIVATION_"), ("dd-reduce-tensor-op", "DD_REDUCE_TENSOR_"),
+                                          ("dd-op-tensor-op", "DD_OP_TENSOR_")])
+def test_every_header_enumerator_has_its_keyword(table, prefix):
+    """Every enumerator of the header appears in the Clojure table under the keyword its C name spells
+    (DD_ACTIVATION_GELU_TANH -> :gelu-tanh), apart from the ones the tables name after the reference."""
+    aliases = {"DD_ACTIVATION_SIGMOID": ":sigmoid", "DD_DATA_INT8": ":byte"}
+    clj = _clj_map(table)
+    for name, code in header_enums().items():
+        if name.startswith(prefix):
+            kw = aliases.get(name, ":" + name[len(prefix):].lower().replace("_", "-"))
+            assert clj.get(kw) == code, (name, kw)
+
+
 def test_status_codes_match_the_header():
     enums = {k: v for k, v in header_enums().items() if k.startswith("DD_STATUS_")}
     clj = _clj_map("dd-status-codes")
