@@ -658,6 +658,18 @@ def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
         measure("%s forward, bf16 tensors" % mode, "[256,256,28,28] bf16", n * 4, n,
                 lambda adm=adm: core.activation_forward(h, adm, 1.0, db, xb, 0.0, db, yb16))
     del xb, yb16
+    # activation kinds of the DNNL backend's table (run-time-switched families): forward and backward
+    for mode, coef, shift in (("gelu-tanh", 0.0, 0.0), ("swish", 1.0, 0.0), ("hardswish", 1.0 / 6.0, 0.5)):
+        adm = core.activation_descriptor(mode, True, coef, shift)
+        measure("%s forward" % mode, "[256,256,28,28] f32", n * 8, n,
+                lambda adm=adm: core.activation_forward(h, adm, 1.0, d4, x, 0.0, d4, y))
+        measure("%s backward" % mode, "[256,256,28,28] f32", n * 12, n,
+                lambda adm=adm: core.activation_backward(h, adm, 1.0, d4, None, d4, z, d4, x, 0.0, d4, y))
+    # oneDNN's norm-lp-sum with p = 3 over (C,H,W): |x|^p element by element
+    rl = core.reduce_tensor_descriptor("norm-lp-sum", "float", True, 3.0, 1e-6)
+    yl = torch.empty(256, dtype=torch.float32, device=dev)
+    measure("reduce norm-lp-sum p=3 over (C,H,W)", "[256,256,28,28] f32", n * 4, n,
+            lambda: core.reduce_tensor(h, rl, 1.0, d4, x, 0.0, core.tensor_descriptor([256, 1, 1, 1], "float", "nchw"), yl))
     # N and C swapped (nchw -> cnhw): rows of 784 elements
     measure("reorder nchw -> cnhw", "[256,256,28,28] f32", n * 8, n,
             lambda: core.transform_tensor(h, 1.0, d4, x, 0.0,

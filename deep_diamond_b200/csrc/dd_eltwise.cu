@@ -217,6 +217,8 @@ __device__ __forceinline__ C dd_act_fwd(C x, C coef, C shift, bool nanProp, int 
   typedef dd_math<C> M;
   if (MODE == DD_ACT_FAM_CHEAP) return dd_ext_cheap_fwd<C>(kind, x, coef, shift);
   if (MODE == DD_ACT_FAM_TRANS) return dd_ext_trans_fwd<C>(kind, x, coef, shift);
+  // swish and gelu-tanh have kernels of their own (packed fp32 forms below); this is their scalar form
+  if (MODE == DD_ACTIVATION_SWISH || MODE == DD_ACTIVATION_GELU_TANH) return dd_ext_trans_fwd<C>(MODE, x, coef, shift);
   if constexpr (LIGHT != 0 && sizeof(C) == 4) {
     if (MODE == DD_ACTIVATION_SIGMOID) return dd_sigmoid_light(x);
     if (MODE == DD_ACTIVATION_TANH) return LIGHT == 2 ? dd_tanh_sfu(x) : dd_tanh_light(x);
@@ -250,6 +252,7 @@ __device__ __forceinline__ C dd_act_bwd(C x, C dy, C coef, C shift = (C)0, int k
   typedef dd_math<C> M;
   if (MODE == DD_ACT_FAM_CHEAP) return dd_ext_cheap_bwd<C>(kind, x, dy, coef, shift);
   if (MODE == DD_ACT_FAM_TRANS) return dd_ext_trans_bwd<C>(kind, x, dy, coef, shift);
+  if (MODE == DD_ACTIVATION_SWISH || MODE == DD_ACTIVATION_GELU_TANH) return dd_ext_trans_bwd<C>(MODE, x, dy, coef, shift);
   if constexpr (LIGHT != 0 && sizeof(C) == 4) {
     if (MODE == DD_ACTIVATION_SIGMOID) return dd_mul_rn(dy, dd_dsigmoid_light(x));
     if (MODE == DD_ACTIVATION_TANH) return dd_mul_rn(dy, dd_dtanh_light(x));
@@ -278,12 +281,25 @@ template <int MODE> struct dd_act_packed { static constexpr bool value = false; 
 template <> struct dd_act_packed<DD_ACTIVATION_SIGMOID> { static constexpr bool value = true; };
 template <> struct dd_act_packed<DD_ACTIVATION_TANH> { static constexpr bool value = true; };
 template <> struct dd_act_packed<DD_ACTIVATION_ELU> { static constexpr bool value = true; };
+template <> struct dd_act_packed<DD_ACTIVATION_SWISH> { static constexpr bool value = true; };
+template <> struct dd_act_packed<DD_ACTIVATION_GELU_TANH> { static constexpr bool value = true; };
+
+// g and g' of gelu-tanh on two lanes: g = sqrt(2/pi) x (1 + 0.044715 x^2)
+__device__ __forceinline__ float2 dd_gelu_g2(float2 x, float2 x2) {
+  typedef dd_lane<float2> L;
+  return L::mul(L::mul(L::bc(0.7978845608028654f), x), L::fma(L::bc(0.044715f), x2, L::bc(1.0f)));
+}
 
 template <int MODE>
 __device__ __forceinline__ float2 dd_act_fwd2(float2 x, float coef) {
   typedef dd_lane<float2> L;
   if (MODE == DD_ACTIVATION_SIGMOID) return dd_sigmoid<float2>(x);
   if (MODE == DD_ACTIVATION_TANH) return dd_tanh<float2>(x);
+  if (MODE == DD_ACTIVATION_SWISH) return L::mul(x, dd_sigmoid<float2>(L::mul(L::bc(coef), x)));
+  if (MODE == DD_ACTIVATION_GELU_TANH) {
+    const float2 g = dd_gelu_g2(x, L::mul(x, x));
+    return L::mul(x, dd_sigmoid<float2>(L::add(g, g)));
+  }
   return L::sel_pos(x, x, L::mul(L::bc(coef), dd_expm1_neg<float2>(x)));  // ELU
 }
 
@@ -294,6 +310,19 @@ __device__ __forceinline__ float2 dd_act_bwd2(float2 x, float2 dy, float coef) {
     return L::mul(dy, dd_e_over_one_plus_e_sq<float2, 0>(L::neg_abs_clamped<1>(x, -104.0f)));
   if (MODE == DD_ACTIVATION_TANH)
     return L::mul(dy, dd_e_over_one_plus_e_sq<float2, 2>(L::neg_abs_clamped<2>(x, -104.0f)));
+  if (MODE == DD_ACTIVATION_SWISH) {  // s + t s (1 - s), t = a x
+    const float2 t = L::mul(L::bc(coef), x);
+    const float2 ds = dd_e_over_one_plus_e_sq<float2, 0>(L::neg_abs_clamped<1>(t, -104.0f));
+    return L::mul(dy, L::fma(t, ds, dd_sigmoid<float2>(t)));
+  }
+  if (MODE == DD_ACTIVATION_GELU_TANH) {  // s + 2 x g' s (1 - s), s = sigma(2g)
+    const float2 x2 = L::mul(x, x);
+    const float2 g = dd_gelu_g2(x, x2);
+    const float2 gp = L::mul(L::bc(0.7978845608028654f), L::fma(L::bc(0.134145f), x2, L::bc(1.0f)));
+    const float2 g2 = L::add(g, g);
+    const float2 ds = dd_e_over_one_plus_e_sq<float2, 0>(L::neg_abs_clamped<1>(g2, -104.0f));
+    return L::mul(dy, L::fma(L::mul(L::add(x, x), gp), ds, dd_sigmoid<float2>(g2)));
+  }
   return L::sel_pos(x, dy, L::mul(dy, L::mul(L::bc(coef), dd_exp_neg_rounded<float2>(x))));  // ELU
 }
 
@@ -315,9 +344,9 @@ struct ddEltFlatParams {
 };
 
 // PLAIN: alpha == 1 and beta == 0 (what every layer passes): no blend arithmetic at all.
-// (the two run-time-switched families get 64 registers: the math library's slow paths spill at 32)
+// (the run-time-switched transcendental family gets 64 registers: the math library's slow paths spill at 32)
 template <typename T, typename C, int MODE, bool BWD, bool PLAIN>
-__global__ void __launch_bounds__(256, MODE >= DD_ACT_FAM_CHEAP ? 4 : 8) dd_elt_flat_kernel(ddEltFlatParams p) {
+__global__ void __launch_bounds__(256, MODE == DD_ACT_FAM_TRANS ? 4 : 8) dd_elt_flat_kernel(ddEltFlatParams p) {
   dd_pdl_prologue();
   constexpr int V = 16 / sizeof(T);
   const T *x = (const T *)p.x;
@@ -582,8 +611,10 @@ static ddStatus_t dispatch_mode(ddHandle_t h, int mode, const ddCanon &c, const 
     case DD_ACTIVATION_CLIP_V2: case DD_ACTIVATION_TANH_DST_BWD: case DD_ACTIVATION_ELU_DST_BWD:
     case DD_ACTIVATION_SQRT_DST_BWD: case DD_ACTIVATION_LOGISTIC_DST_BWD: case DD_ACTIVATION_EXP_DST_BWD:
       return launch_elt<T, C, DD_ACT_FAM_CHEAP, BWD>(h, c, x, dy, out, alpha, beta, act);
-    case DD_ACTIVATION_EXP: case DD_ACTIVATION_LOG: case DD_ACTIVATION_SOFT_RELU: case DD_ACTIVATION_SWISH:
-    case DD_ACTIVATION_GELU_TANH: case DD_ACTIVATION_GELU_ERF: case DD_ACTIVATION_POW: case DD_ACTIVATION_MISH:
+    case DD_ACTIVATION_SWISH: return launch_elt<T, C, DD_ACTIVATION_SWISH, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_GELU_TANH: return launch_elt<T, C, DD_ACTIVATION_GELU_TANH, BWD>(h, c, x, dy, out, alpha, beta, act);
+    case DD_ACTIVATION_EXP: case DD_ACTIVATION_LOG: case DD_ACTIVATION_SOFT_RELU:
+    case DD_ACTIVATION_GELU_ERF: case DD_ACTIVATION_POW: case DD_ACTIVATION_MISH:
       return launch_elt<T, C, DD_ACT_FAM_TRANS, BWD>(h, c, x, dy, out, alpha, beta, act);
   }
   DD_FAIL(h, DD_STATUS_BAD_PARAM, "activation: unknown mode %d", mode);

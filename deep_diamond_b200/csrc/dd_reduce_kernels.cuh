@@ -58,7 +58,12 @@ struct dd_red {
   }
   // acc (+)= pre(v); pw: the exponent of the general Lp sum, unused by every other kind
   static __device__ __forceinline__ C accum(C acc, C v, bool nanProp, C pw) {
-    if (OPC == DD_OPC_SUMPOW) return dd_add_rn(acc, dd_pow(dd_abs(v), pw));
+    if (OPC == DD_OPC_SUMPOW) {  // p = 3 and p = 4 by multiplication, any other p through pow
+      const C a = dd_abs(v), a2 = dd_mul_rn(a, a);
+      if (pw == (C)3) return dd_fma(a2, a, acc);
+      if (pw == (C)4) return dd_fma(a2, a2, acc);
+      return dd_add_rn(acc, dd_pow(a, pw));
+    }
     if (OPC == DD_OPC_SUM) return dd_add_rn(acc, v);
     if (OPC == DD_OPC_SUMABS) return dd_add_rn(acc, dd_abs(v));
     if (OPC == DD_OPC_SUMSQ) return dd_fma(v, v, acc);

@@ -700,7 +700,13 @@ typedef struct {
 } red_ctx;
 
 /* |v|^p of one element, in the arithmetic of the accumulator */
-static float lp_term_f(float v, double p) { return p == 1.0 ? fabsf(v) : (p == 2.0 ? v * v : powf(fabsf(v), (float)p)); }
+static float lp_term_f(float v, double p) {
+  if (p == 1.0) return fabsf(v);
+  if (p == 2.0) return v * v;
+  if (p == 3.0) return v * v * fabsf(v);
+  if (p == 4.0) return (v * v) * (v * v);
+  return powf(fabsf(v), (float)p);
+}
 static double lp_term_d(double v, double p) { return p == 1.0 ? fabs(v) : (p == 2.0 ? v * v : pow(fabs(v), p)); }
 
 static double red_value(const red_ctx *c, int64_t r) {
