@@ -324,8 +324,10 @@ DD_API ddStatus_t ddActivationForward(ddHandle_t handle, ddActivationDescriptor_
 /* dx = alpha*act'(x)*dy + beta*dx.  Argument order is cudnnActivationBackward's
  * (cudnn/impl.clj:228-235).  The derivative is taken from x (the forward SOURCE), which is what
  * the reference's DNNL backend does (eltwise-bwd-args SRC, DIFF_DST, DIFF_SRC,
- * dnnl/core.clj:382-388); y is accepted for signature compatibility, may be NULL and is never
- * read.  dx may alias dy or x. */
+ * dnnl/core.clj:382-388); y is accepted for signature compatibility, may be NULL and is not
+ * read -- except by the *_DST_BWD kinds, which take the derivative from y (the forward result), as
+ * oneDNN's *_use_dst_for_bwd algorithms do, and leave xDesc and x unread (they may be NULL).  dx may
+ * alias dy or x.  DD_ACTIVATION_ROUND has no backward (NOT_SUPPORTED). */
 DD_API ddStatus_t ddActivationBackward(ddHandle_t handle, ddActivationDescriptor_t act, const void *alpha,
                                 ddTensorDescriptor_t yDesc, const void *y,
                                 ddTensorDescriptor_t dyDesc, const void *dy,

@@ -5,7 +5,8 @@ Run where PyTorch with oneDNN is installed:  python tests/golden/make_onednn_fix
 The reference (Deep Diamond's DNNL backend) calls the same oneDNN primitives through JavaCPP
 (eltwise forward: dnnl/impl.clj:324-331; reorder: :372-376; sum: :345-359; binary: :363-368); the
 oneDNN bundled with PyTorch is a different release from the one the reference pins (3.13), which
-the fixture records.  What PyTorch does not expose through mkldnn tensors (elu, eltwise backward,
+the fixture records.  What PyTorch does not expose through mkldnn tensors (elu, the other kinds of the
+reference's eltwise table apart from gelu-erf, eltwise backward,
 broadcast binary, reductions, plain nhwc reorders, int8) has no fixture here.
 """
 import os
@@ -26,6 +27,7 @@ def main():
     out["relu"] = torch.relu(tx).to_dense().numpy().reshape(-1)
     out["logistic"] = torch.sigmoid(tx).to_dense().numpy().reshape(-1)
     out["tanh"] = torch.tanh(tx).to_dense().numpy().reshape(-1)
+    out["gelu_erf"] = torch.nn.functional.gelu(tx).to_dense().numpy().reshape(-1)  # eltwise_gelu_erf
 
     rng = np.random.default_rng(6)
     c = rng.standard_normal(N).astype(np.float32)
