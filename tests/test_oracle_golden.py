@@ -328,6 +328,60 @@ def test_reduction_norm_lp_kinds(oracle):
     assert np.array_equal(y, (2.0 * (np.abs(xs).sum(axis=3, keepdims=True) + 0.5) + 3.0).astype(np.float32))
 
 
+def test_eltwise_kinds_of_the_dnnl_table(oracle):
+    """The kinds of dnnl/constants.clj:277-308 beyond the cuDNN set.  The reference holds no known
+    answer for them, so the restatement is pinned two ways: forward values against numpy / math on the
+    definitions oneDNN documents, and every derivative against a central difference of its own forward
+    (both in double)."""
+    import math
+    x = np.array([-3.0, -1.5, -0.25, 0.0, 0.25, 1.5, 3.0], np.float32)
+    xd = x.astype(np.float64)
+    sig = lambda t: 1.0 / (1.0 + np.exp(-t))
+    erf = np.vectorize(math.erf)
+    expect = {
+        ("square", 0, 0): xd * xd, ("exp", 0, 0): np.exp(xd), ("swish", 1.25, 0): xd * sig(1.25 * xd),
+        ("soft-relu", 1.5, 0): np.log1p(np.exp(1.5 * xd)) / 1.5,
+        ("gelu-tanh", 0, 0): 0.5 * xd * (1 + np.tanh(math.sqrt(2 / math.pi) * (xd + 0.044715 * xd ** 3))),
+        ("gelu-erf", 0, 0): 0.5 * xd * (1 + erf(xd / math.sqrt(2))),
+        ("hardswish", 1 / 6, 0.5): xd * np.clip(xd / 6 + 0.5, 0, 1), ("clip", -0.75, 1.5): np.clip(xd, -0.75, 1.5),
+        ("clip-v2", -0.75, 1.5): np.clip(xd, -0.75, 1.5), ("mish", 0, 0): xd * np.tanh(np.log1p(np.exp(xd))),
+        ("round", 0, 0): np.round(xd),
+    }
+    for (kind, a, b), ref in expect.items():
+        got = oracle.eltwise_fwd_truth(kind, x, coef=a, shift=b)
+        assert np.allclose(got, ref, rtol=1e-12, atol=1e-15), kind
+        got32 = oracle.eltwise_fwd(kind, x, np.zeros_like(x), coef=a, shift=b)
+        assert np.allclose(got32, ref, rtol=3e-7, atol=1e-9), kind
+    pos = np.abs(x) + np.float32(0.5)
+    for (kind, a, b), ref in {("sqrt", 0, 0): np.sqrt(pos.astype(np.float64)), ("log", 0, 0): np.log(pos.astype(np.float64)),
+                              ("pow", 0.5, 2.5): 0.5 * pos.astype(np.float64) ** 2.5}.items():
+        assert np.allclose(oracle.eltwise_fwd_truth(kind, pos, coef=a, shift=b), ref, rtol=1e-12), kind
+    assert oracle.eltwise_fwd("round", np.array([0.5, 1.5, 2.5, -0.5], np.float32), np.zeros(4, np.float32)).tolist() == [0, 2, 2, -0]
+    # derivatives against central differences (points kept away from the kinks of clip and hardswish)
+    pts = np.linspace(-4, 4, 161).astype(np.float32) + np.float32(0.0131)
+    h = 2.0 ** -10
+    for kind, a, b, dom in (("square", 0, 0, "any"), ("exp", 0, 0, "any"), ("swish", 1.25, 0, "any"), ("soft-relu", 1.5, 0, "any"),
+                            ("gelu-tanh", 0, 0, "any"), ("gelu-erf", 0, 0, "any"), ("hardswish", 1 / 6, 0.5, "any"),
+                            ("clip", -0.75, 1.5, "any"), ("clip-v2", -0.75, 1.5, "any"), ("mish", 0, 0, "any"),
+                            ("sqrt", 0, 0, "pos"), ("log", 0, 0, "pos"), ("pow", 0.5, 2.5, "pos")):
+        p = (np.abs(pts) + np.float32(0.25)) if dom == "pos" else pts
+        lo, hi = (p - np.float32(h)).astype(np.float32), (p + np.float32(h)).astype(np.float32)
+        num = (oracle.eltwise_fwd_truth(kind, hi, a, b) - oracle.eltwise_fwd_truth(kind, lo, a, b)) / (hi.astype(np.float64) - lo)
+        der = oracle.eltwise_bwd_truth(kind, p, np.ones_like(p), a, b)
+        assert np.allclose(num, der, rtol=2e-5, atol=2e-5), (kind, np.abs(num - der).max())
+    # the *-dst-bwd kinds: the derivative written in terms of the forward result equals the one from the source
+    g = np.ones_like(pts)
+    for kind, base, a in (("tanh-dst-bwd", "tanh", 0), ("logistic-dst-bwd", "logistic", 0), ("elu-dst-bwd", "elu", 1.5),
+                          ("exp-dst-bwd", "exp", 0), ("relu-dst-bwd", "relu", 0.25)):
+        y = oracle.eltwise_fwd_truth(base, pts, coef=a)
+        from_dst = oracle.eltwise_bwd_truth(kind, y.astype(np.float32), g, a)
+        from_src = oracle.eltwise_bwd_truth(base, pts, g, a)
+        assert np.allclose(from_dst, from_src, rtol=1e-5, atol=1e-6), kind
+    ps = np.abs(pts) + np.float32(0.25)
+    y = np.sqrt(ps.astype(np.float64))
+    assert np.allclose(oracle.eltwise_bwd_truth("sqrt-dst-bwd", y.astype(np.float32), g), 0.5 / y, rtol=1e-6)
+
+
 # ----------------------------------------------------------------------------- real oneDNN -----
 
 def fixtures():
