@@ -218,6 +218,20 @@ __global__ void __launch_bounds__((dd_tile_geom<S, D>::NT), (RAW ? dd_tile_geom<
 #pragma unroll
           for (int k = 0; k < 4; k++) outv[4 * w + k] = make_uint4(c[k][0], c[k][1], c[k][2], c[k][3]);
         }
+      } else if constexpr (std::is_same<S, float>::value && std::is_same<C, float>::value &&
+                           (std::is_same<D, __nv_bfloat16>::value || std::is_same<D, __half>::value)) {
+        // two rows at a time: one packed conversion (cvt.rn.{bf16x2,f16x2}.f32) makes the adjacent pair
+        // reg[i][j], reg[i][j+1]; each half is the same rounding as the single conversion
+#pragma unroll
+        for (int j = 0; j < VD; j += 2) {
+          const float *s0 = (const float *)&in[j], *s1 = (const float *)&in[j + 1];
+#pragma unroll
+          for (int i = 0; i < VS; i++) {
+            const float lo = dd_scale(alpha, s0[i]), hi = dd_scale(alpha, s1[i]);
+            if constexpr (std::is_same<D, __nv_bfloat16>::value) *(__nv_bfloat162 *)&reg[i][j] = __floats2bfloat162_rn(lo, hi);
+            else *(__half2 *)&reg[i][j] = __floats2half2_rn(lo, hi);
+          }
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < VD; j++) {
