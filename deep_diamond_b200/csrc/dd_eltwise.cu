@@ -378,13 +378,15 @@ __global__ void __launch_bounds__(256, MODE == DD_ACT_FAM_TRANS ? 4 : 8) dd_elt_
           rv[k + 1] = PLAIN ? dd_store<T, float>(v.y) : dd_store<T, float>(dd_blend(alpha, v.y, beta, dd_load<float, T>(ov[k + 1]), useOld));
         }
       } else {
+        C vals[V];
 #pragma unroll
         for (int k = 0; k < V; k++) {
           C xc = dd_load<C, T>(xv[k]);
           C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef, shift, p.act.kind)
                     : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp, p.act.kind);
-          rv[k] = PLAIN ? dd_store<T, C>(v) : dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
+          vals[k] = PLAIN ? v : dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld);
         }
+        dd_store_n<T, C, V>(rv, vals);
       }
       *(uint4 *)(out + i * V) = res;
     }
@@ -496,13 +498,15 @@ __global__ void __launch_bounds__(256) dd_elt_rows_kernel(ddEltStridedParams p) 
     uint4 res;
     const T *xv = (const T *)&xin, *dv = (const T *)&din, *ov = (const T *)&oin;
     T *rv = (T *)&res;
+    C vals[V];
 #pragma unroll
     for (int k = 0; k < V; k++) {
       C xc = dd_load<C, T>(xv[k]);
       C v = BWD ? dd_act_bwd<C, MODE, dd_light<T>::value>(xc, dd_load<C, T>(dv[k]), coef, shift, p.act.kind)
                 : dd_act_fwd<C, MODE, dd_light<T>::value>(xc, coef, shift, nanProp, p.act.kind);
-      rv[k] = dd_store<T, C>(dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld));
+      vals[k] = dd_blend(alpha, v, beta, dd_load<C, T>(ov[k]), useOld);
     }
+    dd_store_n<T, C, V>(rv, vals);
     *(uint4 *)(out + off[2]) = res;
   }
 }

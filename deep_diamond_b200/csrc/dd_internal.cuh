@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <type_traits>
 
 #include <nvtx3/nvToolsExt.h>
 
@@ -360,6 +361,23 @@ template <> struct dd_store_t<int64_t, double> {
   }
 };
 template <typename T, typename C> __device__ __forceinline__ T dd_store(C v) { return dd_store_t<T, C>::f(v); }
+
+// N consecutive results into their storage type (dst 4-byte aligned).  float -> bf16 / f16 goes two
+// at a time through the packed conversion (cvt.rn.{bf16x2,f16x2}.f32: each half rounds exactly as the
+// single conversion does), half the conversion instructions and no packing of 16-bit halves.
+template <typename T, typename C, int N>
+__device__ __forceinline__ void dd_store_n(T *dst, const C *v) {
+  if constexpr (std::is_same<C, float>::value && N % 2 == 0 && std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+    for (int k = 0; k < N; k += 2) *(__nv_bfloat162 *)&dst[k] = __floats2bfloat162_rn(v[k], v[k + 1]);
+  } else if constexpr (std::is_same<C, float>::value && N % 2 == 0 && std::is_same<T, __half>::value) {
+#pragma unroll
+    for (int k = 0; k < N; k += 2) *(__half2 *)&dst[k] = __floats2half2_rn(v[k], v[k + 1]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < N; k++) dst[k] = dd_store<T, C>(v[k]);
+  }
+}
 
 // alpha*v + beta*old, each product and the sum rounded separately (no FMA contraction), a factor
 // of exactly 1 skipped and beta == 0 not reading `old`.  The CPU oracle follows the same rule.

@@ -110,19 +110,21 @@ __global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
       uint4 res;
       const T *av = (const T *)&ain, *bv = (const T *)&bin, *ov = (const T *)&oin;
       T *rv = (T *)&res;
+      C rs[V];
 #pragma unroll
       for (int k = 0; k < V; k++) {
         C a = dd_times(a1, dd_load<C, T>(av[k]));  // readA == 0: a1 == 0 and av == 0, the term is +0
         C b = BMODE == 0 ? dd_times(a2, dd_load<C, T>(bv[k])) : bs;
         C r = dd_binop<C>(op, a, b);
         if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
-        rv[k] = dd_store<T, C>(r);
+        rs[k] = r;
         if (BMODE == 2 && ++pos2 == p.inner) {  // the next element starts the next channel's run
           pos2 = 0;
           if (++ch2 == p.channels) ch2 = 0;
           bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch2 * p.sB)));
         }
       }
+      dd_store_n<T, C, V>(rv, rs);
       *(uint4 *)(Cp + e0) = res;
     }
     done = nv * V;
@@ -189,14 +191,16 @@ __global__ void __launch_bounds__(256) dd_op_rows_kernel(ddOpStridedParams p, in
     uint4 res;
     const T *av = (const T *)&ain, *bv = (const T *)&bin, *ov = (const T *)&oin;
     T *rv = (T *)&res;
+    C rs[V];
 #pragma unroll
     for (int k = 0; k < V; k++) {
       C a = dd_times(a1, dd_load<C, T>(av[k]));
       C b = bInner ? dd_times(a2, dd_load<C, T>(bv[k])) : bs;
       C r = dd_binop<C>(p.op, a, b);
       if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
-      rv[k] = dd_store<T, C>(r);
+      rs[k] = r;
     }
+    dd_store_n<T, C, V>(rv, rs);
     *(uint4 *)(Cp + off[2]) = res;
   }
 }
@@ -490,7 +494,7 @@ __global__ void __launch_bounds__(256) dd_sum_kernel(ddSumParams p) {
       uint4 res;
       T *rv = (T *)&res;
 #pragma unroll
-      for (int k = 0; k < V; k++) rv[k] = dd_store<T, C>(acc[k]);
+      dd_store_n<T, C, V>(rv, acc);
       *(uint4 *)(dst + i * V) = res;
     }
     done = nv * V;

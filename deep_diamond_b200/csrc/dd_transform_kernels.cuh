@@ -35,6 +35,22 @@ struct dd_cvt<S, S, C, true> {
   static __device__ __forceinline__ S blend(S v, C, C, S) { return v; }
 };
 
+// The non-blending conversion of V consecutive elements: float -> bf16 / f16 in packed pairs
+// (dd_store_n), anything else element by element.
+template <typename S, typename D, typename C, bool RAW, int V>
+__device__ __forceinline__ void dd_cvt_n(const S *sv, D *dv, C alpha) {
+  if constexpr (!RAW && std::is_same<S, float>::value && std::is_same<C, float>::value && sizeof(D) == 2 &&
+                (std::is_same<D, __nv_bfloat16>::value || std::is_same<D, __half>::value)) {
+    float t[V];
+#pragma unroll
+    for (int k = 0; k < V; k++) t[k] = dd_scale(alpha, sv[k]);
+    dd_store_n<D, float, V>(dv, t);
+  } else {
+#pragma unroll
+    for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::f(sv[k], alpha);
+  }
+}
+
 // ------------------------------------------------------------------ flat ---------------------
 
 // BYTES of payload moved with the widest legal accesses (16-byte units above 16 bytes).
@@ -99,8 +115,7 @@ __global__ void __launch_bounds__(256) dd_flat_kernel(ddFlatParams p) {
 #pragma unroll
         for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::blend(sv[k], alpha, beta, ov[k]);
       } else {
-#pragma unroll
-        for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::f(sv[k], alpha);
+        dd_cvt_n<S, D, C, RAW, V>(sv, dv, alpha);
       }
       dd_vstore<V * sizeof(D)>(y + i * V, out);
     }
@@ -489,8 +504,7 @@ __global__ void __launch_bounds__(256) dd_rows_kernel(ddStridedXformParams p) {
 #pragma unroll
       for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::blend(sv[k], alpha, beta, ov[k]);
     } else {
-#pragma unroll
-      for (int k = 0; k < V; k++) dv[k] = dd_cvt<S, D, C, RAW>::f(sv[k], alpha);
+      dd_cvt_n<S, D, C, RAW, V>(sv, dv, alpha);
     }
     dd_vstore<V * sizeof(D)>(y + off[1], out);
   }
