@@ -60,6 +60,17 @@ def main():
                     ok = within(got, want, full, alpha, (0, 2, 3))
                 if not ok:
                     failures.append((path, op, alpha, beta, float(np.abs(got - want).max())))
+        # oneDNN's norm kinds with p and epsilon: the ranks exchange sums of |x|^p, epsilon and the root follow
+        for kind, pw, eps in (("norm-lp-sum", 3.0, 0.5), ("norm-lp-power-p-max", 2.0, 1e6), ("norm-lp-max", 1.0, 0.0)):
+            want = np.zeros([1, 64, 1, 1], np.float32)
+            oracle.reduce_lp(kind, pw, eps, full, want)
+            y = torch.zeros(64, device=fact.device)
+            sh.reduce_tensor(core.reduce_tensor_descriptor(kind, "float", True, pw, eps), 1.0, xd, x, 0.0,
+                             core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y)
+            fact.synchronize()
+            got = y.cpu().numpy().reshape(want.shape)
+            if not (np.abs(got - want) <= 1e-5 * np.abs(want)).all():
+                failures.append((path, kind, pw, eps, float(np.abs(got - want).max())))
         # all ranks must hold identical bits for the replicated results
         y = torch.zeros(64, device=fact.device)
         sh.reduce_tensor(core.reduce_tensor_descriptor("add", "float"), 1.0, xd, x, 0.0,
