@@ -41,6 +41,16 @@ __device__ __forceinline__ float dd_fmax(float a, float b) { return fmaxf(a, b);
 __device__ __forceinline__ double dd_fmax(double a, double b) { return fmax(a, b); }
 __device__ __forceinline__ float dd_fmin(float a, float b) { return fminf(a, b); }
 __device__ __forceinline__ double dd_fmin(double a, double b) { return fmin(a, b); }
+__device__ __forceinline__ float dd_fmax_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float dd_fmin_nan(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
 __device__ __forceinline__ float dd_sqrt(float v) { return __fsqrt_rn(v); }
 __device__ __forceinline__ double dd_sqrt(double v) { return __dsqrt_rn(v); }
 __device__ __forceinline__ float dd_div(float a, float b) { return __fdiv_rn(a, b); }
@@ -79,13 +89,115 @@ struct dd_red {
     // propagate: a NaN on either side wins (b beats a only when it compares so or is NaN; a NaN in a
     // survives because every comparison with it is false).  Otherwise IEEE maxNum/minNum: the number wins.
     if (nanProp) {
-      if (OPC == DD_OPC_MIN) return (b < a || b != b) ? b : a;
-      return (b > a || b != b) ? b : a;
+      if constexpr (sizeof(C) == 4) {  // one instruction: the NaN-propagating forms of min / max
+        if (OPC == DD_OPC_MIN) return dd_fmin_nan(a, b);
+        return dd_fmax_nan(a, b);
+      } else {
+        if (OPC == DD_OPC_MIN) return (b < a || b != b) ? b : a;
+        return (b > a || b != b) ? b : a;
+      }
     }
     if (OPC == DD_OPC_MIN) return dd_fmin(a, b);
     return dd_fmax(a, b);
   }
 };
+
+template <int OPC> struct dd_is_minmax { static constexpr bool value = OPC == DD_OPC_MIN || OPC == DD_OPC_MAX || OPC == DD_OPC_AMAX; };
+
+// acc[k] (+)= wv[k] for the V elements of one 16-byte load.  For min / max / amax the NaN mode, which
+// is the same for the whole grid, is branched on once per vector so that each element is ONE
+// instruction (max / max.NaN) instead of both forms and a select.
+template <typename T, typename C, int OPC, int V>
+__device__ __forceinline__ void dd_accum_vec(C (&acc)[V], const T *wv, bool nanProp, C pw) {
+  if constexpr (dd_is_minmax<OPC>::value) {
+    if (nanProp) {
+#pragma unroll
+      for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), true, pw);
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), false, pw);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp, pw);
+  }
+}
+
+// min / max / amax of 16-bit element types in their own packed form (max.{NaN.}bf16x2 / f16x2: two
+// elements per instruction, no conversion; the result is one of the inputs, so nothing is rounded).
+template <typename T> struct dd_pack2;
+template <> struct dd_pack2<__nv_bfloat16> { typedef __nv_bfloat162 P; static constexpr unsigned NEG_INF2 = 0xFF80FF80u, POS_INF2 = 0x7F807F80u; };
+template <> struct dd_pack2<__half> { typedef __half2 P; static constexpr unsigned NEG_INF2 = 0xFC00FC00u, POS_INF2 = 0x7C007C00u; };
+
+template <typename T, int OPC>
+__device__ __forceinline__ unsigned dd_minmax2_identity() {
+  return OPC == DD_OPC_MIN ? dd_pack2<T>::POS_INF2 : (OPC == DD_OPC_MAX ? dd_pack2<T>::NEG_INF2 : 0u);
+}
+
+template <typename T, int OPC, bool NANPROP>
+__device__ __forceinline__ unsigned dd_minmax2(unsigned a, unsigned b) {
+  typedef typename dd_pack2<T>::P P;
+  P pa = *(const P *)&a, pb = *(const P *)&b, r;
+  if (OPC == DD_OPC_AMAX) pb = __habs2(pb);
+  if (OPC == DD_OPC_MIN) r = NANPROP ? __hmin2_nan(pa, pb) : __hmin2(pa, pb);
+  else r = NANPROP ? __hmax2_nan(pa, pb) : __hmax2(pa, pb);
+  return *(const unsigned *)&r;
+}
+
+// pacc = min/max(pacc, v) over the four packed pairs of a 16-byte vector
+template <typename T, int OPC>
+__device__ __forceinline__ void dd_minmax_packed(uint4 &pacc, const uint4 &v, bool nanProp) {
+  if (nanProp) {
+    pacc.x = dd_minmax2<T, OPC, true>(pacc.x, v.x); pacc.y = dd_minmax2<T, OPC, true>(pacc.y, v.y);
+    pacc.z = dd_minmax2<T, OPC, true>(pacc.z, v.z); pacc.w = dd_minmax2<T, OPC, true>(pacc.w, v.w);
+  } else {
+    pacc.x = dd_minmax2<T, OPC, false>(pacc.x, v.x); pacc.y = dd_minmax2<T, OPC, false>(pacc.y, v.y);
+    pacc.z = dd_minmax2<T, OPC, false>(pacc.z, v.z); pacc.w = dd_minmax2<T, OPC, false>(pacc.w, v.w);
+  }
+}
+
+// acc (+)= every element of one 16-byte load (the row kernels' scalar accumulator)
+template <typename T, typename C, int OPC, int V>
+__device__ __forceinline__ C dd_accum_run(C acc, const T *wv, bool nanProp, C pw) {
+  if constexpr (dd_is_minmax<OPC>::value && sizeof(T) == 2 && V == 8) {
+    // fold the vector's four pairs in packed form, then the two survivors in float
+    const uint4 v = *(const uint4 *)wv;
+    unsigned m;
+    if (nanProp) {
+      const unsigned lo = OPC == DD_OPC_AMAX ? dd_minmax2<T, OPC, true>(0u, v.x) : v.x;  // |.| of the first operand too
+      m = dd_minmax2<T, OPC, true>(dd_minmax2<T, OPC, true>(lo, v.y), v.z);
+      m = dd_minmax2<T, OPC, true>(m, v.w);
+    } else {
+      const unsigned lo = OPC == DD_OPC_AMAX ? dd_minmax2<T, OPC, false>(0u, v.x) : v.x;
+      m = dd_minmax2<T, OPC, false>(dd_minmax2<T, OPC, false>(lo, v.y), v.z);
+      m = dd_minmax2<T, OPC, false>(m, v.w);
+    }
+    const T *mv = (const T *)&m;
+    // the pair is already |.| for amax, so the plain max finishes it
+    constexpr int FIN = OPC == DD_OPC_MIN ? DD_OPC_MIN : DD_OPC_MAX;
+    if (nanProp) {
+      acc = dd_red<C, FIN>::comb(acc, dd_load<C, T>(mv[0]), true);
+      acc = dd_red<C, FIN>::comb(acc, dd_load<C, T>(mv[1]), true);
+    } else {
+      acc = dd_red<C, FIN>::comb(acc, dd_load<C, T>(mv[0]), false);
+      acc = dd_red<C, FIN>::comb(acc, dd_load<C, T>(mv[1]), false);
+    }
+    return acc;
+  } else if constexpr (dd_is_minmax<OPC>::value) {
+    if (nanProp) {
+#pragma unroll
+      for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), true, pw);
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), false, pw);
+    }
+    return acc;
+  } else {
+#pragma unroll
+    for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, pw);
+    return acc;
+  }
+}
 
 // ---- cross-GPU exchange: constants and cell helpers (the protocol is described further down) ----
 #define DD_PEER_MAX 8
@@ -550,8 +662,7 @@ __global__ void __launch_bounds__(256, PEER ? 4 : 0) dd_reduce_row_kernel(ddRedP
       for (int q = 0; q < U; q++) {
         if (ok[q]) {
           const T *wv = (const T *)&raw[q];
-#pragma unroll
-          for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
+          acc = dd_accum_run<T, C, OPC, V>(acc, wv, nanProp, (C)p.lpP);
         }
       }
     }
@@ -614,8 +725,7 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
           for (int c = 0; c < CPR; c++)
             if (q < left && okc[c]) {
               const T *wv = (const T *)&raw[q * CPR + c];
-#pragma unroll
-              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
+              acc = dd_accum_run<T, C, OPC, V>(acc, wv, nanProp, (C)p.lpP);
             }
       }
     } else {
@@ -636,8 +746,7 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
           for (int c = 0; c < CPR; c++)
             if (okc[c]) {
               const T *wv = (const T *)&raw[q * CPR + c];
-#pragma unroll
-              for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
+              acc = dd_accum_run<T, C, OPC, V>(acc, wv, nanProp, (C)p.lpP);
             }
       }
       for (; r < nrows; r++) {
@@ -650,8 +759,7 @@ __global__ void __launch_bounds__(256, 4) dd_reduce_rowl_kernel(ddRedParams p) {
         for (int c = 0; c < CPR; c++)
           if (okc[c]) {
             const T *wv = (const T *)&raw[c];
-#pragma unroll
-            for (int k = 0; k < V; k++) acc = dd_red<C, OPC>::accum(acc, dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
+            acc = dd_accum_run<T, C, OPC, V>(acc, wv, nanProp, (C)p.lpP);
           }
       }
     }
@@ -707,8 +815,7 @@ __global__ void __launch_bounds__(256, (PEER || sizeof(T) == 2) ? 4 : 8) dd_redu
       for (int q = 0; q < U; q++) {
         if (ok[q]) {
           const T *wv = (const T *)&raw[q];
-#pragma unroll
-          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
+          dd_accum_vec<T, C, OPC, V>(acc, wv, nanProp, (C)p.lpP);
         }
       }
     }
@@ -786,6 +893,11 @@ __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRe
   C acc[V];
 #pragma unroll
   for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::identity();
+  // min / max / amax of a 16-bit type: the running value stays in the packed 16-bit form (four
+  // instructions per 16-byte load) and is widened once, after the last row
+  constexpr bool PACKED = sizeof(T) == 2 && dd_is_minmax<OPC>::value;
+  uint4 pacc;
+  if constexpr (PACKED) pacc.x = pacc.y = pacc.z = pacc.w = dd_minmax2_identity<T, OPC>();
   if (k2 < p.K2 && ty < TY && lo + ty < hi) {
     const T *ptr = (const T *)p.x + k1 * p.sxK1 + k2 * p.sxK2 + (lo + ty) * p.sxR1;
     const int64_t step = (int64_t)TY * p.sxR1;
@@ -801,10 +913,18 @@ __global__ void __launch_bounds__(DD_COLC_THREADS, 8) dd_reduce_colc_kernel(ddRe
 #pragma unroll
       for (int q = 0; q < U; q++)
         if (q < left) {
-          const T *wv = (const T *)&raw[q];
-#pragma unroll
-          for (int k = 0; k < V; k++) acc[k] = dd_red<C, OPC>::accum(acc[k], dd_load<C, T>(wv[k]), nanProp, (C)p.lpP);
+          if constexpr (PACKED) {
+            dd_minmax_packed<T, OPC>(pacc, raw[q], nanProp);
+          } else {
+            const T *wv = (const T *)&raw[q];
+            dd_accum_vec<T, C, OPC, V>(acc, wv, nanProp, (C)p.lpP);
+          }
         }
+    }
+    if constexpr (PACKED) {  // the packed accumulators become the float ones the combine below works on
+      const T *pv = (const T *)&pacc;
+#pragma unroll
+      for (int k = 0; k < V; k++) acc[k] = dd_load<C, T>(pv[k]);
     }
   }
   if (ty < TY) {
