@@ -89,11 +89,23 @@ __global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
         const int64_t ch = dd_channel_of(p, e0);
         bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch * p.sB)));
       }
-      // BMODE 2: runs of B's value (7 x 7 maps: 49 elements) that are not whole vectors; a vector may
-      // straddle channels, so each element takes its own (the walk below), the accesses to A and C
-      // staying 16 bytes wide
+      // BMODE 2, 3, 4: runs of B's value that are not whole vectors, the accesses to A and C staying 16
+      // bytes wide.  3: a run is at least a vector long (7 x 7 maps: 49 elements), so at most one run ends
+      // inside a vector.  4: runs of one element and a whole vector inside one pixel (nhwc bias): B's
+      // values are one aligned 16-byte load.  2: anything else, each element stepping the position
       int64_t ch2 = 0, pos2 = 0;
-      if (BMODE == 2) {
+      if (BMODE == 4) {
+        // nhwc: consecutive elements are consecutive channels and a whole vector lies inside one pixel
+        int64_t ch0;
+        if (p.fast) {
+          uint32_t q, r;
+          dd_divmod((uint32_t)e0, p.fdChannels, q, r);
+          ch0 = r;
+        } else {
+          ch0 = e0 % p.channels;
+        }
+        bin = __ldg((const uint4 *)(B + ch0));
+      } else if (BMODE == 2 || BMODE == 3) {
         if (p.fast) {
           uint32_t q, r, c;
           dd_divmod((uint32_t)e0, p.fdInner, q, r);
@@ -111,17 +123,45 @@ __global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
       const T *av = (const T *)&ain, *bv = (const T *)&bin, *ov = (const T *)&oin;
       T *rv = (T *)&res;
       C rs[V];
+      if (BMODE == 4) {
 #pragma unroll
-      for (int k = 0; k < V; k++) {
-        C a = dd_times(a1, dd_load<C, T>(av[k]));  // readA == 0: a1 == 0 and av == 0, the term is +0
-        C b = BMODE == 0 ? dd_times(a2, dd_load<C, T>(bv[k])) : bs;
-        C r = dd_binop<C>(op, a, b);
-        if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
-        rs[k] = r;
-        if (BMODE == 2 && ++pos2 == p.inner) {  // the next element starts the next channel's run
-          pos2 = 0;
-          if (++ch2 == p.channels) ch2 = 0;
-          bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch2 * p.sB)));
+        for (int k = 0; k < V; k++) {
+          C a = dd_times(a1, dd_load<C, T>(av[k]));
+          C r = dd_binop<C>(op, a, dd_times(a2, dd_load<C, T>(bv[k])));
+          if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
+          rs[k] = r;
+        }
+      } else if (BMODE == 3) {
+        // a run is at least a vector long, so at most ONE run ends inside this vector: both channels'
+        // values are fetched up front and each element selects (no per-element position counter, no
+        // load in the middle of the loop)
+        const int64_t leftInRun = p.inner - pos2;
+        const int kb = leftInRun < V ? (int)leftInRun : V;  // elements from kb on belong to the next channel
+        C bs1 = bs;
+        if (kb < V) {
+          const int64_t chn = ch2 + 1 == p.channels ? 0 : ch2 + 1;
+          bs1 = dd_times(a2, dd_load<C, T>(__ldg(B + chn * p.sB)));
+        }
+#pragma unroll
+        for (int k = 0; k < V; k++) {
+          C a = dd_times(a1, dd_load<C, T>(av[k]));
+          C r = dd_binop<C>(op, a, k < kb ? bs : bs1);
+          if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
+          rs[k] = r;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < V; k++) {
+          C a = dd_times(a1, dd_load<C, T>(av[k]));  // readA == 0: a1 == 0 and av == 0, the term is +0
+          C b = BMODE == 0 ? dd_times(a2, dd_load<C, T>(bv[k])) : bs;
+          C r = dd_binop<C>(op, a, b);
+          if (useOld) r = dd_add_rn(r, dd_mul_rn(beta, dd_load<C, T>(ov[k])));
+          rs[k] = r;
+          if (BMODE == 2 && ++pos2 == p.inner) {  // the next element starts the next channel's run
+            pos2 = 0;
+            if (++ch2 == p.channels) ch2 = 0;
+            bs = dd_times(a2, dd_load<C, T>(__ldg(B + ch2 * p.sB)));
+          }
         }
       }
       dd_store_n<T, C, V>(rv, rs);
@@ -287,6 +327,10 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
     p.vec = (bits & 15) == 0;
     if (bmode == 1 && inner % V != 0) bmode = dd_tune("DD_OP_MIXED", 1) ? 2 : (p.vec = 0, 1);
     p.bmode = bmode;
+    if (bmode == 2) {
+      if (inner == 1 && sB == 1 && channels % V == 0 && ((uintptr_t)B & 15) == 0) bmode = 4;
+      else if (inner >= V) bmode = 3;
+    }
     p.fast = c.total < 0x7fffffffLL;
     if (p.fast) {
       p.fdInner = dd_fastdiv((uint32_t)inner);
@@ -294,11 +338,17 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
     }
     unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, dd_tune("DD_OPFLAT_CPS", 8));
     // add and mul (bias, per-channel scale, axpy, sum) get their own instantiations
-    if (bmode == 2) {
-      if (op == DD_OP_TENSOR_ADD) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 2>, grid, 256, h->stream, p);
-      else if (op == DD_OP_TENSOR_MUL) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 2>, grid, 256, h->stream, p);
+    if (bmode >= 2) {
+      // add and mul in the two forms layers meet (bias and per-channel scale on nchw maps that are not
+      // whole vectors, and on nhwc); every other combination shares the run-time-op instantiation
+      if (op == DD_OP_TENSOR_ADD && bmode == 3) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 3>, grid, 256, h->stream, p);
+      else if (op == DD_OP_TENSOR_MUL && bmode == 3) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 3>, grid, 256, h->stream, p);
+      else if (op == DD_OP_TENSOR_ADD && bmode == 4) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 4>, grid, 256, h->stream, p);
+      else if (op == DD_OP_TENSOR_MUL && bmode == 4) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_MUL, 4>, grid, 256, h->stream, p);
+      else if (bmode == 3) dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 3>, grid, 256, h->stream, p);
+      else if (bmode == 4) dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 4>, grid, 256, h->stream, p);
       else dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 2>, grid, 256, h->stream, p);
-      DD_LAUNCHED(h, "optensor/flat-bcast-mixed");
+      DD_LAUNCHED(h, bmode == 4 ? "optensor/flat-bcast-vector" : "optensor/flat-bcast-mixed");
       return DD_STATUS_SUCCESS;
     }
     if (op == DD_OP_TENSOR_ADD && bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 0>, grid, 256, h->stream, p);

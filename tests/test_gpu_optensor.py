@@ -44,11 +44,13 @@ def test_op_tensor_broadcast(fact, dev, oracle, shape, bshape, op):
 
 @pytest.mark.parametrize("op", ["add", "mul", "max"])
 @pytest.mark.parametrize("shape,layout", [([6, 40, 7, 7], "nchw"), ([3, 24, 13, 13], "nchw"), ([5, 3, 1, 5], "nchw"),
-                                          ([4, 36, 6, 6], "nhwc"), ([2, 1000, 3, 3], "nchw")])
+                                          ([4, 36, 6, 6], "nhwc"), ([2, 1000, 3, 3], "nchw"), ([4, 6, 5, 6], "nhwc"),
+                                          ([8, 10, 1, 3], "nchw")])
 def test_channel_runs_that_are_not_whole_vectors(fact, dev, oracle, op, shape, layout):
-    """Bias / per-channel scale where a channel's run (49, 169, 5, 9 elements; 1 for nhwc) is not a
+    """Bias / per-channel scale where a channel's run (49, 169, 5, 9, 3 elements; 1 for nhwc) is not a
     multiple of four floats: A and C still move as 16-byte vectors and each element takes its own
-    channel's value."""
+    channel's value.  Three forms: a run at least a vector long (at most one run ends inside a
+    vector), nhwc with a whole number of vectors per pixel (B read as vectors), and the element walk."""
     bshape = [1, shape[1], 1, 1]
     st = oracle.default_strides(shape) if layout == "nchw" else oracle.nhwc_strides(shape)
     bst = oracle.default_strides(bshape)
@@ -61,9 +63,32 @@ def test_channel_runs_that_are_not_whole_vectors(fact, dev, oracle, op, shape, l
         core.op_tensor(fact.handle, op, a1, core.tensor_descriptor(shape, "float", st), ta, a2,
                        core.tensor_descriptor(bshape, "float", bst), tb, beta,
                        core.tensor_descriptor(shape, "float", st), tc)
-        assert fact.handle.last_kernel() == "optensor/flat-bcast-mixed"
+        vector_b = layout == "nhwc" and shape[1] % 4 == 0
+        assert fact.handle.last_kernel() == ("optensor/flat-bcast-vector" if vector_b else "optensor/flat-bcast-mixed")
         got = dev.get(tc, np.float32)
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (op, a1, a2, beta)
+
+
+@pytest.mark.parametrize("shape,layout,kernel", [([6, 40, 7, 7], "nchw", "optensor/flat-bcast-mixed"),
+                                                 ([3, 24, 13, 13], "nchw", "optensor/flat-bcast-mixed"),
+                                                 ([4, 40, 6, 6], "nhwc", "optensor/flat-bcast-vector"),
+                                                 ([4, 12, 5, 6], "nhwc", "optensor/flat-bcast-mixed"),
+                                                 ([8, 10, 1, 3], "nchw", "optensor/flat-bcast-mixed")])
+def test_bias_on_bf16_maps_that_are_not_whole_vectors(fact, dev, oracle, shape, layout, kernel):
+    """The same three forms with eight elements per vector (bf16): bias add y = 0.5*b[c] + y, bit-exact
+    against the oracle (float arithmetic, one rounding to bf16)."""
+    bshape = [1, shape[1], 1, 1]
+    st = oracle.default_strides(shape) if layout == "nchw" else oracle.nhwc_strides(shape)
+    to_bf16 = lambda v: (v.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    y0, b = to_bf16(rnd(shape, 31)), to_bf16(rnd(bshape, 32, 0.5, 1.5))
+    want = y0.copy()
+    oracle.add_tensor(0.5, oracle.as_layout(b, bshape, oracle.default_strides(bshape)), 1.0,
+                      oracle.as_layout(want, shape, st), tag="bf16")
+    ty, tb = dev.put(y0), dev.put(b)
+    core.add_tensor(fact.handle, 0.5, core.tensor_descriptor(bshape, "bf16", "nchw"), tb, 1.0,
+                    core.tensor_descriptor(shape, "bf16", st), ty)
+    assert fact.handle.last_kernel() == kernel
+    assert np.array_equal(dev.get(ty, np.uint16), want)
 
 
 @pytest.mark.parametrize("op", ["add", "mul", "max"])
