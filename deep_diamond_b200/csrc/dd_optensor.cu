@@ -178,6 +178,47 @@ __global__ void __launch_bounds__(256, 8) dd_op_flat_kernel(ddOpFlatParams p) {
   }
 }
 
+// Bias / per-channel scale (B constant over a run that is a whole number of vectors), no blend with
+// the old C: TWO vectors per thread-iteration.  The operation is usually in place (C == A), so the
+// compiler cannot start the next iteration's load before this one's store; here both loads (and both
+// channel look-ups) go out before the first store.
+template <typename T, typename C, int OP>
+__global__ void __launch_bounds__(256, 8) dd_op_bcast2_kernel(ddOpFlatParams p) {
+  dd_pdl_prologue();
+  constexpr int V = 16 / sizeof(T);
+  const T *A = (const T *)p.A;
+  const T *B = (const T *)p.B;
+  T *Cp = (T *)p.C;
+  const C a1 = (C)p.alpha1, a2 = (C)p.alpha2;
+  const uint32_t nv = (uint32_t)(p.n / V), nthreads = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += 2 * nthreads) {
+    const uint32_t i2 = i + nthreads;
+    const bool two = i2 < nv;
+    const uint4 x0 = *(const uint4 *)(A + (size_t)i * V);
+    uint4 x1 = make_uint4(0, 0, 0, 0);
+    if (two) x1 = *(const uint4 *)(A + (size_t)i2 * V);
+    uint32_t q, c0, c1, r;
+    q = dd_div(i * V, p.fdInner);
+    dd_divmod(q, p.fdChannels, r, c0);
+    q = dd_div((two ? i2 : i) * V, p.fdInner);
+    dd_divmod(q, p.fdChannels, r, c1);
+    const C b0 = dd_times(a2, dd_load<C, T>(__ldg(B + (int64_t)c0 * p.sB)));
+    const C b1 = dd_times(a2, dd_load<C, T>(__ldg(B + (int64_t)c1 * p.sB)));
+    uint4 y0, y1;
+    C r0[V], r1[V];
+    const T *v0 = (const T *)&x0, *v1 = (const T *)&x1;
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+      r0[k] = dd_binop<C>(OP, dd_times(a1, dd_load<C, T>(v0[k])), b0);
+      r1[k] = dd_binop<C>(OP, dd_times(a1, dd_load<C, T>(v1[k])), b1);
+    }
+    dd_store_n<T, C, V>((T *)&y0, r0);
+    dd_store_n<T, C, V>((T *)&y1, r1);
+    *(uint4 *)(Cp + (size_t)i * V) = y0;
+    if (two) *(uint4 *)(Cp + (size_t)i2 * V) = y1;
+  }
+}
+
 struct ddOpStridedParams {
   const void *A;
   const void *B;
@@ -349,6 +390,16 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
       else if (bmode == 4) dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 4>, grid, 256, h->stream, p);
       else dd_launch_pdl(dd_op_flat_kernel<T, C, -1, 2>, grid, 256, h->stream, p);
       DD_LAUNCHED(h, bmode == 4 ? "optensor/flat-bcast-vector" : "optensor/flat-bcast-mixed");
+      return DD_STATUS_SUCCESS;
+    }
+    if (bmode == 1 && (op == DD_OP_TENSOR_ADD || op == DD_OP_TENSOR_MUL) && beta == 0.0 && readA && p.vec && p.fast &&
+        p.n % V == 0 && p.n / V <= (int64_t)h->smCount * 8 * 256 * 16 && dd_tune("DD_OP_BCAST2", 1)) {
+      // small tensors only (at most 16 vectors per thread of a resident grid): [128,512,14,14] f32 19.07 -> 18.38 us;
+      // on 205 MB tensors the one-vector kernel measured 3 % faster
+      unsigned g2 = dd_flat_grid(h, (p.n / V + 1) / 2, 256, dd_tune("DD_OPFLAT_CPS", 8));
+      if (op == DD_OP_TENSOR_ADD) dd_launch_pdl(dd_op_bcast2_kernel<T, C, DD_OP_TENSOR_ADD>, g2, 256, h->stream, p);
+      else dd_launch_pdl(dd_op_bcast2_kernel<T, C, DD_OP_TENSOR_MUL>, g2, 256, h->stream, p);
+      DD_LAUNCHED(h, "optensor/flat-bcast");
       return DD_STATUS_SUCCESS;
     }
     if (op == DD_OP_TENSOR_ADD && bmode == 0) dd_launch_pdl(dd_op_flat_kernel<T, C, DD_OP_TENSOR_ADD, 0>, grid, 256, h->stream, p);
