@@ -544,7 +544,7 @@ def ops_table(torch, fact, core, oracle, peak, sharded=None, world=1, profile_on
             n * 2, n, c5s8, 2 * max(sets, 3), 10, rid="c5_s8")
     del x, y, q, qs, zs
 
-    if not only_sharded_configs and world == 1 and not profile_only:
+    if not only_sharded_configs and world == 1:
         # reductions away from configuration 4: 16-bit element types, and 784-long runs
         shp = [256, 256, 28, 28]
         n = int(np.prod(shp))
