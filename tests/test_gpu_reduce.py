@@ -172,6 +172,54 @@ def test_nan_propagation(fact, dev):
     assert dev.get(ty, np.float32)[0] == 6.0
 
 
+@pytest.mark.parametrize("tag,np_t", [("float", np.float32), ("half", np.float16), ("bf16", None), ("double", np.float64)])
+@pytest.mark.parametrize("op", ["max", "min", "amax"])
+def test_nan_modes_on_every_min_max_path(fact, dev, oracle, tag, np_t, op):
+    """A NaN among the reduced elements comes out as NaN with propagation on and is ignored with it
+    off, through the row, column and generic kernels and, for the 16-bit types, through the packed
+    forms (max.NaN.bf16x2 / f16x2); outputs whose elements hold no NaN are exact either way."""
+    rng = np.random.default_rng(41)
+    for shape, yshape in (([6, 32, 12, 16], [1, 32, 1, 1]), ([6, 32, 12, 16], [6, 1, 12, 16]), ([96, 96, 28, 28], [96, 1, 28, 28]),
+                          ([16, 128, 28, 28], [1, 128, 1, 1]), ([2, 3, 4, 5], [2, 3, 4, 1])):
+        n = int(np.prod(shape))
+        xf = (rng.standard_normal(n) * 3).astype(np.float32)
+        if tag == "bf16":
+            bits = (xf.view(np.uint32) >> 16).astype(np.uint16)
+            vals = (bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+            store, nan_bits = bits, np.uint16(0x7FC0)
+        else:
+            store = xf.astype(np_t)
+            vals = store.astype(np.float64)
+            nan_bits = np_t(np.nan)
+        hit = rng.choice(n, size=max(1, n // 997), replace=False)
+        store = store.copy()
+        store[hit] = nan_bits
+        has_nan = np.zeros(n, bool)
+        has_nan[hit] = True
+        axes = tuple(i for i in range(4) if yshape[i] == 1 and shape[i] != 1)
+        v = np.abs(vals) if op == "amax" else vals
+        fill = -np.inf if op in ("max", "amax") else np.inf
+        clean = np.where(has_nan, fill, v).reshape(shape)
+        ref = clean.max(axis=axes) if op != "min" else clean.min(axis=axes)
+        any_nan = has_nan.reshape(shape).any(axis=axes)
+        xd, yd = core.tensor_descriptor(shape, tag, "nchw"), core.tensor_descriptor(yshape, tag, "nchw")
+        tx = dev.put(store)
+        for prop in (True, False):
+            ty = dev.empty(ref.size * store.itemsize)
+            core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor(op, "double" if tag == "double" else "float", prop),
+                               1.0, xd, tx, 0.0, yd, ty)
+            raw = dev.get(ty, store.dtype)
+            got = (raw.astype(np.uint32) << 16).view(np.float32).astype(np.float64) if tag == "bf16" else raw.astype(np.float64)
+            got = got.reshape(ref.shape)
+            if prop:
+                assert np.isnan(got[any_nan]).all(), (shape, yshape, fact.handle.last_kernel())
+                assert np.array_equal(got[~any_nan], ref[~any_nan]), (shape, yshape, fact.handle.last_kernel())
+            else:
+                all_nan = ~np.isfinite(ref)   # an output all of whose elements are NaN: not produced by these inputs
+                assert not all_nan.any()
+                assert np.array_equal(got, ref), (shape, yshape, fact.handle.last_kernel())
+
+
 def test_convolution_bwd_bias(fact, dev, oracle):
     """The bias gradient (cudnn/core.clj:344-350) is the (N,H,W) sum: db = alpha * sum(dy) + beta * db."""
     shape, bshape = [16, 48, 9, 7], [1, 48, 1, 1]
