@@ -1,8 +1,8 @@
 // ddTensorEquals: any-mismatch test over two strided views of one data type.  Replaces the five
 // rank-specific kernels of the reference (blas-plus.cu:9-101), which run one thread per (n,c,h)
 // with serial inner loops; here every element gets a thread (16-byte vectors when both views are
-// dense).  A warp that sees a mismatch raises the flag at once and stops; every fourth pass the
-// others look at the flag and stop too, so tensors that differ cost a fraction of a full pass
+// dense).  A warp that sees a mismatch raises the flag at once and stops; after every pass (four
+// vectors of each operand) the others look at the flag and stop too, so tensors that differ cost a fraction of a full pass
 // (equal tensors read everything: 2*sizeof(T) algorithmic bytes per element).  Comparison is the
 // typed `!=` of the reference (NaN differs from everything, -0 equals +0).
 #include "dd_internal.cuh"
@@ -32,19 +32,35 @@ __global__ void __launch_bounds__(256) dd_equals_kernel(ddEqParams p) {
     int64_t done = 0;
     if (((((uintptr_t)x) | ((uintptr_t)y)) & 15) == 0) {
       const int64_t nv = n / V;
-      int pass = 0;
-      for (int64_t i = tid; i < nv; i += nthreads) {
-        uint4 a = *(const uint4 *)(x + i * V), b = *(const uint4 *)(y + i * V);
-        const T *av = (const T *)&a, *bv = (const T *)&b;
+      // four vectors of each operand per pass: the eight loads go out together (a vote after every
+      // vector would hold each pass back until its own two loads had come in), then one vote and one
+      // look at the flag
+      constexpr int U = 4;
+      for (int64_t i = tid; i < nv; i += U * nthreads) {
+        uint4 a[U], b[U];
 #pragma unroll
-        for (int k = 0; k < V; k++) diff |= dd_ne<T>(av[k], bv[k]);
+        for (int u = 0; u < U; u++) {
+          const int64_t j = i + u * nthreads;
+          if (j < nv) {
+            a[u] = *(const uint4 *)(x + j * V);
+            b[u] = *(const uint4 *)(y + j * V);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          if (i + u * nthreads < nv) {
+            const T *av = (const T *)&a[u], *bv = (const T *)&b[u];
+#pragma unroll
+            for (int k = 0; k < V; k++) diff |= dd_ne<T>(av[k], bv[k]);
+          }
+        }
         // the lanes of a warp run this loop in step (trip counts differ by one at most)
         const unsigned found = __ballot_sync(__activemask(), diff);
         if (found) {
           if ((threadIdx.x & 31) == __ffs(found) - 1) atomicAdd(p.flag, 1);
           break;
         }
-        if ((++pass & 3) == 0 && *(volatile const int *)p.flag != 0) break;
+        if (*(volatile const int *)p.flag != 0) break;
       }
       done = nv * V;
     }
