@@ -4,12 +4,17 @@ generic paths (canonicalisation, dim merging, kernel-family choice, ragged tiles
 that the hand-picked cases of the other files only sample.  Each case fills the destination with a
 canary first, so a write outside the described view also fails the comparison.
 """
+import os
+
 import numpy as np
 import pytest
 
 from deep_diamond_b200 import core
 
 pytestmark = pytest.mark.gpu
+
+# DD_TEST_SEED_OFFSET=k shifts every generator's seed: the same tests over other random shapes
+SEED_OFFSET = int(os.environ.get("DD_TEST_SEED_OFFSET", "0"))
 
 NP = {"float": np.float32, "double": np.float64, "half": np.float16, "byte": np.int8,
       "int": np.int32, "uint8": np.uint8, "bf16": np.uint16, "long": np.int64}
@@ -57,7 +62,7 @@ def canary(n, np_t):
 
 @pytest.mark.parametrize("seed", range(12))
 def test_random_transforms(fact, dev, oracle, seed):
-    rng = np.random.default_rng(1000 + seed)
+    rng = np.random.default_rng(1000 + 100 * SEED_OFFSET + seed)
     types = list(NP)
     for _ in range(25):
         shape = random_shape(rng, big=rng.random() < 0.5)
@@ -84,7 +89,7 @@ def test_random_transforms(fact, dev, oracle, seed):
 
 @pytest.mark.parametrize("seed", range(6))
 def test_random_op_tensors(fact, dev, oracle, seed):
-    rng = np.random.default_rng(2000 + seed)
+    rng = np.random.default_rng(2000 + 100 * SEED_OFFSET + seed)
     ops = ["add", "mul", "min", "max", "sub"]
     for _ in range(25):
         shape = random_shape(rng, big=rng.random() < 0.5)
@@ -112,7 +117,7 @@ def test_random_op_tensors(fact, dev, oracle, seed):
 
 @pytest.mark.parametrize("seed", range(8))
 def test_random_reductions(fact, dev, oracle, seed):
-    rng = np.random.default_rng(3000 + seed)
+    rng = np.random.default_rng(3000 + 100 * SEED_OFFSET + seed)
     ops = ["add", "avg", "max", "min", "amax", "norm1", "norm2"]
     for _ in range(20):
         shape = random_shape(rng, big=rng.random() < 0.6)
@@ -154,7 +159,7 @@ def test_random_reductions(fact, dev, oracle, seed):
 
 @pytest.mark.parametrize("seed", range(4))
 def test_random_activations_on_views(fact, dev, oracle, seed):
-    rng = np.random.default_rng(4000 + seed)
+    rng = np.random.default_rng(4000 + 100 * SEED_OFFSET + seed)
     for _ in range(20):
         shape = random_shape(rng, big=True)
         sx, sy, sg = random_layout(rng, shape), random_layout(rng, shape), random_layout(rng, shape)
