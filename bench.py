@@ -666,7 +666,7 @@ def next_rows_table(torch, fact, core, oracle, peak, profile_only=False):
         measure("%s backward" % mode, "[256,256,28,28] f32", n * 12, n,
                 lambda adm=adm: core.activation_backward(h, adm, 1.0, d4, None, d4, z, d4, x, 0.0, d4, y))
     # oneDNN's norm-lp-sum with p = 3 over (C,H,W): |x|^p element by element
-    rl = core.reduce_tensor_descriptor("norm-lp-sum", "float", True, 3.0, 1e-6)
+    rl = core.reduce_tensor_descriptor("norm-lp-sum", "float", True, p=3.0, eps=1e-6)
     yl = torch.empty(256, dtype=torch.float32, device=dev)
     measure("reduce norm-lp-sum p=3 over (C,H,W)", "[256,256,28,28] f32", n * 4, n,
             lambda: core.reduce_tensor(h, rl, 1.0, d4, x, 0.0, core.tensor_descriptor([256, 1, 1, 1], "float", "nchw"), yl))

@@ -81,6 +81,7 @@ _SIGS = {
     "ddSetReduceTensorDescriptor": [_vp, _int, _int, _int],
     "ddSetReduceTensorDescriptorLp": [_vp, _int, _int, _int, ctypes.c_double, ctypes.c_double],
     "ddGetReduceTensorDescriptorLp": [_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)],
+    "ddSetReduceTensorDescriptorIndices": [_vp, _int],
     "ddGetReduceTensorDescriptor": [_vp, ctypes.POINTER(_int), ctypes.POINTER(_int),
                                     ctypes.POINTER(_int)],
     "ddGetReductionIndicesSize": [_vp, _vp, _vp, _vp, ctypes.POINTER(_sz)],

@@ -222,6 +222,12 @@
    :norm-lp-power-p-max 11
    :norm-lp-power-p-sum 12})
 
+(def ^{:const true
+       :doc "cudnn/constants.clj:182-184."}
+  dd-reduce-tensor-indices
+  {:no-indices 0
+   :flattened 1})
+
 (defn dec-reduce-tensor-op [^long op]
   (case op
     0 :add

@@ -207,7 +207,8 @@
 ;; =========================== Reduce ====================================================
 
 (defn reduce-tensor-descriptor
-  "After reduce-tensor-descriptor, cudnn/core.clj:188-205; indices are never produced.  The
+  "After reduce-tensor-descriptor, cudnn/core.clj:188-205: the 4-argument arity is the reference's
+  (op comp-type nan-opt indices), :flattened asking min / max / amax for the positions too.  The
   5-argument arity carries the p and epsilon of the DNNL backend's `reduction`
   (dnnl/core.clj:796-803) for the :norm-lp-* kinds."
   ([op comp-type nan-opt p eps]
@@ -217,6 +218,13 @@
                                   (enc-keyword dd-data-type comp-type)
                                   (enc-nan-propagation nan-opt)
                                   (double p) (double eps))
+       (catch Exception e
+         (destroy-reduce-tensor-descriptor* rtd)
+         (throw e)))))
+  ([op comp-type nan-opt indices]
+   (let [rtd (reduce-tensor-descriptor op comp-type nan-opt)]
+     (try
+       (reduce-tensor-descriptor-indices* rtd (enc-keyword dd-reduce-tensor-indices indices))
        (catch Exception e
          (destroy-reduce-tensor-descriptor* rtd)
          (throw e)))))

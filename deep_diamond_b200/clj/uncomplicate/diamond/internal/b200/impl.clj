@@ -96,6 +96,7 @@
 (defdowncall dd-get-reduce-tensor-descriptor      "ddGetReduceTensorDescriptor" I [P P P P])
 (defdowncall dd-set-reduce-tensor-descriptor-lp   "ddSetReduceTensorDescriptorLp" I [P I I I D D])
 (defdowncall dd-get-reduce-tensor-descriptor-lp   "ddGetReduceTensorDescriptorLp" I [P P P])
+(defdowncall dd-set-reduce-tensor-descriptor-indices "ddSetReduceTensorDescriptorIndices" I [P I])
 (defdowncall dd-get-reduction-indices-size        "ddGetReductionIndicesSize" I [P P P P P])
 (defdowncall dd-get-reduction-workspace-size      "ddGetReductionWorkspaceSize" I [P P P P P])
 (defdowncall dd-reduce-tensor                     "ddReduceTensor" I [P P P L P L P P P P P P])
@@ -457,6 +458,9 @@
      (invoke dd-set-reduce-tensor-descriptor-lp (seg rtd) (int op) (int comp-type) (int nan-opt)
              (double p) (double eps))
      rtd)))
+
+(defn reduce-tensor-descriptor-indices* [rtd ^long indices]
+  (with-check nil (invoke dd-set-reduce-tensor-descriptor-indices (seg rtd) (int indices)) rtd))
 
 (defn destroy-reduce-tensor-descriptor* [rtd]
   (with-check nil (invoke dd-destroy-reduce-tensor-descriptor (seg rtd)) true))

@@ -52,6 +52,9 @@ REDUCE_NAME = {0: "add", 1: "mul", 2: "min", 3: "max", 4: "amax", 5: "avg", 6: "
                8: "mul-no-zeros", 9: "norm-lp-max", 10: "norm-lp-sum", 11: "norm-lp-power-p-max",
                12: "norm-lp-power-p-sum"}
 
+# cudnn/constants.clj:182-184
+REDUCE_INDICES = {"no-indices": 0, "flattened": 1}
+
 
 def enc_keyword(table, kw, what="keyword"):
     """``enc-keyword``: unknown keywords raise like ``dragan-says-ex``."""

@@ -8,7 +8,7 @@ import ctypes
 from . import _lib
 from ._lib import DiamondError, check, lib
 from .constants import (ACTIVATION_MODE, ACTIVATION_NAME, DATA_TYPE, DATA_TYPE_NAME,
-                        DATA_TYPE_WIDTH, OP_TENSOR, REDUCE_NAME, REDUCE_OP, enc_keyword,
+                        DATA_TYPE_WIDTH, OP_TENSOR, REDUCE_INDICES, REDUCE_NAME, REDUCE_OP, enc_keyword,
                         layout_strides)
 
 
@@ -329,7 +329,7 @@ def activation_backward(handle, ad, alpha, desc_y, buf_y, desc_dy, buf_dy, desc_
 # ============================ Reduce ==============================================
 
 class ReduceTensorDescriptor:
-    def __init__(self, op, comp_type="float", nan_opt=True, p=None, eps=None):
+    def __init__(self, op, comp_type="float", nan_opt=True, indices=None, p=None, eps=None):
         d = ctypes.c_void_p()
         check(lib.ddCreateReduceTensorDescriptor(ctypes.byref(d)), None)
         self.ptr = d
@@ -340,6 +340,8 @@ class ReduceTensorDescriptor:
         else:
             st = lib.ddSetReduceTensorDescriptorLp(d, self.op, comp, 1 if nan_opt else 0,
                                                    2.0 if p is None else float(p), 0.0 if eps is None else float(eps))
+        if st == 0 and indices is not None:
+            st = lib.ddSetReduceTensorDescriptorIndices(d, enc_keyword(REDUCE_INDICES, indices, "reduce indices"))
         if st != 0:
             lib.ddDestroyReduceTensorDescriptor(d)
             check(st, None, "ddSetReduceTensorDescriptor")
@@ -357,10 +359,12 @@ class ReduceTensorDescriptor:
         return True
 
 
-def reduce_tensor_descriptor(op, comp_type="float", nan_opt=True, p=None, eps=None):
-    """``reduce-tensor-descriptor`` (:188-203).  ``p`` and ``eps`` are the two extra arguments of the
-    DNNL backend's ``reduction`` (dnnl/core.clj:796-803), read by the ``norm-lp-*`` kinds."""
-    return ReduceTensorDescriptor(op, comp_type, nan_opt, p, eps)
+def reduce_tensor_descriptor(op, comp_type="float", nan_opt=True, indices=None, p=None, eps=None):
+    """``reduce-tensor-descriptor`` (:188-203), whose fourth argument is ``indices`` (``"flattened"``:
+    min / max / amax also report where the result was found; ``"no-indices"``).  ``p`` and ``eps``
+    are the two extra arguments of the DNNL backend's ``reduction`` (dnnl/core.clj:796-803), read by
+    the ``norm-lp-*`` kinds."""
+    return ReduceTensorDescriptor(op, comp_type, nan_opt, indices, p, eps)
 
 
 def reduction_indices_size(handle, rtd, desc_x, desc_y):
@@ -382,10 +386,14 @@ def reduce_tensor(handle, rtd, *args):
     """``reduce-tensor`` (:213-231).  The 10-argument arity takes caller-owned indices and
     workspace; the 6-argument arity uses the handle's own scratch -- where the reference allocates
     and frees two device buffers on every call (:223-231), this one allocates nothing."""
+    ind, ind_bytes = None, 0
     if len(args) == 8:
-        _indices, workspace, alpha, desc_x, buf_x, beta, desc_y, buf_y = args
+        indices, workspace, alpha, desc_x, buf_x, beta, desc_y, buf_y = args
         ws = _ptr(workspace)
         ws_bytes = workspace.numel() * workspace.element_size() if hasattr(workspace, "numel") else 0
+        if indices is not None:
+            ind = _ptr(indices)
+            ind_bytes = indices.numel() * indices.element_size() if hasattr(indices, "numel") else 0
     elif len(args) == 6:
         alpha, desc_x, buf_x, beta, desc_y, buf_y = args
         ws, ws_bytes = None, 0
@@ -393,7 +401,7 @@ def reduce_tensor(handle, rtd, *args):
         raise TypeError("reduce_tensor takes 6 or 8 arguments after the descriptor")
     dx, dy = desc(desc_x), desc(desc_y)
     a, b = _scalar(alpha, dx.dtype_code), _scalar(beta, dy.dtype_code)
-    check(lib.ddReduceTensor(handle.ptr, rtd.ptr, None, 0, ws, ws_bytes, ctypes.byref(a), dx.ptr,
+    check(lib.ddReduceTensor(handle.ptr, rtd.ptr, ind, ind_bytes, ws, ws_bytes, ctypes.byref(a), dx.ptr,
                              _ptr(buf_x), ctypes.byref(b), dy.ptr, _ptr(buf_y)), handle.ptr,
           "ddReduceTensor")
     return handle

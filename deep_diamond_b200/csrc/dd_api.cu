@@ -349,6 +349,7 @@ ddStatus_t ddSetReduceTensorDescriptor(ddReduceTensorDescriptor_t r, ddReduceTen
   r->nan = nanOpt;
   r->p = 2.0;
   r->eps = 0.0;
+  r->indices = 0;
   return DD_STATUS_SUCCESS;
 }
 
@@ -359,6 +360,13 @@ ddStatus_t ddSetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t r, ddReduceT
   if (st != DD_STATUS_SUCCESS) return st;
   r->p = p;
   r->eps = eps;
+  return DD_STATUS_SUCCESS;
+}
+
+ddStatus_t ddSetReduceTensorDescriptorIndices(ddReduceTensorDescriptor_t r, ddReduceTensorIndices_t indices) {
+  if (!r || ((int)indices != DD_REDUCE_TENSOR_NO_INDICES && (int)indices != DD_REDUCE_TENSOR_FLATTENED_INDICES))
+    return DD_STATUS_BAD_PARAM;
+  r->indices = (int)indices;
   return DD_STATUS_SUCCESS;
 }
 
@@ -529,6 +537,11 @@ ddStatus_t ddActivationBackward(ddHandle_t h, ddActivationDescriptor_t act, cons
                                 dd_read_scalar(beta, dxd->dtype), dxd, dx);
 }
 
+static bool dd_wants_indices(const ddReduceTensorStruct *red) {
+  return red->indices == DD_REDUCE_TENSOR_FLATTENED_INDICES &&
+         (red->op == DD_REDUCE_TENSOR_MIN || red->op == DD_REDUCE_TENSOR_MAX || red->op == DD_REDUCE_TENSOR_AMAX);
+}
+
 static ddStatus_t check_reduce_shapes(ddHandle_t h, const ddTensorStruct *xd, const ddTensorStruct *yd) {
   if (xd->nd != yd->nd) DD_FAIL(h, DD_STATUS_BAD_PARAM, "reduce: x and y ranks differ");
   for (int i = 0; i < xd->nd; i++)
@@ -540,9 +553,16 @@ static ddStatus_t check_reduce_shapes(ddHandle_t h, const ddTensorStruct *xd, co
 ddStatus_t ddGetReductionIndicesSize(ddHandle_t h, ddReduceTensorDescriptor_t red,
                                      ddTensorDescriptor_t xd, ddTensorDescriptor_t yd, size_t *bytes) {
   DD_CHECK_HANDLE(h);
-  (void)red; (void)xd; (void)yd;
   if (!bytes) DD_FAIL(h, DD_STATUS_BAD_PARAM, "null pointer");
   *bytes = 0;
+  if (red && dd_wants_indices(red)) {
+    DD_CHECK(dd_check_desc(h, xd, "reduce x"));
+    DD_CHECK(dd_check_desc(h, yd, "reduce y"));
+    DD_CHECK(check_reduce_shapes(h, xd, yd));
+    size_t nout = 1;
+    for (int i = 0; i < yd->nd; i++) nout *= (size_t)yd->dims[i];
+    *bytes = nout * sizeof(unsigned);
+  }
   return DD_STATUS_SUCCESS;
 }
 
@@ -561,8 +581,6 @@ ddStatus_t ddReduceTensor(ddHandle_t h, ddReduceTensorDescriptor_t red, void *in
                           ddTensorDescriptor_t xd, const void *x, const void *beta,
                           ddTensorDescriptor_t yd, void *y) {
   DD_RANGE("ddReduceTensor");
-  (void)indices;
-  (void)indicesBytes;
   DD_CHECK_HANDLE(h);
   if (!red) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddReduceTensor: null reduce descriptor");
   DD_CHECK(dd_check_desc(h, xd, "ddReduceTensor x"));
@@ -571,9 +589,19 @@ ddStatus_t ddReduceTensor(ddHandle_t h, ddReduceTensorDescriptor_t red, void *in
   DD_CHECK(check_reduce_shapes(h, xd, yd));
   if (!dd_type_is_float(xd->dtype) || !dd_type_is_float(yd->dtype))
     DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "ddReduceTensor: data types must be floating point");
+  if (dd_wants_indices(red)) {
+    size_t nout = 1;
+    for (int i = 0; i < yd->nd; i++) nout *= (size_t)yd->dims[i];
+    if (!indices || indicesBytes < nout * sizeof(unsigned))
+      DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddReduceTensor: the indices buffer holds %zu bytes, %zu are needed",
+              indices ? indicesBytes : (size_t)0, nout * sizeof(unsigned));
+    if (x == y) DD_FAIL(h, DD_STATUS_BAD_PARAM, "ddReduceTensor: indices need x after y is written; x and y must differ");
+  }
   // alpha and beta follow the compute type like cuDNN's: float unless the tensors are double
-  return dd_reduce_impl(h, red, ws, wsBytes, dd_read_scalar(alpha, xd->dtype), xd, x,
-                        dd_read_scalar(beta, yd->dtype), yd, y, false, nullptr);
+  DD_CHECK(dd_reduce_impl(h, red, ws, wsBytes, dd_read_scalar(alpha, xd->dtype), xd, x,
+                          dd_read_scalar(beta, yd->dtype), yd, y, false, nullptr));
+  if (dd_wants_indices(red)) return dd_reduce_indices_impl(h, red, xd, x, yd, (unsigned *)indices);
+  return DD_STATUS_SUCCESS;
 }
 
 // db = alpha * sum of dy over every dim where db's extent is 1 (N, H, W for a [1,C,1,1] bias)

@@ -45,6 +45,7 @@ struct ddReduceTensorStruct {
   ddNanPropagation_t nan;
   double p = 2.0;    // the NORM_LP kinds: exponent and epsilon
   double eps = 0.0;
+  int indices = 0;   // DD_REDUCE_TENSOR_FLATTENED_INDICES: positions of the min / max / amax are wanted
 };
 
 struct ddContext {
@@ -462,6 +463,8 @@ ddStatus_t dd_reduce_ws_size(ddHandle_t h, const ddReduceTensorStruct *red,
 ddStatus_t dd_reduce_impl(ddHandle_t h, const ddReduceTensorStruct *red, void *ws, size_t wsBytes,
                           double alpha, const ddTensorStruct *xd, const void *x, double beta,
                           const ddTensorStruct *yd, void *y, bool partialOnly, void *partialOut);
+ddStatus_t dd_reduce_indices_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd, const void *x,
+                                  const ddTensorStruct *yd, unsigned *indices);
 ddStatus_t dd_reduce_finish_impl(ddHandle_t h, const ddReduceTensorStruct *red, const void *partial,
                                  double count, double alpha, double beta, const ddTensorStruct *xd,
                                  const ddTensorStruct *yd, void *y);

@@ -739,3 +739,109 @@ extern "C" ddStatus_t ddReduceTensorNoAlloc(void *stream, ddReduceTensorOp_t op,
   if (st != DD_STATUS_SUCCESS) noalloc_msg(errbuf, errbufLen, ctx.msg);
   return st;
 }
+
+// ---- positions of the min / max / amax (the reference's :flattened indices) --------------------
+// One warp per output scans the reduced elements again in the flattened order of the ORIGINAL dims
+// (not the canonical ones: the position is defined over the tensor as the caller described it) and
+// keeps the first element that wins; lanes stride over the range, then a shuffle tree picks the
+// winner with the smaller position among equals.  A second pass over x, not tuned: the option is
+// there for completeness.
+struct ddRedIndexParams {
+  const void *x;
+  unsigned *indices;
+  int nk, nr;
+  int64_t kd[DD_DIM_MAX], kx[DD_DIM_MAX];  // kept dims in original order: extent, x stride
+  int64_t rd[DD_DIM_MAX], rx[DD_DIM_MAX];  // reduced dims in original order: extent, x stride
+  int64_t nout, nred;
+  int op, nanProp;
+};
+
+// does candidate (v, i) beat the holder (b, bi)?  NaN with propagation: the first NaN wins outright.
+template <typename C>
+__device__ __forceinline__ bool dd_index_beats(int op, bool nanProp, C v, unsigned i, C b, unsigned bi) {
+  const bool vn = v != v, bn = b != b;
+  if (vn || bn) {
+    if (!nanProp) return bn && !vn;          // a number beats the NaN placeholder; NaN never beats a number
+    if (vn && bn) return i < bi;
+    return vn;
+  }
+  if (v == b) return i < bi;
+  return op == DD_REDUCE_TENSOR_MIN ? v < b : v > b;
+}
+
+template <typename T, typename C>
+__global__ void __launch_bounds__(256) dd_reduce_indices_kernel(ddRedIndexParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const bool nanProp = p.nanProp != 0;
+  for (int64_t o = warp; o < p.nout; o += nwarps) {
+    int64_t ox = 0, rem = o;
+    for (int d = p.nk - 1; d >= 0; d--) {
+      const int64_t q = rem / p.kd[d];
+      ox += (rem - q * p.kd[d]) * p.kx[d];
+      rem = q;
+    }
+    C best = (C)0;
+    unsigned bi = 0xffffffffu;  // nothing held yet
+    for (int64_t i = lane; i < p.nred; i += 32) {
+      int64_t off = ox, rr = i;
+      for (int d = p.nr - 1; d >= 0; d--) {
+        const int64_t q = rr / p.rd[d];
+        off += (rr - q * p.rd[d]) * p.rx[d];
+        rr = q;
+      }
+      C v = dd_load<C, T>(((const T *)p.x)[off]);
+      if (p.op == DD_REDUCE_TENSOR_AMAX) v = v < (C)0 ? -v : v;
+      if (bi == 0xffffffffu || dd_index_beats<C>(p.op, nanProp, v, (unsigned)i, best, bi)) {
+        best = v;
+        bi = (unsigned)i;
+      }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+      const C ob = __shfl_xor_sync(0xffffffffu, best, d);
+      const unsigned obi = __shfl_xor_sync(0xffffffffu, bi, d);
+      if (obi != 0xffffffffu && (bi == 0xffffffffu || dd_index_beats<C>(p.op, nanProp, ob, obi, best, bi))) {
+        best = ob;
+        bi = obi;
+      }
+    }
+    if (lane == 0) p.indices[o] = bi == 0xffffffffu ? 0u : bi;
+  }
+}
+
+ddStatus_t dd_reduce_indices_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd, const void *x,
+                                  const ddTensorStruct *yd, unsigned *indices) {
+  ddRedIndexParams p;
+  memset(&p, 0, sizeof(p));
+  p.x = x;
+  p.indices = indices;
+  p.op = (int)red->op;
+  p.nanProp = red->nan == DD_PROPAGATE_NAN;
+  p.nout = p.nred = 1;
+  for (int i = 0; i < xd->nd; i++) {
+    if (yd->dims[i] == 1 && xd->dims[i] != 1) {
+      p.rd[p.nr] = xd->dims[i]; p.rx[p.nr] = xd->strides[i]; p.nr++;
+      p.nred *= xd->dims[i];
+    } else {
+      p.kd[p.nk] = xd->dims[i]; p.kx[p.nk] = xd->strides[i]; p.nk++;
+      p.nout *= xd->dims[i];
+    }
+  }
+  if (p.nred > 0xfffffffeLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: 32-bit positions cannot address %lld reduced elements", (long long)p.nred);
+  const int64_t warpsWanted = p.nout;
+  int64_t ctas = (warpsWanted + 7) / 8;
+  const int64_t cap = (int64_t)h->smCount * 16;
+  if (ctas > cap) ctas = cap;
+  if (ctas < 1) ctas = 1;
+  switch (xd->dtype) {
+    case DD_DATA_FLOAT: dd_reduce_indices_kernel<float, float><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
+    case DD_DATA_DOUBLE: dd_reduce_indices_kernel<double, double><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
+    case DD_DATA_HALF: dd_reduce_indices_kernel<__half, float><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
+    case DD_DATA_BFLOAT16: dd_reduce_indices_kernel<__nv_bfloat16, float><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
+    default: DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data types must be floating point");
+  }
+  DD_LAUNCHED(h, "reduce/positions");
+  return DD_STATUS_SUCCESS;
+}

@@ -156,6 +156,9 @@ typedef enum {
   DD_REDUCE_TENSOR_NORM_LP_POWER_P_SUM = 12
 } ddReduceTensorOp_t;
 
+/* cudnnReduceTensorIndices_t, cudnn/constants.clj:182-184 (:no-indices, :flattened). */
+typedef enum { DD_REDUCE_TENSOR_NO_INDICES = 0, DD_REDUCE_TENSOR_FLATTENED_INDICES = 1 } ddReduceTensorIndices_t;
+
 typedef struct ddContext *ddHandle_t;
 typedef struct ddTensorStruct *ddTensorDescriptor_t;
 typedef struct ddActivationStruct *ddActivationDescriptor_t;
@@ -341,7 +344,7 @@ DD_API ddStatus_t ddActivationBackward(ddHandle_t handle, ddActivationDescriptor
  * cudnn/core.clj:188-231) and oneDNN reduction (dnnl/impl.clj:557-562, dnnl/core.clj:796-803).
  * Reduced dims are those where y's dim is 1 and x's is not.  Accumulation is fp32 (fp64 for
  * DD_DATA_DOUBLE) in a fixed tree order: results are run-to-run identical.
- * y = alpha*reduce(x) + beta*y.  No indices are produced (indices size is always 0).
+ * y = alpha*reduce(x) + beta*y.  Indices are produced only on request (ddSetReduceTensorDescriptorIndices).
  * Workspace: pass the size ddGetReductionWorkspaceSize returns, or workspace == NULL to use the
  * handle's own scratch (then the size needed must not exceed DD_HANDLE_SCRATCH_BYTES - 64 KB). */
 #define DD_HANDLE_SCRATCH_BYTES (8u << 20)
@@ -359,6 +362,15 @@ DD_API ddStatus_t ddSetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t desc,
                                          ddDataType_t compType, ddNanPropagation_t nanOpt, double p,
                                          double eps);
 DD_API ddStatus_t ddGetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t desc, double *p, double *eps);
+/* The `indices` argument of the reference's 4-argument reduce-tensor-descriptor (cudnn/core.clj:188-196).
+ * With DD_REDUCE_TENSOR_FLATTENED_INDICES and op MIN, MAX or AMAX, ddReduceTensor also writes, for every
+ * output, the position of the element that gave the result as a 32-bit unsigned offset into the
+ * flattened (row-major, original dim order) block of the reduced dims: the FIRST such element; with NaN
+ * propagation on, the first NaN if there is one.  The indices buffer holds one value per output in the
+ * row-major order of y's dims; ddGetReductionIndicesSize gives its size (0 for every other op or
+ * without this setting).  The positions come from a second launch that scans x again (one warp per
+ * output): it is there for completeness, not tuned. */
+DD_API ddStatus_t ddSetReduceTensorDescriptorIndices(ddReduceTensorDescriptor_t desc, ddReduceTensorIndices_t indices);
 DD_API ddStatus_t ddGetReductionIndicesSize(ddHandle_t handle, ddReduceTensorDescriptor_t red,
                                      ddTensorDescriptor_t xDesc, ddTensorDescriptor_t yDesc,
                                      size_t *bytes);

@@ -65,7 +65,7 @@ def main():
             want = np.zeros([1, 64, 1, 1], np.float32)
             oracle.reduce_lp(kind, pw, eps, full, want)
             y = torch.zeros(64, device=fact.device)
-            sh.reduce_tensor(core.reduce_tensor_descriptor(kind, "float", True, pw, eps), 1.0, xd, x, 0.0,
+            sh.reduce_tensor(core.reduce_tensor_descriptor(kind, "float", True, p=pw, eps=eps), 1.0, xd, x, 0.0,
                              core.tensor_descriptor([1, 64, 1, 1], "float", "nchw"), y)
             fact.synchronize()
             got = y.cpu().numpy().reshape(want.shape)

@@ -255,9 +255,17 @@ def test_every_header_enumerator_has_its_keyword(table, prefix):
     aliases = {"DD_ACTIVATION_SIGMOID": ":sigmoid", "DD_DATA_INT8": ":byte"}
     clj = _clj_map(table)
     for name, code in header_enums().items():
-        if name.startswith(prefix):
+        if name.startswith(prefix) and not name.endswith("_INDICES"):
             kw = aliases.get(name, ":" + name[len(prefix):].lower().replace("_", "-"))
             assert clj.get(kw) == code, (name, kw)
+
+
+def test_reduce_indices_table():
+    """cudnn/constants.clj:182-184 :no-indices / :flattened against the header and the Python table."""
+    from deep_diamond_b200 import constants as K
+    enums, clj = header_enums(), _clj_map("dd-reduce-tensor-indices")
+    assert clj[":no-indices"] == enums["DD_REDUCE_TENSOR_NO_INDICES"] == K.REDUCE_INDICES["no-indices"]
+    assert clj[":flattened"] == enums["DD_REDUCE_TENSOR_FLATTENED_INDICES"] == K.REDUCE_INDICES["flattened"]
 
 
 def test_status_codes_match_the_header():

@@ -267,7 +267,7 @@ def test_norm_lp_kinds(fact, dev, oracle, kind, p, eps):
             _, truth = oracle.reduce_lp(kind, p, eps, data.reshape(shape), want, alpha=1.5, beta=0.5, want_truth=True)
             tx, ty = dev.put(data), dev.put(y0)
             xd, yd = core.tensor_descriptor(shape, dtype, "nchw"), core.tensor_descriptor(yshape, dtype, "nchw")
-            rtd = core.reduce_tensor_descriptor(kind, dtype, True, p, eps)
+            rtd = core.reduce_tensor_descriptor(kind, dtype, True, p=p, eps=eps)
             assert rtd.lp() == (p, eps)
             core.reduce_tensor(fact.handle, rtd, 1.5, xd, tx, 0.5, yd, ty)
             got = dev.get(ty, np_t).reshape(yshape).astype(np.float64)
@@ -284,8 +284,8 @@ def test_norm_lp_matches_the_named_norms_bit_for_bit(fact, dev, oracle):
     xd, yd = core.tensor_descriptor(shape, "float", "nchw"), core.tensor_descriptor(yshape, "float", "nchw")
     tx = dev.put(data)
     outs = {}
-    for name, args in (("norm2", ("norm2",)), ("lp2", ("norm-lp-sum", "float", True, 2.0, 0.0)),
-                       ("norm1", ("norm1",)), ("lp1", ("norm-lp-sum", "float", True, 1.0, 0.0))):
+    for name, args in (("norm2", ("norm2",)), ("lp2", ("norm-lp-sum", "float", True, None, 2.0, 0.0)),
+                       ("norm1", ("norm1",)), ("lp1", ("norm-lp-sum", "float", True, None, 1.0, 0.0))):
         ty = dev.put(np.zeros(32, np.float32))
         core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor(*args), 1.0, xd, tx, 0.0, yd, ty)
         outs[name] = dev.get(ty, np.float32)
@@ -296,4 +296,63 @@ def test_norm_lp_matches_the_named_norms_bit_for_bit(fact, dev, oracle):
 def test_norm_lp_bad_p(fact):
     from deep_diamond_b200.constants import DiamondError
     with pytest.raises(DiamondError):
-        core.reduce_tensor_descriptor("norm-lp-sum", "float", True, 0.5, 0.0)
+        core.reduce_tensor_descriptor("norm-lp-sum", "float", True, p=0.5, eps=0.0)
+
+
+@pytest.mark.parametrize("tag,np_t", [("float", np.float32), ("double", np.float64), ("half", np.float16)])
+@pytest.mark.parametrize("op", ["max", "min", "amax"])
+def test_flattened_indices(fact, dev, tag, np_t, op):
+    """The reference's 4-argument reduce-tensor-descriptor (cudnn/core.clj:188-196) with :flattened:
+    min / max / amax also report the position of the winning element as an offset into the
+    row-major block of the reduced dims (original dim order), the first one among equals; other ops
+    and :no-indices need no buffer.  Checked against numpy's argmax / argmin on duplicated and
+    NaN-carrying data, on permuted strides too."""
+    import torch
+    rng = np.random.default_rng(77)
+    cases = [([6, 20, 12, 16], [1, 20, 1, 1], "nchw"), ([6, 20, 12, 16], [6, 1, 12, 16], "nchw"), ([6, 20, 12, 16], [6, 20, 1, 1], "nhwc"),
+             ([3, 5, 7, 11], [1, 5, 1, 11], "nchw"), ([4, 8, 64, 64], [4, 1, 1, 1], "nchw"), ([2, 3, 4, 5], [1, 1, 1, 1], "nhwc")]
+    for shape, yshape, layout in cases:
+        n = int(np.prod(shape))
+        logical = rng.integers(-40, 40, size=shape).astype(np_t)        # many ties
+        logical.reshape(-1)[rng.choice(n, 3, replace=False)] = np.nan
+        axes = tuple(i for i in range(4) if yshape[i] == 1 and shape[i] != 1)
+        kept = tuple(i for i in range(4) if i not in axes)
+        # storage in the chosen layout
+        if layout == "nhwc":
+            store = np.ascontiguousarray(logical.transpose(0, 2, 3, 1)).reshape(-1)
+        else:
+            store = logical.reshape(-1).copy()
+        xd = core.tensor_descriptor(shape, tag, layout)
+        yd = core.tensor_descriptor(yshape, tag, "nchw")
+        # reduced block flattened in original dim order, one row per output (outputs in row-major order of y)
+        block = logical.transpose(kept + axes).reshape(int(np.prod([shape[i] for i in kept])) if kept else 1, -1).astype(np.float64)
+        v = np.abs(block) if op == "amax" else block
+        for prop in (True, False):
+            rtd = core.reduce_tensor_descriptor(op, "double" if tag == "double" else "float", prop, "flattened")
+            need = core.reduction_indices_size(fact.handle, rtd, xd, yd)
+            assert need == block.shape[0] * 4
+            ind = torch.full((block.shape[0],), 0x7fffffff, dtype=torch.int32, device=fact.device)
+            ws = torch.empty(max(core.reduction_workspace_size(fact.handle, rtd, xd, yd), 16), dtype=torch.uint8, device=fact.device)
+            ty = dev.empty(block.shape[0] * store.itemsize)
+            core.reduce_tensor(fact.handle, rtd, ind, ws, 1.0, xd, dev.put(store), 0.0, yd, ty)
+            assert fact.handle.last_kernel() == "reduce/positions"
+            fact.synchronize()
+            got = ind.cpu().numpy().astype(np.int64)
+            if prop:
+                filled = np.where(np.isnan(v), np.inf if op != "min" else -np.inf, v)   # a NaN wins
+            else:
+                filled = np.where(np.isnan(v), -np.inf if op != "min" else np.inf, v)   # a NaN never wins
+            want = filled.argmin(axis=1) if op == "min" else filled.argmax(axis=1)
+            assert np.array_equal(got, want), (shape, yshape, layout, op, prop)
+            # and the value at that position is the reduction's result
+            res = dev.get(ty, np_t).astype(np.float64)
+            picked = v[np.arange(block.shape[0]), got]
+            assert np.array_equal(np.isnan(res), np.isnan(picked)) and np.array_equal(res[~np.isnan(res)], picked[~np.isnan(res)])
+    # no buffer needed without the setting, or for an op that has no position
+    xd, yd = core.tensor_descriptor([2, 3, 4, 5], tag, "nchw"), core.tensor_descriptor([1, 3, 1, 1], tag, "nchw")
+    assert core.reduction_indices_size(fact.handle, core.reduce_tensor_descriptor(op, "float", True), xd, yd) == 0
+    assert core.reduction_indices_size(fact.handle, core.reduce_tensor_descriptor("add", "float", True, "flattened"), xd, yd) == 0
+    from deep_diamond_b200._lib import DiamondError
+    with pytest.raises(DiamondError):   # asked for, not given a buffer
+        core.reduce_tensor(fact.handle, core.reduce_tensor_descriptor(op, "float", True, "flattened"), 1.0, xd,
+                           dev.put(np.zeros(120, np_t)), 0.0, yd, dev.empty(3 * 8))
