@@ -811,6 +811,39 @@ __global__ void __launch_bounds__(256) dd_reduce_indices_kernel(ddRedIndexParams
   }
 }
 
+// The same scan with one THREAD per output, for reductions across a strided dim with the unit-stride
+// dim kept (max over C of nchw): consecutive threads then read consecutive addresses.
+template <typename T, typename C>
+__global__ void __launch_bounds__(256) dd_reduce_indices_thread_kernel(ddRedIndexParams p) {
+  const bool nanProp = p.nanProp != 0;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < p.nout; o += nthreads) {
+    int64_t ox = 0, rem = o;
+    for (int d = p.nk - 1; d >= 0; d--) {
+      const int64_t q = rem / p.kd[d];
+      ox += (rem - q * p.kd[d]) * p.kx[d];
+      rem = q;
+    }
+    C best = (C)0;
+    unsigned bi = 0xffffffffu;
+    for (int64_t i = 0; i < p.nred; i++) {
+      int64_t off = ox, rr = i;
+      for (int d = p.nr - 1; d >= 0; d--) {
+        const int64_t q = rr / p.rd[d];
+        off += (rr - q * p.rd[d]) * p.rx[d];
+        rr = q;
+      }
+      C v = dd_load<C, T>(((const T *)p.x)[off]);
+      if (p.op == DD_REDUCE_TENSOR_AMAX) v = v < (C)0 ? -v : v;
+      if (bi == 0xffffffffu || dd_index_beats<C>(p.op, nanProp, v, (unsigned)i, best, bi)) {
+        best = v;
+        bi = (unsigned)i;
+      }
+    }
+    p.indices[o] = bi == 0xffffffffu ? 0u : bi;
+  }
+}
+
 ddStatus_t dd_reduce_indices_impl(ddHandle_t h, const ddReduceTensorStruct *red, const ddTensorStruct *xd, const void *x,
                                   const ddTensorStruct *yd, unsigned *indices) {
   ddRedIndexParams p;
@@ -830,18 +863,29 @@ ddStatus_t dd_reduce_indices_impl(ddHandle_t h, const ddReduceTensorStruct *red,
     }
   }
   if (p.nred > 0xfffffffeLL) DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: 32-bit positions cannot address %lld reduced elements", (long long)p.nred);
-  const int64_t warpsWanted = p.nout;
-  int64_t ctas = (warpsWanted + 7) / 8;
+  // the unit-stride dim of x kept and at least a few thousand outputs: a thread per output reads
+  // coalesced; otherwise a warp per output, its lanes along the reduced range
+  bool unitKept = false;
+  for (int d = 0; d < p.nk; d++)
+    if (p.kx[d] == 1 && p.kd[d] > 1) unitKept = true;
+  const bool perThread = unitKept && p.nout >= 4096;
   const int64_t cap = (int64_t)h->smCount * 16;
+  int64_t ctas = perThread ? (p.nout + 255) / 256 : (p.nout + 7) / 8;
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
+#define DD_LAUNCH_POSITIONS(T, C)                                                                          \
+  do {                                                                                                     \
+    if (perThread) dd_reduce_indices_thread_kernel<T, C><<<(unsigned)ctas, 256, 0, h->stream>>>(p);       \
+    else dd_reduce_indices_kernel<T, C><<<(unsigned)ctas, 256, 0, h->stream>>>(p);                         \
+  } while (0)
   switch (xd->dtype) {
-    case DD_DATA_FLOAT: dd_reduce_indices_kernel<float, float><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
-    case DD_DATA_DOUBLE: dd_reduce_indices_kernel<double, double><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
-    case DD_DATA_HALF: dd_reduce_indices_kernel<__half, float><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
-    case DD_DATA_BFLOAT16: dd_reduce_indices_kernel<__nv_bfloat16, float><<<(unsigned)ctas, 256, 0, h->stream>>>(p); break;
+    case DD_DATA_FLOAT: DD_LAUNCH_POSITIONS(float, float); break;
+    case DD_DATA_DOUBLE: DD_LAUNCH_POSITIONS(double, double); break;
+    case DD_DATA_HALF: DD_LAUNCH_POSITIONS(__half, float); break;
+    case DD_DATA_BFLOAT16: DD_LAUNCH_POSITIONS(__nv_bfloat16, float); break;
     default: DD_FAIL(h, DD_STATUS_NOT_SUPPORTED, "reduce: data types must be floating point");
   }
+#undef DD_LAUNCH_POSITIONS
   DD_LAUNCHED(h, "reduce/positions");
   return DD_STATUS_SUCCESS;
 }

@@ -368,8 +368,8 @@ DD_API ddStatus_t ddGetReduceTensorDescriptorLp(ddReduceTensorDescriptor_t desc,
  * flattened (row-major, original dim order) block of the reduced dims: the FIRST such element; with NaN
  * propagation on, the first NaN if there is one.  The indices buffer holds one value per output in the
  * row-major order of y's dims; ddGetReductionIndicesSize gives its size (0 for every other op or
- * without this setting).  The positions come from a second launch that scans x again (one warp per
- * output): it is there for completeness, not tuned. */
+ * without this setting).  The positions come from a second launch that scans x again (a warp per
+ * output, or a thread per output when the unit-stride dim is kept): there for completeness, not tuned. */
 DD_API ddStatus_t ddSetReduceTensorDescriptorIndices(ddReduceTensorDescriptor_t desc, ddReduceTensorIndices_t indices);
 DD_API ddStatus_t ddGetReductionIndicesSize(ddHandle_t handle, ddReduceTensorDescriptor_t red,
                                      ddTensorDescriptor_t xDesc, ddTensorDescriptor_t yDesc,

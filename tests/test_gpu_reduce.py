@@ -310,7 +310,8 @@ def test_flattened_indices(fact, dev, tag, np_t, op):
     import torch
     rng = np.random.default_rng(77)
     cases = [([6, 20, 12, 16], [1, 20, 1, 1], "nchw"), ([6, 20, 12, 16], [6, 1, 12, 16], "nchw"), ([6, 20, 12, 16], [6, 20, 1, 1], "nhwc"),
-             ([3, 5, 7, 11], [1, 5, 1, 11], "nchw"), ([4, 8, 64, 64], [4, 1, 1, 1], "nchw"), ([2, 3, 4, 5], [1, 1, 1, 1], "nhwc")]
+             ([3, 5, 7, 11], [1, 5, 1, 11], "nchw"), ([4, 8, 64, 64], [4, 1, 1, 1], "nchw"), ([2, 3, 4, 5], [1, 1, 1, 1], "nhwc"),
+             ([8, 24, 32, 32], [8, 1, 32, 32], "nchw")]   # 8192 outputs, unit-stride dim kept: a thread per output
     for shape, yshape, layout in cases:
         n = int(np.prod(shape))
         logical = rng.integers(-40, 40, size=shape).astype(np_t)        # many ties
