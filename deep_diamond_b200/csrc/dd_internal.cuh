@@ -409,22 +409,26 @@ __device__ __forceinline__ void dd_offsets32(const ddStridedParams<NOPS> &p, uin
 
 template <int NOPS, typename I>
 __device__ __forceinline__ void dd_offsets(const ddStridedParams<NOPS> &p, I idx, int64_t (&off)[NOPS]) {
-  if (sizeof(I) == 4 || p.total < 0x7fffffffLL) {
+  if constexpr (sizeof(I) == 4) {
     dd_offsets32<NOPS>(p, (uint32_t)idx, off);
-    return;
+  } else {
+    if (p.total < 0x7fffffffLL) {
+      dd_offsets32<NOPS>(p, (uint32_t)idx, off);
+      return;
+    }
+#pragma unroll
+    for (int o = 0; o < NOPS; o++) off[o] = 0;
+    for (int d = p.nd - 1; d > 0; d--) {
+      I dim = (I)p.dims[d];
+      I q = idx / dim;
+      I r = idx - q * dim;
+#pragma unroll
+      for (int o = 0; o < NOPS; o++) off[o] += (int64_t)r * p.st[o][d];
+      idx = q;
+    }
+#pragma unroll
+    for (int o = 0; o < NOPS; o++) off[o] += (int64_t)idx * p.st[o][0];
   }
-#pragma unroll
-  for (int o = 0; o < NOPS; o++) off[o] = 0;
-  for (int d = p.nd - 1; d > 0; d--) {
-    I dim = (I)p.dims[d];
-    I q = idx / dim;
-    I r = idx - q * dim;
-#pragma unroll
-    for (int o = 0; o < NOPS; o++) off[o] += (int64_t)r * p.st[o][d];
-    idx = q;
-  }
-#pragma unroll
-  for (int o = 0; o < NOPS; o++) off[o] += (int64_t)idx * p.st[o][0];
 }
 
 #endif  // __CUDACC__

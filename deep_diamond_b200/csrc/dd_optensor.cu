@@ -594,7 +594,6 @@ __global__ void __launch_bounds__(256) dd_sum_kernel(ddSumParams p) {
       }
       uint4 res;
       T *rv = (T *)&res;
-#pragma unroll
       dd_store_n<T, C, V>(rv, acc);
       *(uint4 *)(dst + i * V) = res;
     }
