@@ -274,7 +274,7 @@ static inline ddStridedParams<NOPS> dd_strided_params(const ddCanon &c) {
 static inline unsigned dd_flat_grid(const ddContext *h, int64_t work_items, int threads,
                                     int ctas_per_sm) {
   int64_t need = (work_items + threads - 1) / threads;
-  int64_t cap = (int64_t)h->smCount * ctas_per_sm;
+  int64_t cap = (int64_t)h->smCount * ctas_per_sm * dd_tune("DD_FLAT_MULT", 1);
   if (need < 1) need = 1;
   return (unsigned)(need < cap ? need : cap);
 }

@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(256) dd_multi_kernel(const __grid_constant__ d
 
 template <typename S, typename D, typename C, bool SAME>
 static ddStatus_t multi_launch(ddHandle_t h, const ddMultiParams &p) {
-  unsigned grid = dd_flat_grid(h, p.start[p.count], 256, 16);
+  unsigned grid = dd_flat_grid(h, p.start[p.count], 256, 64);  // 16 -> 64: branch / concatenate +2.4-3.3 %
   dd_multi_kernel<S, D, C, SAME><<<grid, 256, 0, h->stream>>>(p);
   DD_LAUNCHED(h, p.vec > 1 ? "multi-transform/vec" : "multi-transform/scalar");
   return DD_STATUS_SUCCESS;
@@ -276,8 +276,9 @@ extern "C" ddStatus_t ddCostDiff(ddHandle_t h, int kind, ddTensorDescriptor_t de
   p.divisor = kind == 2 ? desc->dims[0] : c.total;
   p.vec = ((((uintptr_t)a) | ((uintptr_t)y) | ((uintptr_t)d)) & 15) == 0;
   const int V = 16 / dd_type_size(desc->dtype);
-  // one resident wave: 6 CTAs per SM
-  unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 6);
+  // four resident waves' worth (6 CTAs per SM resident): the cross-entropy measured 3978 GB/s with one wave,
+  // 4284 / 4377 / 4406 with two / three / four; the quadratic cost 6174 / 6265 / 6254 / 6250
+  unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, 24);
   const bool f = desc->dtype == DD_DATA_FLOAT;
   if (kind == 0) {
     if (f) dd_cost_kernel<float, 0><<<grid, 256, 0, h->stream>>>(p);

@@ -377,7 +377,7 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
       p.fdInner = dd_fastdiv((uint32_t)inner);
       p.fdChannels = dd_fastdiv((uint32_t)channels);
     }
-    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, dd_tune("DD_OPFLAT_CPS", 8));
+    unsigned grid = dd_flat_grid(h, (p.n + V - 1) / V, 256, dd_tune("DD_OPFLAT_CPS", 32));
     // add and mul (bias, per-channel scale, axpy, sum) get their own instantiations
     if (bmode >= 2) {
       // add and mul in the two forms layers meet (bias and per-channel scale on nchw maps that are not
@@ -396,7 +396,7 @@ static ddStatus_t optensor_typed(ddHandle_t h, ddOpTensorOp_t op, double alpha1,
         p.n % V == 0 && p.n / V <= (int64_t)h->smCount * 8 * 256 * 16 && dd_tune("DD_OP_BCAST2", 1)) {
       // small tensors only (at most 16 vectors per thread of a resident grid): [128,512,14,14] f32 19.07 -> 18.38 us;
       // on 205 MB tensors the one-vector kernel measured 3 % faster
-      unsigned g2 = dd_flat_grid(h, (p.n / V + 1) / 2, 256, dd_tune("DD_OPFLAT_CPS", 8));
+      unsigned g2 = dd_flat_grid(h, (p.n / V + 1) / 2, 256, dd_tune("DD_OPFLAT_CPS", 32));
       if (op == DD_OP_TENSOR_ADD) dd_launch_pdl(dd_op_bcast2_kernel<T, C, DD_OP_TENSOR_ADD>, g2, 256, h->stream, p);
       else dd_launch_pdl(dd_op_bcast2_kernel<T, C, DD_OP_TENSOR_MUL>, g2, 256, h->stream, p);
       DD_LAUNCHED(h, "optensor/flat-bcast");
@@ -527,7 +527,7 @@ static ddStatus_t fill_typed(ddHandle_t h, const ddTensorStruct *yd, void *y, do
   p.scale = scale;
   p.flat = c.nd == 1 && c.st[0][0] == 1;
   constexpr int V = 16 / sizeof(T);
-  unsigned grid = dd_flat_grid(h, p.flat ? (c.total + V - 1) / V : c.total, 256, 16);
+  unsigned grid = dd_flat_grid(h, p.flat ? (c.total + V - 1) / V : c.total, 256, 48);  // 16 -> 48: fill +6.7 %, scale +1.8 %
   dd_fill_kernel<T, C><<<grid, 256, 0, h->stream>>>(p);
   DD_LAUNCHED(h, scale ? (p.flat ? "scale/flat" : "scale/strided") : (p.flat ? "set/flat" : "set/strided"));
   return DD_STATUS_SUCCESS;
